@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Benchmark of the Tucker core-convolution hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A step is one pass of the core conv over the eight sweep shapes
+(H=W, R1=R2) in {(56,32),(56,64),(28,64),(28,128),(14,128),(14,256),(7,256),(7,512)},
+3x3, stride 1, pad 1, fp32, batch 64 per GPU (weak scaling: every rank runs its own batch,
+no collective on the data path).  Rank 0 prints ONE JSON line.
+
+  value          layer-images/s = (8 layers x 64 images x N GPUs) / time per step, inputs resident in HBM
+  e2e            the same work through the layer objects of the C ABI with HOST buffers
+                 (tdc_conv_forward_host: copy in, run, copy out), pinned host memory
+  roofline       the core-conv kernel against the fp32 FMA peak of the device (every sweep
+                 shape is FP32-pipe bound by algorithmic count), plus its HBM figure
+  cpu_baseline   the reference's CPU path for the same step (torch F.conv2d on the host cores)
+  layers         per-shape kernel time at batch 64 and batch 1, and cuDNN through torch
+                 (allow_tf32=False) beside it
+
+`--impl reference` times the reference's CPU implementation of the path (the three
+F.conv2d calls of inference/TKConv.py:90-95 reduce to the core call for this step) on the
+host cores of the box, on a bounded batch sample.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "ppopp23-tdc_b200"))
+
+SWEEP = [(56, 32, 32), (56, 64, 64), (28, 64, 64), (28, 128, 128), (14, 128, 128), (14, 256, 256),
+         (7, 256, 256), (7, 512, 512)]
+BATCH = 64
+METRIC, UNIT = "core_conv_sweep_throughput", "layer-images/s"
+
+
+def conv_flops(B, H, R1, R2):
+    return 2.0 * B * R2 * R1 * 9 * H * H
+
+
+def conv_bytes(B, H, R1, R2):
+    return 4.0 * (B * R1 * H * H + B * R2 * H * H + R2 * R1 * 9)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], sm_max_mhz=d.get("sm_max_mhz", 1965.0), source="measured")
+    return dict(hbm_gbs=6650.0, sm_max_mhz=1965.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.f, self.p = index, None, None
+
+    def __enter__(self):
+        try:
+            self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                       "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.f,
+                                      stderr=subprocess.DEVNULL)
+        except Exception:
+            self.p = None
+        return self
+
+    def __exit__(self, *a):
+        if self.p is not None:
+            self.p.terminate()
+            try:
+                self.p.wait(timeout=5)
+            except Exception:
+                self.p.kill()
+
+    def summary(self):
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        if self.f is None:
+            return out
+        try:
+            self.f.flush()
+            rows = [r.split(",") for r in open(self.f.name).read().strip().splitlines() if r.count(",") >= 8]
+            os.unlink(self.f.name)
+        except Exception:
+            return out
+        if not rows:
+            return out
+        sm = [float(r[1]) for r in rows]
+        out["sm_mhz"] = statistics.median(sm)
+        out["sm_max_mhz"] = float(rows[0][2])
+        out["power_w_max"] = max(float(r[3]) for r in rows)
+        out["samples"] = len(rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for i, n in enumerate(names):
+            if any("Active" in r[5 + i] and "Not" not in r[5 + i] for r in rows):
+                out["reasons"].append(n)
+        return out
+
+
+def cpu_core_step(torch, batch, threads):
+    """The reference's CPU path for one step at `batch` images per layer; returns seconds."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle as O
+    torch.set_num_threads(threads)
+    layers = []
+    g = torch.Generator().manual_seed(9)
+    for (H, R1, R2) in SWEEP:
+        x = torch.randn(batch, R1, H, H, generator=g)
+        w = torch.randn(R2, R1, 3, 3, generator=g) * (2.0 / (R2 * 9)) ** 0.5
+        layers.append((O.TKConv2dCRef(None, w, None, None, 1, 1), x))
+
+    def step():
+        with torch.no_grad():
+            for m, x in layers:
+                m.core(x)
+    return step
+
+
+def run_reference(args):
+    """Reference arm: the CPU implementation of the path on the host cores, bounded sample."""
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    sample_b = 8
+    step = cpu_core_step(torch, sample_b, cores)
+    for _ in range(max(args.warmup, 1)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = len(SWEEP) * sample_b / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "core-conv sweep, 8 shapes, 3x3 s1 p1 fp32, batch %d per layer (sample of the batch-64 step)" % sample_b,
+                   "impl": "torch.nn.functional.conv2d on CPU, the call TKConv2dC.forward makes (inference/TKConv.py:92-93)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": "batch %d of 64 per layer, all 8 shapes, %d steps" % (sample_b, args.steps)},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip per-layer table, cuDNN and CPU baselines")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import tdc_b200 as T      # raises if libtdc_b200.so is missing: there is no fallback
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    stream = torch.cuda.current_stream()
+
+    # ---- resident inputs: x ~ N(0,1), Kaiming-normal weights, seeded on the CPU ------------
+    layers = []
+    for i, (H, R1, R2) in enumerate(SWEEP):
+        g = torch.Generator().manual_seed(2100 + i + 1000 * rank)
+        x = torch.randn(BATCH, R1, H, H, generator=g)
+        w = torch.randn(R2, R1, 3, 3, generator=g) * (2.0 / (R2 * 9)) ** 0.5
+        xd = x.to(dev)
+        wd = T.permute_weights(w.to(dev))
+        y = torch.empty(BATCH, R2, H, H, device=dev)
+        tile = T.select_tile(BATCH, R1, H, H, R2, 3, 3, 1, 1)
+        layers.append(dict(H=H, R1=R1, R2=R2, x=xd, w=wd, y=y, tile=tile, x_host=x, w_host=w))
+
+    def step():
+        for L in layers:
+            T.core_conv2d(L["x"], L["w"], 1, 1, w_layout=T.W_CRSK, tile=L["tile"], out=L["y"])
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        barrier()
+    ms_total = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = len(SWEEP) * BATCH * world / (ms_step * 1e-3)
+    clocks = clk.summary()
+
+    # ---- per-kernel timing of the dominant kernel, live, on the launching stream -----------
+    peaks = measured_peaks()
+    sm_count = T.query_device().sm_count
+    fp32_peak = sm_count * 128 * 2 * peaks["sm_max_mhz"] * 1e6 / 1e12     # TFLOP/s at the max SM clock
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def time_layer(fn, iters=10, warm=3):
+        for _ in range(warm):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()                        # evict L2 (256 MB > 126 MB) outside the timed pair
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream); fn(); b.record(stream)
+            b.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        return statistics.median(ts)
+
+    per_layer = []
+    for L in layers:
+        us = time_layer(lambda L=L: T.core_conv2d(L["x"], L["w"], 1, 1, w_layout=T.W_CRSK, tile=L["tile"], out=L["y"]))
+        fl, by = conv_flops(BATCH, L["H"], L["R1"], L["R2"]), conv_bytes(BATCH, L["H"], L["R1"], L["R2"])
+        per_layer.append(dict(H=L["H"], R1=L["R1"], R2=L["R2"], B=BATCH, us=us, tflops=fl / us / 1e6,
+                              frac_fp32=fl / us / 1e6 / fp32_peak, gbs=by / us / 1e3,
+                              tile=list(L["tile"].as_tuple())))
+    dom = max(per_layer, key=lambda r: r["us"])
+    tot_fl = sum(conv_flops(BATCH, r["H"], r["R1"], r["R2"]) for r in per_layer)
+    tot_us = sum(r["us"] for r in per_layer)
+    roofline = {
+        "bound": "fp32", "achieved": tot_fl / tot_us / 1e6, "peak": fp32_peak, "unit": "TFLOP/s",
+        "frac": tot_fl / tot_us / 1e6 / fp32_peak, "traffic": None,
+        "kernel": "conv_f32_kernel (3x3 s1), all 8 sweep launches of a step, L2 flushed before each",
+        "peak_source": "SMs x 128 lanes x 2 x max SM clock from MEASURED_PEAKS.json (%s)" % peaks["source"],
+        "dominant_launch": {k: dom[k] for k in ("H", "R1", "R2", "us", "tflops", "frac_fp32")},
+        "hbm": {"achieved": sum(conv_bytes(BATCH, r["H"], r["R1"], r["R2"]) for r in per_layer) / tot_us / 1e3,
+                "peak": peaks["hbm_gbs"], "unit": "GB/s"},
+    }
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "core-conv sweep: 8 shapes (H,R1=R2) 56/32 56/64 28/64 28/128 14/128 14/256 7/256 7/512, 3x3 s1 p1, batch 64 per GPU",
+                   "l2": "working set of a step (inputs+outputs 288 MB) exceeds the 126 MB L2; per-layer timings flush L2 explicitly",
+                   "parallelism": "batch shards, no collective" if world > 1 else "single GPU"},
+        "clocks": clocks, "gpu_launches": len(SWEEP) * args.steps, "roofline": roofline,
+        "us_per_layer_b64": ms_step * 1e3 / len(SWEEP),
+    }
+
+    # ---- end to end through the layer objects with HOST buffers (pinned) -------------------
+    lib = T.lib
+    hosts = []
+    for L in layers:
+        h = C.c_void_p()
+        wk = L["w_host"].contiguous()
+        T._lib.check(lib.tdc_conv_create(C.byref(h), BATCH, L["R1"], L["H"], L["H"], L["R2"], 1, 3, 3, 1,
+                                         C.c_void_p(wk.data_ptr()), None))
+        T._lib.check(lib.tdc_conv_set_tile(h, C.byref(L["tile"])))
+        xin = L["x_host"].pin_memory()
+        yout = torch.empty(BATCH, L["R2"], L["H"], L["H"]).pin_memory()
+        hosts.append((h, xin, yout))
+    h2d = sum(x.numel() * 4 for _, x, _ in hosts)
+    d2h = sum(y.numel() * 4 for _, _, y in hosts)
+
+    def e2e_step():
+        for h, xin, yout in hosts:
+            T._lib.check(lib.tdc_conv_forward_host(h, C.c_void_p(xin.data_ptr()), C.c_void_p(yout.data_ptr())))
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    line["e2e"] = {"value": len(SWEEP) * BATCH * world / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                   "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3,
+                   "api": "tdc_conv_forward_host per layer (pinned host buffers; copies inside the timed region)"}
+    # one parity probe of the end-to-end output against the resident path
+    e2e_ok = bool(torch.equal(hosts[0][2].to(dev), layers[0]["y"]))
+    line["e2e"]["matches_resident_path"] = e2e_ok
+    for h, _, _ in hosts:
+        lib.tdc_conv_destroy(h)
+
+    # ---- extras on rank 0 of a single-GPU run: batch-1 latency, cuDNN, CPU baseline ---------
+    if rank == 0 and world == 1 and not args.no_extras:
+        import torch.nn.functional as F
+        torch.backends.cudnn.benchmark = True
+        torch.backends.cudnn.allow_tf32 = False
+        torch.backends.cuda.matmul.allow_tf32 = False
+        table = []
+        for L, r64 in zip(layers, per_layer):
+            H, R1, R2 = L["H"], L["R1"], L["R2"]
+            wk = L["w_host"].to(dev)
+            x1 = L["x"][:1].contiguous()
+            t1 = T.select_tile(1, R1, H, H, R2, 3, 3, 1, 1)
+            y1 = torch.empty(1, R2, H, H, device=dev)
+            us1 = time_layer(lambda: T.core_conv2d(x1, L["w"], 1, 1, w_layout=T.W_CRSK, tile=t1, out=y1), iters=20)
+            cud64 = time_layer(lambda: F.conv2d(L["x"], wk, None, 1, 1))
+            cud1 = time_layer(lambda: F.conv2d(x1, wk, None, 1, 1), iters=20)
+            err = float((F.conv2d(L["x"][:2], wk, None, 1, 1) - L["y"][:2]).abs().max() / L["y"][:2].abs().max())
+            table.append(dict(H=H, R1=R1, R2=R2, us_b64=r64["us"], frac_fp32_b64=r64["frac_fp32"], cudnn_us_b64=cud64,
+                              us_b1=us1, frac_fp32_b1=conv_flops(1, H, R1, R2) / us1 / 1e6 / fp32_peak, cudnn_us_b1=cud1,
+                              tile_b64=r64["tile"], tile_b1=list(t1.as_tuple()), rel_err_vs_cudnn=err))
+        line["layers"] = table
+        gm = lambda v: float(torch.tensor(v).log().mean().exp())
+        line["speedup_vs_cudnn_geomean"] = {"b64": gm([r["cudnn_us_b64"] / r["us_b64"] for r in table]),
+                                            "b1": gm([r["cudnn_us_b1"] / r["us_b1"] for r in table]),
+                                            "cudnn": "torch F.conv2d, cudnn.benchmark=True, allow_tf32=False, version %s" % torch.backends.cudnn.version()}
+        cores = os.cpu_count() or 1
+        sample_b = 8
+        cstep = cpu_core_step(torch, sample_b, cores)
+        cstep()
+        t0 = time.perf_counter()
+        n = 0
+        while n < 3 or (time.perf_counter() - t0 < 10.0 and n < 50):
+            cstep(); n += 1
+        cdt = (time.perf_counter() - t0) / n
+        line["cpu_baseline"] = {"value": len(SWEEP) * sample_b / cdt, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": "batch %d of 64 per layer, all 8 shapes, %d passes of torch F.conv2d on CPU" % (sample_b, n)}
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

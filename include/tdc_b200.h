@@ -1,0 +1,211 @@
+/*
+ * tdc_b200.h — C ABI of libtdc_b200.so: the core convolution of a Tucker-factorised
+ * conv layer (and the 1x1 convs around it) as hand-written sm_100a CUDA.
+ *
+ * Every entry point is extern "C", takes plain pointers and sizes, never throws and
+ * never exits the process: it returns a tdc_status and leaves a message readable with
+ * tdc_last_error_string() (thread-local).  All device work is asynchronous on the
+ * stream the caller passes (a cudaStream_t cast to void*; NULL = the default stream).
+ * Unless a comment says otherwise, pointers are DEVICE pointers to contiguous fp32
+ * arrays that the caller owns.
+ *
+ * Naming.  The reference's CUDA drivers call the core conv's input channels C and its
+ * output channels N, and hard-wire batch 1.  Here:  B = batch, C = input channels (R1
+ * of the Tucker block), K = output channels (R2), H,W = input height/width, R,S =
+ * filter height/width.  Output size: Ho = (H + 2*pad - R)/stride + 1, same for Wo.
+ *
+ * Each declaration cites the reference interface it stands in for, as
+ * path-in-reference:line.
+ */
+#ifndef TDC_B200_H
+#define TDC_B200_H
+
+#include <stddef.h>
+
+#if defined(__GNUC__)
+#define TDC_API __attribute__((visibility("default")))
+#else
+#define TDC_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum tdc_status {
+    TDC_OK              = 0,
+    TDC_ERR_NULL        = 1, /* a required pointer is NULL                          */
+    TDC_ERR_SHAPE       = 2, /* a dimension is <= 0, or the output would be empty   */
+    TDC_ERR_UNSUPPORTED = 3, /* filter size / stride / layout this build lacks      */
+    TDC_ERR_TILE        = 4, /* the tile does not fit the shape or the device       */
+    TDC_ERR_SMEM        = 5, /* the tile needs more shared memory than a CTA has    */
+    TDC_ERR_CUDA        = 6, /* a CUDA runtime call failed (message has the reason) */
+    TDC_ERR_WORKSPACE   = 7, /* workspace missing or too small                      */
+    TDC_ERR_NO_DEVICE   = 8  /* no CUDA device / driver                             */
+} tdc_status;
+
+/* Filter memory layouts. KCRS is torch's core_kernel[R2][R1][kh][kw]
+ * (inference/TKConv.py:63); CRSK is the reference CUDA kernel's k[c][r][s][n]
+ * (A100-evaluation/TDC-LAYERS-ORACLE/template_benchmark_cudnn.template:396). */
+#define TDC_W_KCRS 0
+#define TDC_W_CRSK 1
+
+/* Epilogue flags for tdc_conv2d_f32. */
+#define TDC_EPI_NONE 0
+#define TDC_EPI_RELU 1
+
+/*
+ * Tiling parameters.  th, tw, tc keep the meaning of the reference generators' TH, TW,
+ * TC macros (template_benchmark_cudnn.template:14-16; gen_from_occupancy.py:113-139):
+ * output rows per thread, output columns per thread, input channels staged per chunk.
+ * The reference fixes "one output channel per thread, all N channels per block"; on
+ * B200 those two become parameters (tn, nog), and a CTA may own several images of a
+ * small feature map (imgs) and split the staged channels over ks thread slices whose
+ * partial sums are reduced in shared memory in a fixed order (no atomics).
+ * A field left 0 is chosen by tdc_select_tile.
+ */
+typedef struct tdc_tile {
+    int th;   /* output rows per thread                (1 or 2)                    */
+    int tw;   /* output columns per thread             (4, 7 or 8)                 */
+    int tc;   /* input channels per staged chunk       (multiple of ks)            */
+    int tn;   /* output channels per thread            (4 or 8)                    */
+    int nog;  /* output-channel groups per CTA         (CTA covers tn*nog channels)*/
+    int gy;   /* thread rows per CTA per image         (CTA covers gy*th rows)     */
+    int gx;   /* thread columns per CTA per image      (CTA covers gx*tw columns)  */
+    int imgs; /* images per CTA (>1 only if gy,gx cover the whole output map)      */
+    int ks;   /* channel slices per CTA (in-CTA split of the reduction)            */
+} tdc_tile;
+
+/* What the selector needs to know about a device; fill with tdc_query_device or by
+ * hand (the analytical model of TDC-LAYERS-MODELING/model.py:264-265 takes the same
+ * kind of constants: num_sm, num_threads). */
+typedef struct tdc_devinfo {
+    int sm_count;        /* 148 on B200                                  */
+    int smem_per_cta;    /* opt-in dynamic shared memory per CTA, bytes  */
+    int regs_per_sm;     /* 65536                                        */
+    int threads_per_sm;  /* 2048                                         */
+} tdc_devinfo;
+
+/* Launch facts of one (shape, tile) pair, for table builders and tests. */
+typedef struct tdc_launch_info {
+    int    grid_x, grid_y;   /* CTAs                                     */
+    int    threads;          /* threads per CTA                          */
+    size_t smem_bytes;       /* dynamic shared memory per CTA            */
+    int    regs_per_thread;  /* of the kernel variant, from the runtime  */
+    int    ctas_per_sm;      /* occupancy API result                     */
+} tdc_launch_info;
+
+TDC_API const char* tdc_last_error_string(void);
+TDC_API int         tdc_version(void);
+
+/* Device facts. No counterpart in the reference (constants are hard-coded at
+ * A100-evaluation/TDC-LAYERS-MODELING/model.py:264-265). device < 0 = current. */
+TDC_API int tdc_query_device(int device, tdc_devinfo* out);
+
+/*
+ * The hot path: y = cross-correlation(x, w), zero padding, no bias.
+ * Stands in for (1) the core step of TKConv2dC.forward, F.conv2d(out, core_kernel,
+ * None, stride, padding) at inference/TKConv.py:92-93, and (2) the reference kernel
+ * conv2d(float* input, const float* kernel, float* outputs) with its launch
+ * <<<TCS*THS, N*TWS, smem>>> at template_benchmark_cudnn.template:365-402,490-492.
+ * Differences a caller can rely on: any batch, stride 1 or 2, R=S in {1,3} on the fast
+ * path and any R,S <= 7 on the generic path, y need NOT be zeroed first (the reference
+ * kernel accumulates with atomicAdd into a zeroed buffer), results are run-to-run
+ * bit-identical for a given tile.
+ *   x [B][C][H][W], w per w_layout, y [B][K][Ho][Wo]; tile may be NULL (auto).
+ */
+TDC_API int tdc_core_conv2d_f32(const float* x, const float* w, float* y,
+                        int B, int C, int H, int W, int K, int R, int S,
+                        int pad, int stride, int w_layout,
+                        const tdc_tile* tile, void* stream);
+
+/* Same conv with the epilogue of the last 1x1 step of TKConv2dC.forward,
+ * F.conv2d(out, last_kernel, bias) at inference/TKConv.py:94 (bias may be NULL), and
+ * an optional ReLU (the Activation that follows a block's BatchNorm,
+ * A100-evaluation/EndToEnd/resnet18-tk/src/BasicBlock.cu:44-51). */
+TDC_API int tdc_conv2d_f32(const float* x, const float* w, const float* bias, float* y,
+                   int B, int C, int H, int W, int K, int R, int S,
+                   int pad, int stride, int w_layout, int epilogue,
+                   const tdc_tile* tile, void* stream);
+
+/* KCRS -> CRSK, once per weight load.  Replaces nothing in the reference (its drivers
+ * fill k[c][r][s][n] with ones directly, template_benchmark_cudnn.template:425-428);
+ * needed because TKConv.py stores core_kernel as [R2][R1][kh][kw]. */
+TDC_API int tdc_permute_weights(const float* w_kcrs, float* w_crsk,
+                        int K, int C, int R, int S, void* stream);
+
+/*
+ * Tile selection.  Stands in for the analytical selector modeling()/build_table() of
+ * A100-evaluation/TDC-LAYERS-MODELING/model.py:135-234 (same cost terms: filter, input
+ * and output volumes and a flops*waves latency term), re-derived for B200's SM count,
+ * shared memory and register file.  dev may be NULL (current device is queried).
+ */
+TDC_API int tdc_select_tile(int B, int C, int H, int W, int K, int R, int S,
+                    int pad, int stride, const tdc_devinfo* dev, tdc_tile* out);
+
+/* Completes the zero fields of *tile for the shape, checks it against the device and
+ * reports the launch it would produce (no launch happens).  The reference computes the
+ * same facts in its occupancy probe, A100-evaluation/Gen-occupancy/template.cu:278-285. */
+TDC_API int tdc_tile_info(int B, int C, int H, int W, int K, int R, int S, int pad, int stride,
+                  tdc_tile* tile, tdc_launch_info* info);
+
+/* Modelled cost (arbitrary units, lower is better) of a completed tile: the quantity
+ * tdc_select_tile minimises.  Mirrors build_table's (K, I, O, flops*waves) tuple,
+ * model.py:157-184; vols[0..3] receive those four terms when vols != NULL. */
+TDC_API int tdc_tile_cost(int B, int C, int H, int W, int K, int R, int S, int pad, int stride,
+                  const tdc_tile* tile, const tdc_devinfo* dev, double* cost, double* vols);
+
+/*
+ * The Tucker block of TKConv2dC.forward, inference/TKConv.py:90-95:
+ *   z1 = conv1x1(x, w1[R1][C]);  z2 = conv(z1, wcore, stride, pad);
+ *   y  = conv1x1(z2, w3[K][R2]) + bias.
+ * Also the TkConv::forward chain conv1->conv2->conv3 of
+ * A100-evaluation/EndToEnd/resnet18-tk/src/BasicBlock.cu:27-32.
+ * The two intermediates live in `workspace` (tdc_tk_block_workspace_bytes), which is
+ * sized to stay resident in B200's L2 for the benchmark shapes; the three steps run
+ * back to back on `stream`.  w1 is [R1][C], w3 is [K][R2] (torch 1x1 layouts), wcore per
+ * w_layout.  bias may be NULL.  epilogue as in tdc_conv2d_f32.
+ */
+TDC_API size_t tdc_tk_block_workspace_bytes(int B, int C, int H, int W, int R1, int R2, int K,
+                                    int R, int S, int pad, int stride);
+TDC_API int tdc_tk_block_f32(const float* x, const float* w1, const float* wcore, const float* w3,
+                     const float* bias, float* y,
+                     int B, int C, int H, int W, int R1, int R2, int K, int R, int S,
+                     int pad, int stride, int w_layout, int epilogue,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Layer objects with the surface of the reference's end-to-end classes:
+ * Conv::initialize(b,c,h,w,n,pad,r,s,stride,weightFile,use_bias) / float* Conv::forward(float*)
+ * (A100-evaluation/EndToEnd/resnet18-tk/inc/common.h:38-69, src/Conv.cu:2-125) and
+ * TkConv::initialize(C,N1,N2,N3,h,w,...,down_sample) / forward (common.h:158-166,
+ * src/BasicBlock.cu:15-32).  As there, a layer owns its weights and its output buffer
+ * and forward() returns that buffer; unlike there, weights are supplied by the caller
+ * (HOST pointers, KCRS; NULL = all ones as the reference fills them), errors come back
+ * as status codes, and destroy() frees what create() allocated.
+ * The *_host variants take HOST input/output: copy in, run, copy out, synchronise — the
+ * shape of the per-shape drivers' main() (template_benchmark_cudnn.template:412-498).
+ */
+typedef struct tdc_conv   tdc_conv;
+typedef struct tdc_tkconv tdc_tkconv;
+
+TDC_API int  tdc_conv_create(tdc_conv** out, int b, int c, int h, int w, int n, int pad,
+                     int r, int s, int stride, const float* host_w_kcrs,
+                     const float* host_bias /* NULL = no bias */);
+TDC_API int  tdc_conv_set_tile(tdc_conv* l, const tdc_tile* tile);
+TDC_API int  tdc_conv_forward(tdc_conv* l, const float* dev_in, float** dev_out, void* stream);
+TDC_API int  tdc_conv_forward_host(tdc_conv* l, const float* host_in, float* host_out);
+TDC_API void tdc_conv_destroy(tdc_conv* l);
+
+TDC_API int  tdc_tkconv_create(tdc_tkconv** out, int b, int C, int N1, int N2, int N3, int h, int w,
+                       int r, int s, int pad, int stride,
+                       const float* host_w1, const float* host_wcore_kcrs,
+                       const float* host_w3, const float* host_bias);
+TDC_API int  tdc_tkconv_forward(tdc_tkconv* l, const float* dev_in, float** dev_out, void* stream);
+TDC_API int  tdc_tkconv_forward_host(tdc_tkconv* l, const float* host_in, float* host_out);
+TDC_API void tdc_tkconv_destroy(tdc_tkconv* l);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TDC_B200_H */

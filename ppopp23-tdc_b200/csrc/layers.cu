@@ -1,0 +1,187 @@
+// Layer objects with the surface of the reference's end-to-end classes
+// (A100-evaluation/EndToEnd/resnet18-tk/inc/common.h:38-69,158-166; src/Conv.cu:2-125;
+// src/BasicBlock.cu:15-32): a layer is created for one fixed shape, owns its weights and
+// its output buffer, and forward() hands back that buffer.  The *_host calls wrap the
+// same forward in the copy-in / run / copy-out sequence of the per-shape drivers' main()
+// (A100-evaluation/TDC-LAYERS-ORACLE/template_benchmark_cudnn.template:412-498).
+#include <cuda_runtime.h>
+#include <cstdio>
+#include <vector>
+#include "../../include/tdc_b200.h"
+
+struct tdc_conv {
+    int b, c, h, w, n, pad, r, s, stride, ho, wo;
+    float *kernel = nullptr, *bias = nullptr, *output = nullptr, *staging_in = nullptr;
+    bool has_tile = false;
+    tdc_tile tile{};
+};
+
+struct tdc_tkconv {
+    int b, C, N1, N2, N3, h, w, r, s, pad, stride, ho, wo;
+    float *w1 = nullptr, *wcore = nullptr, *w3 = nullptr, *bias = nullptr;
+    float *output = nullptr, *staging_in = nullptr;
+    void* workspace = nullptr;
+    size_t workspace_bytes = 0;
+};
+
+namespace {
+
+// Sets the library's error text through a failing call of its own (keeps one writer).
+int cuda_fail(const char* what, cudaError_t e) {
+    fprintf(stderr, "tdc_b200: %s: %s\n", what, cudaGetErrorString(e));
+    return TDC_ERR_CUDA;
+}
+
+int upload(float** dst, const float* host, size_t n, float fill_if_null) {
+    cudaError_t e = cudaMalloc((void**)dst, n * sizeof(float));
+    if (e != cudaSuccess) return cuda_fail("cudaMalloc", e);
+    if (host) e = cudaMemcpy(*dst, host, n * sizeof(float), cudaMemcpyHostToDevice);
+    else {
+        std::vector<float> ones(n, fill_if_null);
+        e = cudaMemcpy(*dst, ones.data(), n * sizeof(float), cudaMemcpyHostToDevice);
+    }
+    return e == cudaSuccess ? TDC_OK : cuda_fail("cudaMemcpy", e);
+}
+
+}  // namespace
+
+extern "C" {
+
+void tdc_conv_destroy(tdc_conv* l) {
+    if (!l) return;
+    cudaFree(l->kernel); cudaFree(l->bias); cudaFree(l->output); cudaFree(l->staging_in);
+    delete l;
+}
+
+int tdc_conv_create(tdc_conv** out, int b, int c, int h, int w, int n, int pad, int r, int s, int stride,
+                    const float* host_w_kcrs, const float* host_bias) {
+    if (!out) return TDC_ERR_NULL;
+    *out = nullptr;
+    if (b <= 0 || c <= 0 || h <= 0 || w <= 0 || n <= 0 || r <= 0 || s <= 0 || stride <= 0 || pad < 0 ||
+        h + 2 * pad < r || w + 2 * pad < s)
+        return TDC_ERR_SHAPE;
+    tdc_conv* l = new tdc_conv;
+    l->b = b; l->c = c; l->h = h; l->w = w; l->n = n; l->pad = pad; l->r = r; l->s = s; l->stride = stride;
+    l->ho = (h + 2 * pad - r) / stride + 1;
+    l->wo = (w + 2 * pad - s) / stride + 1;
+    int rc;
+    // Filter is kept channel-last ([c][r][s][n], the reference kernel's own layout) so the
+    // kernel stages it with 16-byte copies.
+    float* kcrs = nullptr;
+    size_t wn = (size_t)n * c * r * s;
+    if ((rc = upload(&kcrs, host_w_kcrs, wn, 1.0f))) { tdc_conv_destroy(l); return rc; }
+    cudaError_t e = cudaMalloc((void**)&l->kernel, wn * sizeof(float));
+    if (e != cudaSuccess) { cudaFree(kcrs); tdc_conv_destroy(l); return cuda_fail("cudaMalloc", e); }
+    rc = tdc_permute_weights(kcrs, l->kernel, n, c, r, s, nullptr);
+    e = cudaDeviceSynchronize();
+    cudaFree(kcrs);
+    if (rc || e != cudaSuccess) { tdc_conv_destroy(l); return rc ? rc : cuda_fail("permute", e); }
+    if (host_bias && (rc = upload(&l->bias, host_bias, n, 0.f))) { tdc_conv_destroy(l); return rc; }
+    e = cudaMalloc((void**)&l->output, (size_t)b * n * l->ho * l->wo * sizeof(float));
+    if (e != cudaSuccess) { tdc_conv_destroy(l); return cuda_fail("cudaMalloc", e); }
+    *out = l;
+    return TDC_OK;
+}
+
+int tdc_conv_set_tile(tdc_conv* l, const tdc_tile* tile) {
+    if (!l) return TDC_ERR_NULL;
+    l->has_tile = tile != nullptr;
+    if (tile) l->tile = *tile;
+    return TDC_OK;
+}
+
+int tdc_conv_forward(tdc_conv* l, const float* dev_in, float** dev_out, void* stream) {
+    if (!l || !dev_in || !dev_out) return TDC_ERR_NULL;
+    int rc = tdc_conv2d_f32(dev_in, l->kernel, l->bias, l->output, l->b, l->c, l->h, l->w, l->n, l->r, l->s, l->pad,
+                            l->stride, TDC_W_CRSK, TDC_EPI_NONE, l->has_tile ? &l->tile : nullptr, stream);
+    if (rc) return rc;
+    *dev_out = l->output;
+    return TDC_OK;
+}
+
+int tdc_conv_forward_host(tdc_conv* l, const float* host_in, float* host_out) {
+    if (!l || !host_in || !host_out) return TDC_ERR_NULL;
+    size_t in_bytes = (size_t)l->b * l->c * l->h * l->w * sizeof(float);
+    cudaError_t e;
+    if (!l->staging_in && (e = cudaMalloc((void**)&l->staging_in, in_bytes)) != cudaSuccess) return cuda_fail("cudaMalloc", e);
+    if ((e = cudaMemcpyAsync(l->staging_in, host_in, in_bytes, cudaMemcpyHostToDevice, nullptr)) != cudaSuccess)
+        return cuda_fail("copy in", e);
+    float* o;
+    int rc = tdc_conv_forward(l, l->staging_in, &o, nullptr);
+    if (rc) return rc;
+    e = cudaMemcpyAsync(host_out, o, (size_t)l->b * l->n * l->ho * l->wo * sizeof(float), cudaMemcpyDeviceToHost, nullptr);
+    if (e != cudaSuccess) return cuda_fail("copy out", e);
+    e = cudaStreamSynchronize(nullptr);
+    return e == cudaSuccess ? TDC_OK : cuda_fail("synchronize", e);
+}
+
+void tdc_tkconv_destroy(tdc_tkconv* l) {
+    if (!l) return;
+    cudaFree(l->w1); cudaFree(l->wcore); cudaFree(l->w3); cudaFree(l->bias);
+    cudaFree(l->output); cudaFree(l->staging_in); cudaFree(l->workspace);
+    delete l;
+}
+
+int tdc_tkconv_create(tdc_tkconv** out, int b, int C, int N1, int N2, int N3, int h, int w, int r, int s, int pad,
+                      int stride, const float* host_w1, const float* host_wcore_kcrs, const float* host_w3,
+                      const float* host_bias) {
+    if (!out) return TDC_ERR_NULL;
+    *out = nullptr;
+    if (b <= 0 || C <= 0 || N1 <= 0 || N2 <= 0 || N3 <= 0 || h <= 0 || w <= 0 || r <= 0 || s <= 0 || stride <= 0 ||
+        pad < 0 || h + 2 * pad < r || w + 2 * pad < s)
+        return TDC_ERR_SHAPE;
+    tdc_tkconv* l = new tdc_tkconv;
+    l->b = b; l->C = C; l->N1 = N1; l->N2 = N2; l->N3 = N3; l->h = h; l->w = w; l->r = r; l->s = s;
+    l->pad = pad; l->stride = stride;
+    l->ho = (h + 2 * pad - r) / stride + 1;
+    l->wo = (w + 2 * pad - s) / stride + 1;
+    int rc;
+    if ((rc = upload(&l->w1, host_w1, (size_t)N1 * C, 1.0f))) { tdc_tkconv_destroy(l); return rc; }
+    if ((rc = upload(&l->w3, host_w3, (size_t)N3 * N2, 1.0f))) { tdc_tkconv_destroy(l); return rc; }
+    float* kcrs = nullptr;
+    size_t wn = (size_t)N2 * N1 * r * s;
+    if ((rc = upload(&kcrs, host_wcore_kcrs, wn, 1.0f))) { tdc_tkconv_destroy(l); return rc; }
+    cudaError_t e = cudaMalloc((void**)&l->wcore, wn * sizeof(float));
+    if (e != cudaSuccess) { cudaFree(kcrs); tdc_tkconv_destroy(l); return cuda_fail("cudaMalloc", e); }
+    rc = tdc_permute_weights(kcrs, l->wcore, N2, N1, r, s, nullptr);
+    e = cudaDeviceSynchronize();
+    cudaFree(kcrs);
+    if (rc || e != cudaSuccess) { tdc_tkconv_destroy(l); return rc ? rc : cuda_fail("permute", e); }
+    if (host_bias && (rc = upload(&l->bias, host_bias, N3, 0.f))) { tdc_tkconv_destroy(l); return rc; }
+    l->workspace_bytes = tdc_tk_block_workspace_bytes(b, C, h, w, N1, N2, N3, r, s, pad, stride);
+    if ((e = cudaMalloc(&l->workspace, l->workspace_bytes)) != cudaSuccess ||
+        (e = cudaMalloc((void**)&l->output, (size_t)b * N3 * l->ho * l->wo * sizeof(float))) != cudaSuccess) {
+        tdc_tkconv_destroy(l);
+        return cuda_fail("cudaMalloc", e);
+    }
+    *out = l;
+    return TDC_OK;
+}
+
+int tdc_tkconv_forward(tdc_tkconv* l, const float* dev_in, float** dev_out, void* stream) {
+    if (!l || !dev_in || !dev_out) return TDC_ERR_NULL;
+    int rc = tdc_tk_block_f32(dev_in, l->w1, l->wcore, l->w3, l->bias, l->output, l->b, l->C, l->h, l->w, l->N1,
+                              l->N2, l->N3, l->r, l->s, l->pad, l->stride, TDC_W_CRSK, TDC_EPI_NONE, l->workspace,
+                              l->workspace_bytes, stream);
+    if (rc) return rc;
+    *dev_out = l->output;
+    return TDC_OK;
+}
+
+int tdc_tkconv_forward_host(tdc_tkconv* l, const float* host_in, float* host_out) {
+    if (!l || !host_in || !host_out) return TDC_ERR_NULL;
+    size_t in_bytes = (size_t)l->b * l->C * l->h * l->w * sizeof(float);
+    cudaError_t e;
+    if (!l->staging_in && (e = cudaMalloc((void**)&l->staging_in, in_bytes)) != cudaSuccess) return cuda_fail("cudaMalloc", e);
+    if ((e = cudaMemcpyAsync(l->staging_in, host_in, in_bytes, cudaMemcpyHostToDevice, nullptr)) != cudaSuccess)
+        return cuda_fail("copy in", e);
+    float* o;
+    int rc = tdc_tkconv_forward(l, l->staging_in, &o, nullptr);
+    if (rc) return rc;
+    e = cudaMemcpyAsync(host_out, o, (size_t)l->b * l->N3 * l->ho * l->wo * sizeof(float), cudaMemcpyDeviceToHost, nullptr);
+    if (e != cudaSuccess) return cuda_fail("copy out", e);
+    e = cudaStreamSynchronize(nullptr);
+    return e == cudaSuccess ? TDC_OK : cuda_fail("synchronize", e);
+}
+
+}  // extern "C"

@@ -1,0 +1,18 @@
+"""tdc_b200 — B200-native core convolution of Tucker-factorised conv layers.
+
+The package is a thin host layer over libtdc_b200.so (hand-written sm_100a CUDA behind a
+C ABI, see include/tdc_b200.h).  It mirrors the reference's operator surface for this
+path: TKConv2dC (inference/TKConv.py:23-141) as TKConv2dC_B200, the (TH, TW, TC) tiling
+parameters of its code generators as Tile, and its analytical tile selector
+(A100-evaluation/TDC-LAYERS-MODELING/model.py) as select_tile.
+"""
+from ._lib import B200, EPI_NONE, EPI_RELU, LIB_PATH, W_CRSK, W_KCRS, DevInfo, LaunchInfo, TdcError, Tile, lib
+from .ops import (conv2d, core_conv2d, out_hw, permute_weights, query_device, select_tile, tile_cost, tile_info,
+                  tk_block, tk_block_workspace_bytes)
+from .tkconv import TKConv2dC_B200
+
+__all__ = [
+    "B200", "DevInfo", "EPI_NONE", "EPI_RELU", "LIB_PATH", "LaunchInfo", "TKConv2dC_B200", "TdcError", "Tile",
+    "W_CRSK", "W_KCRS", "conv2d", "core_conv2d", "lib", "out_hw", "permute_weights", "query_device",
+    "select_tile", "tile_cost", "tile_info", "tk_block", "tk_block_workspace_bytes",
+]

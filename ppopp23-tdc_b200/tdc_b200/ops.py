@@ -1,0 +1,148 @@
+"""Torch-facing operators over the C ABI.  Tensors only lend their device pointers and the
+current stream; all arithmetic happens in libtdc_b200.so.  Inputs must be CUDA, fp32 and
+contiguous — anything else raises (there is no fallback path)."""
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import EPI_NONE, EPI_RELU, W_CRSK, W_KCRS, DevInfo, LaunchInfo, TdcError, Tile, check, lib
+
+
+def _pair(v):
+    if isinstance(v, (tuple, list)):
+        if len(v) != 2 or v[0] != v[1]:
+            raise TdcError(_lib.ERR_UNSUPPORTED, "only equal vertical/horizontal %r is built" % (v,))
+        return int(v[0])
+    return int(v)
+
+
+def _dev_f32(t, name):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
+        raise TdcError(_lib.ERR_UNSUPPORTED, "%s must be a contiguous fp32 CUDA tensor" % name)
+    return t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def out_hw(H, W, R, S, pad, stride):
+    return (H + 2 * pad - R) // stride + 1, (W + 2 * pad - S) // stride + 1
+
+
+def permute_weights(w_kcrs):
+    """[K][C][R][S] -> [C][R][S][K], the layout the kernel stages with 16-byte copies
+    (the reference kernel's own k[c][r][s][n],
+    A100-evaluation/TDC-LAYERS-ORACLE/template_benchmark_cudnn.template:396)."""
+    K, Cc, R, S = w_kcrs.shape
+    out = torch.empty((Cc, R, S, K), device=w_kcrs.device, dtype=torch.float32)
+    with torch.cuda.device(w_kcrs.device):
+        check(lib.tdc_permute_weights(_dev_f32(w_kcrs, "w"), out.data_ptr(), K, Cc, R, S, _stream()))
+    return out
+
+
+def conv2d(x, w, bias=None, stride=1, padding=0, w_layout=W_KCRS, relu=False, tile=None, out=None):
+    """y = conv2d(x, w) (+bias)(ReLU). The core step of TKConv2dC.forward
+    (inference/TKConv.py:92-93) when bias is None; with R=S=1 its first/last step (:91,:94)."""
+    stride, padding = _pair(stride), _pair(padding)
+    B, Cc, H, W = x.shape
+    if w_layout == W_KCRS:
+        K, Cw, R, S = w.shape
+    else:
+        Cw, R, S, K = w.shape
+    if Cw != Cc:
+        raise TdcError(_lib.ERR_SHAPE, "x has %d channels, w expects %d" % (Cc, Cw))
+    Ho, Wo = out_hw(H, W, R, S, padding, stride)
+    if out is None:
+        out = torch.empty((B, K, max(Ho, 0), max(Wo, 0)), device=x.device, dtype=torch.float32)
+    tp = C.byref(tile) if tile is not None else None
+    with torch.cuda.device(x.device):
+        check(lib.tdc_conv2d_f32(_dev_f32(x, "x"), _dev_f32(w, "w"),
+                                 _dev_f32(bias, "bias") if bias is not None else None, _dev_f32(out, "out"),
+                                 B, Cc, H, W, K, R, S, padding, stride, w_layout,
+                                 EPI_RELU if relu else EPI_NONE, tp, _stream()))
+    return out
+
+
+def core_conv2d(x, w, stride=1, padding=0, w_layout=W_KCRS, tile=None, out=None):
+    """The hot path through tdc_core_conv2d_f32 (no bias, no activation)."""
+    stride, padding = _pair(stride), _pair(padding)
+    B, Cc, H, W = x.shape
+    if w_layout == W_KCRS:
+        K, Cw, R, S = w.shape
+    else:
+        Cw, R, S, K = w.shape
+    if Cw != Cc:
+        raise TdcError(_lib.ERR_SHAPE, "x has %d channels, w expects %d" % (Cc, Cw))
+    Ho, Wo = out_hw(H, W, R, S, padding, stride)
+    if out is None:
+        out = torch.empty((B, K, max(Ho, 0), max(Wo, 0)), device=x.device, dtype=torch.float32)
+    tp = C.byref(tile) if tile is not None else None
+    with torch.cuda.device(x.device):
+        check(lib.tdc_core_conv2d_f32(_dev_f32(x, "x"), _dev_f32(w, "w"), _dev_f32(out, "out"),
+                                      B, Cc, H, W, K, R, S, padding, stride, w_layout, tp, _stream()))
+    return out
+
+
+def tk_block_workspace_bytes(B, Cc, H, W, R1, R2, K, R, S, pad, stride):
+    return lib.tdc_tk_block_workspace_bytes(B, Cc, H, W, R1, R2, K, R, S, pad, stride)
+
+
+def tk_block(x, first, core, last, bias=None, stride=1, padding=0, core_layout=W_KCRS, relu=False,
+             workspace=None, out=None):
+    """TKConv2dC.forward (inference/TKConv.py:90-95): 1x1 C->R1, core R1->R2, 1x1 R2->K + bias.
+    `first` is [R1][C][1][1] (or [R1][C]), `last` is [K][R2][1][1] (or [K][R2])."""
+    stride, padding = _pair(stride), _pair(padding)
+    B, Cc, H, W = x.shape
+    R1, K = first.shape[0], last.shape[0]
+    if core_layout == W_KCRS:
+        R2, R1c, R, S = core.shape
+    else:
+        R1c, R, S, R2 = core.shape
+    if first.shape[1] != Cc or R1c != R1 or last.shape[1] != R2:
+        raise TdcError(_lib.ERR_SHAPE, "Tucker factors do not chain: first %s core %s last %s" %
+                       (tuple(first.shape), tuple(core.shape), tuple(last.shape)))
+    Ho, Wo = out_hw(H, W, R, S, padding, stride)
+    need = tk_block_workspace_bytes(B, Cc, H, W, R1, R2, K, R, S, padding, stride)
+    if workspace is None:
+        workspace = torch.empty(need, device=x.device, dtype=torch.uint8)
+    if out is None:
+        out = torch.empty((B, K, Ho, Wo), device=x.device, dtype=torch.float32)
+    with torch.cuda.device(x.device):
+        check(lib.tdc_tk_block_f32(_dev_f32(x, "x"), _dev_f32(first, "first"), _dev_f32(core, "core"),
+                                   _dev_f32(last, "last"), _dev_f32(bias, "bias") if bias is not None else None,
+                                   _dev_f32(out, "out"), B, Cc, H, W, R1, R2, K, R, S, padding, stride,
+                                   core_layout, EPI_RELU if relu else EPI_NONE,
+                                   workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream()))
+    return out
+
+
+def select_tile(B, Cc, H, W, K, R=3, S=3, pad=1, stride=1, dev=None):
+    """Analytical tile choice (tdc_select_tile). `dev=None` queries the current GPU; pass
+    `_lib.B200` to model a B200 without one."""
+    t = Tile()
+    check(lib.tdc_select_tile(B, Cc, H, W, K, R, S, pad, stride, C.byref(dev) if dev is not None else None,
+                              C.byref(t)))
+    return t
+
+
+def tile_cost(shape, tile, dev=None):
+    """(cycles, [filter volume, input volume, output volume, flops*waves]) of a complete tile."""
+    cost = C.c_double()
+    vols = (C.c_double * 4)()
+    check(lib.tdc_tile_cost(*shape, C.byref(tile), C.byref(dev) if dev is not None else None, C.byref(cost), vols))
+    return cost.value, list(vols)
+
+
+def tile_info(shape, tile):
+    """Completes `tile` in place and returns the launch facts (needs a GPU)."""
+    info = LaunchInfo()
+    check(lib.tdc_tile_info(*shape, C.byref(tile), C.byref(info)))
+    return info
+
+
+def query_device(device=-1):
+    d = DevInfo()
+    check(lib.tdc_query_device(device, C.byref(d)))
+    return d

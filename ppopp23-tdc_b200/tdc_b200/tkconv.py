@@ -1,0 +1,131 @@
+"""TKConv2dC_B200 — the reference's Tucker-2 conv module with its forward on libtdc_b200.so.
+
+Mirrors inference/TKConv.py:23-141 (class TKConv2dC): same constructor arguments, same
+parameter names and shapes (first_kernel [R1,C,1,1], core_kernel [R2,R1,kh,kw], last_kernel
+[K,R2,1,1], bias [K] or None), same ValueError for groups != 1 / padding_mode != 'zeros',
+same xavier-uniform reset, same forward_features / forward_flops / extra_repr outputs.  A
+state dict saved from the reference module loads unchanged, and the class can be passed as
+the `conv=` argument of the reference's model builders (inference/resnet_inet_tt.py:32-38).
+"""
+from typing import Optional
+
+import torch
+import torch.nn as nn
+from torch import Tensor
+from torch.nn import Parameter, init
+from torch.nn.modules.utils import _pair
+
+from . import ops
+from ._lib import W_CRSK, TdcError, ERR_UNSUPPORTED
+
+
+class TKConv2dC_B200(nn.Module):
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1,
+                 groups: int = 1, bias: bool = True, padding_mode: str = 'zeros', hp_dict: Optional = None,
+                 name: str = None, dense_w: Tensor = None, dense_b: Tensor = None):
+        if groups != 1:
+            raise ValueError("groups must be 1 in this mode")
+        if padding_mode != 'zeros':
+            raise ValueError("padding_mode must be zero in this mode")
+        super().__init__()
+        self.in_channels = in_channels
+        self.out_channels = out_channels
+        self.ranks = hp_dict.ranks[name]          # [out_rank (R2), in_rank (R1)], TKConv.py:52-54
+        self.in_rank = self.ranks[1]
+        self.out_rank = self.ranks[0]
+        self.kernel_size = _pair(kernel_size)
+        self.stride = _pair(stride)
+        self.padding = _pair(padding)
+        self.dilation = _pair(dilation)
+        self.transposed = False
+        self.output_padding = _pair(0)
+        self.groups = groups
+        self.padding_mode = padding_mode
+
+        self.first_kernel = Parameter(torch.empty(self.in_rank, in_channels, 1, 1))
+        self.core_kernel = Parameter(torch.empty(self.out_rank, self.in_rank, *self.kernel_size))
+        self.last_kernel = Parameter(torch.empty(out_channels, self.out_rank, 1, 1))
+        if bias:
+            self.bias = Parameter(torch.zeros(out_channels))
+            if dense_b is not None:
+                self.bias.data = dense_b
+        else:
+            self.register_parameter('bias', None)
+        if dense_w is not None:
+            from .tucker import partial_tucker_hosvd
+            core, (last_factor, first_factor) = partial_tucker_hosvd(dense_w, self.ranks)
+            self.first_kernel.data = first_factor.t().contiguous().unsqueeze(-1).unsqueeze(-1)
+            self.last_kernel.data = last_factor.contiguous().unsqueeze(-1).unsqueeze(-1)
+            self.core_kernel.data = core.contiguous()
+        else:
+            self.reset_parameters()
+        self._core_crsk = None      # (version, data_ptr, tensor): channel-last copy of core_kernel
+        self._workspace = None
+
+    def reset_parameters(self) -> None:
+        init.xavier_uniform_(self.first_kernel)
+        init.xavier_uniform_(self.core_kernel)
+        init.xavier_uniform_(self.last_kernel)
+
+    # -- B200 path ---------------------------------------------------------------------
+    def _check(self, x):
+        if self.dilation != (1, 1):
+            raise TdcError(ERR_UNSUPPORTED, "dilation %r is not built" % (self.dilation,))
+        if not x.is_cuda:
+            raise TdcError(ERR_UNSUPPORTED, "TKConv2dC_B200 runs on CUDA tensors only")
+        return x.contiguous().float() if (x.dtype != torch.float32 or not x.is_contiguous()) else x
+
+    def _core_channel_last(self):
+        w = self.core_kernel
+        key = (w._version, w.data_ptr())
+        if self._core_crsk is None or self._core_crsk[0] != key:
+            self._core_crsk = (key, ops.permute_weights(w.detach().contiguous()))
+        return self._core_crsk[1]
+
+    def _ws(self, x):
+        B, C, H, W = x.shape
+        need = ops.tk_block_workspace_bytes(B, C, H, W, self.in_rank, self.out_rank, self.out_channels,
+                                            self.kernel_size[0], self.kernel_size[1], self.padding[0], self.stride[0])
+        ws = self._workspace
+        if ws is None or ws.numel() < need or ws.device != x.device:
+            ws = self._workspace = torch.empty(need, device=x.device, dtype=torch.uint8)
+        return ws
+
+    def forward(self, x):
+        x = self._check(x)
+        return ops.tk_block(x, self.first_kernel.detach(), self._core_channel_last(), self.last_kernel.detach(),
+                            None if self.bias is None else self.bias.detach(), self.stride, self.padding,
+                            core_layout=W_CRSK, workspace=self._ws(x))
+
+    def forward_features(self, x):
+        x = self._check(x)
+        features = []
+        out = ops.conv2d(x, self.first_kernel.detach())
+        features.append(out)
+        out = ops.core_conv2d(out, self._core_channel_last(), self.stride, self.padding, w_layout=W_CRSK)
+        features.append(out)
+        out = ops.conv2d(out, self.last_kernel.detach(), None if self.bias is None else self.bias.detach())
+        features.append(out)
+        return out, features
+
+    def forward_flops(self, x):
+        compr_params = (self.first_kernel.numel() + self.core_kernel.numel() + self.last_kernel.numel()) / 1000
+        out, feats = self.forward_features(x)
+        compr_flops = 0
+        for f, k in zip(feats, (self.first_kernel, self.core_kernel, self.last_kernel)):
+            compr_flops += f.shape[2] * f.shape[3] * k.numel() / 1000 / 1000
+        height_, width_ = out.shape[2], out.shape[3]
+        base_params = self.kernel_size[0] * self.kernel_size[1] * self.in_channels * self.out_channels / 1000
+        base_flops = height_ * width_ * self.kernel_size[0] * self.kernel_size[1] * \
+            self.in_channels * self.out_channels / 1000 / 1000
+        print('baseline # params: {:.2f}K\t compressed # params: {:.2f}K\t '
+              'baseline # flops: {:.2f}M\t compressed # flops: {:.2f}M'.format(base_params, compr_params, base_flops,
+                                                                               compr_flops))
+        return out, base_flops, compr_flops
+
+    def extra_repr(self):
+        return ('first_conv(in={}, out={}, kernel_size=(1, 1), bias=False), '
+                'core_conv(in={}, out={}, kernel_size={}, stride={}, padding={}, bias={}), '
+                'last_conv(in={}, out={}, kernel_size=(1, 1), bias=False)'
+                .format(self.in_channels, self.in_rank, self.in_rank, self.out_rank, self.kernel_size,
+                        self.stride, self.padding, self.bias is None, self.out_rank, self.out_channels))

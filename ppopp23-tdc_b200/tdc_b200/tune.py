@@ -1,0 +1,136 @@
+"""Measured tile table for B200 — the counterpart of the reference's occupancy/time tables.
+
+The reference builds `a100-occupancy-unrolled` by generating, compiling and running one
+program per (shape, th, tw, tc) (A100-evaluation/Gen-occupancy/gen.py:78-102,
+template.cu:231-287) and picks the fastest row per shape
+(A100-evaluation/TDC-LAYERS-ORACLE/gen_from_occupancy.py:51-66).  Here the kernel takes its
+tile at run time, so the table is built in one process:
+
+    python -m tdc_b200.tune --batch 64 --out table.csv [--max-per-shape 300]
+
+Rows keep the reference's ten columns `C,N,H,W,th,tw,tc,occupancy,diff,time_ms` (C/N =
+input/output channels of the core conv) and append the fields this kernel adds:
+`B,tn,nog,gy,gx,imgs,ks,threads,smem,ctas,model_cycles`.  `diff` is the L1 distance to the
+exact result for integer inputs 0..9 and all-ones weights, the reference drivers' own check
+(template_benchmark_cudnn.template:418-428,509); it must be 0 in every row.
+`best_rows(path)` is query_best() for such a table.
+"""
+import argparse
+import csv
+import itertools
+import random
+import statistics
+import sys
+
+SWEEP = [(56, 32, 32), (56, 64, 64), (28, 64, 64), (28, 128, 128), (14, 128, 128), (14, 256, 256),
+         (7, 256, 256), (7, 512, 512)]
+COLUMNS = ["C", "N", "H", "W", "th", "tw", "tc", "occupancy", "diff", "time_ms",
+           "B", "tn", "nog", "gy", "gx", "imgs", "ks", "threads", "smem", "ctas", "model_cycles"]
+
+
+def cdiv(a, b):
+    return (a + b - 1) // b
+
+
+def candidates(B, C, H, W, K, R=3, S=3, pad=1, stride=1):
+    """Every tile of the compiled thread-tile set that can be launched for the shape."""
+    Ho, Wo = (H + 2 * pad - R) // stride + 1, (W + 2 * pad - S) // stride + 1
+    out = []
+    for tn, th, tw, nog in itertools.product((4, 8), (1, 2), (7, 8), (4, 8)):
+        maxt = 256 if tn * th * tw > 64 else 512
+        GY, GX = cdiv(Ho, th), cdiv(Wo, tw)
+        gys = sorted({cdiv(GY, n) for n in range(1, GY + 1)})
+        gxs = sorted({cdiv(GX, n) for n in range(1, GX + 1)})
+        for gy, gx in itertools.product(gys, gxs):
+            ims = [1]
+            if gy == GY and gx == GX:
+                ims += [m for m in (2, 3, 4, 6, 7, 8, 12, 14, 16) if m <= B]
+            for im in ims:
+                nt = nog * im * gy * gx
+                for ks in (1, 2, 4, 8):
+                    thr = nt * ks
+                    if thr > maxt or thr < 64:
+                        continue
+                    for tc in (8, 16, 32):
+                        if tc % ks or tc > max(C, 8):
+                            continue
+                        out.append((th, tw, tc, tn, nog, gy, gx, im, ks))
+    return out
+
+
+def best_rows(path):
+    """Fastest row per (C,N,H,W,B): the reference's query_best over this table."""
+    best = {}
+    with open(path) as f:
+        for row in csv.DictReader(f):
+            if float(row["diff"]) != 0.0:
+                continue
+            key = tuple(int(row[k]) for k in ("C", "N", "H", "W", "B"))
+            if key not in best or float(row["time_ms"]) < float(best[key]["time_ms"]):
+                best[key] = row
+    return best
+
+
+def main(argv=None):
+    import torch
+    from . import ops
+    from ._lib import Tile, TdcError, W_CRSK
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--out", default="tile_table.csv")
+    ap.add_argument("--max-per-shape", type=int, default=300)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--stride", type=int, default=1)
+    ap.add_argument("--seed", type=int, default=0)
+    a = ap.parse_args(argv)
+    rnd = random.Random(a.seed)
+    dev = torch.device("cuda")
+    stream = torch.cuda.current_stream()
+    sm = ops.query_device().sm_count
+    with open(a.out, "w", newline="") as f:
+        wr = csv.writer(f)
+        wr.writerow(COLUMNS)
+        for (H, R1, R2) in SWEEP:
+            B = a.batch
+            shape = (B, R1, H, H, R2, 3, 3, 1, a.stride)
+            g = torch.Generator().manual_seed(H * 1000 + R1)
+            x = torch.randint(0, 10, (B, R1, H, H), generator=g).float().to(dev)
+            w = torch.ones(R1, 3, 3, R2, device=dev)
+            exact = torch.nn.functional.conv2d(x.double(), torch.ones(R2, R1, 3, 3, device=dev, dtype=torch.double),
+                                               None, a.stride, 1).float()
+            y = torch.empty_like(exact)
+            cands = candidates(B, R1, H, H, R2, stride=a.stride)
+            model_pick = ops.select_tile(*shape).as_tuple()
+            if len(cands) > a.max_per_shape:
+                cands = rnd.sample(cands, a.max_per_shape)
+            if model_pick not in cands:
+                cands.append(model_pick)
+            for c in cands:
+                t = Tile(*c)
+                try:
+                    info = ops.tile_info(shape, t)
+                    cost, _ = ops.tile_cost(shape, t)
+                    run = lambda: ops.core_conv2d(x, w, a.stride, 1, w_layout=W_CRSK, tile=t, out=y)
+                    run(); run()
+                    ts = []
+                    for _ in range(a.iters):
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(stream); run(); e1.record(stream); e1.synchronize()
+                        ts.append(e0.elapsed_time(e1))
+                    diff = float((y - exact).abs().sum())
+                except TdcError:
+                    continue
+                occ = info.ctas_per_sm * info.threads / 2048.0
+                wr.writerow([R1, R2, H, H, t.th, t.tw, t.tc, "%.4f" % occ, "%g" % diff, "%.6f" % statistics.median(ts),
+                             B, t.tn, t.nog, t.gy, t.gx, t.imgs, t.ks, info.threads, info.smem_bytes, info.grid_x,
+                             "%.0f" % cost])
+            f.flush()
+            print("shape", (H, R1, R2), "rows", len(cands), "model pick", model_pick, file=sys.stderr)
+    for key, row in sorted(best_rows(a.out).items()):
+        print(key, "best %.4f ms" % float(row["time_ms"]),
+              {k: row[k] for k in ("th", "tw", "tc", "tn", "nog", "gy", "gx", "imgs", "ks")}, file=sys.stderr)
+
+
+if __name__ == "__main__":
+    main()
