@@ -193,7 +193,7 @@ def main():
         xd = x.to(dev)
         wd = T.permute_weights(w.to(dev))
         y = torch.empty(BATCH, R2, H, H, device=dev)
-        tile = T.select_tile(BATCH, R1, H, H, R2, 3, 3, 1, 1)
+        tile = T.best_tile(BATCH, R1, H, H, R2, 3, 3, 1, 1)
         layers.append(dict(H=H, R1=R1, R2=R2, x=xd, w=wd, y=y, tile=tile, x_host=x, w_host=w))
 
     def step():
@@ -326,7 +326,7 @@ def main():
             H, R1, R2 = L["H"], L["R1"], L["R2"]
             wk = L["w_host"].to(dev)
             x1 = L["x"][:1].contiguous()
-            t1 = T.select_tile(1, R1, H, H, R2, 3, 3, 1, 1)
+            t1 = T.best_tile(1, R1, H, H, R2, 3, 3, 1, 1)
             y1 = torch.empty(1, R2, H, H, device=dev)
             us1 = time_layer(lambda: T.core_conv2d(x1, L["w"], 1, 1, w_layout=T.W_CRSK, tile=t1, out=y1), iters=20)
             cud64 = time_layer(lambda: F.conv2d(L["x"], wk, None, 1, 1))

@@ -172,6 +172,7 @@ TDC_API int tdc_tk_block_f32(const float* x, const float* w1, const float* wcore
                      const float* bias, float* y,
                      int B, int C, int H, int W, int R1, int R2, int K, int R, int S,
                      int pad, int stride, int w_layout, int epilogue,
+                     const tdc_tile* core_tile /* NULL = auto */,
                      void* workspace, size_t workspace_bytes, void* stream);
 
 /*

@@ -270,7 +270,8 @@ size_t tdc_tk_block_workspace_bytes(int B, int C, int H, int W, int R1, int R2, 
 
 int tdc_tk_block_f32(const float* x, const float* w1, const float* wcore, const float* w3, const float* bias,
                      float* y, int B, int C, int H, int W, int R1, int R2, int K, int R, int S, int pad, int stride,
-                     int w_layout, int epilogue, void* workspace, size_t workspace_bytes, void* stream) {
+                     int w_layout, int epilogue, const tdc_tile* core_tile, void* workspace, size_t workspace_bytes,
+                     void* stream) {
     if (!x || !w1 || !wcore || !w3 || !y) return fail(TDC_ERR_NULL, "x, w1, wcore, w3 and y must be non-NULL");
     size_t need = tdc_tk_block_workspace_bytes(B, C, H, W, R1, R2, K, R, S, pad, stride);
     if (need == 0) return fail(TDC_ERR_SHAPE, "bad Tucker block shape");
@@ -283,7 +284,7 @@ int tdc_tk_block_f32(const float* x, const float* w1, const float* wcore, const 
     int rc;
     // 1x1 convs take their filter as [out][in] = KCRS with R=S=1.
     if ((rc = launch_conv(x, w1, nullptr, z1, Shape{B, C, H, W, R1, 1, 1, 0, 1}, TDC_W_KCRS, TDC_EPI_NONE, nullptr, st))) return rc;
-    if ((rc = launch_conv(z1, wcore, nullptr, z2, Shape{B, R1, H, W, R2, R, S, pad, stride}, w_layout, TDC_EPI_NONE, nullptr, st))) return rc;
+    if ((rc = launch_conv(z1, wcore, nullptr, z2, Shape{B, R1, H, W, R2, R, S, pad, stride}, w_layout, TDC_EPI_NONE, core_tile, st))) return rc;
     return launch_conv(z2, w3, bias, y, Shape{B, R2, Ho, Wo, K, 1, 1, 0, 1}, TDC_W_KCRS, epilogue, nullptr, st);
 }
 

@@ -16,6 +16,13 @@
 //     output needs no zeroing; the sum over channels has a fixed order;
 //   * input patch (with its zero-padding halo) and the weight chunk are staged with
 //     cp.async into a two-stage ring, the next chunk in flight while this one is used;
+//   * the inner loop is shaped by the one resource that binds an fp32 direct conv on
+//     this machine, the shared-memory return path (128 B per clock per SM against 128
+//     FMAs per clock per SM): a channel's TN x 9 weights are read once into registers,
+//     each staged input row is read once and used for every filter row it meets, and
+//     the tallest thread tiles (TH = 4) reach ~12 FMAs per word loaded;
+//   * the staged filter is laid out [tap][TN/4][NOG][4] so the eight lanes that share a
+//     128-byte shared-memory wavefront read one contiguous, conflict-free line;
 //   * `ks` thread slices may split the channels of a chunk (small feature maps leave
 //     too few pixels to fill 148 SMs otherwise); slices are summed through shared
 //     memory in slice order.
@@ -86,6 +93,17 @@ __device__ __forceinline__ void load_window(const float* p, float (&v)[LEN]) {
     } else {
 #pragma unroll
         for (int i = 0; i < LEN; ++i) v[i] = p[i];
+    }
+}
+
+// One tap's TN weights of this thread's channel group: float4 h of the group sits at
+// (h*NOG + ocg)*4 in the tap's row; `p` already points at ocg*4.
+template <int TN, int NOG>
+__device__ __forceinline__ void load_taps(const float* p, float (&v)[TN]) {
+#pragma unroll
+    for (int h = 0; h < TN / 4; ++h) {
+        float4 q = *reinterpret_cast<const float4*>(p + h * NOG * 4);
+        v[4 * h + 0] = q.x; v[4 * h + 1] = q.y; v[4 * h + 2] = q.z; v[4 * h + 3] = q.w;
     }
 }
 
@@ -169,7 +187,8 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
             for (int i = tid; i < items; i += nthr) {
                 int q = i / V, v = i - q * V;
                 bool ok = (oc0 + 4 * v) < a.K;
-                cp_async16(w_s + q * OCB + 4 * v, src + (long long)q * a.K + (ok ? 4 * v : 0), ok);
+                int og = v / (TN / 4), h = v - og * (TN / 4);
+                cp_async16(w_s + q * OCB + (h * NOG + og) * 4, src + (long long)q * a.K + (ok ? 4 * v : 0), ok);
             }
         } else {
             const int rows  = tcc * RS;
@@ -183,7 +202,8 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
                 const float* src = a.w + (ok ? (long long)(oc0 + ol) * a.ws_k + (long long)(c0 + cl) * a.ws_c +
                                                    (long long)rs * a.ws_rs
                                              : 0);
-                cp_async4(w_s + q * OCB + ol, src, ok);
+                int og = ol / TN, rem = ol - og * TN;
+                cp_async4(w_s + q * OCB + ((rem >> 2) * NOG + og) * 4 + (rem & 3), src, ok);
             }
         }
     };
@@ -214,29 +234,33 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
 
         const int tcc = min(a.tc, a.C - kc * a.tc);
         const float* in_s = cur + win;
-        const float* w_s  = cur + in_stage + ocg * TN;
+        const float* w_s  = cur + in_stage + ocg * 4;
 
         if constexpr (!RT) {
+            constexpr int IN_ROWS = (TH - 1) * STRIDE + KH;
 #pragma unroll CUNR
             for (int cl = ksl; cl < tcc; cl += a.ks) {
                 const float* ip = in_s + cl * a.patch;
                 const float* wp = w_s + cl * (KH * KW * OCB);
+                float wr[KH * KW][TN];
 #pragma unroll
-                for (int r = 0; r < KH; ++r) {
-                    float wr[KW][TN];
+                for (int q = 0; q < KH * KW; ++q) load_taps<TN, NOG>(wp + q * OCB, wr[q]);
 #pragma unroll
-                    for (int s = 0; s < KW; ++s) load_window<TN, true>(wp + (r * KW + s) * OCB, wr[s]);
+                for (int i = 0; i < IN_ROWS; ++i) {
+                    float row[ROWLEN];
+                    load_window<ROWLEN, VEC>(ip + i * a.in_wp, row);
 #pragma unroll
-                    for (int o = 0; o < TH; ++o) {
-                        float row[ROWLEN];
-                        load_window<ROWLEN, VEC>(ip + (o * STRIDE + r) * a.in_wp, row);
+                    for (int r = 0; r < KH; ++r) {
+                        // input row i meets filter row r in output row o = (i - r) / STRIDE
+                        if ((i - r) < 0 || (i - r) % STRIDE != 0 || (i - r) / STRIDE >= TH) continue;
+                        const int o = (i - r) / STRIDE;
 #pragma unroll
                         for (int s = 0; s < KW; ++s)
 #pragma unroll
                             for (int j = 0; j < TN; ++j)
 #pragma unroll
                                 for (int p = 0; p < TW; ++p)
-                                    acc[j][o][p] = fmaf(wr[s][j], row[p * STRIDE + s], acc[j][o][p]);
+                                    acc[j][o][p] = fmaf(wr[r * KW + s][j], row[p * STRIDE + s], acc[j][o][p]);
                     }
                 }
             }
@@ -247,7 +271,7 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
                 for (int r = 0; r < R; ++r)
                     for (int s = 0; s < S; ++s) {
                         float wv[TN];
-                        load_window<TN, true>(wp + (r * S + s) * OCB, wv);
+                        load_taps<TN, NOG>(wp + (r * S + s) * OCB, wv);
                         const float* rp = ip + r * a.in_wp + s;
 #pragma unroll
                         for (int p = 0; p < TW; ++p) {

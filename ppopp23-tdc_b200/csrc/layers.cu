@@ -161,7 +161,7 @@ int tdc_tkconv_create(tdc_tkconv** out, int b, int C, int N1, int N2, int N3, in
 int tdc_tkconv_forward(tdc_tkconv* l, const float* dev_in, float** dev_out, void* stream) {
     if (!l || !dev_in || !dev_out) return TDC_ERR_NULL;
     int rc = tdc_tk_block_f32(dev_in, l->w1, l->wcore, l->w3, l->bias, l->output, l->b, l->C, l->h, l->w, l->N1,
-                              l->N2, l->N3, l->r, l->s, l->pad, l->stride, TDC_W_CRSK, TDC_EPI_NONE, l->workspace,
+                              l->N2, l->N3, l->r, l->s, l->pad, l->stride, TDC_W_CRSK, TDC_EPI_NONE, nullptr, l->workspace,
                               l->workspace_bytes, stream);
     if (rc) return rc;
     *dev_out = l->output;

@@ -31,14 +31,15 @@ constexpr int maxt_for(int tn, int th, int tw) { return (tn * th * tw > 64) ? 25
             (const void*)&conv_f32_kernel<KH, KW, ST, TN, TH, TW, NOG, maxt_for(TN, TH, TW)>      \
     }
 
-// The thread tiles every filter family is compiled for.
+// The thread tiles every filter family is compiled for: (TN, TH, TW, NOG).
 #define TDC_FOR_ALL_TILES(X, KH, KW, ST)                                                          \
-    X(KH, KW, ST, 8, 2, 7, 4), X(KH, KW, ST, 8, 2, 7, 8), X(KH, KW, ST, 8, 2, 8, 4),              \
-    X(KH, KW, ST, 8, 2, 8, 8), X(KH, KW, ST, 8, 1, 7, 4), X(KH, KW, ST, 8, 1, 7, 8),              \
-    X(KH, KW, ST, 8, 1, 8, 4), X(KH, KW, ST, 8, 1, 8, 8), X(KH, KW, ST, 4, 2, 7, 4),              \
-    X(KH, KW, ST, 4, 2, 7, 8), X(KH, KW, ST, 4, 2, 8, 4), X(KH, KW, ST, 4, 2, 8, 8),              \
-    X(KH, KW, ST, 4, 1, 7, 4), X(KH, KW, ST, 4, 1, 7, 8), X(KH, KW, ST, 4, 1, 8, 4),              \
-    X(KH, KW, ST, 4, 1, 8, 8)
+    X(KH, KW, ST, 4, 4, 8, 8), X(KH, KW, ST, 4, 4, 8, 16), X(KH, KW, ST, 4, 4, 7, 8),             \
+    X(KH, KW, ST, 4, 4, 7, 16), X(KH, KW, ST, 8, 2, 8, 4), X(KH, KW, ST, 8, 2, 8, 8),             \
+    X(KH, KW, ST, 8, 2, 7, 4), X(KH, KW, ST, 8, 2, 7, 8), X(KH, KW, ST, 4, 2, 8, 8),              \
+    X(KH, KW, ST, 4, 2, 8, 16), X(KH, KW, ST, 4, 2, 7, 8), X(KH, KW, ST, 4, 2, 7, 16),            \
+    X(KH, KW, ST, 8, 1, 8, 4), X(KH, KW, ST, 8, 1, 8, 8), X(KH, KW, ST, 8, 1, 7, 4),              \
+    X(KH, KW, ST, 8, 1, 7, 8), X(KH, KW, ST, 4, 1, 8, 4), X(KH, KW, ST, 4, 1, 8, 8),              \
+    X(KH, KW, ST, 4, 1, 7, 4), X(KH, KW, ST, 4, 1, 7, 8)
 
 #define TDC_FOR_ROW_TILES(X, KH, KW, ST)                                                          \
     X(KH, KW, ST, 8, 1, 7, 4), X(KH, KW, ST, 8, 1, 7, 8), X(KH, KW, ST, 8, 1, 8, 4),              \

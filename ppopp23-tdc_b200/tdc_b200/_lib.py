@@ -55,7 +55,7 @@ _PROTOTYPES = {
     "tdc_tile_cost": (_i, [_i] * 9 + [C.POINTER(Tile), C.POINTER(DevInfo), C.POINTER(C.c_double),
                                       C.POINTER(C.c_double)]),
     "tdc_tk_block_workspace_bytes": (_sz, [_i] * 11),
-    "tdc_tk_block_f32": (_i, [_p] * 6 + [_i] * 13 + [_p, _sz, _p]),
+    "tdc_tk_block_f32": (_i, [_p] * 6 + [_i] * 13 + [C.POINTER(Tile), _p, _sz, _p]),
     "tdc_conv_create": (_i, [C.POINTER(_p)] + [_i] * 9 + [_p, _p]),
     "tdc_conv_set_tile": (_i, [_p, C.POINTER(Tile)]),
     "tdc_conv_forward": (_i, [_p, _p, C.POINTER(_p), _p]),

@@ -1,0 +1,83 @@
+"""Per-shape layer driver — the run-time counterpart of the reference's generated drivers.
+
+The reference emits one program per shape whose main() fills the input with rand()%10 and the
+filter with ones, times cuDNN and one un-warmed launch of its kernel with a cudaEvent pair,
+prints `N,C,H,W,<times>,<speedups>,diff` and appends the row to a CSV
+(A100-evaluation/TDC-LAYERS-ORACLE/template_benchmark_cudnn.template:412-514; shapes and
+compile loop at compile_run.py:14-52).  Here shape and tile are arguments:
+
+    python -m tdc_b200.layer_driver --shape 64,64,56,56 [--batch 1] [--tile th,tw,tc,tn,nog,gy,gx,imgs,ks]
+                                    [--filter 3] [--stride 1] [--pad 1] [--iters 20] [--csv out.csv]
+
+`--shape` is C,N,H,W in the reference's naming (C input, N output channels of the core
+conv).  Output row: N,C,H,W,B,cudnn_ms,tdc_first_ms,tdc_ms,speedup,frac_fp32,diff — `diff` is
+the reference's L1 check (exact integers expected: 0), `tdc_first_ms` its protocol (first
+launch, no warm-up), `tdc_ms` the warmed median.
+"""
+import argparse
+import statistics
+import sys
+
+
+def main(argv=None):
+    import torch
+    import torch.nn.functional as F
+    from . import ops
+    from ._lib import Tile, W_CRSK
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", required=True, help="C,N,H,W (reference naming)")
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--tile", default=None)
+    ap.add_argument("--filter", type=int, default=3)
+    ap.add_argument("--stride", type=int, default=1)
+    ap.add_argument("--pad", type=int, default=1)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-cudnn", action="store_true")
+    ap.add_argument("--csv", default=None)
+    a = ap.parse_args(argv)
+    Cc, N, H, W = (int(v) for v in a.shape.split(","))
+    B, k = a.batch, a.filter
+    dev = torch.device("cuda")
+    stream = torch.cuda.current_stream()
+    g = torch.Generator().manual_seed(1)
+    x = torch.randint(0, 10, (B, Cc, H, W), generator=g).float().to(dev)
+    w = torch.ones(Cc, k, k, N, device=dev)
+    tile = Tile(*(int(v) for v in a.tile.split(","))) if a.tile else ops.select_tile(B, Cc, H, W, N, k, k, a.pad, a.stride)
+    Ho, Wo = ops.out_hw(H, W, k, k, a.pad, a.stride)
+    y = torch.empty(B, N, Ho, Wo, device=dev)
+
+    def timed(fn):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream); fn(); e1.record(stream); e1.synchronize()
+        return e0.elapsed_time(e1)
+
+    run = lambda: ops.core_conv2d(x, w, a.stride, a.pad, w_layout=W_CRSK, tile=tile, out=y)
+    first = timed(run)
+    for _ in range(3):
+        run()
+    tdc = statistics.median(timed(run) for _ in range(a.iters))
+    exact = F.conv2d(x.double(), torch.ones(N, Cc, k, k, device=dev, dtype=torch.double), None, a.stride, a.pad)
+    diff = float((y.double() - exact).abs().sum())
+    cud = float("nan")
+    if not a.no_cudnn:
+        torch.backends.cudnn.benchmark = True
+        torch.backends.cudnn.allow_tf32 = False
+        wk = torch.ones(N, Cc, k, k, device=dev)
+        for _ in range(3):
+            F.conv2d(x, wk, None, a.stride, a.pad)
+        cud = statistics.median(timed(lambda: F.conv2d(x, wk, None, a.stride, a.pad)) for _ in range(a.iters))
+    sm = ops.query_device().sm_count
+    flops = 2.0 * B * N * Cc * k * k * Ho * Wo
+    frac = flops / (tdc * 1e-3) / (sm * 128 * 2 * 1.965e9)
+    row = "%d,%d,%d,%d,%d,%f,%f,%f,%f,%f,%g" % (N, Cc, H, W, B, cud, first, tdc, cud / tdc, frac, diff)
+    print(row)
+    print("tile", tile, file=sys.stderr)
+    if a.csv:
+        with open(a.csv, "a") as f:
+            f.write(row + "\n")
+    return 0 if diff == 0 else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

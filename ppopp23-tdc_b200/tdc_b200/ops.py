@@ -90,7 +90,7 @@ def tk_block_workspace_bytes(B, Cc, H, W, R1, R2, K, R, S, pad, stride):
 
 
 def tk_block(x, first, core, last, bias=None, stride=1, padding=0, core_layout=W_KCRS, relu=False,
-             workspace=None, out=None):
+             workspace=None, out=None, core_tile=None):
     """TKConv2dC.forward (inference/TKConv.py:90-95): 1x1 C->R1, core R1->R2, 1x1 R2->K + bias.
     `first` is [R1][C][1][1] (or [R1][C]), `last` is [K][R2][1][1] (or [K][R2])."""
     stride, padding = _pair(stride), _pair(padding)
@@ -114,7 +114,7 @@ def tk_block(x, first, core, last, bias=None, stride=1, padding=0, core_layout=W
                                    _dev_f32(last, "last"), _dev_f32(bias, "bias") if bias is not None else None,
                                    _dev_f32(out, "out"), B, Cc, H, W, R1, R2, K, R, S, padding, stride,
                                    core_layout, EPI_RELU if relu else EPI_NONE,
-                                   workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream()))
+                                   C.byref(core_tile) if core_tile is not None else None, workspace.data_ptr(), workspace.numel() * workspace.element_size(), _stream()))
     return out
 
 

@@ -15,7 +15,7 @@ from torch import Tensor
 from torch.nn import Parameter, init
 from torch.nn.modules.utils import _pair
 
-from . import ops
+from . import ops, tiles
 from ._lib import W_CRSK, TdcError, ERR_UNSUPPORTED
 
 
@@ -93,9 +93,12 @@ class TKConv2dC_B200(nn.Module):
 
     def forward(self, x):
         x = self._check(x)
+        B, _, H, W = x.shape
+        tile = tiles.table_tile(B, self.in_rank, H, W, self.out_rank, self.kernel_size[0], self.kernel_size[1],
+                                self.padding[0], self.stride[0])     # measured table first, model otherwise
         return ops.tk_block(x, self.first_kernel.detach(), self._core_channel_last(), self.last_kernel.detach(),
                             None if self.bias is None else self.bias.detach(), self.stride, self.padding,
-                            core_layout=W_CRSK, workspace=self._ws(x))
+                            core_layout=W_CRSK, workspace=self._ws(x), core_tile=tile)
 
     def forward_features(self, x):
         x = self._check(x)

@@ -36,7 +36,9 @@ def candidates(B, C, H, W, K, R=3, S=3, pad=1, stride=1):
     """Every tile of the compiled thread-tile set that can be launched for the shape."""
     Ho, Wo = (H + 2 * pad - R) // stride + 1, (W + 2 * pad - S) // stride + 1
     out = []
-    for tn, th, tw, nog in itertools.product((4, 8), (1, 2), (7, 8), (4, 8)):
+    tiles = [(tn, th, tw, nog) for (tn, th, nogs) in ((4, 4, (8, 16)), (8, 2, (4, 8)), (4, 2, (8, 16)), (8, 1, (4, 8)),
+                                                        (4, 1, (4, 8))) for tw in (7, 8) for nog in nogs]
+    for tn, th, tw, nog in tiles:
         maxt = 256 if tn * th * tw > 64 else 512
         GY, GX = cdiv(Ho, th), cdiv(Wo, tw)
         gys = sorted({cdiv(GY, n) for n in range(1, GY + 1)})
@@ -49,7 +51,7 @@ def candidates(B, C, H, W, K, R=3, S=3, pad=1, stride=1):
                 nt = nog * im * gy * gx
                 for ks in (1, 2, 4, 8):
                     thr = nt * ks
-                    if thr > maxt or thr < 64:
+                    if thr > maxt or thr < (64 if B > 1 else 32):
                         continue
                     for tc in (8, 16, 32):
                         if tc % ks or tc > max(C, 8):
@@ -83,6 +85,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--stride", type=int, default=1)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--best-out", default=None, help="also write the fastest row per shape to this CSV")
     a = ap.parse_args(argv)
     rnd = random.Random(a.seed)
     dev = torch.device("cuda")
@@ -127,9 +130,16 @@ def main(argv=None):
                              "%.0f" % cost])
             f.flush()
             print("shape", (H, R1, R2), "rows", len(cands), "model pick", model_pick, file=sys.stderr)
-    for key, row in sorted(best_rows(a.out).items()):
+    best = best_rows(a.out)
+    for key, row in sorted(best.items()):
         print(key, "best %.4f ms" % float(row["time_ms"]),
               {k: row[k] for k in ("th", "tw", "tc", "tn", "nog", "gy", "gx", "imgs", "ks")}, file=sys.stderr)
+    if a.best_out:
+        with open(a.best_out, "w", newline="") as f:
+            wr = csv.DictWriter(f, fieldnames=COLUMNS + ["R", "stride"])
+            wr.writeheader()
+            for key, row in sorted(best.items()):
+                wr.writerow(dict(row, R=3, stride=a.stride))
 
 
 if __name__ == "__main__":

@@ -71,7 +71,7 @@ def test_selector_gives_a_launchable_tile(T, B, H, R1, R2):
     cost, vols = T.tile_cost(shape, t, T.B200)
     assert cost > 0 and vols[2] == B * R2 * H * H and vols[0] > 0 and vols[1] > 0 and vols[3] > 0
     # the selected tile is the argmin among a handful of hand-made alternatives
-    for alt in [T.Tile(1, 7, 8, 8, 4, 1, 1, 1, 1), T.Tile(2, 7, 8, 8, 4, 2, 2, 1, 1), T.Tile(1, 8, 4, 4, 8, 1, 1, 1, 1)]:
+    for alt in [T.Tile(1, 7, 8, 8, 4, 1, 1, 1, 1), T.Tile(2, 7, 8, 8, 4, 2, 2, 1, 1), T.Tile(1, 8, 4, 4, 8, 1, 1, 1, 1), T.Tile(4, 8, 8, 4, 8, 1, 1, 1, 1)]:
         try:
             c2, _ = T.tile_cost(shape, alt, T.B200)
         except T.TdcError:

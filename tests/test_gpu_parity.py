@@ -55,8 +55,9 @@ def test_cfg1_single_core_conv(T):
 TILES = [
     # th tw tc tn nog gy gx imgs ks
     (2, 7, 8, 8, 4, 2, 2, 1, 1), (2, 8, 4, 8, 8, 2, 1, 1, 1), (1, 7, 8, 8, 4, 4, 2, 1, 2), (1, 8, 16, 4, 8, 3, 2, 1, 4),
-    (2, 7, 16, 4, 4, 7, 2, 2, 1), (2, 8, 8, 4, 8, 7, 2, 1, 2), (1, 7, 32, 4, 4, 14, 2, 2, 2), (1, 8, 8, 8, 8, 14, 2, 1, 1),
-    (2, 7, 6, 8, 8, 1, 1, 1, 3),
+    (2, 7, 4, 4, 8, 7, 2, 2, 1), (2, 8, 8, 4, 16, 7, 2, 1, 2), (1, 7, 8, 4, 4, 14, 2, 2, 2), (1, 8, 8, 8, 8, 14, 2, 1, 1),
+    (2, 7, 6, 8, 8, 1, 1, 1, 3), (4, 7, 8, 4, 8, 2, 2, 1, 1), (4, 8, 8, 4, 16, 4, 2, 1, 1), (4, 7, 4, 4, 16, 4, 2, 2, 1),
+    (4, 8, 16, 4, 8, 1, 1, 1, 2),
 ]
 
 
