@@ -176,6 +176,40 @@ TDC_API int tdc_tk_block_f32(const float* x, const float* w1, const float* wcore
                      void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The Tucker block for callers that must not allocate device memory.  No counterpart in the
+ * reference (its layers cudaMalloc whatever they need when they are initialised).
+ *
+ * Who needs it: code that runs where cudaMalloc is off the table — a serving loop whose
+ * whole memory budget was handed to one arena at start-up, a plug-in living inside a host
+ * framework that owns the allocator and forbids side allocations, a step that may only
+ * enqueue work on a stream.  tdc_tk_block_f32 asks such a caller for a workspace it has no
+ * way to produce.  This variant keeps the two intermediates (z1, z2) in a fixed array that
+ * is part of the library image instead: TDC_STATIC_WORKSPACE_BYTES of device memory that
+ * every GPU holds from the moment it loads the library until the process exits, whether or
+ * not this function is ever called.
+ *
+ * Same arguments, results and status codes as tdc_tk_block_f32 minus the workspace pair; the
+ * caller still passes x, the factors and y.  It returns TDC_ERR_WORKSPACE, with the needed and
+ * the available byte counts in the message, when tdc_tk_block_workspace_bytes(...) for the shape
+ * exceeds TDC_STATIC_WORKSPACE_BYTES.  It performs no cudaMalloc/cudaFree and calls nothing that
+ * does.
+ *
+ * Set-up: the first call on each device looks up the array's device address (once, with that
+ * device current).  Make that first call during start-up, before any stream capture begins.
+ *
+ * Sharing: all calls on a device use the same array and it keeps whatever the previous call
+ * left there; both intermediates are fully overwritten before they are read, so nothing needs
+ * clearing.  Two calls that overlap on the GPU (different streams, or different host threads
+ * without ordering between their streams) race on it — serialise them.
+ */
+#define TDC_STATIC_WORKSPACE_BYTES (32u << 20)   /* 32 MiB: every benchmark Tucker block up to batch 32 */
+TDC_API int tdc_tk_block_f32_static(const float* x, const float* w1, const float* wcore, const float* w3,
+                     const float* bias, float* y,
+                     int B, int C, int H, int W, int R1, int R2, int K, int R, int S,
+                     int pad, int stride, int w_layout, int epilogue,
+                     const tdc_tile* core_tile /* NULL = auto */, void* stream);
+
+/*
  * Layer objects with the surface of the reference's end-to-end classes:
  * Conv::initialize(b,c,h,w,n,pad,r,s,stride,weightFile,use_bias) / float* Conv::forward(float*)
  * (A100-evaluation/EndToEnd/resnet18-tk/inc/common.h:38-69, src/Conv.cu:2-125) and

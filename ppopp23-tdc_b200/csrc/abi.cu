@@ -289,3 +289,47 @@ int tdc_tk_block_f32(const float* x, const float* w1, const float* wcore, const 
 }
 
 }  // extern "C"
+
+// ---- the no-allocation variant of the Tucker block ---------------------------------------
+// The intermediates live in this array, which is part of the library image: a GPU holds it
+// from library load to process exit.  Its name is only a handle in host code; the device
+// address the kernels need comes from cudaGetSymbolAddress, looked up once per device.
+static __device__ __align__(256) unsigned char g_static_workspace[TDC_STATIC_WORKSPACE_BYTES];
+
+namespace {
+std::map<int, void*> g_static_ws_ptr;   // device -> address of g_static_workspace there
+
+int static_workspace(void** out) {
+    int device, rc;
+    if ((rc = current_device(&device))) return rc;
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_static_ws_ptr.find(device);
+    if (it == g_static_ws_ptr.end()) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_workspace);   // current device == `device`
+        if (e != cudaSuccess || !p)
+            return fail(TDC_ERR_CUDA, "cudaGetSymbolAddress(static workspace): %s", cudaGetErrorString(e));
+        it = g_static_ws_ptr.emplace(device, p).first;
+    }
+    *out = it->second;
+    return TDC_OK;
+}
+}  // namespace
+
+extern "C" int tdc_tk_block_f32_static(const float* x, const float* w1, const float* wcore, const float* w3,
+                                       const float* bias, float* y, int B, int C, int H, int W, int R1, int R2,
+                                       int K, int R, int S, int pad, int stride, int w_layout, int epilogue,
+                                       const tdc_tile* core_tile, void* stream) {
+    size_t need = tdc_tk_block_workspace_bytes(B, C, H, W, R1, R2, K, R, S, pad, stride);
+    if (need == 0) return fail(TDC_ERR_SHAPE, "bad Tucker block shape");
+    if (need > (size_t)TDC_STATIC_WORKSPACE_BYTES)
+        return fail(TDC_ERR_WORKSPACE,
+                    "this Tucker block needs %zu bytes for its intermediates, the built-in workspace holds %zu; "
+                    "use tdc_tk_block_f32 with a caller-provided workspace",
+                    need, (size_t)TDC_STATIC_WORKSPACE_BYTES);
+    void* ws = nullptr;
+    int rc = static_workspace(&ws);
+    if (rc) return rc;
+    return tdc_tk_block_f32(x, w1, wcore, w3, bias, y, B, C, H, W, R1, R2, K, R, S, pad, stride, w_layout, epilogue,
+                            core_tile, ws, (size_t)TDC_STATIC_WORKSPACE_BYTES, stream);
+}

@@ -41,6 +41,7 @@ class LaunchInfo(C.Structure):
 
 # B200 as the selector sees it when no device can be queried (CPU-side tests, table tools).
 B200 = DevInfo(148, 232448, 65536, 2048)
+STATIC_WORKSPACE_BYTES = 32 << 20   # TDC_STATIC_WORKSPACE_BYTES
 
 _i, _p, _sz = C.c_int, C.c_void_p, C.c_size_t
 _PROTOTYPES = {
@@ -56,6 +57,7 @@ _PROTOTYPES = {
                                       C.POINTER(C.c_double)]),
     "tdc_tk_block_workspace_bytes": (_sz, [_i] * 11),
     "tdc_tk_block_f32": (_i, [_p] * 6 + [_i] * 13 + [C.POINTER(Tile), _p, _sz, _p]),
+    "tdc_tk_block_f32_static": (_i, [_p] * 6 + [_i] * 13 + [C.POINTER(Tile), _p]),
     "tdc_conv_create": (_i, [C.POINTER(_p)] + [_i] * 9 + [_p, _p]),
     "tdc_conv_set_tile": (_i, [_p, C.POINTER(Tile)]),
     "tdc_conv_forward": (_i, [_p, _p, C.POINTER(_p), _p]),
