@@ -60,8 +60,9 @@ typedef enum tdc_status {
  * output rows per thread, output columns per thread, input channels staged per chunk.
  * The reference fixes "one output channel per thread, all N channels per block"; on
  * B200 those two become parameters (tn, nog), and a CTA may own several images of a
- * small feature map (imgs) and split the staged channels over ks thread slices whose
- * partial sums are reduced in shared memory in a fixed order (no atomics).
+ * small feature map (imgs), split the staged channels over ks thread slices, and split
+ * the channel chunks over the kc CTAs of a thread-block cluster; partial sums are reduced
+ * in (distributed) shared memory in a fixed order (no atomics).
  * A field left 0 is chosen by tdc_select_tile.
  */
 typedef struct tdc_tile {
@@ -74,6 +75,9 @@ typedef struct tdc_tile {
     int gx;   /* thread columns per CTA per image      (CTA covers gx*tw columns)  */
     int imgs; /* images per CTA (>1 only if gy,gx cover the whole output map)      */
     int ks;   /* channel slices per CTA (in-CTA split of the reduction)            */
+    int kc;   /* CTAs per thread-block cluster that share one output tile, each    *
+               * walking a range of channel chunks; summed over distributed shared  *
+               * memory in rank order (1..8; 1 = no cluster)                        */
 } tdc_tile;
 
 /* What the selector needs to know about a device; fill with tdc_query_device or by

@@ -56,7 +56,7 @@ static void parallel_pairs(int B, int K, pair_fn fn, void* ctx) {
 }
 typedef struct {
     const float *x, *w, *bias; float* y;
-    int B, C, H, W, K, R, S, pad, stride, w_layout, use_fma, relu, tc, ks;
+    int B, C, H, W, K, R, S, pad, stride, w_layout, use_fma, relu, tc, ks, kc;
 } conv_ctx;
 
 #define W_KCRS 0
@@ -102,34 +102,40 @@ static void f32_pair(int b, int k, void* q) {
 }
 void tdc_oracle_conv2d_f32(const float* x, const float* w, const float* bias, float* y, int B, int C, int H,
                            int W, int K, int R, int S, int pad, int stride, int w_layout, int use_fma, int relu) {
-    conv_ctx c = {x, w, bias, y, B, C, H, W, K, R, S, pad, stride, w_layout, use_fma, relu, 0, 0};
+    conv_ctx c = {x, w, bias, y, B, C, H, W, K, R, S, pad, stride, w_layout, use_fma, relu, 0, 0, 1};
     parallel_pairs(B, K, f32_pair, &c);
 }
 
 /* Same sum in the order the CUDA kernel uses when a CTA splits each staged chunk of
  * `tc` channels over `ks` slices: slice j owns channels j, j+ks, ... of every chunk and
  * sums them (c, r, s ascending, fmaf, padding taps included as +0*w which leaves the
- * value unchanged); then the slices are added 0 + 1 + 2 + ...  Bit-exact twin of the
- * device result for that (tc, ks). */
+ * value unchanged); then the slices are added 0 + 1 + 2 + ...; when the chunks are split
+ * over the kc CTAs of a cluster, each CTA does that for its range of chunks and the CTAs
+ * are added in rank order.  Bit-exact twin of the device result for that (tc, ks, kc). */
 static void sliced_pair(int b, int k, void* q) {
     UNPACK(q)
-    const int tc = q_->tc, ks = q_->ks;
+    const int tc = q_->tc, ks = q_->ks, kc = q_->kc;
+    const int nchunks = (C + tc - 1) / tc, cpr = (nchunks + kc - 1) / kc;
             for (int oy = 0; oy < Ho; ++oy)
                 for (int ox = 0; ox < Wo; ++ox) {
                     float total = 0.f;
-                    for (int j = 0; j < ks; ++j) {
-                        float acc = 0.f;
-                        for (int c0 = 0; c0 < C; c0 += tc)
-                            for (int c = c0 + j; c < c0 + tc && c < C; c += ks)
-                                for (int r = 0; r < R; ++r)
-                                    for (int s = 0; s < S; ++s) {
-                                        int iy = oy * stride - pad + r, ix = ox * stride - pad + s;
-                                        float xv = (iy < 0 || iy >= H || ix < 0 || ix >= W)
-                                                       ? 0.f
-                                                       : x[(((size_t)b * C + c) * H + iy) * W + ix];
-                                        acc = fmaf(w[widx(w_layout, K, C, R, S, k, c, r, s)], xv, acc);
-                                    }
-                        total = (j == 0) ? acc : total + acc;
+                    for (int rank = 0; rank < kc; ++rank) {            /* CTAs of a cluster, rank order */
+                        float rsum = 0.f;
+                        for (int j = 0; j < ks; ++j) {                 /* slices of a CTA, slice order   */
+                            float acc = 0.f;
+                            for (int ch = rank * cpr; ch < (rank + 1) * cpr && ch < nchunks; ++ch)
+                                for (int c = ch * tc + j; c < (ch + 1) * tc && c < C; c += ks)
+                                    for (int r = 0; r < R; ++r)
+                                        for (int s = 0; s < S; ++s) {
+                                            int iy = oy * stride - pad + r, ix = ox * stride - pad + s;
+                                            float xv = (iy < 0 || iy >= H || ix < 0 || ix >= W)
+                                                           ? 0.f
+                                                           : x[(((size_t)b * C + c) * H + iy) * W + ix];
+                                            acc = fmaf(w[widx(w_layout, K, C, R, S, k, c, r, s)], xv, acc);
+                                        }
+                            rsum = (j == 0) ? acc : rsum + acc;
+                        }
+                        total = (rank == 0) ? rsum : total + rsum;
                     }
                     if (bias) total += bias[k];
                     if (relu) total = fmaxf(total, 0.f);
@@ -138,8 +144,8 @@ static void sliced_pair(int b, int k, void* q) {
 }
 void tdc_oracle_conv2d_f32_sliced(const float* x, const float* w, const float* bias, float* y, int B, int C,
                                   int H, int W, int K, int R, int S, int pad, int stride, int w_layout, int tc,
-                                  int ks, int relu) {
-    conv_ctx c = {x, w, bias, y, B, C, H, W, K, R, S, pad, stride, w_layout, 1, relu, tc, ks};
+                                  int ks, int kc, int relu) {
+    conv_ctx c = {x, w, bias, y, B, C, H, W, K, R, S, pad, stride, w_layout, 1, relu, tc, ks, kc};
     parallel_pairs(B, K, sliced_pair, &c);
 }
 
@@ -167,7 +173,7 @@ static void f64_pair(int b, int k, void* q) {
 }
 void tdc_oracle_conv2d_f64(const float* x, const float* w, const float* bias, float* y, int B, int C, int H,
                            int W, int K, int R, int S, int pad, int stride, int w_layout, int relu) {
-    conv_ctx c = {x, w, bias, y, B, C, H, W, K, R, S, pad, stride, w_layout, 0, relu, 0, 0};
+    conv_ctx c = {x, w, bias, y, B, C, H, W, K, R, S, pad, stride, w_layout, 0, relu, 0, 0, 1};
     parallel_pairs(B, K, f64_pair, &c);
 }
 

@@ -89,8 +89,9 @@ def conv2d_f32(x, w, bias=None, pad=0, stride=1, w_layout=W_KCRS, use_fma=True, 
     return y
 
 
-def conv2d_f32_sliced(x, w, tc, ks, bias=None, pad=0, stride=1, w_layout=W_KCRS, relu=False):
-    """Bit-exact twin of the device kernel for channel chunk `tc` split over `ks` slices."""
+def conv2d_f32_sliced(x, w, tc, ks, bias=None, pad=0, stride=1, w_layout=W_KCRS, relu=False, kc=1):
+    """Bit-exact twin of the device kernel for channel chunk `tc` split over `ks` slices of a CTA
+    and `kc` CTAs of a cluster."""
     x, xp = _f(x); w, wp = _f(w)
     B, Cc, H, W, K, R, S = _dims(x, w, w_layout)
     Ho, Wo = out_hw(H, W, R, S, pad, stride)
@@ -99,7 +100,7 @@ def conv2d_f32_sliced(x, w, tc, ks, bias=None, pad=0, stride=1, w_layout=W_KCRS,
     if bias is not None:
         bias, bp = _f(bias)
     lib().tdc_oracle_conv2d_f32_sliced(xp, wp, bp, y.ctypes.data_as(C.c_void_p), B, Cc, H, W, K, R, S, pad, stride,
-                                       w_layout, tc, ks, int(relu))
+                                       w_layout, tc, ks, kc, int(relu))
     return y
 
 

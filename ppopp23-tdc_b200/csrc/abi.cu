@@ -68,13 +68,13 @@ int check_shape(const Shape& s) {
 }
 
 bool tile_complete(const tdc_tile& t) {
-    return t.th && t.tw && t.tc && t.tn && t.nog && t.gy && t.gx && t.imgs && t.ks;
+    return t.th && t.tw && t.tc && t.tn && t.nog && t.gy && t.gx && t.imgs && t.ks && t.kc;
 }
 
 // Completes *t (zero fields) for the shape on `dev`; caches fully automatic choices.
 int complete_tile(const Shape& s, int device, const tdc_devinfo& dev, tdc_tile* t) {
     if (tile_complete(*t)) return TDC_OK;
-    const bool all_auto = !t->th && !t->tw && !t->tc && !t->tn && !t->nog && !t->gy && !t->gx && !t->imgs && !t->ks;
+    const bool all_auto = !t->th && !t->tw && !t->tc && !t->tn && !t->nog && !t->gy && !t->gx && !t->imgs && !t->ks && !t->kc;
     ShapeKey key{device, s.B, s.C, s.H, s.W, s.K, s.R, s.S, s.pad, s.stride};
     if (all_auto && device >= 0) {
         std::lock_guard<std::mutex> lk(g_mu);
@@ -122,6 +122,7 @@ int launch_conv(const float* x, const float* w, const float* bias, float* y, con
     a.in_rows = g.in_rows; a.in_wp = g.in_wp; a.patch = g.patch;
     a.tiles_y = g.tiles_y; a.tiles_x = g.tiles_x; a.img_groups = g.img_groups; a.n_ocb = g.n_ocb;
     a.stage_floats = g.stage_floats;
+    a.kc = t.kc; a.chunks_per_rank = g.chunks_per_rank;
 
     {
         std::lock_guard<std::mutex> lk(g_mu);
@@ -133,7 +134,18 @@ int launch_conv(const float* x, const float* w, const float* bias, float* y, con
         }
     }
     void* args[] = {&a};
-    cudaError_t e = cudaLaunchKernel(g.v->fn, dim3((unsigned)g.ctas), dim3(g.threads), args, g.smem_bytes, stream);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)g.ctas);
+    cfg.blockDim = dim3(g.threads);
+    cfg.dynamicSmemBytes = g.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (t.kc > 1) {   // the kc CTAs of a tile form one thread-block cluster
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = t.kc; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+    }
+    cudaError_t e = cudaLaunchKernelExC(&cfg, g.v->fn, args);
     if (e != cudaSuccess) return fail(TDC_ERR_CUDA, "launch: %s", cudaGetErrorString(e));
     return TDC_OK;
 }

@@ -27,6 +27,7 @@
 //     too few pixels to fill 148 SMs otherwise); slices are summed through shared
 //     memory in slice order.
 #pragma once
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -44,6 +45,8 @@ struct ConvArgs {
     int relu;
     // runtime part of the tile
     int tc, gy, gx, imgs, ks;
+    int kc;              // CTAs of a cluster that share one output tile, each a range of chunks
+    int chunks_per_rank;
     // derived by the host
     int in_rows, in_wp;  // rows / padded width of one image's staged input patch
     int patch;           // imgs * in_rows * in_wp, rounded up to a multiple of 4
@@ -127,7 +130,9 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
     const int tid  = threadIdx.x;
 
     // ---- which tile is this CTA ------------------------------------------------
-    int bid = blockIdx.x;
+    // The kc CTAs of a cluster are consecutive in blockIdx.x and work on the same tile.
+    int bid = blockIdx.x / a.kc;
+    const int crank = blockIdx.x - bid * a.kc;
     const int ocb = bid % a.n_ocb;  bid /= a.n_ocb;
     const int txi = bid % a.tiles_x; bid /= a.tiles_x;
     const int tyi = bid % a.tiles_y; bid /= a.tiles_y;
@@ -216,15 +221,19 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
 #pragma unroll
             for (int p = 0; p < TW; ++p) acc[j][o][p] = 0.f;
 
-    const int nchunks = (a.C + a.tc - 1) / a.tc;
-    stage_chunk(0, min(a.tc, a.C), stages);
-    cp_async_commit();
+    const int nchunks_all = (a.C + a.tc - 1) / a.tc;
+    const int kc_begin = crank * a.chunks_per_rank;
+    const int nchunks  = min(nchunks_all, kc_begin + a.chunks_per_rank);   // this CTA walks [kc_begin, nchunks)
+    if (kc_begin < nchunks) {
+        stage_chunk(kc_begin * a.tc, min(a.tc, a.C - kc_begin * a.tc), stages);
+        cp_async_commit();
+    }
 
-    for (int kc = 0; kc < nchunks; ++kc) {
-        float* cur = stages + (kc & 1) * a.stage_floats;
+    for (int kc = kc_begin; kc < nchunks; ++kc) {
+        float* cur = stages + ((kc - kc_begin) & 1) * a.stage_floats;
         if (kc + 1 < nchunks) {
             int c1 = (kc + 1) * a.tc;
-            stage_chunk(c1, min(a.tc, a.C - c1), stages + ((kc + 1) & 1) * a.stage_floats);
+            stage_chunk(c1, min(a.tc, a.C - c1), stages + ((kc + 1 - kc_begin) & 1) * a.stage_floats);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -308,6 +317,36 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
                         for (int p = 0; p < TW; ++p)
                             acc[j][o][p] += red[((k - 1) * NACC + (j * TH + o) * TW + p) * NT + t];
         }
+    }
+    // ---- sum the CTAs of a cluster through distributed shared memory, rank 1 first --------
+    if (a.kc > 1) {
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        float* red = stages;
+        // slice 0 of every rank > 0 publishes its sums; a thread only overwrites entries that
+        // it alone read in the slice reduction above, so no barrier is needed before this
+        if (crank > 0 && ksl == 0) {
+#pragma unroll
+            for (int j = 0; j < TN; ++j)
+#pragma unroll
+                for (int o = 0; o < TH; ++o)
+#pragma unroll
+                    for (int p = 0; p < TW; ++p) red[((j * TH + o) * TW + p) * NT + t] = acc[j][o][p];
+        }
+        cluster.sync();
+        if (crank == 0 && ksl == 0) {
+            for (int r = 1; r < a.kc; ++r) {
+                const float* peer = cluster.map_shared_rank(red, r);
+#pragma unroll
+                for (int j = 0; j < TN; ++j)
+#pragma unroll
+                    for (int o = 0; o < TH; ++o)
+#pragma unroll
+                        for (int p = 0; p < TW; ++p) acc[j][o][p] += peer[((j * TH + o) * TW + p) * NT + t];
+            }
+        }
+        cluster.sync();   // peers keep their shared memory alive until rank 0 has read it
+        if (crank != 0) return;
     }
     if (ksl != 0) return;
 

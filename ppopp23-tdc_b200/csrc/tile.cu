@@ -51,11 +51,12 @@ int make_geometry(const Shape& s, const tdc_tile& t, const tdc_devinfo& dev, Geo
     const char* dummy;
     if (!why) why = &dummy;
     if (t.th <= 0 || t.tw <= 0 || t.tc <= 0 || t.tn <= 0 || t.nog <= 0 || t.gy <= 0 || t.gx <= 0 ||
-        t.imgs <= 0 || t.ks <= 0) { *why = "tile has a field <= 0"; return TDC_ERR_TILE; }
+        t.imgs <= 0 || t.ks <= 0 || t.kc <= 0) { *why = "tile has a field <= 0"; return TDC_ERR_TILE; }
     const Variant* v = find_variant(s, t);
     if (!v) { *why = "no compiled kernel for this filter size / stride / (tn,th,tw,nog)"; return TDC_ERR_UNSUPPORTED; }
     const int Ho = s.Ho(), Wo = s.Wo();
     if (t.tc % t.ks) { *why = "tc must be a multiple of ks"; return TDC_ERR_TILE; }
+    if (t.kc > 8) { *why = "kc (cluster size) must be 1..8"; return TDC_ERR_TILE; }
     if (t.imgs > 1 && (t.gy * t.th < Ho || t.gx * t.tw < Wo)) {
         *why = "imgs > 1 needs gy*th >= Ho and gx*tw >= Wo"; return TDC_ERR_TILE;
     }
@@ -94,9 +95,10 @@ int make_geometry(const Shape& s, const tdc_tile& t, const tdc_devinfo& dev, Geo
     if ((long long)t.imgs * s.C * s.H * s.W >= (1ll << 31)) { *why = "images of one CTA exceed 2^31 elements"; return TDC_ERR_TILE; }
     g->stage_floats = t.tc * g->patch + t.tc * s.R * s.S * t.tn * t.nog;
     size_t ring = 2 * (size_t)g->stage_floats;
-    size_t red  = (size_t)(t.ks - 1) * t.tn * t.th * t.tw * g->nt;
+    size_t red  = (size_t)std::max(t.ks - 1, t.kc > 1 ? 1 : 0) * t.tn * t.th * t.tw * g->nt;
     g->smem_bytes = 4 * ((size_t)g->patch + std::max(ring, red));
-    g->ctas = (long long)g->n_ocb * g->tiles_x * g->tiles_y * g->img_groups;
+    g->chunks_per_rank = cdiv(cdiv(s.C, t.tc), t.kc);
+    g->ctas = (long long)g->n_ocb * g->tiles_x * g->tiles_y * g->img_groups * t.kc;
     if (g->ctas >= (1ll << 31)) { *why = "grid too large"; return TDC_ERR_TILE; }
     if (g->smem_bytes > (size_t)dev.smem_per_cta) { *why = "tile needs more shared memory than a CTA may have"; return TDC_ERR_SMEM; }
     return TDC_OK;
@@ -133,7 +135,7 @@ static double issue_eff(double w) {
 double tile_cost(const Shape& s, const tdc_tile& t, const Geometry& g, const tdc_devinfo& dev, double* vols) {
     const Variant& v = *g.v;
     const int RS = s.R * s.S, ocb = t.tn * t.nog, nacc = t.tn * t.th * t.tw;
-    const int nchunks = cdiv(s.C, t.tc);
+    const int nchunks = std::min(cdiv(s.C, t.tc), g.chunks_per_rank);   // chunks the busiest CTA of a cluster walks
     // instructions one thread issues per input channel it owns
     double fma = (double)nacc * RS;
     double w_lds = RS * t.tn / 4.0, in_lds;
@@ -160,7 +162,7 @@ double tile_cost(const Shape& s, const tdc_tile& t, const Geometry& g, const tdc
     for (int kc = 0; kc < nchunks; ++kc) ch_per_thread += cdiv(std::min(t.tc, s.C - kc * t.tc), t.ks);
     double loader = nchunks * ((double)t.tc * g.patch / g.threads * 7.0 +
                                (double)t.tc * RS * ocb / 4.0 / g.threads * 8.0 + 60.0);
-    double reduce = t.ks > 1 ? 2.5 * nacc * (t.ks - 1) : 0.0;
+    double reduce = (t.ks > 1 ? 2.5 * nacc * (t.ks - 1) : 0.0) + (t.kc > 1 ? 2500.0 + 8.0 * nacc * (t.kc - 1) : 0.0);
     double fixed = (double)g.patch / g.threads * 30.0 + 900.0 + 3.0 * nacc;
     double per_thread = ch_per_thread * per_ch + loader + reduce + fixed;
 
@@ -222,16 +224,24 @@ int select_tile(const Shape& s, const tdc_devinfo& dev, const tdc_tile& fx, tdc_
                 for (int ks : kss) {
                     const int thr = nt * ks;
                     if (thr > v->maxt) continue;
+                    const long long base_ctas = (long long)cdiv(s.K, v->tn * v->nog) * cdiv(Ho, gy * v->th) *
+                                                cdiv(Wo, gx * v->tw) * cdiv(s.B, im);
+                    std::vector<int> kcs;
+                    if (fx.kc) kcs.push_back(fx.kc);
+                    else { kcs.push_back(1); if (base_ctas < 2 * dev.sm_count) for (int k : {2, 4, 8}) kcs.push_back(k); }
+                    for (int kcl : kcs) {
                     std::vector<int> tcs;
                     if (fx.tc) tcs.push_back(fx.tc);
                     else for (int c : {4, 8, 16, 32}) if (c % ks == 0 && (c <= s.C || c == rup(std::min(c, s.C), ks))) tcs.push_back(c);
                     if (tcs.empty()) tcs.push_back(rup(std::min(4, s.C), ks));
                     for (int tc : tcs) {
-                        tdc_tile t{v->th, v->tw, tc, v->tn, v->nog, gy, gx, im, ks};
+                        if (kcl > 1 && cdiv(s.C, tc) < kcl) continue;   // fewer chunks than ranks
+                        tdc_tile t{v->th, v->tw, tc, v->tn, v->nog, gy, gx, im, ks, kcl};
                         Geometry g;
                         if (make_geometry(s, t, dev, &g, nullptr) != TDC_OK) continue;
                         double c = tile_cost(s, t, g, dev, nullptr);
                         if (c < best) { best = c; bt = t; }
+                    }
                     }
                 }
             }

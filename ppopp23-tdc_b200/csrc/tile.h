@@ -20,6 +20,7 @@ struct Geometry {
     int tiles_y, tiles_x, img_groups, n_ocb;
     int threads, nt;           // threads per CTA, threads of one channel slice
     int stage_floats;
+    int chunks_per_rank;       // channel chunks each CTA of a cluster walks
     size_t smem_bytes;
     long long ctas;
 };

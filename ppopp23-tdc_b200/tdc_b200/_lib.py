@@ -21,7 +21,7 @@ class TdcError(RuntimeError):
 class Tile(C.Structure):
     """tdc_tile; th/tw/tc as in the reference generators' TH/TW/TC
     (A100-evaluation/TDC-LAYERS-ORACLE/gen_from_occupancy.py:113-139)."""
-    _fields_ = [(n, C.c_int) for n in ("th", "tw", "tc", "tn", "nog", "gy", "gx", "imgs", "ks")]
+    _fields_ = [(n, C.c_int) for n in ("th", "tw", "tc", "tn", "nog", "gy", "gx", "imgs", "ks", "kc")]
 
     def as_tuple(self):
         return tuple(getattr(self, n) for n, _ in self._fields_)

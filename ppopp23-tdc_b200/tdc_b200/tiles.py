@@ -31,7 +31,7 @@ def load_tables(paths=None):
                                                                               int(row.get("stride", 1) or 1))
                 t = float(row["time_ms"])
                 if key not in out or t < out[key][1]:
-                    out[key] = (tuple(int(row[k]) for k in _FIELDS), t)
+                    out[key] = (tuple(int(row[k]) for k in _FIELDS) + (int(row.get("kc", 1) or 1),), t)
     return out
 
 

@@ -64,6 +64,7 @@ def test_selector_gives_a_launchable_tile(T, B, H, R1, R2):
     t = T.select_tile(*shape, dev=T.B200)
     assert all(v > 0 for v in t.as_tuple())
     assert t.tc % t.ks == 0
+    assert 1 <= t.kc <= 8
     threads = t.ks * t.nog * t.imgs * t.gy * t.gx
     assert 1 <= threads <= (256 if t.tn * t.th * t.tw > 64 else 512)
     if t.imgs > 1:
@@ -71,7 +72,7 @@ def test_selector_gives_a_launchable_tile(T, B, H, R1, R2):
     cost, vols = T.tile_cost(shape, t, T.B200)
     assert cost > 0 and vols[2] == B * R2 * H * H and vols[0] > 0 and vols[1] > 0 and vols[3] > 0
     # the selected tile is the argmin among a handful of hand-made alternatives
-    for alt in [T.Tile(1, 7, 8, 8, 4, 1, 1, 1, 1), T.Tile(2, 7, 8, 8, 4, 2, 2, 1, 1), T.Tile(1, 8, 4, 4, 8, 1, 1, 1, 1), T.Tile(4, 8, 8, 4, 8, 1, 1, 1, 1)]:
+    for alt in [T.Tile(1, 7, 8, 8, 4, 1, 1, 1, 1, 1), T.Tile(2, 7, 8, 8, 4, 2, 2, 1, 1, 1), T.Tile(1, 8, 4, 4, 8, 1, 1, 1, 1, 1), T.Tile(4, 8, 8, 4, 8, 1, 1, 1, 1, 1)]:
         try:
             c2, _ = T.tile_cost(shape, alt, T.B200)
         except T.TdcError:
@@ -90,16 +91,16 @@ def test_tile_cost_rejects_inconsistent_tiles(T):
     from tdc_b200 import _lib
     shape = (1, 32, 56, 56, 32, 3, 3, 1, 1)
     with pytest.raises(T.TdcError) as e:
-        T.tile_cost(shape, T.Tile(2, 7, 8, 8, 4, 2, 2, 3, 1), T.B200)       # imgs>1 without covering the map
+        T.tile_cost(shape, T.Tile(2, 7, 8, 8, 4, 2, 2, 3, 1, 1), T.B200)       # imgs>1 without covering the map
     assert e.value.code == _lib.ERR_TILE
     with pytest.raises(T.TdcError) as e:
-        T.tile_cost(shape, T.Tile(2, 7, 6, 8, 4, 2, 2, 1, 4), T.B200)       # tc % ks
+        T.tile_cost(shape, T.Tile(2, 7, 6, 8, 4, 2, 2, 1, 4, 1), T.B200)       # tc % ks
     assert e.value.code == _lib.ERR_TILE
     with pytest.raises(T.TdcError) as e:
-        T.tile_cost(shape, T.Tile(3, 7, 8, 8, 4, 2, 2, 1, 1), T.B200)       # th=3 is not compiled
+        T.tile_cost(shape, T.Tile(3, 7, 8, 8, 4, 2, 2, 1, 1, 1), T.B200)       # th=3 is not compiled
     assert e.value.code == _lib.ERR_UNSUPPORTED
     with pytest.raises(T.TdcError) as e:
-        T.tile_cost(shape, T.Tile(2, 7, 32, 8, 8, 28, 8, 1, 1), T.B200)     # too many threads
+        T.tile_cost(shape, T.Tile(2, 7, 32, 8, 8, 28, 8, 1, 1, 1), T.B200)     # too many threads
     assert e.value.code == _lib.ERR_TILE
 
 

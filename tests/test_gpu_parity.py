@@ -53,11 +53,15 @@ def test_cfg1_single_core_conv(T):
 
 # ---- bit-exact twin: same summation order on the CPU ---------------------------------------
 TILES = [
-    # th tw tc tn nog gy gx imgs ks
-    (2, 7, 8, 8, 4, 2, 2, 1, 1), (2, 8, 4, 8, 8, 2, 1, 1, 1), (1, 7, 8, 8, 4, 4, 2, 1, 2), (1, 8, 16, 4, 8, 3, 2, 1, 4),
-    (2, 7, 4, 4, 8, 7, 2, 2, 1), (2, 8, 8, 4, 16, 7, 2, 1, 2), (1, 7, 8, 4, 4, 14, 2, 2, 2), (1, 8, 8, 8, 8, 14, 2, 1, 1),
-    (2, 7, 6, 8, 8, 1, 1, 1, 3), (4, 7, 8, 4, 8, 2, 2, 1, 1), (4, 8, 8, 4, 16, 4, 2, 1, 1), (4, 7, 4, 4, 16, 4, 2, 2, 1),
-    (4, 8, 16, 4, 8, 1, 1, 1, 2),
+    # th tw tc tn nog gy gx imgs ks kc
+    (2, 7, 8, 8, 4, 2, 2, 1, 1, 1), (2, 8, 4, 8, 8, 2, 1, 1, 1, 1), (1, 7, 8, 8, 4, 4, 2, 1, 2, 1), (1, 8, 16, 4, 8, 3, 2, 1, 4, 1),
+    (2, 7, 4, 4, 8, 7, 2, 2, 1, 1), (2, 8, 8, 4, 16, 7, 2, 1, 2, 1), (1, 7, 8, 4, 4, 14, 2, 2, 2, 1), (1, 8, 8, 8, 8, 14, 2, 1, 1, 1),
+    (2, 7, 6, 8, 8, 1, 1, 1, 3, 1), (4, 7, 8, 4, 8, 2, 2, 1, 1, 1), (4, 8, 8, 4, 16, 4, 2, 1, 1, 1), (4, 7, 4, 4, 16, 4, 2, 2, 1, 1),
+    (4, 8, 16, 4, 8, 1, 1, 1, 2, 1),
+    # chunks split over the CTAs of a cluster (kc), alone and together with slices (ks); 20 channels
+    # in chunks of 4 = 5 chunks, so with kc = 4 the ranks get 2, 2, 1 and 0 chunks
+    (1, 7, 4, 4, 4, 2, 2, 1, 1, 2), (1, 8, 4, 4, 8, 7, 2, 1, 2, 4), (2, 7, 4, 4, 8, 7, 2, 2, 1, 4), (4, 7, 2, 4, 8, 2, 2, 1, 2, 8),
+    (1, 7, 8, 8, 4, 14, 2, 1, 4, 2),
 ]
 
 
@@ -68,7 +72,7 @@ def test_bit_exact_against_ordered_oracle(T, tile, stride):
     x, w = draw_core(100 + sum(tile), B, R1, R2, H, W)
     t = T.Tile(*tile)
     y = T.core_conv2d(x.cuda(), w.cuda(), stride, 1, tile=t).cpu().numpy()
-    ref = O.conv2d_f32_sliced(x.numpy(), w.numpy(), tc=t.tc, ks=t.ks, pad=1, stride=stride)
+    ref = O.conv2d_f32_sliced(x.numpy(), w.numpy(), tc=t.tc, ks=t.ks, kc=t.kc, pad=1, stride=stride)
     assert np.array_equal(y, ref), (tile, stride, rel_err(y, ref))
     # and run-to-run identical
     y2 = T.core_conv2d(x.cuda(), w.cuda(), stride, 1, tile=t).cpu().numpy()
@@ -219,7 +223,7 @@ def test_errors_on_device(T):
         T.core_conv2d(x, w, 3, 1)
     assert e.value.code == _lib.ERR_UNSUPPORTED
     with pytest.raises(T.TdcError) as e:
-        T.core_conv2d(x, w, 1, 1, tile=T.Tile(2, 7, 8, 8, 4, 64, 8, 1, 1))
+        T.core_conv2d(x, w, 1, 1, tile=T.Tile(2, 7, 8, 8, 4, 64, 8, 1, 1, 1))
     assert e.value.code == _lib.ERR_TILE
     with pytest.raises(T.TdcError) as e:
         T.tk_block(x, torch.zeros(4, 8).cuda(), torch.zeros(4, 4, 3, 3).cuda(), torch.zeros(6, 4).cuda(),

@@ -57,6 +57,9 @@ def test_sliced_order_is_a_reordering_only(built):
     assert np.array_equal(O.conv2d_f32_sliced(c["z1"], c["core"], tc=4, ks=1, pad=1), a)
     b = O.conv2d_f32_sliced(c["z1"], c["core"], tc=4, ks=2, pad=1)
     assert rel_err(b, a) <= 1e-6 and not np.array_equal(a, b)
+    c2 = O.conv2d_f32_sliced(c["z1"], c["core"], tc=2, ks=1, kc=2, pad=1)     # 8 channels: ranks get 2 chunks each
+    assert rel_err(c2, a) <= 1e-6 and not np.array_equal(a, c2)
+    assert np.array_equal(O.conv2d_f32_sliced(c["z1"], c["core"], tc=4, ks=1, kc=1, pad=1), a)
 
 
 # Shapes and tiles of the reference's shipped drivers (C, N, H, W, TH, TW, TC): the #defines of
