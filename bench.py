@@ -157,6 +157,101 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def torch_reference_forward(torch, m, x):
+    """The reference's GPU path for the same network and weights: the three F.conv2d calls of
+    TKConv2dC.forward (inference/TKConv.py:90-95) per Tucker conv and the module sequence of
+    TTBasicBlock / TTResNet (inference/resnet_inet_tt.py:102-117,380-394), i.e. cuDNN through
+    torch.  A reported baseline; none of the product's kernels run here."""
+    F = torch.nn.functional
+
+    def conv(c, t):
+        if hasattr(c, "first_kernel"):
+            t = F.conv2d(t, c.first_kernel)
+            t = F.conv2d(t, c.core_kernel, None, c.stride, c.padding)
+            return F.conv2d(t, c.last_kernel, c.bias)
+        return F.conv2d(t, c.weight, c.bias, c.stride, c.padding)
+
+    def bn(b, t):
+        return F.batch_norm(t, b.running_mean, b.running_var, b.weight, b.bias, False, 0.0, b.eps)
+
+    x = F.max_pool2d(F.relu(bn(m.bn1, conv(m.conv1, x))), 3, 2, 1)
+    for layer in (m.layer1, m.layer2, m.layer3, m.layer4):
+        for blk in layer:
+            out = F.relu(bn(blk.bn1, conv(blk.conv1, x)))
+            out = bn(blk.bn2, conv(blk.conv2, out))
+            idt = x if blk.downsample is None else bn(blk.downsample[1], conv(blk.downsample[0], x))
+            x = F.relu(out + idt)
+    return m.fc(torch.flatten(F.adaptive_avg_pool2d(x, 1), 1))
+
+
+def bench_resnet(torch, T, dev, dist, world, rank, stream):
+    """images/s of the TK-compressed ResNet-18 (ranks round8(0.5*channels), random init, eval) at
+    batch 256 per GPU and its batch-1 latency, with the cuDNN path on the same weights beside it."""
+    from tdc_b200.parallel import gather_slices
+    model = T.fill_deterministic(T.tkc_resnet18().eval(), seed=0).to(dev)
+    out = {}
+    with torch.no_grad():
+        for B, iters in ((256, 5), (1, 30)):
+            x = torch.randn(B, 3, 224, 224, generator=torch.Generator().manual_seed(4001 + rank)).to(dev)
+
+            def fwd():
+                y = model(x)
+                return gather_slices(y, B * world) if (dist is not None and B > 1) else y
+            for _ in range(3):
+                y = fwd()
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(iters):
+                y = fwd()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / iters
+            if dist is not None:
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            key = "b%d" % B
+            out[key] = {"ms": ms, "images_per_s": B * (world if B > 1 else 1) / (ms * 1e-3)}
+            if world == 1:
+                torch.backends.cudnn.benchmark = True
+                torch.backends.cudnn.allow_tf32 = False
+                for _ in range(3):
+                    yr = torch_reference_forward(torch, model, x)
+                torch.cuda.synchronize()
+                e0.record(stream)
+                for _ in range(iters):
+                    yr = torch_reference_forward(torch, model, x)
+                e1.record(stream)
+                torch.cuda.synchronize()
+                out[key]["cudnn_ms"] = e0.elapsed_time(e1) / iters
+                out[key]["rel_err_vs_cudnn"] = float((y[:B] - yr).abs().max() / yr.abs().max())
+        if world == 1:
+            # batch-1 latency with the whole forward captured in a CUDA graph (launch-bound otherwise)
+            x1 = torch.randn(1, 3, 224, 224, generator=torch.Generator().manual_seed(4001)).to(dev)
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                for _ in range(3):
+                    model(x1)
+            torch.cuda.current_stream().wait_stream(s)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                yg = model(x1)
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); [graph.replay() for _ in range(30)]; e1.record()
+            torch.cuda.synchronize()
+            out["b1"]["graph_ms"] = e0.elapsed_time(e1) / 30
+            out["b1"]["graph_matches_eager"] = bool(torch.equal(yg, model(x1)))
+    out["config"] = "ResNet-18 [2,2,2,2], all sixteen 3x3 convs Tucker with R=round8(0.5*ch), 224x224 N(0,1) images, fp32, eval"
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -314,6 +409,10 @@ def main():
     line["e2e"]["matches_resident_path"] = e2e_ok
     for h, _, _ in hosts:
         lib.tdc_conv_destroy(h)
+
+    # ---- TK-compressed ResNet-18 forward (every rank its own batch; one gather of the logits) --
+    if not args.no_extras:
+        line["tk_resnet18"] = bench_resnet(torch, T, dev, dist, world, rank, stream)
 
     # ---- extras on rank 0 of a single-GPU run: batch-1 latency, cuDNN, CPU baseline ---------
     if rank == 0 and world == 1 and not args.no_extras:

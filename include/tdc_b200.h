@@ -132,6 +132,23 @@ TDC_API int tdc_conv2d_f32(const float* x, const float* w, const float* bias, fl
                    int pad, int stride, int w_layout, int epilogue,
                    const tdc_tile* tile, void* stream);
 
+/* Epilogue of the *_epi entry points:  y = relu?( conv * scale[k] + bias[k] + residual ).
+ * It is what follows a Tucker conv in the reference's blocks, folded into the last launch:
+ * the bias of TKConv.py:94, an inference-mode BatchNorm as a per-channel scale and shift
+ * (BatchNorm.cu:54-71 of the end-to-end skeleton; bn1/bn2 at inference/resnet_inet_tt.py:105-110),
+ * the residual add and the ReLU (resnet_inet_tt.py:112-115).  Any pointer may be NULL. */
+typedef struct tdc_epilogue {
+    const float* scale;     /* [K]                                         */
+    const float* bias;      /* [K]                                         */
+    const float* residual;  /* [B][K][Ho][Wo], same layout as y            */
+    int          relu;      /* != 0: max(.,0) last                         */
+} tdc_epilogue;
+
+TDC_API int tdc_conv2d_epi_f32(const float* x, const float* w, float* y,
+                   int B, int C, int H, int W, int K, int R, int S,
+                   int pad, int stride, int w_layout, const tdc_epilogue* epi,
+                   const tdc_tile* tile, void* stream);
+
 /* KCRS -> CRSK, once per weight load.  Replaces nothing in the reference (its drivers
  * fill k[c][r][s][n] with ones directly, template_benchmark_cudnn.template:425-428);
  * needed because TKConv.py stores core_kernel as [R2][R1][kh][kw]. */
@@ -176,6 +193,13 @@ TDC_API int tdc_tk_block_f32(const float* x, const float* w1, const float* wcore
                      const float* bias, float* y,
                      int B, int C, int H, int W, int R1, int R2, int K, int R, int S,
                      int pad, int stride, int w_layout, int epilogue,
+                     const tdc_tile* core_tile /* NULL = auto */,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* tdc_tk_block_f32 with the full epilogue on its last step (epi may be NULL). */
+TDC_API int tdc_tk_block_epi_f32(const float* x, const float* w1, const float* wcore, const float* w3, float* y,
+                     int B, int C, int H, int W, int R1, int R2, int K, int R, int S,
+                     int pad, int stride, int w_layout, const tdc_epilogue* epi,
                      const tdc_tile* core_tile /* NULL = auto */,
                      void* workspace, size_t workspace_bytes, void* stream);
 

@@ -46,6 +46,19 @@ def import_tkconv():
     return TKConv
 
 
+def import_resnet():
+    """Returns the reference's resnet_inet_tt module (TTResNet, TTBasicBlock, ...), unmodified.
+    Besides tensorly it imports timm only for its model registry decorator and for loading
+    pre-trained checkpoints (inference/resnet_inet_tt.py:15-16,451-455); a stub with an identity
+    `register_model` is enough to build and run the networks."""
+    import_tkconv()
+    reg = _stub("timm.models.registry", register_model=lambda f: f)
+    models = _stub("timm.models", registry=reg)
+    _stub("timm", models=models, create_model=_unavailable)
+    import resnet_inet_tt   # noqa: the reference's module name
+    return resnet_inet_tt
+
+
 class Ranks:
     """Stand-in for the hp_dict objects of inference/hp_dicts/*.py: `.ranks[name] -> [R2, R1]`."""
 

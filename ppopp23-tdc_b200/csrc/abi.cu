@@ -92,8 +92,17 @@ int complete_tile(const Shape& s, int device, const tdc_devinfo& dev, tdc_tile* 
     return TDC_OK;
 }
 
+int launch_conv_epi(const float* x, const float* w, const tdc_epilogue& epi, float* y, const Shape& s, int w_layout,
+                    const tdc_tile* tile_in, cudaStream_t stream);
+
 int launch_conv(const float* x, const float* w, const float* bias, float* y, const Shape& s, int w_layout,
                 int epilogue, const tdc_tile* tile_in, cudaStream_t stream) {
+    tdc_epilogue epi{nullptr, bias, nullptr, (epilogue & TDC_EPI_RELU) ? 1 : 0};
+    return launch_conv_epi(x, w, epi, y, s, w_layout, tile_in, stream);
+}
+
+int launch_conv_epi(const float* x, const float* w, const tdc_epilogue& epi, float* y, const Shape& s, int w_layout,
+                    const tdc_tile* tile_in, cudaStream_t stream) {
     if (!x || !w || !y) return fail(TDC_ERR_NULL, "x, w and y must be non-NULL");
     int rc = check_shape(s);
     if (rc) return rc;
@@ -110,14 +119,14 @@ int launch_conv(const float* x, const float* w, const float* bias, float* y, con
     if ((rc = make_geometry(s, t, dev, &g, &why))) return fail(rc, "%s", why);
 
     ConvArgs a;
-    a.x = x; a.w = w; a.bias = bias; a.y = y;
+    a.x = x; a.w = w; a.bias = epi.bias; a.scale = epi.scale; a.residual = epi.residual; a.y = y;
     a.B = s.B; a.C = s.C; a.H = s.H; a.W = s.W; a.K = s.K; a.Ho = s.Ho(); a.Wo = s.Wo(); a.pad = s.pad;
     a.R = s.R; a.S = s.S;
     const int RS = s.R * s.S;
     if (w_layout == TDC_W_KCRS) { a.ws_k = (long long)s.C * RS; a.ws_c = RS; a.ws_rs = 1; }
     else                        { a.ws_k = 1; a.ws_c = (long long)RS * s.K; a.ws_rs = s.K; }
     a.w_vec = (w_layout == TDC_W_CRSK && s.K % 4 == 0 && (reinterpret_cast<uintptr_t>(w) % 16 == 0)) ? 1 : 0;
-    a.relu = (epilogue & TDC_EPI_RELU) ? 1 : 0;
+    a.relu = epi.relu ? 1 : 0;
     a.tc = t.tc; a.gy = t.gy; a.gx = t.gx; a.imgs = t.imgs; a.ks = t.ks;
     a.in_rows = g.in_rows; a.in_wp = g.in_wp; a.patch = g.patch;
     a.tiles_y = g.tiles_y; a.tiles_x = g.tiles_x; a.img_groups = g.img_groups; a.n_ocb = g.n_ocb;
@@ -184,6 +193,13 @@ int tdc_conv2d_f32(const float* x, const float* w, const float* bias, float* y, 
                    int R, int S, int pad, int stride, int w_layout, int epilogue, const tdc_tile* tile, void* stream) {
     return launch_conv(x, w, bias, y, Shape{B, C, H, W, K, R, S, pad, stride}, w_layout, epilogue, tile,
                        (cudaStream_t)stream);
+}
+
+int tdc_conv2d_epi_f32(const float* x, const float* w, float* y, int B, int C, int H, int W, int K, int R, int S,
+                       int pad, int stride, int w_layout, const tdc_epilogue* epi, const tdc_tile* tile, void* stream) {
+    tdc_epilogue e{nullptr, nullptr, nullptr, 0};
+    if (epi) e = *epi;
+    return launch_conv_epi(x, w, e, y, Shape{B, C, H, W, K, R, S, pad, stride}, w_layout, tile, (cudaStream_t)stream);
 }
 
 int tdc_permute_weights(const float* w_kcrs, float* w_crsk, int K, int C, int R, int S, void* stream) {
@@ -280,10 +296,10 @@ size_t tdc_tk_block_workspace_bytes(int B, int C, int H, int W, int R1, int R2, 
     return 4 * (((z1 + 63) / 64) * 64 + z2);
 }
 
-int tdc_tk_block_f32(const float* x, const float* w1, const float* wcore, const float* w3, const float* bias,
-                     float* y, int B, int C, int H, int W, int R1, int R2, int K, int R, int S, int pad, int stride,
-                     int w_layout, int epilogue, const tdc_tile* core_tile, void* workspace, size_t workspace_bytes,
-                     void* stream) {
+int tdc_tk_block_epi_f32(const float* x, const float* w1, const float* wcore, const float* w3, float* y, int B, int C,
+                         int H, int W, int R1, int R2, int K, int R, int S, int pad, int stride, int w_layout,
+                         const tdc_epilogue* epi, const tdc_tile* core_tile, void* workspace, size_t workspace_bytes,
+                         void* stream) {
     if (!x || !w1 || !wcore || !w3 || !y) return fail(TDC_ERR_NULL, "x, w1, wcore, w3 and y must be non-NULL");
     size_t need = tdc_tk_block_workspace_bytes(B, C, H, W, R1, R2, K, R, S, pad, stride);
     if (need == 0) return fail(TDC_ERR_SHAPE, "bad Tucker block shape");
@@ -293,11 +309,22 @@ int tdc_tk_block_f32(const float* x, const float* w1, const float* wcore, const 
     float* z1 = (float*)workspace;
     float* z2 = z1 + (((size_t)B * R1 * H * W + 63) / 64) * 64;
     cudaStream_t st = (cudaStream_t)stream;
+    tdc_epilogue e{nullptr, nullptr, nullptr, 0};
+    if (epi) e = *epi;
     int rc;
     // 1x1 convs take their filter as [out][in] = KCRS with R=S=1.
     if ((rc = launch_conv(x, w1, nullptr, z1, Shape{B, C, H, W, R1, 1, 1, 0, 1}, TDC_W_KCRS, TDC_EPI_NONE, nullptr, st))) return rc;
     if ((rc = launch_conv(z1, wcore, nullptr, z2, Shape{B, R1, H, W, R2, R, S, pad, stride}, w_layout, TDC_EPI_NONE, core_tile, st))) return rc;
-    return launch_conv(z2, w3, bias, y, Shape{B, R2, Ho, Wo, K, 1, 1, 0, 1}, TDC_W_KCRS, epilogue, nullptr, st);
+    return launch_conv_epi(z2, w3, e, y, Shape{B, R2, Ho, Wo, K, 1, 1, 0, 1}, TDC_W_KCRS, nullptr, st);
+}
+
+int tdc_tk_block_f32(const float* x, const float* w1, const float* wcore, const float* w3, const float* bias,
+                     float* y, int B, int C, int H, int W, int R1, int R2, int K, int R, int S, int pad, int stride,
+                     int w_layout, int epilogue, const tdc_tile* core_tile, void* workspace, size_t workspace_bytes,
+                     void* stream) {
+    tdc_epilogue e{nullptr, bias, nullptr, (epilogue & TDC_EPI_RELU) ? 1 : 0};
+    return tdc_tk_block_epi_f32(x, w1, wcore, w3, y, B, C, H, W, R1, R2, K, R, S, pad, stride, w_layout, &e, core_tile,
+                                workspace, workspace_bytes, stream);
 }
 
 }  // extern "C"

@@ -37,6 +37,8 @@ struct ConvArgs {
     const float* x;      // [B][C][H][W]
     const float* w;      // element (k,c,rs) at k*ws_k + c*ws_c + rs*ws_rs
     const float* bias;   // [K] or nullptr
+    const float* scale;  // [K] or nullptr: y = conv * scale + bias (a folded BatchNorm)
+    const float* residual;  // [B][K][Ho][Wo] or nullptr, added before the ReLU
     float*       y;      // [B][K][Ho][Wo]
     int B, C, H, W, K, Ho, Wo, pad;
     int R, S;            // filter size (used by the runtime-size variant only)
@@ -350,7 +352,7 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
     }
     if (ksl != 0) return;
 
-    // ---- epilogue: bias, ReLU, store ----------------------------------------------------
+    // ---- epilogue: scale, bias, residual, ReLU, store ----------------------------------------------------
     const int b = b0 + iml;
     if (b >= a.B) return;
     const int oyb = oy0 + gyi * TH, oxb = ox0 + gxi * TW;
@@ -360,7 +362,9 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
         const int oc = oc0 + ocg * TN + j;
         if (oc >= a.K) continue;
         const float bv = a.bias ? a.bias[oc] : 0.f;
-        float* yp = a.y + ((long long)b * a.K + oc) * a.Ho * a.Wo;
+        const float sv = a.scale ? a.scale[oc] : 1.f;
+        const long long plane = ((long long)b * a.K + oc) * a.Ho * a.Wo;
+        float* yp = a.y + plane;
 #pragma unroll
         for (int o = 0; o < TH; ++o) {
             const int oy = oyb + o;
@@ -368,7 +372,8 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
             float* yr = yp + (long long)oy * a.Wo + oxb;
 #pragma unroll
             for (int p = 0; p < TW; ++p) {
-                float v = acc[j][o][p] + bv;
+                float v = a.scale ? fmaf(acc[j][o][p], sv, bv) : acc[j][o][p] + bv;
+                if (a.residual && oxb + p < a.Wo) v += a.residual[plane + (long long)oy * a.Wo + oxb + p];
                 acc[j][o][p] = a.relu ? fmaxf(v, 0.f) : v;
             }
             bool stored = false;

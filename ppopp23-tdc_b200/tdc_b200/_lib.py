@@ -30,6 +30,11 @@ class Tile(C.Structure):
         return "Tile(" + ", ".join("%s=%d" % (n, getattr(self, n)) for n, _ in self._fields_) + ")"
 
 
+class Epilogue(C.Structure):
+    """tdc_epilogue: y = relu?(conv * scale[k] + bias[k] + residual); NULL pointers are skipped."""
+    _fields_ = [("scale", C.c_void_p), ("bias", C.c_void_p), ("residual", C.c_void_p), ("relu", C.c_int)]
+
+
 class DevInfo(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("sm_count", "smem_per_cta", "regs_per_sm", "threads_per_sm")]
 
@@ -50,6 +55,8 @@ _PROTOTYPES = {
     "tdc_query_device": (_i, [_i, C.POINTER(DevInfo)]),
     "tdc_core_conv2d_f32": (_i, [_p, _p, _p] + [_i] * 10 + [C.POINTER(Tile), _p]),
     "tdc_conv2d_f32": (_i, [_p, _p, _p, _p] + [_i] * 11 + [C.POINTER(Tile), _p]),
+    "tdc_conv2d_epi_f32": (_i, [_p, _p, _p] + [_i] * 10 + [C.POINTER(Epilogue), C.POINTER(Tile), _p]),
+    "tdc_tk_block_epi_f32": (_i, [_p] * 5 + [_i] * 12 + [C.POINTER(Epilogue), C.POINTER(Tile), _p, _sz, _p]),
     "tdc_permute_weights": (_i, [_p, _p, _i, _i, _i, _i, _p]),
     "tdc_select_tile": (_i, [_i] * 9 + [C.POINTER(DevInfo), C.POINTER(Tile)]),
     "tdc_tile_info": (_i, [_i] * 9 + [C.POINTER(Tile), C.POINTER(LaunchInfo)]),

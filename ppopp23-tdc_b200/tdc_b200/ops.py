@@ -118,6 +118,72 @@ def tk_block(x, first, core, last, bias=None, stride=1, padding=0, core_layout=W
     return out
 
 
+def _epilogue(scale, bias, residual, relu):
+    e = _lib.Epilogue()
+    e.scale = _dev_f32(scale, "scale") if scale is not None else None
+    e.bias = _dev_f32(bias, "bias") if bias is not None else None
+    e.residual = _dev_f32(residual, "residual") if residual is not None else None
+    e.relu = 1 if relu else 0
+    return e
+
+
+def conv2d_epi(x, w, scale=None, bias=None, residual=None, relu=False, stride=1, padding=0, w_layout=W_KCRS,
+               tile=None, out=None):
+    """y = relu?(conv(x, w) * scale[k] + bias[k] + residual): a conv with a folded inference-mode
+    BatchNorm, the residual add and the ReLU of the reference's blocks
+    (inference/resnet_inet_tt.py:102-117) in one launch."""
+    stride, padding = _pair(stride), _pair(padding)
+    B, Cc, H, W = x.shape
+    if w_layout == W_KCRS:
+        K, Cw, R, S = w.shape
+    else:
+        Cw, R, S, K = w.shape
+    if Cw != Cc:
+        raise TdcError(_lib.ERR_SHAPE, "x has %d channels, w expects %d" % (Cc, Cw))
+    Ho, Wo = out_hw(H, W, R, S, padding, stride)
+    if out is None:
+        out = torch.empty((B, K, Ho, Wo), device=x.device, dtype=torch.float32)
+    if residual is not None and tuple(residual.shape) != tuple(out.shape):
+        raise TdcError(_lib.ERR_SHAPE, "residual %s does not match the output %s" % (tuple(residual.shape), tuple(out.shape)))
+    e = _epilogue(scale, bias, residual, relu)
+    with torch.cuda.device(x.device):
+        check(lib.tdc_conv2d_epi_f32(_dev_f32(x, "x"), _dev_f32(w, "w"), _dev_f32(out, "out"), B, Cc, H, W, K, R, S,
+                                     padding, stride, w_layout, C.byref(e), C.byref(tile) if tile is not None else None,
+                                     _stream()))
+    return out
+
+
+def tk_block_epi(x, first, core, last, scale=None, bias=None, residual=None, relu=False, stride=1, padding=0,
+                 core_layout=W_KCRS, workspace=None, out=None, core_tile=None):
+    """tk_block with the full epilogue on its last 1x1 step."""
+    stride, padding = _pair(stride), _pair(padding)
+    B, Cc, H, W = x.shape
+    R1, K = first.shape[0], last.shape[0]
+    if core_layout == W_KCRS:
+        R2, R1c, R, S = core.shape
+    else:
+        R1c, R, S, R2 = core.shape
+    if first.shape[1] != Cc or R1c != R1 or last.shape[1] != R2:
+        raise TdcError(_lib.ERR_SHAPE, "Tucker factors do not chain: first %s core %s last %s" %
+                       (tuple(first.shape), tuple(core.shape), tuple(last.shape)))
+    Ho, Wo = out_hw(H, W, R, S, padding, stride)
+    need = tk_block_workspace_bytes(B, Cc, H, W, R1, R2, K, R, S, padding, stride)
+    if workspace is None:
+        workspace = torch.empty(need, device=x.device, dtype=torch.uint8)
+    if out is None:
+        out = torch.empty((B, K, Ho, Wo), device=x.device, dtype=torch.float32)
+    if residual is not None and tuple(residual.shape) != tuple(out.shape):
+        raise TdcError(_lib.ERR_SHAPE, "residual %s does not match the output %s" % (tuple(residual.shape), tuple(out.shape)))
+    e = _epilogue(scale, bias, residual, relu)
+    with torch.cuda.device(x.device):
+        check(lib.tdc_tk_block_epi_f32(_dev_f32(x, "x"), _dev_f32(first, "first"), _dev_f32(core, "core"),
+                                       _dev_f32(last, "last"), _dev_f32(out, "out"), B, Cc, H, W, R1, R2, K, R, S,
+                                       padding, stride, core_layout, C.byref(e),
+                                       C.byref(core_tile) if core_tile is not None else None, workspace.data_ptr(),
+                                       workspace.numel() * workspace.element_size(), _stream()))
+    return out
+
+
 def select_tile(B, Cc, H, W, K, R=3, S=3, pad=1, stride=1, dev=None):
     """Analytical tile choice (tdc_select_tile). `dev=None` queries the current GPU; pass
     `_lib.B200` to model a B200 without one."""

@@ -1,0 +1,204 @@
+"""TK-compressed ResNet on the B200 kernels — the assembly of the reference's TTResNet.
+
+Mirrors inference/resnet_inet_tt.py: TTBasicBlock (:53-117), TTResNet (:287-394) and the
+`tkc_resnet18` entry (:483-496) for the basic-block nets.  Module names, parameter names and
+shapes are the reference's, so a state dict of `TTResNet(TTBasicBlock, [2,2,2,2],
+conv=TKConv2dC, hp_dict=...)` loads with `load_state_dict` unchanged.  Which 3x3 convs are
+Tucker convs is decided as there: the ones whose `layer{s}.{i}.conv{1,2}.weight` key is in
+`hp_dict.ranks` (value `[R2, R1]`).
+
+Every convolution runs on libtdc_b200.so: the Tucker convs as Tucker blocks, the stem (7x7,
+stride 2) and the 1x1 stride-2 downsample convs through the same kernel family.  In eval mode
+the BatchNorm that follows a conv is folded into that conv's last launch as a per-channel
+scale and shift, together with the residual add and the ReLU (`forward` = one launch chain
+per block, no elementwise passes); max-pool, global average pool and the classifier stay
+torch ops.  Training-mode BatchNorm is not built: `forward` raises outside eval mode.
+"""
+import torch
+import torch.nn as nn
+
+from . import ops, tiles
+from ._lib import ERR_UNSUPPORTED, W_CRSK, TdcError
+from .tkconv import TKConv2dC_B200
+
+
+def round8(v):
+    return int(8 * round(v / 8.0))
+
+
+class HalfRanks:
+    """hp_dict with R1 = round8(0.5*in), R2 = round8(0.5*out) for every 3x3 conv of a basic-block
+    ResNet — the benchmark's rank rule, in the format of inference/hp_dicts/tk_resnet18_hp.py:25-43."""
+
+    def __init__(self, layers=(2, 2, 2, 2), ratio=0.5):
+        self.ranks = {}
+        inplanes = 64
+        for s, (planes, n) in enumerate(zip((64, 128, 256, 512), layers), start=1):
+            for i in range(n):
+                cin = inplanes if i == 0 else planes
+                self.ranks["layer%d.%d.conv1.weight" % (s, i)] = [round8(ratio * planes), round8(ratio * cin)]
+                self.ranks["layer%d.%d.conv2.weight" % (s, i)] = [round8(ratio * planes), round8(ratio * planes)]
+            inplanes = planes
+
+
+class Conv2dB200(nn.Conv2d):
+    """nn.Conv2d parameters (`weight`, `bias`), forward on the B200 kernel."""
+
+    def forward(self, x):
+        return ops.conv2d(x, self.weight.detach(), None if self.bias is None else self.bias.detach(),
+                          self.stride, self.padding)
+
+
+def _fold_bn(bn):
+    """Inference BatchNorm as y = x*scale + shift (fp64 arithmetic, rounded once); cached on the
+    module until one of its tensors changes."""
+    key = tuple((t._version, t.data_ptr()) for t in (bn.running_var, bn.running_mean, bn.weight, bn.bias)
+                if t is not None)
+    hit = getattr(bn, "_tdc_fold", None)
+    if hit is not None and hit[0] == key:
+        return hit[1], hit[2]
+    scale, shift = _fold_bn_now(bn)
+    bn._tdc_fold = (key, scale, shift)
+    return scale, shift
+
+
+def _fold_bn_now(bn):
+    var, mean = bn.running_var.double(), bn.running_mean.double()
+    g = bn.weight.double() if bn.weight is not None else torch.ones_like(var)
+    b = bn.bias.double() if bn.bias is not None else torch.zeros_like(var)
+    scale = g / torch.sqrt(var + bn.eps)
+    return scale.float().contiguous(), (b - mean * scale).float().contiguous()
+
+
+def _tk_or_dense(conv, x, scale, shift, residual, relu):
+    """One conv + folded BN (+ residual) (+ ReLU) in the conv's own launch chain."""
+    if isinstance(conv, TKConv2dC_B200):
+        B, _, H, W = x.shape
+        if conv.bias is not None:
+            shift = shift + conv.bias.detach() * scale
+        tile = tiles.table_tile(B, conv.in_rank, H, W, conv.out_rank, conv.kernel_size[0], conv.kernel_size[1],
+                                conv.padding[0], conv.stride[0])
+        return ops.tk_block_epi(x, conv.first_kernel.detach(), conv._core_channel_last(), conv.last_kernel.detach(),
+                                scale, shift, residual, relu, conv.stride, conv.padding, core_layout=W_CRSK,
+                                workspace=conv._ws(x, shared=True), core_tile=tile)
+    if conv.bias is not None:
+        shift = shift + conv.bias.detach() * scale
+    return ops.conv2d_epi(x, conv.weight.detach(), scale, shift, residual, relu, conv.stride, conv.padding)
+
+
+class TKBasicBlock(nn.Module):
+    """inference/resnet_inet_tt.py:53-117 (TTBasicBlock) with conv = TKConv2dC_B200."""
+    expansion = 1
+
+    def __init__(self, inplanes, planes, stride=1, downsample=None, stage=1, id=0, hp_dict=None):
+        super().__init__()
+        name = "layer%d.%d.conv1.weight" % (stage, id)
+        if name in hp_dict.ranks:
+            self.conv1 = TKConv2dC_B200(inplanes, planes, 3, stride=stride, padding=1, bias=False, hp_dict=hp_dict, name=name)
+        else:
+            self.conv1 = Conv2dB200(inplanes, planes, 3, stride=stride, padding=1, bias=False)
+        self.bn1 = nn.BatchNorm2d(planes)
+        self.relu = nn.ReLU(inplace=True)
+        name = "layer%d.%d.conv2.weight" % (stage, id)
+        if name in hp_dict.ranks:
+            self.conv2 = TKConv2dC_B200(planes, planes, 3, padding=1, bias=False, hp_dict=hp_dict, name=name)
+        else:
+            self.conv2 = Conv2dB200(planes, planes, 3, padding=1, bias=False)
+        self.bn2 = nn.BatchNorm2d(planes)
+        self.downsample = downsample
+        self.stride = stride
+
+    def forward(self, x):
+        if self.training:
+            raise TdcError(ERR_UNSUPPORTED, "training-mode BatchNorm is not built; call .eval()")
+        s1, b1 = _fold_bn(self.bn1)
+        s2, b2 = _fold_bn(self.bn2)
+        out = _tk_or_dense(self.conv1, x, s1, b1, None, True)
+        identity = x
+        if self.downsample is not None:
+            sd, bd = _fold_bn(self.downsample[1])
+            identity = _tk_or_dense(self.downsample[0], x, sd, bd, None, False)
+        return _tk_or_dense(self.conv2, out, s2, b2, identity, True)
+
+
+class TKResNet(nn.Module):
+    """inference/resnet_inet_tt.py:287-394 (TTResNet) for basic blocks."""
+
+    def __init__(self, layers=(2, 2, 2, 2), num_classes=1000, hp_dict=None):
+        super().__init__()
+        hp_dict = hp_dict if hp_dict is not None else HalfRanks(layers)
+        self.inplanes = 64
+        self.conv1 = Conv2dB200(3, 64, kernel_size=7, stride=2, padding=3, bias=False)
+        self.bn1 = nn.BatchNorm2d(64)
+        self.relu = nn.ReLU(inplace=True)
+        self.maxpool = nn.MaxPool2d(kernel_size=3, stride=2, padding=1)
+        self.layer1 = self._make_layer(64, layers[0], 1, 1, hp_dict)
+        self.layer2 = self._make_layer(128, layers[1], 2, 2, hp_dict)
+        self.layer3 = self._make_layer(256, layers[2], 2, 3, hp_dict)
+        self.layer4 = self._make_layer(512, layers[3], 2, 4, hp_dict)
+        self.avgpool = nn.AdaptiveAvgPool2d((1, 1))
+        self.fc = nn.Linear(512, num_classes)
+        for m in self.modules():        # the reference's init loop, resnet_inet_tt.py:335-340
+            if isinstance(m, nn.Conv2d):
+                nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")
+            elif isinstance(m, nn.BatchNorm2d):
+                nn.init.constant_(m.weight, 1)
+                nn.init.constant_(m.bias, 0)
+
+    def _make_layer(self, planes, blocks, stride, stage, hp_dict):
+        downsample = None
+        if stride != 1 or self.inplanes != planes:
+            downsample = nn.Sequential(Conv2dB200(self.inplanes, planes, 1, stride=stride, bias=False),
+                                       nn.BatchNorm2d(planes))
+        layers = [TKBasicBlock(self.inplanes, planes, stride, downsample, stage=stage, id=0, hp_dict=hp_dict)]
+        self.inplanes = planes
+        for i in range(1, blocks):
+            layers.append(TKBasicBlock(planes, planes, stage=stage, id=i, hp_dict=hp_dict))
+        return nn.Sequential(*layers)
+
+    def forward(self, x):
+        if self.training:
+            raise TdcError(ERR_UNSUPPORTED, "training-mode BatchNorm is not built; call .eval()")
+        if not x.is_cuda:
+            raise TdcError(ERR_UNSUPPORTED, "TKResNet runs on CUDA tensors only")
+        x = x.contiguous().float()
+        s, b = _fold_bn(self.bn1)
+        x = _tk_or_dense(self.conv1, x, s, b, None, True)
+        x = self.maxpool(x)
+        x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
+        x = torch.flatten(self.avgpool(x), 1)
+        return self.fc(x)
+
+
+def tkc_resnet18(hp_dict=None, num_classes=1000):
+    """inference/resnet_inet_tt.py:483-496 without the checkpoint load."""
+    return TKResNet((2, 2, 2, 2), num_classes, hp_dict)
+
+
+def fill_deterministic(module, seed=0):
+    """Every parameter and buffer from a generator seeded by (seed, its name): two models with
+    the same state-dict keys — this one and the reference's — get identical values whatever their
+    construction order.  Conv/Tucker kernels Kaiming-normal (fan_out), BatchNorm affine ~ (1, 0)
+    +- 0.1, running mean ~ N(0, 0.1), running var in [0.5, 1.5], classifier ~ N(0, 0.01)."""
+    import zlib
+    sd = module.state_dict()
+    for name in sorted(sd):
+        t = sd[name]
+        if not t.dtype.is_floating_point:
+            continue
+        g = torch.Generator().manual_seed((zlib.crc32(name.encode()) + seed) & 0x7FFFFFFF)
+        if t.dim() == 4:
+            fan_out = t.shape[0] * t.shape[2] * t.shape[3]
+            v = torch.empty(t.shape).normal_(0.0, (2.0 / fan_out) ** 0.5, generator=g)
+        elif name.endswith("running_var"):
+            v = torch.rand(t.shape, generator=g) + 0.5
+        elif name.endswith("running_mean"):
+            v = torch.randn(t.shape, generator=g) * 0.1
+        elif name.endswith("weight") and t.dim() == 1:
+            v = 1.0 + 0.1 * torch.randn(t.shape, generator=g)
+        elif t.dim() == 2:
+            v = torch.randn(t.shape, generator=g) * 0.01
+        else:
+            v = 0.1 * torch.randn(t.shape, generator=g)
+        t.copy_(v.to(t.device))
+    return module

@@ -19,6 +19,9 @@ from . import ops, tiles
 from ._lib import W_CRSK, TdcError, ERR_UNSUPPORTED
 
 
+_SHARED_WS = {}     # device -> uint8 tensor
+
+
 class TKConv2dC_B200(nn.Module):
     def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1,
                  groups: int = 1, bias: bool = True, padding_mode: str = 'zeros', hp_dict: Optional = None,
@@ -82,10 +85,18 @@ class TKConv2dC_B200(nn.Module):
             self._core_crsk = (key, ops.permute_weights(w.detach().contiguous()))
         return self._core_crsk[1]
 
-    def _ws(self, x):
+    def _ws(self, x, shared=False):
+        """Workspace for the block's two intermediates: this module's own, or (shared=True) one
+        buffer per device that all blocks of a network reuse — they run one after another on one
+        stream, and a small shared buffer stays L2-resident."""
         B, C, H, W = x.shape
         need = ops.tk_block_workspace_bytes(B, C, H, W, self.in_rank, self.out_rank, self.out_channels,
                                             self.kernel_size[0], self.kernel_size[1], self.padding[0], self.stride[0])
+        if shared:
+            ws = _SHARED_WS.get(x.device)
+            if ws is None or ws.numel() < need:
+                ws = _SHARED_WS[x.device] = torch.empty(need, device=x.device, dtype=torch.uint8)
+            return ws
         ws = self._workspace
         if ws is None or ws.numel() < need or ws.device != x.device:
             ws = self._workspace = torch.empty(need, device=x.device, dtype=torch.uint8)
