@@ -238,6 +238,36 @@ TDC_API int tdc_tk_block_f32_static(const float* x, const float* w1, const float
                      const tdc_tile* core_tile /* NULL = auto */, void* stream);
 
 /*
+ * Tensor-core variant (tcgen05, TF32 operands, fp32 accumulation in tensor memory).  No
+ * counterpart in the reference, whose kernel and whose cuDNN calls are fp32 FMA code
+ * (template_benchmark_cudnn.template:365-402; inference/TKConv.py:92-93).  Same result
+ * definition as tdc_conv2d_epi_f32 for "same" convolutions: R = S in {1, 3}, stride 1,
+ * pad = (R-1)/2.
+ *   mode 3  "3xTF32": operands split into hi + lo TF32 parts, three MMAs per product;
+ *           fp32-level accuracy (held to the same 1e-5 bar as the fp32 kernels)
+ *   mode 1  plain TF32: one MMA per product; 5e-3 bar; reported separately
+ * Use: tdc_tc_plan_make once per layer shape, tdc_tc_prepare_weights once per weight load
+ * into a caller-owned buffer of plan.weights_bytes, then tdc_conv2d_tc per call.  Every
+ * device-side wait is bounded; tdc_tc_status reads (and synchronises for) the device status
+ * word: 0 = no wait ever ran out.
+ */
+typedef struct tdc_tc_plan {
+    int    C, K, R, S, mode;
+    int    nt;            /* output channels per CTA (MMA N)              */
+    int    cb;            /* channels per stage (one K step = 8)          */
+    int    nkb, n_ocb;    /* channel blocks, output-channel blocks        */
+    int    hl;            /* 2 when operands are split (mode 3), else 1   */
+    size_t weights_bytes; /* size of the pre-arranged filter              */
+} tdc_tc_plan;
+
+TDC_API const char* tdc_tc_last_error_string(void);
+TDC_API int tdc_tc_plan_make(int C, int K, int R, int S, int mode, tdc_tc_plan* out);
+TDC_API int tdc_tc_prepare_weights(const tdc_tc_plan* plan, const float* w, int w_layout, void* wt, void* stream);
+TDC_API int tdc_conv2d_tc(const tdc_tc_plan* plan, const float* x, const void* wt, float* y,
+                          int B, int H, int W, const tdc_epilogue* epi, int flags /* 0 */, void* stream);
+TDC_API int tdc_tc_status(int* out);
+
+/*
  * Layer objects with the surface of the reference's end-to-end classes:
  * Conv::initialize(b,c,h,w,n,pad,r,s,stride,weightFile,use_bias) / float* Conv::forward(float*)
  * (A100-evaluation/EndToEnd/resnet18-tk/inc/common.h:38-69, src/Conv.cu:2-125) and

@@ -1,0 +1,479 @@
+// Tensor-core variant of the core convolution: an implicit GEMM on tcgen05 (sm_100a).
+//
+// The reference computes this step with fp32 FMAs (its CUDA kernel,
+// A100-evaluation/TDC-LAYERS-ORACLE/template_benchmark_cudnn.template:365-402) or leaves it
+// to cuDNN (inference/TKConv.py:92-93); it has no tensor-core path.  On B200 the fp32 FMA
+// pipe is held back by the shared-memory return path, while the 5th-generation tensor cores
+// are idle, so this file maps the same convolution onto tcgen05.mma kind::tf32:
+//
+//   D[128 positions][NT channels] += A_tap[128 positions][8 channels] * B_tap[8 channels][NT]
+//
+// summed over the R*S taps and all channel blocks, accumulator in tensor memory.
+//
+//   * Positions.  Each image is laid out (conceptually) row by row with ONE zero column
+//     after every row and one zero row after the image (row pitch Wp = W + 1).  In that
+//     layout the input of output position g for tap (r, s) is position
+//     g + (r-1)*Wp + (s-1), for every g — the halo of a row is the zero column of its
+//     neighbour.  A CTA owns 128 consecutive positions (possibly spanning images), stages
+//     the patch of positions it needs once per channel block, and every tap reads the same
+//     patch at a different row offset.  Outputs that fall on a zero column/row are dropped.
+//   * Shared-memory operand layout: K-major, no swizzle, [channel/4][row][4 floats]: a
+//     core matrix (8 rows x 16 bytes) is contiguous for ANY starting row, which is what lets
+//     the nine taps address one patch with descriptors that differ only in their start.
+//   * Precision.  mode 3 ("3xTF32"): every operand is split x = hi + lo with hi = tf32(x),
+//     and hi*hi + hi*lo + lo*hi is accumulated in fp32 — products are then exact to ~2^-21,
+//     i.e. fp32-level results (tests hold it to the fp32 bar of 1e-5).  mode 1: plain TF32,
+//     one MMA per tap and step, reported separately at 5e-3.
+//   * The filter is pre-arranged once (tdc_tc_prepare_weights) into the exact shared-memory
+//     image of each (channel block, output block), so staging it is one plain bulk copy
+//     (cp.async.bulk into this CTA's shared memory) that completes on an mbarrier.
+//   * Every wait on an mbarrier is bounded; a wait that runs out records a status word,
+//     the CTA skips to its clean-up (tensor memory is freed) and returns.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <cstdarg>
+#include <cstdio>
+#include "../../include/tdc_b200.h"
+
+namespace tdc_tc {
+
+constexpr int M_TILE   = 128;   // positions per CTA = MMA M
+constexpr int CB       = 8;     // channels per stage = one K step of kind::tf32
+constexpr int THREADS  = 256;
+
+struct Args {
+    const float* x;        // [B][C][H][W]
+    const float* wt;       // pre-arranged filter, see prepare kernel
+    float*       y;        // [B][K][H][W]
+    const float* scale; const float* bias; const float* residual;
+    int relu;
+    int B, C, H, W, K;
+    int taps_r;            // R (= S): 1 or 3
+    int Wp, Lp;            // row pitch and positions per image of the padded position space
+    int P;                 // patch rows staged per CTA (multiple of 8)
+    int nkb;               // channel blocks
+    int n_ocb;             // output-channel blocks
+    int hl;                // 2: hi/lo split (3xTF32), 1: plain TF32
+    int ns;                // stages
+    long long total_pos;   // B * Lp
+    int* status;           // device status word: 0 ok, else first failure code
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait: true when the phase with `parity` has completed, false after ~1 s.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+        if (clock64() - t0 > 2000000000ll) return false;
+    }
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ float to_tf32(float v) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return __uint_as_float(r);
+}
+
+// Shared-memory matrix descriptor: K-major, no swizzle.  lbo = bytes between the two core
+// matrices of one K step (channels 0-3 / 4-7), sbo = bytes between 8-row groups.
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= 1ull << 46;                 // descriptor version of sm_100
+    return d;                        // layout type 0 (no swizzle), base offset 0
+}
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 32 consecutive columns of this warp's 32 tensor-memory lanes -> 32 registers per thread.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+
+// NT output channels and MT tiles of 128 positions per CTA.  Tensor memory holds, per
+// position tile, NT "main" columns (hi*hi) followed by NT "small" columns (hi*lo + lo*hi):
+// the small products never pass through the large running sum, whose rounding inside the
+// tensor core would otherwise swamp them, and fp32 adds main + small once in the epilogue.
+template <int NT, int MT, int TAPS>
+__global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    // carve: barriers | tmem slot | stages { A[hl][CB/4][P][4], B[tap][CB/4][hl*NT][4] }
+    uint64_t* full_bar  = reinterpret_cast<uint64_t*>(smem_raw);           // [ns] filter landed
+    uint64_t* empty_bar = full_bar + 4;                                     // [ns] MMAs of the stage done
+    uint64_t* done_bar  = empty_bar + 4;                                    // all MMAs done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+    int*      abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+    float*    stage0    = reinterpret_cast<float*>(smem_raw + 128);
+
+    constexpr int PPT = (MT * M_TILE + 2 * 260 + THREADS - 1) / THREADS;   // patch rows per thread, W <= 256
+    constexpr uint32_t TMEM_COLS = (uint32_t)(MT * 2 * NT) < 32u ? 32u : (uint32_t)(MT * 2 * NT);
+    constexpr int taps = TAPS;
+    const int a_floats = a.hl * CB * a.P;                  // A part of a stage
+    const int b_floats = a.hl * taps * CB * NT;            // B part of a stage
+    const int stage_floats = a_floats + b_floats;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    const int ocb = blockIdx.x % a.n_ocb;
+    const long long g0 = (long long)(blockIdx.x / a.n_ocb) * (MT * M_TILE);   // first output position
+    const int pad = (a.taps_r - 1) / 2;
+    const long long gp0 = g0 - (long long)pad * (a.Wp + 1);                // position of patch row 0
+    const long long HW = (long long)a.H * a.W;
+
+    if (tid == 0) {
+        // a stage is released, and the tile is done, when each of the MT issuing threads has committed
+        for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], MT); }
+        mbar_init(done_bar, MT);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    // ---- the patch rows this thread stages: global offset of channel 0, or -1 for zeros ----
+    long long src_off[PPT];
+#pragma unroll
+    for (int i = 0; i < PPT; ++i) {
+        const int pp = tid + i * THREADS;
+        src_off[i] = -1;
+        if (pp < a.P) {
+            const long long g = gp0 + pp;
+            if (g >= 0 && g < a.total_pos) {
+                const long long b = g / a.Lp;
+                const int rem = (int)(g - b * a.Lp);
+                const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
+                if (yy < a.H && xx < a.W) src_off[i] = b * a.C * HW + (long long)yy * a.W + xx;
+            }
+        }
+    }
+
+    // instruction descriptors: D fp32, A and B tf32, both K-major, M = 128; N = NT, and N = 2*NT
+    // for the MMA that multiplies the hi input with the filter's hi and lo halves at once
+    const uint32_t idesc_base = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(M_TILE >> 4) << 24);
+    const uint32_t idesc_n  = idesc_base | ((uint32_t)(NT >> 3) << 17);
+    const uint32_t idesc_2n = idesc_base | ((uint32_t)((2 * NT) >> 3) << 17);
+    // leading byte offset = distance between the two 4-channel core matrices of a K step,
+    // stride byte offset = distance between groups of 8 rows (verified on a B200 against the fp64 oracle)
+    const uint32_t a_lbo = (uint32_t)a.P * 16u, a_sbo = 128u;
+    const uint32_t b_lbo = (uint32_t)(a.hl * NT) * 16u, b_sbo = 128u;
+    const uint32_t b_bytes = (uint32_t)b_floats * 4u;
+    const float* wt_cta = a.wt + (long long)ocb * a.nkb * b_floats;
+
+    // start-address offsets of the taps in units of 16 bytes (the descriptors' address unit)
+    uint32_t a_tap16[TAPS], b_tap16[TAPS];
+#pragma unroll
+    for (int tap = 0; tap < TAPS; ++tap) {
+        const int r = tap / a.taps_r, sx = tap - r * a.taps_r;
+        a_tap16[tap] = (uint32_t)((warp < MT ? warp : 0) * M_TILE + r * a.Wp + sx);
+        b_tap16[tap] = (uint32_t)(tap * (CB / 4) * a.hl * NT);
+    }
+
+    float v[PPT][CB];
+    auto prefetch = [&](int kb) {           // global -> registers, channel block kb
+        const int c0 = kb * CB;
+#pragma unroll
+        for (int i = 0; i < PPT; ++i)
+#pragma unroll
+            for (int j = 0; j < CB; ++j)
+                v[i][j] = (src_off[i] >= 0 && c0 + j < a.C) ? __ldg(a.x + src_off[i] + (long long)(c0 + j) * HW) : 0.f;
+    };
+
+    bool ok = true;
+    prefetch(0);
+    if (tid == 0) {                          // filter of block 0
+        mbar_expect_tx(&full_bar[0], b_bytes);
+        bulk_g2s(stage0 + a_floats, wt_cta, b_bytes, &full_bar[0]);
+    }
+
+    for (int kb = 0; kb < a.nkb; ++kb) {
+        const int s = kb % a.ns;
+        float* A = stage0 + (long long)s * stage_floats;
+        // registers -> shared, split into hi (+ lo); stage s was released before its filter copy was issued
+#pragma unroll
+        for (int i = 0; i < PPT; ++i) {
+            const int pp = tid + i * THREADS;
+            if (pp < a.P) {
+#pragma unroll
+                for (int q = 0; q < CB / 4; ++q) {
+                    float4 hi, lo;
+                    hi.x = to_tf32(v[i][4 * q]); hi.y = to_tf32(v[i][4 * q + 1]);
+                    hi.z = to_tf32(v[i][4 * q + 2]); hi.w = to_tf32(v[i][4 * q + 3]);
+                    *reinterpret_cast<float4*>(A + ((q * a.P + pp) << 2)) = hi;
+                    if (a.hl == 2) {
+                        lo.x = v[i][4 * q] - hi.x; lo.y = v[i][4 * q + 1] - hi.y;
+                        lo.z = v[i][4 * q + 2] - hi.z; lo.w = v[i][4 * q + 3] - hi.w;
+                        *reinterpret_cast<float4*>(A + CB * a.P + ((q * a.P + pp) << 2)) = lo;
+                    }
+                }
+            }
+        }
+        // next block: free its stage, start its filter copy, start its input loads
+        if (kb + 1 < a.nkb) {
+            const int s1 = (kb + 1) % a.ns;
+            if (tid == 0) {
+                if (kb + 1 >= a.ns && ok) ok = mbar_wait(&empty_bar[s1], (uint32_t)(((kb + 1) / a.ns - 1) & 1));
+                if (ok) {
+                    mbar_expect_tx(&full_bar[s1], b_bytes);
+                    bulk_g2s(stage0 + (long long)s1 * stage_floats + a_floats, wt_cta + (long long)(kb + 1) * b_floats, b_bytes,
+                             &full_bar[s1]);
+                } else {
+                    *abort_flag = 1;
+                }
+            }
+            prefetch(kb + 1);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores -> visible to the tensor core
+        __syncthreads();
+        if (*abort_flag) break;
+        // Lane 0 of warp mt issues the MMAs of position tile mt (each tile has its own
+        // accumulator columns, so the MT instruction streams need no order between them).
+        if (lane == 0 && warp < MT) {
+            bool landed = mbar_wait(&full_bar[s], (uint32_t)((kb / a.ns) & 1));
+            if (landed) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_base = smem_u32(A), b_base = smem_u32(A + a_floats);
+                const uint64_t a_hi0 = make_desc(a_base, a_lbo, a_sbo);
+                const uint64_t a_lo0 = make_desc(a_base + (uint32_t)(CB * a.P) * 4u, a_lbo, a_sbo);
+                const uint64_t b_hi0 = make_desc(b_base, b_lbo, b_sbo);       // rows 0..NT-1 hi, NT..2NT-1 lo
+                const uint32_t d_main = tmem + (uint32_t)(warp * 2 * NT);
+#pragma unroll
+                for (int tap = 0; tap < TAPS; ++tap) {
+                    const uint64_t a_hi = a_hi0 + a_tap16[tap], b_hi = b_hi0 + b_tap16[tap];
+                    const uint32_t acc = (kb == 0 && tap == 0) ? 0u : 1u;
+                    if (a.hl == 2) {
+                        mma_tf32(d_main, a_hi, b_hi, idesc_2n, acc);                         // main += hi*hi, small += hi*lo
+                        mma_tf32(d_main + NT, a_lo0 + a_tap16[tap], b_hi, idesc_n, 1u);      // small += lo*hi
+                    } else {
+                        mma_tf32(d_main, a_hi, b_hi, idesc_n, acc);
+                    }
+                }
+                mma_commit(&empty_bar[s]);
+                if (kb + 1 == a.nkb) mma_commit(done_bar);
+            } else {
+                *abort_flag = 1;
+            }
+        }
+    }
+
+    // ---- epilogue: tensor memory -> registers -> y (NCHW: lanes = consecutive positions) ----
+    __syncthreads();
+    bool fine = (*abort_flag == 0);
+    if (fine) fine = mbar_wait(done_bar, 0);
+    if (!fine) {
+        if (a.status) atomicCAS(a.status, 0, 1);
+    } else {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int q = warp & 3;                      // the lane quarter this warp may read
+        constexpr int CHUNKS = NT / 32;
+        for (int item = (warp >> 2); item < MT * CHUNKS; item += 2) {
+            const int mt = item / CHUNKS, chunk = item - mt * CHUNKS;
+            const long long g = g0 + mt * M_TILE + q * 32 + lane;
+            long long out_off = -1;
+            if (g < a.total_pos) {
+                const long long b = g / a.Lp;
+                const int rem = (int)(g - b * a.Lp);
+                const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
+                if (yy < a.H && xx < a.W) out_off = b * a.K * HW + (long long)yy * a.W + xx;
+            }
+            uint32_t r[32], r2[32];
+            const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * 2 * NT + chunk * 32);
+            tmem_ld32(taddr, r);
+            if (a.hl == 2) tmem_ld32(taddr + NT, r2);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (out_off >= 0) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int oc = ocb * NT + chunk * 32 + j;
+                    if (oc < a.K) {
+                        float val = __uint_as_float(r[j]);
+                        if (a.hl == 2) val += __uint_as_float(r2[j]);
+                        if (a.scale) val *= a.scale[oc];
+                        if (a.bias) val += a.bias[oc];
+                        const long long o = out_off + (long long)oc * HW;
+                        if (a.residual) val += a.residual[o];
+                        a.y[o] = a.relu ? fmaxf(val, 0.f) : val;
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+}
+
+// Filter [K][C][R][S] (or [C][R][S][K]) -> per (output block, channel block) the exact
+// shared-memory image of a stage's B part: [tap][CB/4][hl*NT][4] (rows 0..NT-1 the hi halves,
+// NT..2NT-1 the lo halves of the same channels), zero-filled past C and K.
+__global__ void prepare_weights_kernel(const float* __restrict__ w, int kcrs, float* __restrict__ wt, int C, int K, int taps,
+                                       int nt, int nkb, int n_ocb, int hl) {
+    const long long per_block = (long long)hl * taps * CB * nt;
+    const long long n = per_block * nkb * n_ocb;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        long long t = i;
+        const int e = (int)(t % 4); t /= 4;
+        const int nn = (int)(t % nt); t /= nt;
+        const int h = (int)(t % hl); t /= hl;
+        const int chunk = (int)(t % (CB / 4)); t /= (CB / 4);
+        const int tap = (int)(t % taps); t /= taps;
+        const int kb = (int)(t % nkb); t /= nkb;
+        const int ocb = (int)t;
+        const int oc = ocb * nt + nn, c = kb * CB + chunk * 4 + e;
+        float val = 0.f;
+        if (oc < K && c < C) val = kcrs ? w[((long long)oc * C + c) * taps + tap] : w[((long long)c * taps + tap) * K + oc];
+        const float hi = to_tf32(val);
+        wt[i] = (h == 0) ? hi : (val - hi);
+    }
+}
+
+}  // namespace tdc_tc
+
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+thread_local char g_tc_err[384] = "";
+int tc_fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_tc_err, sizeof g_tc_err, fmt, ap);
+    va_end(ap);
+    return code;
+}
+__device__ int g_tc_status;   // 0 = every wait of every launch so far completed
+
+int pick_nt(int K) { return K > 64 ? 128 : (K > 32 ? 64 : 32); }
+int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace
+
+extern "C" {
+
+const char* tdc_tc_last_error_string(void) { return g_tc_err; }
+
+int tdc_tc_plan_make(int C, int K, int R, int S, int mode, tdc_tc_plan* out) {
+    if (!out) return tc_fail(TDC_ERR_NULL, "out is NULL");
+    if (C <= 0 || K <= 0) return tc_fail(TDC_ERR_SHAPE, "C=%d K=%d", C, K);
+    if (R != S || (R != 1 && R != 3)) return tc_fail(TDC_ERR_UNSUPPORTED, "the tensor-core path is built for 1x1 and 3x3 filters, not %dx%d", R, S);
+    if (mode != 1 && mode != 3) return tc_fail(TDC_ERR_UNSUPPORTED, "mode %d (1 = TF32, 3 = 3xTF32)", mode);
+    out->C = C; out->K = K; out->R = R; out->S = S; out->mode = mode;
+    out->nt = pick_nt(K);
+    out->cb = tdc_tc::CB;
+    out->nkb = cdiv(C, tdc_tc::CB);
+    out->n_ocb = cdiv(K, out->nt);
+    out->hl = mode == 3 ? 2 : 1;
+    out->weights_bytes = sizeof(float) * (size_t)out->hl * R * S * tdc_tc::CB * out->nt * out->nkb * out->n_ocb;
+    return TDC_OK;
+}
+
+int tdc_tc_prepare_weights(const tdc_tc_plan* p, const float* w, int w_layout, void* wt, void* stream) {
+    if (!p || !w || !wt) return tc_fail(TDC_ERR_NULL, "plan, w and wt must be non-NULL");
+    if (w_layout != TDC_W_KCRS && w_layout != TDC_W_CRSK) return tc_fail(TDC_ERR_UNSUPPORTED, "w_layout %d", w_layout);
+    long long n = (long long)(p->weights_bytes / sizeof(float));
+    int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    tdc_tc::prepare_weights_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(w, w_layout == TDC_W_KCRS, (float*)wt, p->C, p->K,
+                                                                           p->R * p->S, p->nt, p->nkb, p->n_ocb, p->hl);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "prepare launch: %s", cudaGetErrorString(e));
+}
+
+int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y, int B, int H, int W,
+                  const tdc_epilogue* epi, int flags, void* stream) {
+    if (!p || !x || !wt || !y) return tc_fail(TDC_ERR_NULL, "plan, x, wt and y must be non-NULL");
+    if (B <= 0 || H <= 0 || W <= 0) return tc_fail(TDC_ERR_SHAPE, "B=%d H=%d W=%d", B, H, W);
+    if (flags != 0) return tc_fail(TDC_ERR_UNSUPPORTED, "flags must be 0");
+    using namespace tdc_tc;
+    Args a{};
+    a.x = x; a.wt = (const float*)wt; a.y = y;
+    if (epi) { a.scale = epi->scale; a.bias = epi->bias; a.residual = epi->residual; a.relu = epi->relu ? 1 : 0; }
+    a.B = B; a.C = p->C; a.H = H; a.W = W; a.K = p->K; a.taps_r = p->R;
+    const int pad = (p->R - 1) / 2;
+    a.Wp = W + pad;                       // one shared zero column per row when the filter has a halo
+    a.Lp = (H + pad) * a.Wp;              // and one zero row after the image
+    a.total_pos = (long long)B * a.Lp;
+    if (W > 256) return tc_fail(TDC_ERR_UNSUPPORTED, "image width %d is too large for the tensor-core path (max 256)", W);
+    a.nkb = p->nkb; a.n_ocb = p->n_ocb; a.hl = p->hl;
+    const int taps = p->R * p->S;
+    int device;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return tc_fail(TDC_ERR_NO_DEVICE, "cudaGetDevice: %s", cudaGetErrorString(e));
+    int smem_max = 0, sms = 148;
+    cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    // position tiles per CTA: as many as tensor memory holds (512 columns = MT * 2 * NT), fewer
+    // when that would leave SMs without a CTA or the stages would not fit in shared memory
+    int mt = p->nt == 128 ? 2 : 4, ns = 0;
+    size_t stage_bytes = 0;
+    for (;; mt /= 2) {
+        a.P = ((mt * M_TILE + 2 * pad * (a.Wp + 1)) + 7) / 8 * 8;
+        stage_bytes = sizeof(float) * ((size_t)a.hl * CB * a.P + (size_t)a.hl * taps * CB * p->nt);
+        ns = (128 + 3 * stage_bytes <= (size_t)smem_max) ? 3 : 2;
+        const long long ctas_mt = ((a.total_pos + (long long)mt * M_TILE - 1) / ((long long)mt * M_TILE)) * a.n_ocb;
+        const bool fits = 128 + 2 * stage_bytes <= (size_t)smem_max;
+        if (mt == 1 || (fits && ctas_mt >= sms)) { if (!fits) return tc_fail(TDC_ERR_SMEM, "two stages of %zu bytes do not fit in shared memory", stage_bytes); break; }
+    }
+    if (ns > a.nkb) ns = a.nkb > 0 ? a.nkb : 1;
+    a.ns = ns;
+    const size_t smem = 128 + ns * stage_bytes;
+    void* status_ptr = nullptr;
+    e = cudaGetSymbolAddress(&status_ptr, g_tc_status);
+    if (e != cudaSuccess) return tc_fail(TDC_ERR_CUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    a.status = (int*)status_ptr;
+    const long long tiles = (a.total_pos + (long long)mt * M_TILE - 1) / ((long long)mt * M_TILE);
+    const long long ctas = tiles * a.n_ocb;
+    if (ctas >= (1ll << 31)) return tc_fail(TDC_ERR_TILE, "grid too large");
+    const void* fn = nullptr;
+#define TDC_TC_PICK(NT_, MT_) (taps == 9 ? (const void*)&conv_tc_kernel<NT_, MT_, 9> : (const void*)&conv_tc_kernel<NT_, MT_, 1>)
+    if (p->nt == 128) fn = mt == 2 ? TDC_TC_PICK(128, 2) : TDC_TC_PICK(128, 1);
+    else if (p->nt == 64) fn = mt == 4 ? TDC_TC_PICK(64, 4) : (mt == 2 ? TDC_TC_PICK(64, 2) : TDC_TC_PICK(64, 1));
+    else fn = mt == 4 ? TDC_TC_PICK(32, 4) : (mt == 2 ? TDC_TC_PICK(32, 2) : TDC_TC_PICK(32, 1));
+#undef TDC_TC_PICK
+    e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return tc_fail(TDC_ERR_CUDA, "cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(e));
+    void* args[] = {&a};
+    e = cudaLaunchKernel(fn, dim3((unsigned)ctas), dim3(THREADS), args, smem, (cudaStream_t)stream);
+    return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "launch: %s", cudaGetErrorString(e));
+}
+
+int tdc_tc_status(int* out) {
+    if (!out) return tc_fail(TDC_ERR_NULL, "out is NULL");
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_tc_status, sizeof(int));
+    return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
+}
+
+}  // extern "C"

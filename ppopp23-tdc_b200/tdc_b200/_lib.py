@@ -35,6 +35,12 @@ class Epilogue(C.Structure):
     _fields_ = [("scale", C.c_void_p), ("bias", C.c_void_p), ("residual", C.c_void_p), ("relu", C.c_int)]
 
 
+class TcPlan(C.Structure):
+    """tdc_tc_plan: layer-shape facts of the tensor-core variant."""
+    _fields_ = [(n, C.c_int) for n in ("C", "K", "R", "S", "mode", "nt", "cb", "nkb", "n_ocb", "hl")] + \
+               [("weights_bytes", C.c_size_t)]
+
+
 class DevInfo(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("sm_count", "smem_per_cta", "regs_per_sm", "threads_per_sm")]
 
@@ -58,6 +64,11 @@ _PROTOTYPES = {
     "tdc_conv2d_epi_f32": (_i, [_p, _p, _p] + [_i] * 10 + [C.POINTER(Epilogue), C.POINTER(Tile), _p]),
     "tdc_tk_block_epi_f32": (_i, [_p] * 5 + [_i] * 12 + [C.POINTER(Epilogue), C.POINTER(Tile), _p, _sz, _p]),
     "tdc_permute_weights": (_i, [_p, _p, _i, _i, _i, _i, _p]),
+    "tdc_tc_last_error_string": (C.c_char_p, []),
+    "tdc_tc_plan_make": (_i, [_i] * 5 + [C.POINTER(TcPlan)]),
+    "tdc_tc_prepare_weights": (_i, [C.POINTER(TcPlan), _p, _i, _p, _p]),
+    "tdc_conv2d_tc": (_i, [C.POINTER(TcPlan), _p, _p, _p, _i, _i, _i, C.POINTER(Epilogue), _i, _p]),
+    "tdc_tc_status": (_i, [C.POINTER(_i)]),
     "tdc_select_tile": (_i, [_i] * 9 + [C.POINTER(DevInfo), C.POINTER(Tile)]),
     "tdc_tile_info": (_i, [_i] * 9 + [C.POINTER(Tile), C.POINTER(LaunchInfo)]),
     "tdc_tile_cost": (_i, [_i] * 9 + [C.POINTER(Tile), C.POINTER(DevInfo), C.POINTER(C.c_double),

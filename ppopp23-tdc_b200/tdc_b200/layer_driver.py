@@ -35,6 +35,8 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-cudnn", action="store_true")
     ap.add_argument("--csv", default=None)
+    ap.add_argument("--tc", type=int, default=0, choices=[0, 1, 3],
+                    help="run the tensor-core variant instead: 3 = 3xTF32 (fp32-level), 1 = plain TF32")
     a = ap.parse_args(argv)
     Cc, N, H, W = (int(v) for v in a.shape.split(","))
     B, k = a.batch, a.filter
@@ -52,7 +54,12 @@ def main(argv=None):
         e0.record(stream); fn(); e1.record(stream); e1.synchronize()
         return e0.elapsed_time(e1)
 
-    run = lambda: ops.core_conv2d(x, w, a.stride, a.pad, w_layout=W_CRSK, tile=tile, out=y)
+    if a.tc:
+        from .tc import TcConv
+        conv = TcConv(w, mode=a.tc, w_layout=W_CRSK)
+        run = lambda: conv(x, out=y)
+    else:
+        run = lambda: ops.core_conv2d(x, w, a.stride, a.pad, w_layout=W_CRSK, tile=tile, out=y)
     first = timed(run)
     for _ in range(3):
         run()

@@ -1,0 +1,54 @@
+"""Tensor-core variant of the core convolution (tcgen05, TF32 operands) — host side.
+
+`TcConv` holds what the C ABI needs per layer: the plan (tdc_tc_plan_make) and the filter
+pre-arranged for the kernel (tdc_tc_prepare_weights).  mode 3 ("3xTF32") gives fp32-level
+results; mode 1 is plain TF32.  Only "same" convolutions with 1x1 or 3x3 filters and stride 1
+are built; anything else raises.
+"""
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import TcPlan, TdcError, lib
+from .ops import _dev_f32, _epilogue, _stream
+
+
+def _check(code):
+    if code != _lib.OK:
+        raise TdcError(code, lib.tdc_tc_last_error_string().decode())
+
+
+class TcConv:
+    def __init__(self, weight, mode=3, w_layout=_lib.W_KCRS):
+        """weight: [K][C][R][S] (or [C][R][S][K] with w_layout=W_CRSK), fp32 CUDA tensor."""
+        if w_layout == _lib.W_KCRS:
+            K, Cc, R, S = weight.shape
+        else:
+            Cc, R, S, K = weight.shape
+        self.plan = TcPlan()
+        _check(lib.tdc_tc_plan_make(Cc, K, R, S, mode, C.byref(self.plan)))
+        self.C, self.K, self.R, self.mode = Cc, K, R, mode
+        self.wt = torch.empty(self.plan.weights_bytes, dtype=torch.uint8, device=weight.device)
+        with torch.cuda.device(weight.device):
+            _check(lib.tdc_tc_prepare_weights(C.byref(self.plan), _dev_f32(weight, "weight"), w_layout,
+                                              self.wt.data_ptr(), _stream()))
+
+    def __call__(self, x, scale=None, bias=None, residual=None, relu=False, out=None, flags=0):
+        B, Cc, H, W = x.shape
+        if Cc != self.C:
+            raise TdcError(_lib.ERR_SHAPE, "x has %d channels, the filter expects %d" % (Cc, self.C))
+        if out is None:
+            out = torch.empty((B, self.K, H, W), device=x.device, dtype=torch.float32)
+        e = _epilogue(scale, bias, residual, relu)
+        with torch.cuda.device(x.device):
+            _check(lib.tdc_conv2d_tc(C.byref(self.plan), _dev_f32(x, "x"), self.wt.data_ptr(), _dev_f32(out, "out"),
+                                     B, H, W, C.byref(e), flags, _stream()))
+        return out
+
+
+def status():
+    """Device status word of the tensor-core kernels (synchronises): 0 = no bounded wait ran out."""
+    s = C.c_int(-1)
+    _check(lib.tdc_tc_status(C.byref(s)))
+    return s.value
