@@ -39,7 +39,8 @@ namespace tdc_tc {
 
 constexpr int M_TILE   = 128;   // positions per CTA = MMA M
 constexpr int CB       = 8;     // channels per stage = one K step of kind::tf32
-constexpr int THREADS  = 256;
+constexpr int LOADERS  = 256;   // threads of warps 0-7, which stage the input patch
+constexpr int THREADS  = 384;   // + warps 8-11: MMA issuers (lane 0 of each), everyone drains tensor memory
 
 struct Args {
     const float* x;        // [B][C][H][W]
@@ -124,22 +125,28 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 // position tile, NT "main" columns (hi*hi) followed by NT "small" columns (hi*lo + lo*hi):
 // the small products never pass through the large running sum, whose rounding inside the
 // tensor core would otherwise swamp them, and fp32 adds main + small once in the epilogue.
+//
+// Warp roles.  Warps 0-7 (LOADERS) stage the input patch: global -> registers -> hi/lo split
+// -> shared, and one of their threads starts the filter's bulk copy; they run up to `ns`
+// stages ahead.  Lane 0 of warp 8+mt (ISSUERS) issues the MMAs of position tile mt as soon as
+// a stage's mbarrier says the patch is stored and the filter has landed, and commits to the
+// mbarrier that hands the stage back.  There is no CTA-wide barrier in the main loop.  All
+// twelve warps drain tensor memory in the epilogue.
 template <int NT, int MT, int TAPS>
 __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // carve: barriers | tmem slot | stages { A[hl][CB/4][P][4], B[tap][CB/4][hl*NT][4] }
-    uint64_t* full_bar  = reinterpret_cast<uint64_t*>(smem_raw);           // [ns] filter landed
+    uint64_t* full_bar  = reinterpret_cast<uint64_t*>(smem_raw);           // [ns] patch stored + filter landed
     uint64_t* empty_bar = full_bar + 4;                                     // [ns] MMAs of the stage done
     uint64_t* done_bar  = empty_bar + 4;                                    // all MMAs done
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
     int*      abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
     float*    stage0    = reinterpret_cast<float*>(smem_raw + 128);
 
-    constexpr int PPT = (MT * M_TILE + 2 * 260 + THREADS - 1) / THREADS;   // patch rows per thread, W <= 256
+    constexpr int PPT = (MT * M_TILE + 2 * 260 + LOADERS - 1) / LOADERS;   // patch rows per loader thread, W <= 256
     constexpr uint32_t TMEM_COLS = (uint32_t)(MT * 2 * NT) < 32u ? 32u : (uint32_t)(MT * 2 * NT);
-    constexpr int taps = TAPS;
     const int a_floats = a.hl * CB * a.P;                  // A part of a stage
-    const int b_floats = a.hl * taps * CB * NT;            // B part of a stage
+    const int b_floats = a.hl * TAPS * CB * NT;            // B part of a stage
     const int stage_floats = a_floats + b_floats;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -150,14 +157,14 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
     const long long HW = (long long)a.H * a.W;
 
     if (tid == 0) {
-        // a stage is released, and the tile is done, when each of the MT issuing threads has committed
-        for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], MT); }
+        // full: every loader thread arrives once, plus the arrive that announces the filter's bytes;
+        // empty / done: one commit per issuing thread
+        for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], LOADERS + 1); mbar_init(&empty_bar[s], MT); }
         mbar_init(done_bar, MT);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {
-        __syncwarp();
+    if (warp == 8) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -165,133 +172,113 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
-
-    // ---- the patch rows this thread stages: global offset of channel 0, or -1 for zeros ----
-    long long src_off[PPT];
-#pragma unroll
-    for (int i = 0; i < PPT; ++i) {
-        const int pp = tid + i * THREADS;
-        src_off[i] = -1;
-        if (pp < a.P) {
-            const long long g = gp0 + pp;
-            if (g >= 0 && g < a.total_pos) {
-                const long long b = g / a.Lp;
-                const int rem = (int)(g - b * a.Lp);
-                const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
-                if (yy < a.H && xx < a.W) src_off[i] = b * a.C * HW + (long long)yy * a.W + xx;
-            }
-        }
-    }
-
-    // instruction descriptors: D fp32, A and B tf32, both K-major, M = 128; N = NT, and N = 2*NT
-    // for the MMA that multiplies the hi input with the filter's hi and lo halves at once
-    const uint32_t idesc_base = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(M_TILE >> 4) << 24);
-    const uint32_t idesc_n  = idesc_base | ((uint32_t)(NT >> 3) << 17);
-    const uint32_t idesc_2n = idesc_base | ((uint32_t)((2 * NT) >> 3) << 17);
-    // leading byte offset = distance between the two 4-channel core matrices of a K step,
-    // stride byte offset = distance between groups of 8 rows (verified on a B200 against the fp64 oracle)
-    const uint32_t a_lbo = (uint32_t)a.P * 16u, a_sbo = 128u;
-    const uint32_t b_lbo = (uint32_t)(a.hl * NT) * 16u, b_sbo = 128u;
     const uint32_t b_bytes = (uint32_t)b_floats * 4u;
     const float* wt_cta = a.wt + (long long)ocb * a.nkb * b_floats;
 
-    // start-address offsets of the taps in units of 16 bytes (the descriptors' address unit)
-    uint32_t a_tap16[TAPS], b_tap16[TAPS];
-#pragma unroll
-    for (int tap = 0; tap < TAPS; ++tap) {
-        const int r = tap / a.taps_r, sx = tap - r * a.taps_r;
-        a_tap16[tap] = (uint32_t)((warp < MT ? warp : 0) * M_TILE + r * a.Wp + sx);
-        b_tap16[tap] = (uint32_t)(tap * (CB / 4) * a.hl * NT);
-    }
-
-    float v[PPT][CB];
-    auto prefetch = [&](int kb) {           // global -> registers, channel block kb
-        const int c0 = kb * CB;
-#pragma unroll
-        for (int i = 0; i < PPT; ++i)
-#pragma unroll
-            for (int j = 0; j < CB; ++j)
-                v[i][j] = (src_off[i] >= 0 && c0 + j < a.C) ? __ldg(a.x + src_off[i] + (long long)(c0 + j) * HW) : 0.f;
-    };
-
-    bool ok = true;
-    prefetch(0);
-    if (tid == 0) {                          // filter of block 0
-        mbar_expect_tx(&full_bar[0], b_bytes);
-        bulk_g2s(stage0 + a_floats, wt_cta, b_bytes, &full_bar[0]);
-    }
-
-    for (int kb = 0; kb < a.nkb; ++kb) {
-        const int s = kb % a.ns;
-        float* A = stage0 + (long long)s * stage_floats;
-        // registers -> shared, split into hi (+ lo); stage s was released before its filter copy was issued
+    if (warp < 8) {
+        // ================= loaders =================
+        long long src_off[PPT];        // global offset of channel 0 of each owned patch row, -1 = zeros
 #pragma unroll
         for (int i = 0; i < PPT; ++i) {
-            const int pp = tid + i * THREADS;
+            const int pp = tid + i * LOADERS;
+            src_off[i] = -1;
             if (pp < a.P) {
-#pragma unroll
-                for (int q = 0; q < CB / 4; ++q) {
-                    float4 hi, lo;
-                    hi.x = to_tf32(v[i][4 * q]); hi.y = to_tf32(v[i][4 * q + 1]);
-                    hi.z = to_tf32(v[i][4 * q + 2]); hi.w = to_tf32(v[i][4 * q + 3]);
-                    *reinterpret_cast<float4*>(A + ((q * a.P + pp) << 2)) = hi;
-                    if (a.hl == 2) {
-                        lo.x = v[i][4 * q] - hi.x; lo.y = v[i][4 * q + 1] - hi.y;
-                        lo.z = v[i][4 * q + 2] - hi.z; lo.w = v[i][4 * q + 3] - hi.w;
-                        *reinterpret_cast<float4*>(A + CB * a.P + ((q * a.P + pp) << 2)) = lo;
-                    }
+                const long long g = gp0 + pp;
+                if (g >= 0 && g < a.total_pos) {
+                    const long long b = g / a.Lp;
+                    const int rem = (int)(g - b * a.Lp);
+                    const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
+                    if (yy < a.H && xx < a.W) src_off[i] = b * a.C * HW + (long long)yy * a.W + xx;
                 }
             }
         }
-        // next block: free its stage, start its filter copy, start its input loads
-        if (kb + 1 < a.nkb) {
-            const int s1 = (kb + 1) % a.ns;
-            if (tid == 0) {
-                if (kb + 1 >= a.ns && ok) ok = mbar_wait(&empty_bar[s1], (uint32_t)(((kb + 1) / a.ns - 1) & 1));
-                if (ok) {
-                    mbar_expect_tx(&full_bar[s1], b_bytes);
-                    bulk_g2s(stage0 + (long long)s1 * stage_floats + a_floats, wt_cta + (long long)(kb + 1) * b_floats, b_bytes,
-                             &full_bar[s1]);
+        float v[PPT][CB];
+        auto prefetch = [&](int kb) {           // global -> registers, channel block kb
+            const int c0 = kb * CB;
+#pragma unroll
+            for (int i = 0; i < PPT; ++i)
+#pragma unroll
+                for (int j = 0; j < CB; ++j)
+                    v[i][j] = (src_off[i] >= 0 && c0 + j < a.C) ? __ldg(a.x + src_off[i] + (long long)(c0 + j) * HW) : 0.f;
+        };
+        prefetch(0);
+        for (int kb = 0; kb < a.nkb; ++kb) {
+            const int s = kb % a.ns;
+            float* A = stage0 + (long long)s * stage_floats;
+            if (kb >= a.ns && !mbar_wait(&empty_bar[s], (uint32_t)((kb / a.ns - 1) & 1))) { *abort_flag = 1; break; }
+            if (tid == 0) {                      // the filter of this block: one bulk copy into the stage
+                mbar_expect_tx(&full_bar[s], b_bytes);
+                bulk_g2s(A + a_floats, wt_cta + (long long)kb * b_floats, b_bytes, &full_bar[s]);
+            }
+#pragma unroll
+            for (int i = 0; i < PPT; ++i) {
+                const int pp = tid + i * LOADERS;
+                if (pp < a.P) {
+#pragma unroll
+                    for (int q = 0; q < CB / 4; ++q) {
+                        float4 hi, lo;
+                        hi.x = to_tf32(v[i][4 * q]); hi.y = to_tf32(v[i][4 * q + 1]);
+                        hi.z = to_tf32(v[i][4 * q + 2]); hi.w = to_tf32(v[i][4 * q + 3]);
+                        *reinterpret_cast<float4*>(A + ((q * a.P + pp) << 2)) = hi;
+                        if (a.hl == 2) {
+                            lo.x = v[i][4 * q] - hi.x; lo.y = v[i][4 * q + 1] - hi.y;
+                            lo.z = v[i][4 * q + 2] - hi.z; lo.w = v[i][4 * q + 3] - hi.w;
+                            *reinterpret_cast<float4*>(A + CB * a.P + ((q * a.P + pp) << 2)) = lo;
+                        }
+                    }
+                }
+            }
+            if (kb + 1 < a.nkb) prefetch(kb + 1);     // in flight while the next stage is awaited
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[s])) : "memory");
+        }
+    } else if (lane == 0 && warp - 8 < MT) {
+        // ================= MMA issuers: one thread per position tile =================
+        const int mt = warp - 8;
+        // instruction descriptors: D fp32, A and B tf32, both K-major, M = 128; N = NT, and N = 2*NT for
+        // the MMA that multiplies the hi input with the filter's hi and lo halves at once
+        const uint32_t idesc_base = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(M_TILE >> 4) << 24);
+        const uint32_t idesc_n  = idesc_base | ((uint32_t)(NT >> 3) << 17);
+        const uint32_t idesc_2n = idesc_base | ((uint32_t)((2 * NT) >> 3) << 17);
+        // leading byte offset = distance between the two 4-channel core matrices of a K step,
+        // stride byte offset = distance between groups of 8 rows (verified on a B200 against the fp64 oracle)
+        const uint32_t a_lbo = (uint32_t)a.P * 16u, a_sbo = 128u;
+        const uint32_t b_lbo = (uint32_t)(a.hl * NT) * 16u, b_sbo = 128u;
+        uint32_t a_tap16[TAPS], b_tap16[TAPS];     // start offsets of the taps in 16-byte units
+#pragma unroll
+        for (int tap = 0; tap < TAPS; ++tap) {
+            const int r = tap / a.taps_r, sx = tap - r * a.taps_r;
+            a_tap16[tap] = (uint32_t)(mt * M_TILE + r * a.Wp + sx);
+            b_tap16[tap] = (uint32_t)(tap * (CB / 4) * a.hl * NT);
+        }
+        const uint32_t d_main = tmem + (uint32_t)(mt * 2 * NT);
+        for (int kb = 0; kb < a.nkb; ++kb) {
+            const int s = kb % a.ns;
+            if (!mbar_wait(&full_bar[s], (uint32_t)((kb / a.ns) & 1))) { *abort_flag = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float* A = stage0 + (long long)s * stage_floats;
+            const uint32_t a_base = smem_u32(A), b_base = smem_u32(A + a_floats);
+            const uint64_t a_hi0 = make_desc(a_base, a_lbo, a_sbo);
+            const uint64_t a_lo0 = make_desc(a_base + (uint32_t)(CB * a.P) * 4u, a_lbo, a_sbo);
+            const uint64_t b_hi0 = make_desc(b_base, b_lbo, b_sbo);       // rows 0..NT-1 hi, NT..2NT-1 lo
+#pragma unroll
+            for (int tap = 0; tap < TAPS; ++tap) {
+                const uint64_t a_hi = a_hi0 + a_tap16[tap], b_hi = b_hi0 + b_tap16[tap];
+                const uint32_t acc = (kb == 0 && tap == 0) ? 0u : 1u;
+                if (a.hl == 2) {
+                    mma_tf32(d_main, a_hi, b_hi, idesc_2n, acc);                         // main += hi*hi, small += hi*lo
+                    mma_tf32(d_main + NT, a_lo0 + a_tap16[tap], b_hi, idesc_n, 1u);      // small += lo*hi
                 } else {
-                    *abort_flag = 1;
+                    mma_tf32(d_main, a_hi, b_hi, idesc_n, acc);
                 }
             }
-            prefetch(kb + 1);
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores -> visible to the tensor core
-        __syncthreads();
-        if (*abort_flag) break;
-        // Lane 0 of warp mt issues the MMAs of position tile mt (each tile has its own
-        // accumulator columns, so the MT instruction streams need no order between them).
-        if (lane == 0 && warp < MT) {
-            bool landed = mbar_wait(&full_bar[s], (uint32_t)((kb / a.ns) & 1));
-            if (landed) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_base = smem_u32(A), b_base = smem_u32(A + a_floats);
-                const uint64_t a_hi0 = make_desc(a_base, a_lbo, a_sbo);
-                const uint64_t a_lo0 = make_desc(a_base + (uint32_t)(CB * a.P) * 4u, a_lbo, a_sbo);
-                const uint64_t b_hi0 = make_desc(b_base, b_lbo, b_sbo);       // rows 0..NT-1 hi, NT..2NT-1 lo
-                const uint32_t d_main = tmem + (uint32_t)(warp * 2 * NT);
-#pragma unroll
-                for (int tap = 0; tap < TAPS; ++tap) {
-                    const uint64_t a_hi = a_hi0 + a_tap16[tap], b_hi = b_hi0 + b_tap16[tap];
-                    const uint32_t acc = (kb == 0 && tap == 0) ? 0u : 1u;
-                    if (a.hl == 2) {
-                        mma_tf32(d_main, a_hi, b_hi, idesc_2n, acc);                         // main += hi*hi, small += hi*lo
-                        mma_tf32(d_main + NT, a_lo0 + a_tap16[tap], b_hi, idesc_n, 1u);      // small += lo*hi
-                    } else {
-                        mma_tf32(d_main, a_hi, b_hi, idesc_n, acc);
-                    }
-                }
-                mma_commit(&empty_bar[s]);
-                if (kb + 1 == a.nkb) mma_commit(done_bar);
-            } else {
-                *abort_flag = 1;
-            }
+            mma_commit(&empty_bar[s]);
+            if (kb + 1 == a.nkb) mma_commit(done_bar);
         }
     }
 
     // ---- epilogue: tensor memory -> registers -> y (NCHW: lanes = consecutive positions) ----
+    __syncwarp();        // the issuing lane rejoins its warp before the CTA-wide barrier
     __syncthreads();
     bool fine = (*abort_flag == 0);
     if (fine) fine = mbar_wait(done_bar, 0);
@@ -301,7 +288,7 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int q = warp & 3;                      // the lane quarter this warp may read
         constexpr int CHUNKS = NT / 32;
-        for (int item = (warp >> 2); item < MT * CHUNKS; item += 2) {
+        for (int item = (warp >> 2); item < MT * CHUNKS; item += 3) {
             const int mt = item / CHUNKS, chunk = item - mt * CHUNKS;
             const long long g = g0 + mt * M_TILE + q * 32 + lane;
             long long out_off = -1;
@@ -335,7 +322,7 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
 }
 
 // Filter [K][C][R][S] (or [C][R][S][K]) -> per (output block, channel block) the exact
