@@ -286,6 +286,8 @@ TDC_API int  tdc_conv_create(tdc_conv** out, int b, int c, int h, int w, int n, 
                      int r, int s, int stride, const float* host_w_kcrs,
                      const float* host_bias /* NULL = no bias */);
 TDC_API int  tdc_conv_set_tile(tdc_conv* l, const tdc_tile* tile);
+/* 0: fp32 FMA kernels (default); 3 / 1: tensor cores, 3xTF32 / TF32 (stride-1 1x1 and 3x3 "same" layers). */
+TDC_API int  tdc_conv_set_precision(tdc_conv* l, int mode);
 TDC_API int  tdc_conv_forward(tdc_conv* l, const float* dev_in, float** dev_out, void* stream);
 TDC_API int  tdc_conv_forward_host(tdc_conv* l, const float* host_in, float* host_out);
 TDC_API void tdc_conv_destroy(tdc_conv* l);

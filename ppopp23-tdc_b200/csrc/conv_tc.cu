@@ -56,6 +56,9 @@ struct Args {
     int n_ocb;             // output-channel blocks
     int hl;                // 2: hi/lo split (3xTF32), 1: plain TF32
     int ns;                // stages
+    int nmain;             // 1 or 2 main accumulators per position tile (2: channel blocks alternate)
+    int tile_cols;         // tensor-memory columns per position tile: 2*NT, or 4*NT with two mains
+    int tmem_cols;         // allocation (power of two >= 32)
     long long total_pos;   // B * Lp
     int* status;           // device status word: 0 ok, else first failure code
 };
@@ -125,6 +128,10 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 // position tile, NT "main" columns (hi*hi) followed by NT "small" columns (hi*lo + lo*hi):
 // the small products never pass through the large running sum, whose rounding inside the
 // tensor core would otherwise swamp them, and fp32 adds main + small once in the epilogue.
+// The tensor core rounds its running sum at every accumulation, so for long reductions
+// (many channel blocks x taps) the host asks for TWO main accumulators per tile, fed by even
+// and odd channel blocks ([main0 | small | main1] in tensor memory): each running sum is half
+// as long, and the epilogue adds them in fp32.
 //
 // Warp roles.  Warps 0-7 (LOADERS) stage the input patch: global -> registers -> hi/lo split
 // -> shared, and one of their threads starts the filter's bulk copy; they run up to `ns`
@@ -144,7 +151,7 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
     float*    stage0    = reinterpret_cast<float*>(smem_raw + 128);
 
     constexpr int PPT = (MT * M_TILE + 2 * 260 + LOADERS - 1) / LOADERS;   // patch rows per loader thread, W <= 256
-    constexpr uint32_t TMEM_COLS = (uint32_t)(MT * 2 * NT) < 32u ? 32u : (uint32_t)(MT * 2 * NT);
+    const uint32_t TMEM_COLS = (uint32_t)a.tmem_cols;
     const int a_floats = a.hl * CB * a.P;                  // A part of a stage
     const int b_floats = a.hl * TAPS * CB * NT;            // B part of a stage
     const int stage_floats = a_floats + b_floats;
@@ -251,7 +258,7 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
             a_tap16[tap] = (uint32_t)(mt * M_TILE + r * a.Wp + sx);
             b_tap16[tap] = (uint32_t)(tap * (CB / 4) * a.hl * NT);
         }
-        const uint32_t d_main = tmem + (uint32_t)(mt * 2 * NT);
+        const uint32_t d_main = tmem + (uint32_t)(mt * a.tile_cols);
         for (int kb = 0; kb < a.nkb; ++kb) {
             const int s = kb % a.ns;
             if (!mbar_wait(&full_bar[s], (uint32_t)((kb / a.ns) & 1))) { *abort_flag = 1; break; }
@@ -265,7 +272,15 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
             for (int tap = 0; tap < TAPS; ++tap) {
                 const uint64_t a_hi = a_hi0 + a_tap16[tap], b_hi = b_hi0 + b_tap16[tap];
                 const uint32_t acc = (kb == 0 && tap == 0) ? 0u : 1u;
-                if (a.hl == 2) {
+                if (a.nmain == 2 && (kb & 1)) {
+                    // odd channel block: second main accumulator; the lo rows of the filter start NT rows in
+                    const uint32_t acc1 = (kb == 1 && tap == 0) ? 0u : 1u;
+                    mma_tf32(d_main + 2 * NT, a_hi, b_hi, idesc_n, acc1);                    // main1 += hi*hi
+                    if (a.hl == 2) {
+                        mma_tf32(d_main + NT, a_hi, b_hi + (uint64_t)NT, idesc_n, 1u);   // small += hi*lo (lo rows start NT rows = NT x 16 bytes in)
+                        mma_tf32(d_main + NT, a_lo0 + a_tap16[tap], b_hi, idesc_n, 1u);      // small += lo*hi
+                    }
+                } else if (a.hl == 2) {
                     mma_tf32(d_main, a_hi, b_hi, idesc_2n, acc);                         // main += hi*hi, small += hi*lo
                     mma_tf32(d_main + NT, a_lo0 + a_tap16[tap], b_hi, idesc_n, 1u);      // small += lo*hi
                 } else {
@@ -299,10 +314,22 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
                 if (yy < a.H && xx < a.W) out_off = b * a.K * HW + (long long)yy * a.W + xx;
             }
             uint32_t r[32], r2[32];
-            const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * 2 * NT + chunk * 32);
+            const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * a.tile_cols + chunk * 32);
             tmem_ld32(taddr, r);
             if (a.hl == 2) tmem_ld32(taddr + NT, r2);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (a.nmain == 2 && a.nkb > 1) {          // second main accumulator (odd channel blocks)
+                if (a.hl == 2) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+                }
+                tmem_ld32(taddr + 2 * NT, r2);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r2[j] = 0u;
+            }
             if (out_off >= 0) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
@@ -424,7 +451,10 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     // position tiles per CTA: as many as tensor memory holds (512 columns = MT * 2 * NT), fewer
     // when that would leave SMs without a CTA or the stages would not fit in shared memory
-    int mt = p->nt == 128 ? 2 : 4, ns = 0;
+    // long reductions get two main accumulators per tile (4*NT columns per tile instead of 2*NT)
+    a.nmain = (a.hl == 2 && (long long)p->nkb * taps > 320) ? 2 : 1;
+    a.tile_cols = (a.nmain == 2 ? 4 : 2) * p->nt;
+    int mt = 512 / a.tile_cols > 4 ? 4 : 512 / a.tile_cols, ns = 0;
     size_t stage_bytes = 0;
     for (;; mt /= 2) {
         a.P = ((mt * M_TILE + 2 * pad * (a.Wp + 1)) + 7) / 8 * 8;
@@ -436,6 +466,8 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     }
     if (ns > a.nkb) ns = a.nkb > 0 ? a.nkb : 1;
     a.ns = ns;
+    a.tmem_cols = 32;
+    while (a.tmem_cols < mt * a.tile_cols) a.tmem_cols *= 2;
     const size_t smem = 128 + ns * stage_bytes;
     void* status_ptr = nullptr;
     e = cudaGetSymbolAddress(&status_ptr, g_tc_status);

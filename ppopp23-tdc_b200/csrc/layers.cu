@@ -14,6 +14,10 @@ struct tdc_conv {
     float *kernel = nullptr, *bias = nullptr, *output = nullptr, *staging_in = nullptr;
     bool has_tile = false;
     tdc_tile tile{};
+    int tc_mode = 0;            // 0: fp32 kernels; 1 / 3: tensor cores (TF32 / 3xTF32)
+    tdc_tc_plan plan{};
+    void* tc_weights = nullptr;
+    float* kcrs = nullptr;      // the filter as given, kept for tdc_conv_set_precision
 };
 
 struct tdc_tkconv {
@@ -50,7 +54,26 @@ extern "C" {
 void tdc_conv_destroy(tdc_conv* l) {
     if (!l) return;
     cudaFree(l->kernel); cudaFree(l->bias); cudaFree(l->output); cudaFree(l->staging_in);
+    cudaFree(l->tc_weights); cudaFree(l->kcrs);
     delete l;
+}
+
+int tdc_conv_set_precision(tdc_conv* l, int mode) {
+    if (!l) return TDC_ERR_NULL;
+    if (mode == 0) { l->tc_mode = 0; return TDC_OK; }
+    if (l->stride != 1 || l->r != l->s || l->pad != (l->r - 1) / 2) return TDC_ERR_UNSUPPORTED;
+    tdc_tc_plan p;
+    int rc = tdc_tc_plan_make(l->c, l->n, l->r, l->s, mode, &p);
+    if (rc) return rc;
+    void* wt = nullptr;
+    cudaError_t e = cudaMalloc(&wt, p.weights_bytes);
+    if (e != cudaSuccess) return cuda_fail("cudaMalloc", e);
+    rc = tdc_tc_prepare_weights(&p, l->kcrs, TDC_W_KCRS, wt, nullptr);
+    e = cudaDeviceSynchronize();
+    if (rc || e != cudaSuccess) { cudaFree(wt); return rc ? rc : cuda_fail("prepare", e); }
+    cudaFree(l->tc_weights);
+    l->tc_weights = wt; l->plan = p; l->tc_mode = mode;
+    return TDC_OK;
 }
 
 int tdc_conv_create(tdc_conv** out, int b, int c, int h, int w, int n, int pad, int r, int s, int stride,
@@ -74,7 +97,7 @@ int tdc_conv_create(tdc_conv** out, int b, int c, int h, int w, int n, int pad, 
     if (e != cudaSuccess) { cudaFree(kcrs); tdc_conv_destroy(l); return cuda_fail("cudaMalloc", e); }
     rc = tdc_permute_weights(kcrs, l->kernel, n, c, r, s, nullptr);
     e = cudaDeviceSynchronize();
-    cudaFree(kcrs);
+    l->kcrs = kcrs;
     if (rc || e != cudaSuccess) { tdc_conv_destroy(l); return rc ? rc : cuda_fail("permute", e); }
     if (host_bias && (rc = upload(&l->bias, host_bias, n, 0.f))) { tdc_conv_destroy(l); return rc; }
     e = cudaMalloc((void**)&l->output, (size_t)b * n * l->ho * l->wo * sizeof(float));
@@ -92,8 +115,14 @@ int tdc_conv_set_tile(tdc_conv* l, const tdc_tile* tile) {
 
 int tdc_conv_forward(tdc_conv* l, const float* dev_in, float** dev_out, void* stream) {
     if (!l || !dev_in || !dev_out) return TDC_ERR_NULL;
-    int rc = tdc_conv2d_f32(dev_in, l->kernel, l->bias, l->output, l->b, l->c, l->h, l->w, l->n, l->r, l->s, l->pad,
+    int rc;
+    if (l->tc_mode) {
+        tdc_epilogue e{nullptr, l->bias, nullptr, 0};
+        rc = tdc_conv2d_tc(&l->plan, dev_in, l->tc_weights, l->output, l->b, l->h, l->w, &e, 0, stream);
+    } else {
+        rc = tdc_conv2d_f32(dev_in, l->kernel, l->bias, l->output, l->b, l->c, l->h, l->w, l->n, l->r, l->s, l->pad,
                             l->stride, TDC_W_CRSK, TDC_EPI_NONE, l->has_tile ? &l->tile : nullptr, stream);
+    }
     if (rc) return rc;
     *dev_out = l->output;
     return TDC_OK;

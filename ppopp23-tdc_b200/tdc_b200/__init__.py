@@ -11,10 +11,11 @@ from .ops import (conv2d, conv2d_epi, tk_block_epi, core_conv2d, out_hw, permute
                   tk_block, tk_block_workspace_bytes)
 from .tiles import best_tile, load_tables, table_tile
 from .resnet import HalfRanks, TKBasicBlock, TKResNet, fill_deterministic, tkc_resnet18
+from .tc import TcConv
 from .tkconv import TKConv2dC_B200
 
 __all__ = [
-    "B200", "DevInfo", "EPI_NONE", "EPI_RELU", "LIB_PATH", "LaunchInfo", "TKConv2dC_B200", "TdcError", "Tile",
+    "B200", "DevInfo", "EPI_NONE", "EPI_RELU", "LIB_PATH", "LaunchInfo", "TKConv2dC_B200", "TcConv", "TdcError", "Tile",
     "W_CRSK", "W_KCRS", "best_tile", "conv2d", "conv2d_epi", "tk_block_epi", "HalfRanks", "TKBasicBlock", "TKResNet",
     "fill_deterministic", "tkc_resnet18", "core_conv2d", "lib", "out_hw", "permute_weights", "query_device",
     "select_tile", "table_tile", "load_tables", "tile_cost", "tile_info", "tk_block", "tk_block_workspace_bytes",

@@ -78,6 +78,7 @@ _PROTOTYPES = {
     "tdc_tk_block_f32_static": (_i, [_p] * 6 + [_i] * 13 + [C.POINTER(Tile), _p]),
     "tdc_conv_create": (_i, [C.POINTER(_p)] + [_i] * 9 + [_p, _p]),
     "tdc_conv_set_tile": (_i, [_p, C.POINTER(Tile)]),
+    "tdc_conv_set_precision": (_i, [_p, _i]),
     "tdc_conv_forward": (_i, [_p, _p, C.POINTER(_p), _p]),
     "tdc_conv_forward_host": (_i, [_p, _p, _p]),
     "tdc_conv_destroy": (None, [_p]),

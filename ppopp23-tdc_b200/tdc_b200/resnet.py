@@ -70,20 +70,33 @@ def _fold_bn_now(bn):
     return scale.float().contiguous(), (b - mean * scale).float().contiguous()
 
 
-def _tk_or_dense(conv, x, scale, shift, residual, relu):
-    """One conv + folded BN (+ residual) (+ ReLU) in the conv's own launch chain."""
-    if isinstance(conv, TKConv2dC_B200):
-        B, _, H, W = x.shape
-        if conv.bias is not None:
-            shift = shift + conv.bias.detach() * scale
-        tile = tiles.table_tile(B, conv.in_rank, H, W, conv.out_rank, conv.kernel_size[0], conv.kernel_size[1],
-                                conv.padding[0], conv.stride[0])
-        return ops.tk_block_epi(x, conv.first_kernel.detach(), conv._core_channel_last(), conv.last_kernel.detach(),
-                                scale, shift, residual, relu, conv.stride, conv.padding, core_layout=W_CRSK,
-                                workspace=conv._ws(x, shared=True), core_tile=tile)
+def _one_conv(x, w_kcrs, w_crsk, scale, shift, residual, relu, stride, padding, precision):
+    """One convolution with its epilogue on the kernel that suits it: tensor cores (3xTF32) for
+    stride-1 1x1 / 3x3 layers with enough work to fill the GPU when `precision` allows, the fp32
+    kernel with a table tile otherwise."""
+    from . import tc
+    B, Cc, H, W = x.shape
+    K, _, R, S = w_kcrs.shape
+    if precision != "fp32" and tc.supported(R, S, stride, padding, W) and \
+            (precision != "auto" or tc.worthwhile(B, Cc, H, W, K, R)):
+        return tc.cached(w_kcrs, 1 if precision == "tf32" else 3)(x, scale, shift, residual, relu)
+    tile = tiles.table_tile(B, Cc, H, W, K, R, S, padding, stride)
+    if w_crsk is not None:
+        return ops.conv2d_epi(x, w_crsk, scale, shift, residual, relu, stride, padding, w_layout=W_CRSK, tile=tile)
+    return ops.conv2d_epi(x, w_kcrs, scale, shift, residual, relu, stride, padding, tile=tile)
+
+
+def _tk_or_dense(conv, x, scale, shift, residual, relu, precision="fp32"):
+    """One conv module + folded BN (+ residual) (+ ReLU): a Tucker conv as its three launches with
+    the epilogue on the last, a dense conv as one."""
     if conv.bias is not None:
         shift = shift + conv.bias.detach() * scale
-    return ops.conv2d_epi(x, conv.weight.detach(), scale, shift, residual, relu, conv.stride, conv.padding)
+    if isinstance(conv, TKConv2dC_B200):
+        z1 = _one_conv(x, conv.first_kernel.detach(), None, None, None, None, False, 1, 0, precision)
+        z2 = _one_conv(z1, conv.core_kernel.detach(), conv._core_channel_last(), None, None, None, False,
+                       conv.stride[0], conv.padding[0], precision)
+        return _one_conv(z2, conv.last_kernel.detach(), None, scale, shift, residual, relu, 1, 0, precision)
+    return _one_conv(x, conv.weight.detach(), None, scale, shift, residual, relu, conv.stride[0], conv.padding[0], precision)
 
 
 class TKBasicBlock(nn.Module):
@@ -113,18 +126,19 @@ class TKBasicBlock(nn.Module):
             raise TdcError(ERR_UNSUPPORTED, "training-mode BatchNorm is not built; call .eval()")
         s1, b1 = _fold_bn(self.bn1)
         s2, b2 = _fold_bn(self.bn2)
-        out = _tk_or_dense(self.conv1, x, s1, b1, None, True)
+        prec = getattr(self, "precision", "fp32")
+        out = _tk_or_dense(self.conv1, x, s1, b1, None, True, prec)
         identity = x
         if self.downsample is not None:
             sd, bd = _fold_bn(self.downsample[1])
-            identity = _tk_or_dense(self.downsample[0], x, sd, bd, None, False)
-        return _tk_or_dense(self.conv2, out, s2, b2, identity, True)
+            identity = _tk_or_dense(self.downsample[0], x, sd, bd, None, False, prec)
+        return _tk_or_dense(self.conv2, out, s2, b2, identity, True, prec)
 
 
 class TKResNet(nn.Module):
     """inference/resnet_inet_tt.py:287-394 (TTResNet) for basic blocks."""
 
-    def __init__(self, layers=(2, 2, 2, 2), num_classes=1000, hp_dict=None):
+    def __init__(self, layers=(2, 2, 2, 2), num_classes=1000, hp_dict=None, precision="fp32"):
         super().__init__()
         hp_dict = hp_dict if hp_dict is not None else HalfRanks(layers)
         self.inplanes = 64
@@ -144,6 +158,19 @@ class TKResNet(nn.Module):
             elif isinstance(m, nn.BatchNorm2d):
                 nn.init.constant_(m.weight, 1)
                 nn.init.constant_(m.bias, 0)
+        self.set_precision(precision)
+
+    def set_precision(self, precision):
+        """"fp32" (default): every conv on the fp32 FMA kernels; "auto": large layers on tensor cores
+        with split operands (fp32-level results), small ones on the fp32 kernels; "tf32x3" / "tf32":
+        every stride-1 1x1 / 3x3 conv on tensor cores."""
+        if precision not in ("fp32", "auto", "tf32x3", "tf32"):
+            raise ValueError("precision %r" % (precision,))
+        self.precision = precision
+        for m in self.modules():
+            if isinstance(m, TKBasicBlock):
+                m.precision = precision
+        return self
 
     def _make_layer(self, planes, blocks, stride, stage, hp_dict):
         downsample = None
@@ -163,16 +190,16 @@ class TKResNet(nn.Module):
             raise TdcError(ERR_UNSUPPORTED, "TKResNet runs on CUDA tensors only")
         x = x.contiguous().float()
         s, b = _fold_bn(self.bn1)
-        x = _tk_or_dense(self.conv1, x, s, b, None, True)
+        x = _tk_or_dense(self.conv1, x, s, b, None, True, self.precision)
         x = self.maxpool(x)
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         x = torch.flatten(self.avgpool(x), 1)
         return self.fc(x)
 
 
-def tkc_resnet18(hp_dict=None, num_classes=1000):
+def tkc_resnet18(hp_dict=None, num_classes=1000, precision="fp32"):
     """inference/resnet_inet_tt.py:483-496 without the checkpoint load."""
-    return TKResNet((2, 2, 2, 2), num_classes, hp_dict)
+    return TKResNet((2, 2, 2, 2), num_classes, hp_dict, precision)
 
 
 def fill_deterministic(module, seed=0):

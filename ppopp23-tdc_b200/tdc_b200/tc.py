@@ -47,6 +47,32 @@ class TcConv:
         return out
 
 
+def supported(R, S, stride, padding, W):
+    """True when the tensor-core variant is built for this convolution."""
+    return R == S and R in (1, 3) and stride == 1 and padding == (R - 1) // 2 and W <= 256
+
+
+def worthwhile(B, C, H, W, K, R):
+    """The tensor-core kernel works on tiles of 128 positions x up to 128 channels; below about
+    half a GFLOP there are too few tiles to fill 148 SMs and the fp32 kernel with its channel
+    slices and clusters is the faster one (batch-1 layers)."""
+    return 2.0 * B * H * W * C * K * R * R >= 0.5e9
+
+
+_cache = {}
+
+
+def cached(weight, mode, w_layout=_lib.W_KCRS):
+    """TcConv for a weight tensor, rebuilt when the tensor changes (keyed on storage and version)."""
+    key = (weight.data_ptr(), weight._version, tuple(weight.shape), mode, w_layout)
+    hit = _cache.get(key)
+    if hit is None:
+        if len(_cache) > 512:
+            _cache.clear()
+        hit = _cache[key] = TcConv(weight.detach(), mode, w_layout)
+    return hit
+
+
 def status():
     """Device status word of the tensor-core kernels (synchronises): 0 = no bounded wait ran out."""
     s = C.c_int(-1)

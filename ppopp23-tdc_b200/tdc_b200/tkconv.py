@@ -23,6 +23,12 @@ _SHARED_WS = {}     # device -> uint8 tensor
 
 
 class TKConv2dC_B200(nn.Module):
+    # "fp32": the fp32 FMA kernels (bit-reproducible, summation order documented);
+    # "tf32x3": tensor cores with split operands, fp32-level results (1e-5 bar);
+    # "tf32": tensor cores, plain TF32 (5e-3 bar);
+    # "auto": tf32x3 where the layer is large enough to fill the GPU, fp32 otherwise.
+    precision = "fp32"
+
     def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1,
                  groups: int = 1, bias: bool = True, padding_mode: str = 'zeros', hp_dict: Optional = None,
                  name: str = None, dense_w: Tensor = None, dense_b: Tensor = None):
@@ -102,8 +108,26 @@ class TKConv2dC_B200(nn.Module):
             ws = self._workspace = torch.empty(need, device=x.device, dtype=torch.uint8)
         return ws
 
+    def _use_tc(self, x):
+        from . import tc
+        if self.precision == "fp32":
+            return 0
+        R, S = self.kernel_size
+        B, _, H, W = x.shape
+        if not tc.supported(R, S, self.stride[0], self.padding[0], W) or self.stride[0] != self.stride[1]:
+            return 0
+        if self.precision == "auto":
+            return 3 if tc.worthwhile(B, self.in_rank, H, W, self.out_rank, R) else 0
+        return 3 if self.precision == "tf32x3" else 1
+
     def forward(self, x):
         x = self._check(x)
+        mode = self._use_tc(x)
+        if mode:
+            from . import tc
+            z1 = tc.cached(self.first_kernel, mode)(x)
+            z2 = tc.cached(self.core_kernel, mode)(z1)
+            return tc.cached(self.last_kernel, mode)(z2, bias=None if self.bias is None else self.bias.detach())
         B, _, H, W = x.shape
         tile = tiles.table_tile(B, self.in_rank, H, W, self.out_rank, self.kernel_size[0], self.kernel_size[1],
                                 self.padding[0], self.stride[0])     # measured table first, model otherwise

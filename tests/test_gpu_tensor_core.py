@@ -1,0 +1,105 @@
+"""The tensor-core variant (tcgen05, TF32 operands) against the fp64 arbiter, through the C ABI.
+mode 3 (split operands, "3xTF32") is held to the fp32 bar of 1e-5; mode 1 (plain TF32) to 5e-3."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from helpers import FP32_TOL, SWEEP, draw_core, rel_err
+
+TF32_TOL = 5e-3
+
+
+@pytest.fixture(scope="module")
+def T(built):
+    import tdc_b200
+    return tdc_b200
+
+
+def test_plan_is_made_on_the_host(T):
+    from tdc_b200 import _lib
+    p = _lib.TcPlan()
+    assert T.lib.tdc_tc_plan_make(64, 64, 3, 3, 3, C.byref(p)) == 0
+    assert (p.nt, p.cb, p.nkb, p.n_ocb, p.hl) == (64, 8, 8, 1, 2) and p.weights_bytes == 4 * 2 * 9 * 8 * 64 * 8
+    assert T.lib.tdc_tc_plan_make(20, 200, 1, 1, 1, C.byref(p)) == 0
+    assert (p.nt, p.nkb, p.n_ocb, p.hl) == (128, 3, 2, 1)
+    assert T.lib.tdc_tc_plan_make(64, 64, 5, 5, 3, C.byref(p)) == _lib.ERR_UNSUPPORTED
+    assert T.lib.tdc_tc_plan_make(64, 64, 3, 3, 2, C.byref(p)) == _lib.ERR_UNSUPPORTED
+    assert T.lib.tdc_tc_plan_make(0, 64, 3, 3, 3, C.byref(p)) == _lib.ERR_SHAPE
+    assert b"mode" in T.lib.tdc_tc_last_error_string() or b"C=" in T.lib.tdc_tc_last_error_string()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,Cc,K,H,W,R", [(1, 8, 32, 8, 8, 1), (2, 16, 32, 12, 12, 3), (3, 20, 40, 7, 7, 3), (2, 32, 96, 14, 14, 1),
+                                           (5, 33, 130, 9, 13, 3), (1, 3, 5, 1, 1, 1), (2, 7, 9, 2, 3, 3), (1, 128, 128, 28, 28, 3),
+                                           (4, 64, 64, 56, 56, 3), (2, 24, 16, 5, 200, 3)])
+def test_against_arbiter(T, B, Cc, K, H, W, R):
+    from tdc_b200 import tc
+    x, w = draw_core(700 + B + Cc + H, B, Cc, K, H, W, R)
+    ref = O.conv2d_f64(x.numpy(), w.numpy(), pad=(R - 1) // 2)
+    for mode, tol in ((3, FP32_TOL), (1, TF32_TOL)):
+        y = T.TcConv(w.cuda(), mode=mode)(x.cuda()).cpu().numpy()
+        assert y.shape == ref.shape and rel_err(y, ref) <= tol, (mode, rel_err(y, ref))
+    crsk = np.ascontiguousarray(w.numpy().transpose(1, 2, 3, 0))
+    y2 = T.TcConv(torch.from_numpy(crsk).cuda(), mode=3, w_layout=T.W_CRSK)(x.cuda()).cpu().numpy()
+    assert np.array_equal(y, y) and rel_err(y2, ref) <= FP32_TOL
+    assert tc.status() == 0          # no bounded wait ran out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("H,R1,R2", SWEEP)
+def test_sweep_shapes_meet_the_fp32_bar(T, H, R1, R2):
+    """Batch 64 of every sweep shape: four sampled images against the arbiter; integer inputs
+    with all-ones weights exactly (the reference drivers' own check)."""
+    i = SWEEP.index((H, R1, R2))
+    x, w = draw_core(2100 + i, 64, R1, R2, H, H)
+    conv = T.TcConv(w.cuda(), mode=3)
+    y = conv(x.cuda())
+    sel = [0, 21, 42, 63]
+    assert rel_err(y[sel].cpu().numpy(), O.conv2d_f64(x[sel].numpy(), w.numpy(), pad=1)) <= FP32_TOL
+    xi = torch.randint(0, 10, (2, R1, H, H), generator=torch.Generator().manual_seed(i)).float()
+    ones = torch.ones(R2, R1, 3, 3)
+    yi = T.TcConv(ones.cuda(), mode=3)(xi.cuda()).cpu().numpy()
+    assert np.array_equal(yi, O.conv2d_f64(xi.numpy(), ones.numpy(), pad=1))
+
+
+@pytest.mark.gpu
+def test_epilogue_and_errors(T):
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(3, 16, 14, 14, generator=g).cuda()
+    w = (torch.randn(24, 16, 3, 3, generator=g) * 0.1).cuda()
+    scale, shift = (torch.rand(24, generator=g) + 0.5).cuda(), torch.randn(24, generator=g).cuda()
+    res = torch.randn(3, 24, 14, 14, generator=g).cuda()
+    y = T.TcConv(w, mode=3)(x, scale, shift, res, True)
+    ref = torch.relu(torch.nn.functional.conv2d(x.double(), w.double(), padding=1) * scale.double().view(1, -1, 1, 1)
+                     + shift.double().view(1, -1, 1, 1) + res.double())
+    assert rel_err(y.cpu().numpy(), ref.cpu().numpy()) <= FP32_TOL
+    with pytest.raises(T.TdcError):
+        T.TcConv(torch.zeros(4, 4, 5, 5).cuda())
+    with pytest.raises(T.TdcError):
+        T.TcConv(w)(torch.zeros(1, 8, 4, 4).cuda())
+
+
+@pytest.mark.gpu
+def test_module_and_network_precisions(T):
+    class HP:
+        ranks = {"l": [24, 16]}
+    torch.manual_seed(3)
+    m = T.TKConv2dC_B200(32, 48, 3, stride=1, padding=1, bias=True, hp_dict=HP, name="l").cuda()
+    x = torch.randn(4, 32, 28, 28).cuda()
+    with torch.no_grad():
+        y32 = m(x)
+        m.precision = "tf32x3"
+        y3 = m(x)
+        m.precision = "tf32"
+        y1 = m(x)
+    assert rel_err(y3.cpu().numpy(), y32.cpu().numpy()) <= FP32_TOL
+    assert FP32_TOL < rel_err(y1.cpu().numpy(), y32.cpu().numpy()) <= TF32_TOL
+    net = T.fill_deterministic(T.tkc_resnet18().eval(), 0).cuda()
+    xin = torch.randn(8, 3, 224, 224, generator=torch.Generator().manual_seed(1)).cuda()
+    with torch.no_grad():
+        a = net(xin)
+        b = net.set_precision("auto")(xin)
+    assert rel_err(b.cpu().numpy(), a.cpu().numpy()) <= 1e-4
