@@ -19,13 +19,43 @@ _FIELDS = ("th", "tw", "tc", "tn", "nog", "gy", "gx", "imgs", "ks")
 _table = None
 
 
+REFERENCE_COLUMNS = ("C", "N", "H", "W", "th", "tw", "tc", "occupancy", "diff", "time_ms")
+
+
+def read_rows(path):
+    """Rows of a table as dicts.  Tables written by tdc_b200.tune start with a header line; the
+    reference's own tables (a100-occupancy-unrolled, 2080Ti-occupancy*) have none and hold
+    exactly the ten REFERENCE_COLUMNS — both load."""
+    with open(path) as f:
+        first = f.readline()
+        f.seek(0)
+        if first.split(",")[0].strip().isdigit():
+            return [dict(zip(REFERENCE_COLUMNS, (v.strip() for v in ln.split(",")))) for ln in f if ln.strip()]
+        return list(csv.DictReader(f))
+
+
+def query_best(rows, C, N, H, W, B=None):
+    """Fastest row of a shape (the reference's query_best,
+    A100-evaluation/TDC-LAYERS-ORACLE/gen_from_occupancy.py:51-66), exact match on the shape
+    columns; `B` filters tables that have a batch column."""
+    best = None
+    for r in rows:
+        if (int(r["C"]), int(r["N"]), int(r["H"]), int(r["W"])) != (C, N, H, W):
+            continue
+        if B is not None and "B" in r and int(r["B"]) != B:
+            continue
+        if best is None or float(r["time_ms"]) < float(best["time_ms"]):
+            best = r
+    return best
+
+
 def load_tables(paths=None):
     """{(C, N, H, W, B, R, stride): (Tile tuple, time_ms)} from the shipped (or given) CSVs."""
     out = {}
     for path in (paths if paths is not None else sorted(glob.glob(os.path.join(_TABLE_DIR, "*.csv")))):
-        with open(path) as f:
-            for row in csv.DictReader(f):
-                if float(row["diff"]) != 0.0:
+        for row in read_rows(path):
+            if True:
+                if float(row["diff"]) != 0.0 or "tn" not in row:     # reference tables carry no B200 tile fields
                     continue
                 key = tuple(int(row[k]) for k in ("C", "N", "H", "W", "B")) + (int(row.get("R", 3) or 3),
                                                                               int(row.get("stride", 1) or 1))
