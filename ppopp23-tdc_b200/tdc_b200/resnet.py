@@ -89,8 +89,9 @@ def _one_conv(x, w_kcrs, w_crsk, scale, shift, residual, relu, stride, padding, 
 def _tk_or_dense(conv, x, scale, shift, residual, relu, precision="fp32"):
     """One conv module + folded BN (+ residual) (+ ReLU): a Tucker conv as its three launches with
     the epilogue on the last, a dense conv as one."""
-    if conv.bias is not None:
-        shift = shift + conv.bias.detach() * scale
+    if conv.bias is not None:      # y = (conv + bias) * scale + shift  ->  conv * scale + (bias * scale + shift)
+        b = conv.bias.detach() if scale is None else conv.bias.detach() * scale
+        shift = b if shift is None else shift + b
     if isinstance(conv, TKConv2dC_B200):
         z1 = _one_conv(x, conv.first_kernel.detach(), None, None, None, None, False, 1, 0, precision)
         z2 = _one_conv(z1, conv.core_kernel.detach(), conv._core_channel_last(), None, None, None, False,
