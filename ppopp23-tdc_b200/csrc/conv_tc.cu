@@ -139,7 +139,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 // a stage's mbarrier says the patch is stored and the filter has landed, and commits to the
 // mbarrier that hands the stage back.  There is no CTA-wide barrier in the main loop.  All
 // twelve warps drain tensor memory in the epilogue.
-template <int NT, int MT, int TAPS>
+template <int NT, int MT, int TAPS, bool VEC>
 __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // carve: barriers | tmem slot | stages { A[hl][CB/4][P][4], B[tap][CB/4][hl*NT][4] }
@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
     int*      abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
     float*    stage0    = reinterpret_cast<float*>(smem_raw + 128);
 
-    constexpr int PPT = (MT * M_TILE + 2 * 260 + LOADERS - 1) / LOADERS;   // patch rows per loader thread, W <= 256
+    constexpr int PPT = 3;      // patch rows per loader thread: the host keeps P <= 3 * LOADERS
     const uint32_t TMEM_COLS = (uint32_t)a.tmem_cols;
     const int a_floats = a.hl * CB * a.P;                  // A part of a stage
     const int b_floats = a.hl * TAPS * CB * NT;            // B part of a stage
@@ -184,60 +184,130 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
 
     if (warp < 8) {
         // ================= loaders =================
-        long long src_off[PPT];        // global offset of channel 0 of each owned patch row, -1 = zeros
-#pragma unroll
-        for (int i = 0; i < PPT; ++i) {
-            const int pp = tid + i * LOADERS;
-            src_off[i] = -1;
-            if (pp < a.P) {
-                const long long g = gp0 + pp;
-                if (g >= 0 && g < a.total_pos) {
-                    const long long b = g / a.Lp;
-                    const int rem = (int)(g - b * a.Lp);
-                    const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
-                    if (yy < a.H && xx < a.W) src_off[i] = b * a.C * HW + (long long)yy * a.W + xx;
-                }
-            }
-        }
-        float v[PPT][CB];
-        auto prefetch = [&](int kb) {           // global -> registers, channel block kb
-            const int c0 = kb * CB;
-#pragma unroll
-            for (int i = 0; i < PPT; ++i)
-#pragma unroll
-                for (int j = 0; j < CB; ++j)
-                    v[i][j] = (src_off[i] >= 0 && c0 + j < a.C) ? __ldg(a.x + src_off[i] + (long long)(c0 + j) * HW) : 0.f;
-        };
-        prefetch(0);
-        for (int kb = 0; kb < a.nkb; ++kb) {
+        // Two channel blocks of input are always in flight in registers (blocks kb and kb+1 are
+        // loaded while kb-1 is being split and stored), and the filter copies run `ns` stages ahead.
+        auto open_stage = [&](int kb) -> float* {       // wait until the stage is free, start its filter copy
             const int s = kb % a.ns;
             float* A = stage0 + (long long)s * stage_floats;
-            if (kb >= a.ns && !mbar_wait(&empty_bar[s], (uint32_t)((kb / a.ns - 1) & 1))) { *abort_flag = 1; break; }
-            if (tid == 0) {                      // the filter of this block: one bulk copy into the stage
+            if (kb >= a.ns && !mbar_wait(&empty_bar[s], (uint32_t)((kb / a.ns - 1) & 1))) { *abort_flag = 1; return nullptr; }
+            if (tid == 0) {
                 mbar_expect_tx(&full_bar[s], b_bytes);
                 bulk_g2s(A + a_floats, wt_cta + (long long)kb * b_floats, b_bytes, &full_bar[s]);
             }
+            return A;
+        };
+        auto close_stage = [&](int kb) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[kb % a.ns])) : "memory");
+        };
+        auto put = [&](float* A, int q, int pp, float c0, float c1, float c2, float c3) {   // 4 channels of one patch row
+            float4 hi;
+            hi.x = to_tf32(c0); hi.y = to_tf32(c1); hi.z = to_tf32(c2); hi.w = to_tf32(c3);
+            *reinterpret_cast<float4*>(A + ((q * a.P + pp) << 2)) = hi;
+            if (a.hl == 2)
+                *reinterpret_cast<float4*>(A + CB * a.P + ((q * a.P + pp) << 2)) = make_float4(c0 - hi.x, c1 - hi.y, c2 - hi.z, c3 - hi.w);
+        };
+        if constexpr (VEC) {
+            // 1x1 filter, H*W a multiple of 4: a thread owns 4 consecutive positions x 4 channels of
+            // the block; four 16-byte loads (one per channel), transposed in registers into four
+            // 16-byte stores (one per position)
+            constexpr int NI = (MT * M_TILE / 2 + LOADERS - 1) / LOADERS;     // items per thread
+            long long off[NI];
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                const int item = tid + i * LOADERS, quad = item >> 1;
+                off[i] = -1;
+                if (quad * 4 < a.P) {
+                    const long long g = g0 + quad * 4;
+                    if (g < a.total_pos) { const long long b = g / a.Lp; off[i] = b * a.C * HW + (g - b * a.Lp); }
+                }
+            }
+            float4 va[NI][4], vb[NI][4];
+            auto load = [&](int kb, float4 (&v)[NI][4]) {
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    const int c0 = kb * CB + ((tid + i * LOADERS) & 1) * 4;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        v[i][j] = (off[i] >= 0 && c0 + j < a.C) ? __ldg(reinterpret_cast<const float4*>(a.x + off[i] + (long long)(c0 + j) * HW))
+                                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            };
+            auto stage = [&](int kb, float4 (&v)[NI][4]) -> bool {
+                float* A = open_stage(kb);
+                if (!A) return false;
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    const int item = tid + i * LOADERS, q = item & 1, pp = (item >> 1) * 4;
+                    if (pp < a.P) {
+                        put(A, q, pp + 0, v[i][0].x, v[i][1].x, v[i][2].x, v[i][3].x);
+                        put(A, q, pp + 1, v[i][0].y, v[i][1].y, v[i][2].y, v[i][3].y);
+                        put(A, q, pp + 2, v[i][0].z, v[i][1].z, v[i][2].z, v[i][3].z);
+                        put(A, q, pp + 3, v[i][0].w, v[i][1].w, v[i][2].w, v[i][3].w);
+                    }
+                }
+                close_stage(kb);
+                return true;
+            };
+            load(0, va);
+            if (a.nkb > 1) load(1, vb);
+            for (int kb = 0; kb < a.nkb; kb += 2) {
+                if (!stage(kb, va)) break;
+                if (kb + 2 < a.nkb) load(kb + 2, va);
+                if (kb + 1 < a.nkb) {
+                    if (!stage(kb + 1, vb)) break;
+                    if (kb + 3 < a.nkb) load(kb + 3, vb);
+                }
+            }
+        } else {
+            long long src_off[PPT];        // global offset of channel 0 of each owned patch row, -1 = zeros
 #pragma unroll
             for (int i = 0; i < PPT; ++i) {
                 const int pp = tid + i * LOADERS;
+                src_off[i] = -1;
                 if (pp < a.P) {
-#pragma unroll
-                    for (int q = 0; q < CB / 4; ++q) {
-                        float4 hi, lo;
-                        hi.x = to_tf32(v[i][4 * q]); hi.y = to_tf32(v[i][4 * q + 1]);
-                        hi.z = to_tf32(v[i][4 * q + 2]); hi.w = to_tf32(v[i][4 * q + 3]);
-                        *reinterpret_cast<float4*>(A + ((q * a.P + pp) << 2)) = hi;
-                        if (a.hl == 2) {
-                            lo.x = v[i][4 * q] - hi.x; lo.y = v[i][4 * q + 1] - hi.y;
-                            lo.z = v[i][4 * q + 2] - hi.z; lo.w = v[i][4 * q + 3] - hi.w;
-                            *reinterpret_cast<float4*>(A + CB * a.P + ((q * a.P + pp) << 2)) = lo;
-                        }
+                    const long long g = gp0 + pp;
+                    if (g >= 0 && g < a.total_pos) {
+                        const long long b = g / a.Lp;
+                        const int rem = (int)(g - b * a.Lp);
+                        const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
+                        if (yy < a.H && xx < a.W) src_off[i] = b * a.C * HW + (long long)yy * a.W + xx;
                     }
                 }
             }
-            if (kb + 1 < a.nkb) prefetch(kb + 1);     // in flight while the next stage is awaited
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[s])) : "memory");
+            float va[PPT][CB], vb[PPT][CB];
+            auto load = [&](int kb, float (&v)[PPT][CB]) {           // global -> registers, channel block kb
+                const int c0 = kb * CB;
+#pragma unroll
+                for (int i = 0; i < PPT; ++i)
+#pragma unroll
+                    for (int j = 0; j < CB; ++j)
+                        v[i][j] = (src_off[i] >= 0 && c0 + j < a.C) ? __ldg(a.x + src_off[i] + (long long)(c0 + j) * HW) : 0.f;
+            };
+            auto stage = [&](int kb, float (&v)[PPT][CB]) -> bool {
+                float* A = open_stage(kb);
+                if (!A) return false;
+#pragma unroll
+                for (int i = 0; i < PPT; ++i) {
+                    const int pp = tid + i * LOADERS;
+                    if (pp < a.P) {
+#pragma unroll
+                        for (int q = 0; q < CB / 4; ++q) put(A, q, pp, v[i][4 * q], v[i][4 * q + 1], v[i][4 * q + 2], v[i][4 * q + 3]);
+                    }
+                }
+                close_stage(kb);
+                return true;
+            };
+            load(0, va);
+            if (a.nkb > 1) load(1, vb);
+            for (int kb = 0; kb < a.nkb; kb += 2) {
+                if (!stage(kb, va)) break;
+                if (kb + 2 < a.nkb) load(kb + 2, va);
+                if (kb + 1 < a.nkb) {
+                    if (!stage(kb + 1, vb)) break;
+                    if (kb + 3 < a.nkb) load(kb + 3, vb);
+                }
+            }
         }
     } else if (lane == 0 && warp - 8 < MT) {
         // ================= MMA issuers: one thread per position tile =================
@@ -461,7 +531,7 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
         stage_bytes = sizeof(float) * ((size_t)a.hl * CB * a.P + (size_t)a.hl * taps * CB * p->nt);
         ns = (128 + 3 * stage_bytes <= (size_t)smem_max) ? 3 : 2;
         const long long ctas_mt = ((a.total_pos + (long long)mt * M_TILE - 1) / ((long long)mt * M_TILE)) * a.n_ocb;
-        const bool fits = 128 + 2 * stage_bytes <= (size_t)smem_max;
+        const bool fits = 128 + 2 * stage_bytes <= (size_t)smem_max && a.P <= 3 * LOADERS;
         if (mt == 1 || (fits && ctas_mt >= sms)) { if (!fits) return tc_fail(TDC_ERR_SMEM, "two stages of %zu bytes do not fit in shared memory", stage_bytes); break; }
     }
     if (ns > a.nkb) ns = a.nkb > 0 ? a.nkb : 1;
@@ -477,7 +547,10 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     const long long ctas = tiles * a.n_ocb;
     if (ctas >= (1ll << 31)) return tc_fail(TDC_ERR_TILE, "grid too large");
     const void* fn = nullptr;
-#define TDC_TC_PICK(NT_, MT_) (taps == 9 ? (const void*)&conv_tc_kernel<NT_, MT_, 9> : (const void*)&conv_tc_kernel<NT_, MT_, 1>)
+    // 16-byte input loads: 1x1 filter, images a multiple of 4 positions long, 16-byte aligned base
+    const bool vec = taps == 1 && ((long long)H * W) % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
+#define TDC_TC_PICK(NT_, MT_) (taps == 9 ? (const void*)&conv_tc_kernel<NT_, MT_, 9, false> : \
+                               (vec ? (const void*)&conv_tc_kernel<NT_, MT_, 1, true> : (const void*)&conv_tc_kernel<NT_, MT_, 1, false>))
     if (p->nt == 128) fn = mt == 2 ? TDC_TC_PICK(128, 2) : TDC_TC_PICK(128, 1);
     else if (p->nt == 64) fn = mt == 4 ? TDC_TC_PICK(64, 4) : (mt == 2 ? TDC_TC_PICK(64, 2) : TDC_TC_PICK(64, 1));
     else fn = mt == 4 ? TDC_TC_PICK(32, 4) : (mt == 2 ? TDC_TC_PICK(32, 2) : TDC_TC_PICK(32, 1));
