@@ -70,7 +70,7 @@ def _fold_bn_now(bn):
     return scale.float().contiguous(), (b - mean * scale).float().contiguous()
 
 
-def _one_conv(x, w_kcrs, w_crsk, scale, shift, residual, relu, stride, padding, precision):
+def _one_conv(owner, name, x, w_kcrs, w_crsk, scale, shift, residual, relu, stride, padding, precision):
     """One convolution with its epilogue on the kernel that suits it: tensor cores (3xTF32) for
     stride-1 1x1 / 3x3 layers with enough work to fill the GPU when `precision` allows, the fp32
     kernel with a table tile otherwise."""
@@ -79,11 +79,11 @@ def _one_conv(x, w_kcrs, w_crsk, scale, shift, residual, relu, stride, padding, 
     K, _, R, S = w_kcrs.shape
     if precision != "fp32" and tc.supported(R, S, stride, padding, W) and \
             (precision != "auto" or tc.worthwhile(B, Cc, H, W, K, R)):
-        return tc.cached(w_kcrs, 1 if precision == "tf32" else 3)(x, scale, shift, residual, relu)
+        return tc.cached(owner, name, w_kcrs, 1 if precision == "tf32" else 3)(x, scale, shift, residual, relu)
     tile = tiles.table_tile(B, Cc, H, W, K, R, S, padding, stride)
     if w_crsk is not None:
         return ops.conv2d_epi(x, w_crsk, scale, shift, residual, relu, stride, padding, w_layout=W_CRSK, tile=tile)
-    return ops.conv2d_epi(x, w_kcrs, scale, shift, residual, relu, stride, padding, tile=tile)
+    return ops.conv2d_epi(x, w_kcrs.detach(), scale, shift, residual, relu, stride, padding, tile=tile)
 
 
 def _tk_or_dense(conv, x, scale, shift, residual, relu, precision="fp32"):
@@ -93,11 +93,11 @@ def _tk_or_dense(conv, x, scale, shift, residual, relu, precision="fp32"):
         b = conv.bias.detach() if scale is None else conv.bias.detach() * scale
         shift = b if shift is None else shift + b
     if isinstance(conv, TKConv2dC_B200):
-        z1 = _one_conv(x, conv.first_kernel.detach(), None, None, None, None, False, 1, 0, precision)
-        z2 = _one_conv(z1, conv.core_kernel.detach(), conv._core_channel_last(), None, None, None, False,
+        z1 = _one_conv(conv, "first", x, conv.first_kernel, None, None, None, None, False, 1, 0, precision)
+        z2 = _one_conv(conv, "core", z1, conv.core_kernel, conv._core_channel_last(), None, None, None, False,
                        conv.stride[0], conv.padding[0], precision)
-        return _one_conv(z2, conv.last_kernel.detach(), None, scale, shift, residual, relu, 1, 0, precision)
-    return _one_conv(x, conv.weight.detach(), None, scale, shift, residual, relu, conv.stride[0], conv.padding[0], precision)
+        return _one_conv(conv, "last", z2, conv.last_kernel, None, scale, shift, residual, relu, 1, 0, precision)
+    return _one_conv(conv, "weight", x, conv.weight, None, scale, shift, residual, relu, conv.stride[0], conv.padding[0], precision)
 
 
 class TKBasicBlock(nn.Module):

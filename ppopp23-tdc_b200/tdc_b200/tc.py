@@ -59,18 +59,17 @@ def worthwhile(B, C, H, W, K, R):
     return 2.0 * B * H * W * C * K * R * R >= 0.5e9
 
 
-_cache = {}
-
-
-def cached(weight, mode, w_layout=_lib.W_KCRS):
-    """TcConv for a weight tensor, rebuilt when the tensor changes (keyed on storage and version)."""
-    key = (weight.data_ptr(), weight._version, tuple(weight.shape), mode, w_layout)
-    hit = _cache.get(key)
-    if hit is None:
-        if len(_cache) > 512:
-            _cache.clear()
-        hit = _cache[key] = TcConv(weight.detach(), mode, w_layout)
-    return hit
+def cached(owner, name, weight, mode, w_layout=_lib.W_KCRS):
+    """TcConv for `weight`, kept on the module that owns the weight (`owner`) under `name`, and
+    rebuilt when the tensor is written to or replaced (version / storage check).  Keeping it on the
+    owner — not in a table keyed by address — means a freed network's entries can never be taken
+    for those of a new network whose weights happen to land on the same addresses."""
+    store = owner.__dict__.setdefault("_tc_convs", {})
+    key = (weight._version, weight.data_ptr(), tuple(weight.shape))
+    hit = store.get((name, mode, w_layout))
+    if hit is None or hit[0] != key:
+        hit = store[(name, mode, w_layout)] = (key, TcConv(weight.detach(), mode, w_layout))
+    return hit[1]
 
 
 def status():

@@ -125,9 +125,9 @@ class TKConv2dC_B200(nn.Module):
         mode = self._use_tc(x)
         if mode:
             from . import tc
-            z1 = tc.cached(self.first_kernel, mode)(x)
-            z2 = tc.cached(self.core_kernel, mode)(z1)
-            return tc.cached(self.last_kernel, mode)(z2, bias=None if self.bias is None else self.bias.detach())
+            z1 = tc.cached(self, "first", self.first_kernel, mode)(x)
+            z2 = tc.cached(self, "core", self.core_kernel, mode)(z1)
+            return tc.cached(self, "last", self.last_kernel, mode)(z2, bias=None if self.bias is None else self.bias.detach())
         B, _, H, W = x.shape
         tile = tiles.table_tile(B, self.in_rank, H, W, self.out_rank, self.kernel_size[0], self.kernel_size[1],
                                 self.padding[0], self.stride[0])     # measured table first, model otherwise
