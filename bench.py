@@ -12,8 +12,8 @@ no collective on the data path).  Rank 0 prints ONE JSON line.
   value          layer-images/s = (8 layers x 64 images x N GPUs) / time per step, inputs resident in HBM
   e2e            the same work through the layer objects of the C ABI with HOST buffers
                  (tdc_conv_forward_host: copy in, run, copy out), pinned host memory
-  roofline       the core-conv kernel against the fp32 FMA peak of the device (every sweep
-                 shape is FP32-pipe bound by algorithmic count), plus its HBM figure
+  roofline       the step's kernel (tcgen05, 3xTF32) against a third of the dense TF32 peak, with its
+                 HBM figure; the fp32 FMA kernels against the fp32 FMA peak under `fp32_fma_path`
   cpu_baseline   the reference's CPU path for the same step (torch F.conv2d on the host cores)
   layers         per-shape kernel time at batch 64 and batch 1, and cuDNN through torch
                  (allow_tf32=False) beside it
@@ -336,7 +336,7 @@ def main():
             # sees the clocks of this load even when the timed steps take only milliseconds
             t_w = time.perf_counter()
             n_w = 0
-            while n_w < warm or time.perf_counter() - t_w < 0.6:
+            while n_w < warm or (args.steps > 2 and time.perf_counter() - t_w < 0.6):   # short runs (profiling) skip the soak
                 fn(); n_w += 1
                 if n_w % 16 == 0:
                     torch.cuda.synchronize()
@@ -394,9 +394,17 @@ def main():
     tot_by = sum(conv_bytes(BATCH, r["H"], r["R1"], r["R2"]) for r in per_layer)
     dom = max(per_layer, key=lambda r: r["tc3_us"])
     tot_tc3, tot_simt, tot_tc1 = (sum(r[k] for r in per_layer) for k in ("tc3_us", "simt_us", "tc1_us"))
+    # DRAM bytes (read + write) of each launch of the step from one ncu capture of this command
+    # (dram__bytes_read.sum + dram__bytes_write.sum per launch, batch 64); the summary and the command
+    # are in profiles/launch_list_bench.md.  Outputs stay in L2 within a launch, so this is input + filter.
+    NCU_DRAM_MB = {(56, 32): 25.9, (56, 64): 52.7, (28, 64): 13.2, (28, 128): 27.0, (14, 128): 7.7, (14, 256): 17.6,
+                   (7, 256): 8.0, (7, 512): 25.4}
     roofline = {
         "bound": "tensor", "achieved": tot_fl / tot_tc3 / 1e6, "peak": tf32_peak / 3.0, "unit": "TFLOP/s",
-        "frac": tot_fl / tot_tc3 / 1e6 / (tf32_peak / 3.0), "traffic": None,
+        "frac": tot_fl / tot_tc3 / 1e6 / (tf32_peak / 3.0),
+        "traffic": {"bytes_per_launch": NCU_DRAM_MB[(dom["H"], dom["R1"])] * 1e6, "launch": [dom["H"], dom["R1"], dom["R2"]],
+                    "algorithmic_bytes": conv_bytes(BATCH, dom["H"], dom["R1"], dom["R2"]),
+                    "source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, profiles/launch_list_bench.md"},
         "kernel": "conv_tc_kernel (tcgen05 kind::tf32, 3xTF32), the 8 launches of a step, L2 flushed before each",
         "peak_source": "algorithmic FLOPs against (bf16_tflops/2)/3: dense TF32 taken as half the measured cuBLAS bf16 rate of "
                        "MEASURED_PEAKS.json (%s), divided by the three TF32 products each fp32-level product costs" % peaks["source"],
