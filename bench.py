@@ -402,9 +402,11 @@ def main():
     roofline = {
         "bound": "tensor", "achieved": tot_fl / tot_tc3 / 1e6, "peak": tf32_peak / 3.0, "unit": "TFLOP/s",
         "frac": tot_fl / tot_tc3 / 1e6 / (tf32_peak / 3.0),
-        "traffic": {"bytes_per_launch": NCU_DRAM_MB[(dom["H"], dom["R1"])] * 1e6, "launch": [dom["H"], dom["R1"], dom["R2"]],
-                    "algorithmic_bytes": conv_bytes(BATCH, dom["H"], dom["R1"], dom["R2"]),
-                    "source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, profiles/launch_list_bench.md"},
+        "traffic": NCU_DRAM_MB[(dom["H"], dom["R1"])] * 1e6,
+        "traffic_note": {"launch": [dom["H"], dom["R1"], dom["R2"]], "unit": "bytes per launch",
+                         "algorithmic_bytes": conv_bytes(BATCH, dom["H"], dom["R1"], dom["R2"]),
+                         "source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the dominant launch, "
+                                   "profiles/launch_list_bench.md; the output is still in L2 when the launch ends"},
         "kernel": "conv_tc_kernel (tcgen05 kind::tf32, 3xTF32), the 8 launches of a step, L2 flushed before each",
         "peak_source": "algorithmic FLOPs against (bf16_tflops/2)/3: dense TF32 taken as half the measured cuBLAS bf16 rate of "
                        "MEASURED_PEAKS.json (%s), divided by the three TF32 products each fp32-level product costs" % peaks["source"],
