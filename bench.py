@@ -185,6 +185,45 @@ def torch_reference_forward(torch, m, x):
     return m.fc(torch.flatten(F.adaptive_avg_pool2d(x, 1), 1))
 
 
+def bench_tk_block(torch, T, dev, time_layer, peaks):
+    """The whole Tucker block (1x1 C->R1, 3x3 core, 1x1 R2->K) for the ResNet-50 bottleneck middles
+    C=K in {64@56, 128@28, 256@14, 512@7}, R1=R2=C/2, at batch 1 and 32: our three-launch chain
+    (tensor cores with split operands where the layer is large enough, fp32 FMA kernels otherwise)
+    beside the same three convolutions through torch/cuDNN.  HBM floor: x in + y out + filters once."""
+    import torch.nn.functional as F
+
+    class HP:
+        ranks = {}
+    rows = []
+    torch.backends.cudnn.benchmark = True
+    torch.backends.cudnn.allow_tf32 = False
+    for i, (Cc, H) in enumerate(((64, 56), (128, 28), (256, 14), (512, 7))):
+        R = Cc // 2
+        HP.ranks = {"b": [R, R]}
+        m = T.TKConv2dC_B200(Cc, Cc, 3, padding=1, bias=False, hp_dict=HP, name="b")
+        g = torch.Generator().manual_seed(3000 + i)
+        x32 = torch.randn(32, Cc, H, H, generator=g)
+        with torch.no_grad():
+            for p in (m.first_kernel, m.core_kernel, m.last_kernel):
+                p.normal_(0.0, (2.0 / (p.shape[0] * p.shape[2] * p.shape[3])) ** 0.5, generator=g)
+        m = m.to(dev)
+        m.precision = "auto"
+        for B in (1, 32):
+            x = x32[:B].contiguous().to(dev)
+            with torch.no_grad():
+                us = time_layer(lambda: m(x), iters=10)
+                ref = lambda t: F.conv2d(F.conv2d(F.conv2d(t, m.first_kernel), m.core_kernel, None, 1, 1), m.last_kernel)
+                cud = time_layer(lambda: ref(x), iters=10)
+                y64 = ref(x[:2].double()) if False else F.conv2d(F.conv2d(F.conv2d(x[:2].double(), m.first_kernel.double()),
+                                                                           m.core_kernel.double(), None, 1, 1), m.last_kernel.double())
+                err = float((m(x)[:2].double() - y64).abs().max() / y64.abs().max())
+            flops = 2.0 * B * H * H * (Cc * R + 9 * R * R + R * Cc)
+            by = 4.0 * (2 * B * Cc * H * H + 2 * Cc * R + 9 * R * R)
+            rows.append(dict(C=Cc, H=H, R=R, B=B, us=us, cudnn_us=cud, rel_err_fp64=err, tflops=flops / us / 1e6,
+                             hbm_floor_us=by / peaks["hbm_gbs"] / 1e3, gbs=by / us / 1e3))
+    return rows
+
+
 def bench_resnet(torch, T, dev, dist, world, rank, stream):
     """images/s of the TK-compressed ResNet-18 (ranks round8(0.5*channels), random init, eval) at
     batch 256 per GPU and its batch-1 latency, with the cuDNN path on the same weights beside it."""
@@ -483,6 +522,8 @@ def main():
     # ---- TK-compressed ResNet-18 forward (every rank its own batch; one gather of the logits) --
     if not args.no_extras:
         line["tk_resnet18"] = bench_resnet(torch, T, dev, dist, world, rank, stream)
+        if rank == 0 and world == 1:
+            line["tk_block"] = bench_tk_block(torch, T, dev, time_layer, peaks)
 
     # ---- extras on rank 0 of a single-GPU run: batch-1 latency, cuDNN, CPU baseline ---------
     if rank == 0 and world == 1 and not args.no_extras:

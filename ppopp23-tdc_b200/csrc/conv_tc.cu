@@ -33,6 +33,7 @@
 #include <stdint.h>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include "../../include/tdc_b200.h"
 
 namespace tdc_tc {
@@ -525,6 +526,10 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     a.nmain = (a.hl == 2 && (long long)p->nkb * taps > 320) ? 2 : 1;
     a.tile_cols = (a.nmain == 2 ? 4 : 2) * p->nt;
     int mt = 512 / a.tile_cols > 4 ? 4 : 512 / a.tile_cols, ns = 0;
+    // tuning overrides (read per call): TDC_TC_MT caps the position tiles per CTA, TDC_TC_NS fixes the stage count
+    const char* env_mt = getenv("TDC_TC_MT");
+    const char* env_ns = getenv("TDC_TC_NS");
+    if (env_mt && atoi(env_mt) >= 1) while (mt > atoi(env_mt)) mt /= 2;
     size_t stage_bytes = 0;
     for (;; mt /= 2) {
         a.P = ((mt * M_TILE + 2 * pad * (a.Wp + 1)) + 7) / 8 * 8;
@@ -534,6 +539,7 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
         const bool fits = 128 + 2 * stage_bytes <= (size_t)smem_max && a.P <= 3 * LOADERS;
         if (mt == 1 || (fits && ctas_mt >= sms)) { if (!fits) return tc_fail(TDC_ERR_SMEM, "two stages of %zu bytes do not fit in shared memory", stage_bytes); break; }
     }
+    if (env_ns && atoi(env_ns) >= 2 && atoi(env_ns) <= 4 && 128 + atoi(env_ns) * stage_bytes <= (size_t)smem_max) ns = atoi(env_ns);
     if (ns > a.nkb) ns = a.nkb > 0 ? a.nkb : 1;
     a.ns = ns;
     a.tmem_cols = 32;
