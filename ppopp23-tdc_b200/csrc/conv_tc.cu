@@ -61,6 +61,9 @@ struct Args {
     int tile_cols;         // tensor-memory columns per position tile: 2*NT, or 4*NT with two mains
     int tmem_cols;         // allocation (power of two >= 32)
     long long total_pos;   // B * Lp
+    int nbuf;              // persistent kernel: accumulator buffers in tensor memory (1 or 2)
+    int depth;             // persistent kernel: slots of the raw-input ring (cp.async groups in flight)
+    long long ntiles;      // persistent kernel: position tiles x output-channel blocks
     int* status;           // device status word: 0 ok, else first failure code
 };
 
@@ -86,6 +89,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// 4-byte asynchronous copy global -> shared; `real` false writes a zero and reads nothing.
+__device__ __forceinline__ void cp_async4(void* dst, const void* src, bool real) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(real ? 4u : 0u) : "memory");
+}
+// Wait until at most n of this thread's most recent cp.async groups are still in flight (n <= 7).
+__device__ __forceinline__ void cp_async_wait_pending(int n) {
+    switch (n) {
+        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+        case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+        case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+        case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+    }
 }
 __device__ __forceinline__ float to_tf32(float v) {
     uint32_t r;
@@ -123,6 +143,110 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
+}
+
+// One lane of a converged warp, chosen by the hardware.  The MMA issue loops run warp-uniform
+// (every lane waits on the barriers and computes the same descriptors) and only the MMA and
+// commit instructions sit under this predicate: operands the compiler can prove warp-uniform
+// stay in uniform registers, which is what the tensor-core instructions read.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
+// Instruction descriptor: D fp32, A and B tf32, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t make_idesc(int n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(M_TILE >> 4) << 24);
+}
+
+// The MMAs of one channel block (stage) of one position tile.  `a_base` / `b_base`: shared
+// addresses of the stage's patch and filter; `row16`: first patch row of the tile (the unit
+// of a start-address step is 16 bytes = one patch row of 4 channels); `odd`: this block
+// is an odd channel block; `first`: it starts the accumulation of the accumulator it feeds.
+template <int NT, int TAPS>
+__device__ __forceinline__ void issue_block(const Args& a, uint32_t d_main, uint32_t a_base, uint32_t b_base, uint32_t row16,
+                                            bool odd, bool first) {
+    // leading byte offset = distance between the two 4-channel core matrices of a K step,
+    // stride byte offset = distance between groups of 8 rows (verified on a B200 against the fp64 oracle)
+    const uint32_t a_lbo = (uint32_t)a.P * 16u, b_lbo = (uint32_t)(a.hl * NT) * 16u, sbo = 128u;
+    const uint32_t idesc_n = make_idesc(NT), idesc_2n = make_idesc(2 * NT);
+    const uint64_t a_hi0 = make_desc(a_base, a_lbo, sbo) + row16;
+    const uint64_t a_lo0 = make_desc(a_base + (uint32_t)(CB * a.P) * 4u, a_lbo, sbo) + row16;
+    const uint64_t b_hi0 = make_desc(b_base, b_lbo, sbo);       // rows 0..NT-1 hi, NT..2NT-1 lo
+    const uint32_t b_tap = (uint32_t)((CB / 4) * a.hl * NT);    // filter rows per tap, in 16-byte units
+    if (a.hl == 1) {
+#pragma unroll
+        for (int tap = 0; tap < TAPS; ++tap) {
+            const uint32_t a_off = (uint32_t)((tap / (TAPS == 9 ? 3 : 1)) * a.Wp + tap % (TAPS == 9 ? 3 : 1));
+            mma_tf32(d_main, a_hi0 + a_off, b_hi0 + tap * b_tap, idesc_n, (first && tap == 0) ? 0u : 1u);
+        }
+    } else if (a.nmain == 2 && odd) {
+        // odd channel block: second main accumulator; the lo rows of the filter start NT rows (NT x 16 bytes) in
+#pragma unroll
+        for (int tap = 0; tap < TAPS; ++tap) {
+            const uint32_t a_off = (uint32_t)((tap / (TAPS == 9 ? 3 : 1)) * a.Wp + tap % (TAPS == 9 ? 3 : 1));
+            const uint64_t b_hi = b_hi0 + tap * b_tap;
+            mma_tf32(d_main + 2 * NT, a_hi0 + a_off, b_hi, idesc_n, (first && tap == 0) ? 0u : 1u);   // main1 += hi*hi
+            mma_tf32(d_main + NT, a_hi0 + a_off, b_hi + (uint64_t)NT, idesc_n, 1u);                   // small += hi*lo
+            mma_tf32(d_main + NT, a_lo0 + a_off, b_hi, idesc_n, 1u);                                  // small += lo*hi
+        }
+    } else {
+#pragma unroll
+        for (int tap = 0; tap < TAPS; ++tap) {
+            const uint32_t a_off = (uint32_t)((tap / (TAPS == 9 ? 3 : 1)) * a.Wp + tap % (TAPS == 9 ? 3 : 1));
+            const uint64_t b_hi = b_hi0 + tap * b_tap;
+            mma_tf32(d_main, a_hi0 + a_off, b_hi, idesc_2n, (first && tap == 0) ? 0u : 1u);           // main += hi*hi, small += hi*lo
+            mma_tf32(d_main + NT, a_lo0 + a_off, b_hi, idesc_n, 1u);                                  // small += lo*hi
+        }
+    }
+}
+
+// 32 output channels of this thread's position: tensor memory -> registers, with the
+// accumulators of the split (main + small, + second main) added in fp32.
+template <int NT>
+__device__ __forceinline__ void load_chunk(const Args& a, uint32_t taddr, uint32_t (&r)[32]) {
+    tmem_ld32(taddr, r);
+    if (a.hl == 2) {
+        uint32_t r2[32];
+        tmem_ld32(taddr + NT, r2);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) + __uint_as_float(r2[k]));
+        if (a.nmain == 2 && a.nkb > 1) {          // second main accumulator (odd channel blocks)
+            tmem_ld32(taddr + 2 * NT, r2);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) + __uint_as_float(r2[k]));
+        }
+    } else {
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    }
+}
+
+// ... and registers -> y (NCHW: the lanes of a warp hold consecutive positions, so every
+// store instruction writes one contiguous run).  `out_off` < 0: the position is padding.
+__device__ __forceinline__ void store_chunk(const Args& a, const uint32_t (&r)[32], long long out_off, int oc0, long long HW) {
+    if (out_off < 0) return;
+    const long long o0 = out_off + (long long)oc0 * HW;
+    float* yp = a.y + o0;
+    const int n = a.K - oc0;                      // channels of this chunk that exist
+    if (n >= 32 && !a.scale && !a.bias && !a.residual && !a.relu) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) { *yp = __uint_as_float(r[k]); yp += HW; }
+    } else {
+        const float* rp = a.residual ? a.residual + o0 : nullptr;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            if (k < n) {
+                float val = __uint_as_float(r[k]);
+                if (a.scale) val *= __ldg(a.scale + oc0 + k);
+                if (a.bias) val += __ldg(a.bias + oc0 + k);
+                if (rp) val += rp[k * HW];
+                yp[k * HW] = a.relu ? fmaxf(val, 0.f) : val;
+            }
+        }
+    }
 }
 
 // NT output channels and MT tiles of 128 positions per CTA.  Tensor memory holds, per
@@ -310,56 +434,23 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
                 }
             }
         }
-    } else if (lane == 0 && warp - 8 < MT) {
-        // ================= MMA issuers: one thread per position tile =================
-        const int mt = warp - 8;
-        // instruction descriptors: D fp32, A and B tf32, both K-major, M = 128; N = NT, and N = 2*NT for
-        // the MMA that multiplies the hi input with the filter's hi and lo halves at once
-        const uint32_t idesc_base = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(M_TILE >> 4) << 24);
-        const uint32_t idesc_n  = idesc_base | ((uint32_t)(NT >> 3) << 17);
-        const uint32_t idesc_2n = idesc_base | ((uint32_t)((2 * NT) >> 3) << 17);
-        // leading byte offset = distance between the two 4-channel core matrices of a K step,
-        // stride byte offset = distance between groups of 8 rows (verified on a B200 against the fp64 oracle)
-        const uint32_t a_lbo = (uint32_t)a.P * 16u, a_sbo = 128u;
-        const uint32_t b_lbo = (uint32_t)(a.hl * NT) * 16u, b_sbo = 128u;
-        uint32_t a_tap16[TAPS], b_tap16[TAPS];     // start offsets of the taps in 16-byte units
-#pragma unroll
-        for (int tap = 0; tap < TAPS; ++tap) {
-            const int r = tap / a.taps_r, sx = tap - r * a.taps_r;
-            a_tap16[tap] = (uint32_t)(mt * M_TILE + r * a.Wp + sx);
-            b_tap16[tap] = (uint32_t)(tap * (CB / 4) * a.hl * NT);
-        }
-        const uint32_t d_main = tmem + (uint32_t)(mt * a.tile_cols);
-        for (int kb = 0; kb < a.nkb; ++kb) {
-            const int s = kb % a.ns;
-            if (!mbar_wait(&full_bar[s], (uint32_t)((kb / a.ns) & 1))) { *abort_flag = 1; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float* A = stage0 + (long long)s * stage_floats;
-            const uint32_t a_base = smem_u32(A), b_base = smem_u32(A + a_floats);
-            const uint64_t a_hi0 = make_desc(a_base, a_lbo, a_sbo);
-            const uint64_t a_lo0 = make_desc(a_base + (uint32_t)(CB * a.P) * 4u, a_lbo, a_sbo);
-            const uint64_t b_hi0 = make_desc(b_base, b_lbo, b_sbo);       // rows 0..NT-1 hi, NT..2NT-1 lo
-#pragma unroll
-            for (int tap = 0; tap < TAPS; ++tap) {
-                const uint64_t a_hi = a_hi0 + a_tap16[tap], b_hi = b_hi0 + b_tap16[tap];
-                const uint32_t acc = (kb == 0 && tap == 0) ? 0u : 1u;
-                if (a.nmain == 2 && (kb & 1)) {
-                    // odd channel block: second main accumulator; the lo rows of the filter start NT rows in
-                    const uint32_t acc1 = (kb == 1 && tap == 0) ? 0u : 1u;
-                    mma_tf32(d_main + 2 * NT, a_hi, b_hi, idesc_n, acc1);                    // main1 += hi*hi
-                    if (a.hl == 2) {
-                        mma_tf32(d_main + NT, a_hi, b_hi + (uint64_t)NT, idesc_n, 1u);   // small += hi*lo (lo rows start NT rows = NT x 16 bytes in)
-                        mma_tf32(d_main + NT, a_lo0 + a_tap16[tap], b_hi, idesc_n, 1u);      // small += lo*hi
-                    }
-                } else if (a.hl == 2) {
-                    mma_tf32(d_main, a_hi, b_hi, idesc_2n, acc);                         // main += hi*hi, small += hi*lo
-                    mma_tf32(d_main + NT, a_lo0 + a_tap16[tap], b_hi, idesc_n, 1u);      // small += lo*hi
-                } else {
-                    mma_tf32(d_main, a_hi, b_hi, idesc_n, acc);
+    } else {
+        // ================= MMA issuers: warp 8+mt owns position tile mt =================
+        const int mt = __shfl_sync(0xffffffffu, warp - 8, 0);
+        if (mt < MT) {
+            const uint32_t d_main = tmem + (uint32_t)(mt * a.tile_cols);
+            for (int kb = 0; kb < a.nkb; ++kb) {
+                const int s = kb % a.ns;
+                if (!mbar_wait(&full_bar[s], (uint32_t)((kb / a.ns) & 1))) { *abort_flag = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const float* A = stage0 + (long long)s * stage_floats;
+                if (elect_one()) {
+                    issue_block<NT, TAPS>(a, d_main, smem_u32(A), smem_u32(A + a_floats), (uint32_t)(mt * M_TILE), kb & 1, kb < 2 && (kb == 0 || a.nmain == 2));
+                    mma_commit(&empty_bar[s]);
+                    if (kb + 1 == a.nkb) mma_commit(done_bar);
                 }
+                __syncwarp();
             }
-            mma_commit(&empty_bar[s]);
-            if (kb + 1 == a.nkb) mma_commit(done_bar);
         }
     }
 
@@ -384,44 +475,21 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
                 const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
                 if (yy < a.H && xx < a.W) out_off = b * a.K * HW + (long long)yy * a.W + xx;
             }
-            uint32_t r[32], r2[32];
-            const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * a.tile_cols + chunk * 32);
-            tmem_ld32(taddr, r);
-            if (a.hl == 2) tmem_ld32(taddr + NT, r2);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (a.nmain == 2 && a.nkb > 1) {          // second main accumulator (odd channel blocks)
-                if (a.hl == 2) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
-                }
-                tmem_ld32(taddr + 2 * NT, r2);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
-#pragma unroll
-                for (int j = 0; j < 32; ++j) r2[j] = 0u;
-            }
-            if (out_off >= 0) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int oc = ocb * NT + chunk * 32 + j;
-                    if (oc < a.K) {
-                        float val = __uint_as_float(r[j]);
-                        if (a.hl == 2) val += __uint_as_float(r2[j]);
-                        if (a.scale) val *= a.scale[oc];
-                        if (a.bias) val += a.bias[oc];
-                        const long long o = out_off + (long long)oc * HW;
-                        if (a.residual) val += a.residual[o];
-                        a.y[o] = a.relu ? fmaxf(val, 0.f) : val;
-                    }
-                }
-            }
+            uint32_t r[32];
+            load_chunk<NT>(a, tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * a.tile_cols + chunk * 32), r);
+            store_chunk(a, r, out_off, ocb * NT + chunk * 32, HW);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
 }
+
+}  // namespace tdc_tc
+
+#include "conv_tc_persist.cuh"
+
+namespace tdc_tc {
 
 // Filter [K][C][R][S] (or [C][R][S][K]) -> per (output block, channel block) the exact
 // shared-memory image of a stage's B part: [tap][CB/4][hl*NT][4] (rows 0..NT-1 the hi halves,
@@ -520,51 +588,101 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     int smem_max = 0, sms = 148;
     cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    // position tiles per CTA: as many as tensor memory holds (512 columns = MT * 2 * NT), fewer
-    // when that would leave SMs without a CTA or the stages would not fit in shared memory
     // long reductions get two main accumulators per tile (4*NT columns per tile instead of 2*NT)
     a.nmain = (a.hl == 2 && (long long)p->nkb * taps > 320) ? 2 : 1;
     a.tile_cols = (a.nmain == 2 ? 4 : 2) * p->nt;
-    int mt = 512 / a.tile_cols > 4 ? 4 : 512 / a.tile_cols, ns = 0;
-    // tuning overrides (read per call): TDC_TC_MT caps the position tiles per CTA, TDC_TC_NS fixes the stage count
+    // tuning overrides (read per call): TDC_TC_PERSIST=0 selects the one-tile-per-CTA kernel, TDC_TC_MT caps the
+    // position tiles per CTA, TDC_TC_NS fixes the stage count, TDC_TC_NBUF the accumulator buffers
     const char* env_mt = getenv("TDC_TC_MT");
     const char* env_ns = getenv("TDC_TC_NS");
+    const char* env_nbuf = getenv("TDC_TC_NBUF");
+    const char* env_persist = getenv("TDC_TC_PERSIST");
+    // The persistent kernel wins where one CTA per SM fits and a CTA tile is short (split operands, up to 64
+    // output channels per block: prologue and epilogue would otherwise show).  With 128-channel blocks the
+    // one-tile kernel, which drains tensor memory with all its warps, measured faster, and with plain TF32
+    // operands two one-tile CTAs share an SM and overlap by themselves.  TDC_TC_PERSIST=0/1 forces either.
+    const bool persist = env_persist ? atoi(env_persist) != 0 : (p->nt <= 64 && a.hl == 2);
+    int mt = 512 / a.tile_cols > 4 ? 4 : 512 / a.tile_cols, ns = 0, depth = 0, nbuf = 1;   // tensor memory: 512 columns
     if (env_mt && atoi(env_mt) >= 1) while (mt > atoi(env_mt)) mt /= 2;
-    size_t stage_bytes = 0;
-    for (;; mt /= 2) {
-        a.P = ((mt * M_TILE + 2 * pad * (a.Wp + 1)) + 7) / 8 * 8;
-        stage_bytes = sizeof(float) * ((size_t)a.hl * CB * a.P + (size_t)a.hl * taps * CB * p->nt);
-        ns = (128 + 3 * stage_bytes <= (size_t)smem_max) ? 3 : 2;
-        const long long ctas_mt = ((a.total_pos + (long long)mt * M_TILE - 1) / ((long long)mt * M_TILE)) * a.n_ocb;
-        const bool fits = 128 + 2 * stage_bytes <= (size_t)smem_max && a.P <= 3 * LOADERS;
-        if (mt == 1 || (fits && ctas_mt >= sms)) { if (!fits) return tc_fail(TDC_ERR_SMEM, "two stages of %zu bytes do not fit in shared memory", stage_bytes); break; }
+    // 16-byte input loads: 1x1 filter, images a multiple of 4 positions long, 16-byte aligned base
+    const bool vec = taps == 1 && ((long long)H * W) % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
+    const bool ring = persist && !vec;                       // input staged through the raw cp.async ring
+    const char* env_depth = getenv("TDC_TC_DEPTH");
+    size_t stage_bytes = 0, raw_bytes = 0;
+    const size_t header = persist ? P_HEADER : 128;
+    // Position tiles per CTA: the largest candidate (4, 2, 1; what tensor memory and shared memory hold) that still
+    // gives every SM a tile.  One exception: when few position tiles share a large filter, streaming the filter
+    // from L2 once per tile is what bounds the launch; then a larger candidate is taken if the estimate below
+    // (shared-memory traffic at 128 bytes per clock per SM against filter bytes from L2) says it is faster.
+    const double op_bytes = a.hl == 2 ? (4096.0 + 64.0 * p->nt) + (4096.0 + 32.0 * p->nt) : 4096.0 + 32.0 * p->nt;   // per tap and position tile
+    const size_t room = (size_t)smem_max - header;
+    int best_mt = 0, big_mt = 0;
+    double best_cost = 0.0, big_cost = 0.0;
+    bool best_l2_bound = false;
+    for (int m = mt; m >= 1; m /= 2) {
+        const int P = ((m * M_TILE + 2 * pad * (a.Wp + 1)) + 7) / 8 * 8;
+        const size_t sb = sizeof(float) * ((size_t)a.hl * CB * P + (size_t)a.hl * taps * CB * p->nt);
+        const size_t rb = ring ? sizeof(float) * (size_t)CB * P : 0;
+        if (2 * sb + 2 * rb > room || P > 3 * LOADERS) continue;
+        const double ntl = (double)((a.total_pos + (long long)m * M_TILE - 1) / ((long long)m * M_TILE)) * a.n_ocb;
+        const double rounds = (double)(((long long)ntl + sms - 1) / sms);
+        const double tile_clk = a.nkb * (m * taps * op_bytes + (double)sb + 2.0 * rb) / 128.0 + 2000.0 * m * (p->nt / 32);
+        const double l2_clk = ntl * a.nkb * (double)(sizeof(float) * a.hl * taps * CB * p->nt) / 2900.0;
+        const double cost = rounds * tile_clk > l2_clk ? rounds * tile_clk : l2_clk;
+        if (big_mt == 0 || cost < big_cost) { big_mt = m; big_cost = cost; }          // cheapest of the candidates seen so far (all larger or equal)
+        best_mt = m; best_cost = cost; best_l2_bound = l2_clk > rounds * tile_clk;
+        if (ntl >= sms) break;
     }
-    if (env_ns && atoi(env_ns) >= 2 && atoi(env_ns) <= 4 && 128 + atoi(env_ns) * stage_bytes <= (size_t)smem_max) ns = atoi(env_ns);
-    if (ns > a.nkb) ns = a.nkb > 0 ? a.nkb : 1;
+    if (best_mt != 0 && best_l2_bound && big_cost < best_cost) best_mt = big_mt;
+    if (best_mt == 0) return tc_fail(TDC_ERR_SMEM, "two stages of the %dx%d filter block do not fit in shared memory", p->R, p->S);
+    mt = best_mt;
+    // the persistent kernel double-buffers the accumulators when tensor memory has room for it
+    if (persist && 2 * mt * a.tile_cols <= 512 && !(env_nbuf && atoi(env_nbuf) == 1)) nbuf = 2;
+    a.P = ((mt * M_TILE + 2 * pad * (a.Wp + 1)) + 7) / 8 * 8;
+    stage_bytes = sizeof(float) * ((size_t)a.hl * CB * a.P + (size_t)a.hl * taps * CB * p->nt);
+    raw_bytes = ring ? sizeof(float) * (size_t)CB * a.P : 0;
+    if (ring) {
+        // three operand stages when at least four raw slots still fit beside them, else two; then as many raw slots as fit
+        ns = 3 * stage_bytes + 4 * raw_bytes <= room ? 3 : 2;
+        if (env_ns && atoi(env_ns) >= 2 && atoi(env_ns) <= 4 && atoi(env_ns) * stage_bytes + 2 * raw_bytes <= room) ns = atoi(env_ns);
+        depth = (int)((room - ns * stage_bytes) / raw_bytes);
+        if (depth > 8) depth = 8;
+        if (env_depth && atoi(env_depth) >= 2 && atoi(env_depth) <= depth) depth = atoi(env_depth);
+    } else {
+        const int ns_max = persist ? 4 : 3;
+        ns = 2;
+        while (ns < ns_max && (ns + 1) * stage_bytes <= room) ++ns;
+        if (env_ns && atoi(env_ns) >= 2 && atoi(env_ns) <= ns) ns = atoi(env_ns);
+    }
+    if (!persist && ns > a.nkb) ns = a.nkb > 0 ? a.nkb : 1;
     a.ns = ns;
+    a.nbuf = nbuf;
+    a.depth = depth;
     a.tmem_cols = 32;
-    while (a.tmem_cols < mt * a.tile_cols) a.tmem_cols *= 2;
-    const size_t smem = 128 + ns * stage_bytes;
+    while (a.tmem_cols < nbuf * mt * a.tile_cols) a.tmem_cols *= 2;
+    const size_t smem = header + ns * stage_bytes + depth * raw_bytes;
     void* status_ptr = nullptr;
     e = cudaGetSymbolAddress(&status_ptr, g_tc_status);
     if (e != cudaSuccess) return tc_fail(TDC_ERR_CUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
     a.status = (int*)status_ptr;
     const long long tiles = (a.total_pos + (long long)mt * M_TILE - 1) / ((long long)mt * M_TILE);
-    const long long ctas = tiles * a.n_ocb;
-    if (ctas >= (1ll << 31)) return tc_fail(TDC_ERR_TILE, "grid too large");
+    a.ntiles = tiles * a.n_ocb;
+    if (a.ntiles >= (1ll << 31)) return tc_fail(TDC_ERR_TILE, "grid too large");
+    const long long ctas = persist ? (a.ntiles < sms ? a.ntiles : sms) : a.ntiles;
+    const int threads = persist ? P_THREADS : THREADS;
     const void* fn = nullptr;
-    // 16-byte input loads: 1x1 filter, images a multiple of 4 positions long, 16-byte aligned base
-    const bool vec = taps == 1 && ((long long)H * W) % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
-#define TDC_TC_PICK(NT_, MT_) (taps == 9 ? (const void*)&conv_tc_kernel<NT_, MT_, 9, false> : \
-                               (vec ? (const void*)&conv_tc_kernel<NT_, MT_, 1, true> : (const void*)&conv_tc_kernel<NT_, MT_, 1, false>))
+#define TDC_TC_PICK3(KERNEL, NT_, MT_) (taps == 9 ? (const void*)&KERNEL<NT_, MT_, 9, false> : \
+                                        (vec ? (const void*)&KERNEL<NT_, MT_, 1, true> : (const void*)&KERNEL<NT_, MT_, 1, false>))
+#define TDC_TC_PICK(NT_, MT_) (persist ? TDC_TC_PICK3(conv_tc_persist_kernel, NT_, MT_) : TDC_TC_PICK3(conv_tc_kernel, NT_, MT_))
     if (p->nt == 128) fn = mt == 2 ? TDC_TC_PICK(128, 2) : TDC_TC_PICK(128, 1);
     else if (p->nt == 64) fn = mt == 4 ? TDC_TC_PICK(64, 4) : (mt == 2 ? TDC_TC_PICK(64, 2) : TDC_TC_PICK(64, 1));
     else fn = mt == 4 ? TDC_TC_PICK(32, 4) : (mt == 2 ? TDC_TC_PICK(32, 2) : TDC_TC_PICK(32, 1));
 #undef TDC_TC_PICK
+#undef TDC_TC_PICK3
     e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return tc_fail(TDC_ERR_CUDA, "cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(e));
     void* args[] = {&a};
-    e = cudaLaunchKernel(fn, dim3((unsigned)ctas), dim3(THREADS), args, smem, (cudaStream_t)stream);
+    e = cudaLaunchKernel(fn, dim3((unsigned)ctas), dim3(threads), args, smem, (cudaStream_t)stream);
     return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "launch: %s", cudaGetErrorString(e));
 }
 

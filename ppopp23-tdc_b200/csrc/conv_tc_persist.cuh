@@ -1,0 +1,292 @@
+// Persistent form of the tensor-core convolution kernel (included by conv_tc.cu, which holds
+// the description of the algorithm, the operand layouts and the helpers used here).
+//
+// One CTA per SM walks a list of tiles (tile = MT x 128 positions x NT output channels).
+// What a one-tile-per-CTA launch pays per tile — tensor-memory allocation, barrier set-up, a
+// cold first load, and an epilogue during which the tensor core idles — is paid once or hidden:
+//   * loaders (warps 0-7) never stop: the shared-memory stages are a ring that runs across tile
+//     boundaries, so the first channel blocks of the next tile are staged while the MMAs of
+//     this one finish;
+//   * the accumulators are double-buffered in tensor memory (when 2 x MT x columns-per-tile
+//     fits in 512 columns): issuers (lane 0 of warps 8..8+MT-1) start the next tile in the
+//     other buffer while the epilogue warps (12-15) drain this one;
+//   * the epilogue releases its buffer as soon as the values are in registers and only then
+//     does its global stores.
+// Every mbarrier wait is bounded; a wait that runs out raises the CTA's abort flag, every
+// role leaves its loop at the next check, the status word is set and tensor memory is freed.
+#pragma once
+
+namespace tdc_tc {
+
+constexpr int P_THREADS = 512;   // 8 loader warps, 4 issuer warps (one lane each), 4 epilogue warps
+constexpr int P_HEADER  = 256;   // bytes of barriers and flags in front of the stages
+
+template <int NT, int MT, int TAPS, bool VEC>
+__global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    uint64_t* full_bar   = reinterpret_cast<uint64_t*>(smem_raw);    // [ns]  patch stored + filter landed
+    uint64_t* empty_bar  = full_bar + 4;                              // [ns]  MMAs that read the stage are done
+    uint64_t* tfull_bar  = empty_bar + 4;                             // [nbuf*MT] the accumulators of a 128-position tile are complete
+    uint64_t* tempty_bar = tfull_bar + 8;                             // [nbuf*MT] the epilogue has read them
+    uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(tempty_bar + 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float*    stage0     = reinterpret_cast<float*>(smem_raw + P_HEADER);
+
+    constexpr int PPT = 3;
+    const int a_floats = a.hl * CB * a.P, b_floats = a.hl * TAPS * CB * NT, stage_floats = a_floats + b_floats;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int pad = (a.taps_r - 1) / 2;
+    const long long HW = (long long)a.H * a.W;
+    const uint32_t b_bytes = (uint32_t)b_floats * 4u;
+    const int nbuf = a.nbuf;
+    const long long ntiles = a.ntiles;          // position tiles x output-channel blocks
+
+    if (tid == 0) {
+        for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], LOADERS + 1); mbar_init(&empty_bar[s], MT); }
+        for (int b = 0; b < 8; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 128); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)a.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp < 8) {
+        // ================= loaders =================
+        long long it = 0;                        // channel blocks staged so far, over all tiles: stage = it % ns
+        auto open_stage = [&](const float* wt_tile, int kb) -> float* {
+            const int s = (int)(it % a.ns);
+            float* A = stage0 + (long long)s * stage_floats;
+            // use number u of this stage waits for the MMAs of use u-1; the first use passes at once
+            if (!mbar_wait(&empty_bar[s], (uint32_t)(((it / a.ns) & 1) ^ 1))) { *abort_flag = 1; return nullptr; }
+            if (tid == 0) {
+                mbar_expect_tx(&full_bar[s], b_bytes);
+                bulk_g2s(A + a_floats, wt_tile + (long long)kb * b_floats, b_bytes, &full_bar[s]);
+            }
+            return A;
+        };
+        auto close_stage = [&]() {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[it % a.ns])) : "memory");
+            ++it;
+        };
+        auto put = [&](float* A, int q, int pp, float c0, float c1, float c2, float c3) {
+            float4 hi;
+            hi.x = to_tf32(c0); hi.y = to_tf32(c1); hi.z = to_tf32(c2); hi.w = to_tf32(c3);
+            *reinterpret_cast<float4*>(A + ((q * a.P + pp) << 2)) = hi;
+            if (a.hl == 2)
+                *reinterpret_cast<float4*>(A + CB * a.P + ((q * a.P + pp) << 2)) = make_float4(c0 - hi.x, c1 - hi.y, c2 - hi.z, c3 - hi.w);
+        };
+        if constexpr (VEC) {
+            // 1x1 filter, H*W a multiple of 4: a thread owns 4 consecutive positions x 4 channels of a block;
+            // four 16-byte loads (one per channel), transposed in registers into four 16-byte stores
+            for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x) {
+                const int ocb = (int)(t % a.n_ocb);
+                const long long g0 = (t / a.n_ocb) * (MT * M_TILE);
+                const float* wt_tile = a.wt + (long long)ocb * a.nkb * b_floats;
+                bool ok = true;
+                constexpr int NI = (MT * M_TILE / 2 + LOADERS - 1) / LOADERS;
+                long long off[NI];
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    const int quad = (tid + i * LOADERS) >> 1;
+                    off[i] = -1;
+                    if (quad * 4 < a.P) {
+                        const long long g = g0 + quad * 4;
+                        if (g < a.total_pos) { const long long b = g / a.Lp; off[i] = b * a.C * HW + (g - b * a.Lp); }
+                    }
+                }
+                float4 va[NI][4], vb[NI][4];
+                auto load = [&](int kb, float4 (&v)[NI][4]) {
+#pragma unroll
+                    for (int i = 0; i < NI; ++i) {
+                        const int c0 = kb * CB + ((tid + i * LOADERS) & 1) * 4;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            v[i][j] = (off[i] >= 0 && c0 + j < a.C) ? __ldg(reinterpret_cast<const float4*>(a.x + off[i] + (long long)(c0 + j) * HW))
+                                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                };
+                auto stage = [&](int kb, float4 (&v)[NI][4]) -> bool {
+                    float* A = open_stage(wt_tile, kb);
+                    if (!A) return false;
+#pragma unroll
+                    for (int i = 0; i < NI; ++i) {
+                        const int item = tid + i * LOADERS, q = item & 1, pp = (item >> 1) * 4;
+                        if (pp < a.P) {
+                            put(A, q, pp + 0, v[i][0].x, v[i][1].x, v[i][2].x, v[i][3].x);
+                            put(A, q, pp + 1, v[i][0].y, v[i][1].y, v[i][2].y, v[i][3].y);
+                            put(A, q, pp + 2, v[i][0].z, v[i][1].z, v[i][2].z, v[i][3].z);
+                            put(A, q, pp + 3, v[i][0].w, v[i][1].w, v[i][2].w, v[i][3].w);
+                        }
+                    }
+                    close_stage();
+                    return true;
+                };
+                load(0, va);
+                if (a.nkb > 1) load(1, vb);
+                for (int kb = 0; kb < a.nkb && ok; kb += 2) {
+                    ok = stage(kb, va);
+                    if (ok && kb + 2 < a.nkb) load(kb + 2, va);
+                    if (ok && kb + 1 < a.nkb) {
+                        ok = stage(kb + 1, vb);
+                        if (ok && kb + 3 < a.nkb) load(kb + 3, vb);
+                    }
+                }
+                if (!ok) break;
+            }
+        } else {
+            // The input goes global -> (cp.async, 4 bytes, zero-filled where the patch is padding) -> a ring of
+            // raw fp32 slots in shared memory -> registers -> hi/lo split -> operand layout.  A thread copies and
+            // later converts the SAME patch rows, so the ring needs no barrier, only cp.async.wait_group; it runs
+            // `depth` channel blocks ahead and straight across tile boundaries, which keeps enough bytes in
+            // flight to cover the memory latency and leaves no cold start at the beginning of a tile.
+            float* raw0 = stage0 + (long long)a.ns * stage_floats;
+            const int raw_floats = CB * a.P, depth = a.depth;
+            const long long my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+            const long long total = my_tiles * a.nkb;
+            long long src_off[PPT];              // of the tile being copied: offset of channel 0 of each owned row, -1 = zeros
+            long long l_tile = blockIdx.x;       // copy side: tile and channel block of the next block to issue
+            int l_kb = 0;
+            auto issue = [&](long long li) {
+                if (li < total) {
+                    if (l_kb == 0) {
+                        const long long gp0 = (l_tile / a.n_ocb) * (MT * M_TILE) - (long long)pad * (a.Wp + 1);
+#pragma unroll
+                        for (int i = 0; i < PPT; ++i) {
+                            const int pp = tid + i * LOADERS;
+                            src_off[i] = -1;
+                            if (pp < a.P) {
+                                const long long g = gp0 + pp;
+                                if (g >= 0 && g < a.total_pos) {
+                                    const long long b = g / a.Lp;
+                                    const int rem = (int)(g - b * a.Lp);
+                                    const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
+                                    if (yy < a.H && xx < a.W) src_off[i] = b * a.C * HW + (long long)yy * a.W + xx;
+                                }
+                            }
+                        }
+                    }
+                    float* R = raw0 + (li % depth) * raw_floats;
+                    const int c0 = l_kb * CB;
+#pragma unroll
+                    for (int i = 0; i < PPT; ++i) {
+                        const int pp = tid + i * LOADERS;
+                        if (pp < a.P) {
+                            const float* src = a.x + (src_off[i] >= 0 ? src_off[i] + (long long)c0 * HW : 0);
+#pragma unroll
+                            for (int j = 0; j < CB; ++j) {
+                                const bool real = src_off[i] >= 0 && c0 + j < a.C;
+                                cp_async4(R + j * a.P + pp, real ? src + (long long)j * HW : a.x, real);
+                            }
+                        }
+                    }
+                    if (++l_kb == a.nkb) { l_kb = 0; l_tile += gridDim.x; }
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");      // an empty group past the end keeps the count uniform
+            };
+            for (int d = 0; d < depth; ++d) issue(d);
+            long long c_tile = blockIdx.x;
+            int c_kb = 0;
+            for (long long ci = 0; ci < total && !*abort_flag; ++ci) {
+                const float* wt_tile = a.wt + (c_tile % a.n_ocb) * a.nkb * b_floats;
+                float* A = open_stage(wt_tile, c_kb);
+                if (!A) break;
+                cp_async_wait_pending(depth - 1);                         // block ci has landed (this thread's part)
+                const float* R = raw0 + (ci % depth) * raw_floats;
+#pragma unroll
+                for (int i = 0; i < PPT; ++i) {
+                    const int pp = tid + i * LOADERS;
+                    if (pp < a.P) {
+#pragma unroll
+                        for (int q = 0; q < CB / 4; ++q)
+                            put(A, q, pp, R[(4 * q) * a.P + pp], R[(4 * q + 1) * a.P + pp], R[(4 * q + 2) * a.P + pp], R[(4 * q + 3) * a.P + pp]);
+                    }
+                }
+                close_stage();
+                issue(ci + depth);                                         // the slot just read is free again
+                if (++c_kb == a.nkb) { c_kb = 0; c_tile += gridDim.x; }
+            }
+            asm volatile("cp.async.wait_all;" ::: "memory");
+        }
+    }
+    else if (warp < 12) {
+        // ================= MMA issuers: warp 8+mt owns position tile mt =================
+        const int mt = __shfl_sync(0xffffffffu, warp - 8, 0);
+        if (mt < MT) {
+            long long it = 0, j = 0;            // channel blocks consumed so far; tiles done by this CTA
+            for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x, ++j) {
+                const int slot = (int)(j % nbuf) * MT + mt;
+                // the epilogue must have emptied this accumulator slot (its previous use); the first use passes at once
+                if (!mbar_wait(&tempty_bar[slot], (uint32_t)(((j / nbuf) & 1) ^ 1))) { *abort_flag = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d_main = tmem + (uint32_t)(slot * a.tile_cols);
+                bool ok = true;
+                for (int kb = 0; kb < a.nkb; ++kb, ++it) {
+                    const int s = (int)(it % a.ns);
+                    if (!mbar_wait(&full_bar[s], (uint32_t)((it / a.ns) & 1))) { *abort_flag = 1; ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const float* A = stage0 + (long long)s * stage_floats;
+                    if (elect_one()) {
+                        issue_block<NT, TAPS>(a, d_main, smem_u32(A), smem_u32(A + a_floats), (uint32_t)(mt * M_TILE), kb & 1, kb < 2 && (kb == 0 || a.nmain == 2));
+                        mma_commit(&empty_bar[s]);                        // the stage may be refilled when these MMAs are done
+                        if (kb + 1 == a.nkb) mma_commit(&tfull_bar[slot]); // and this position tile's accumulators are complete
+                    }
+                    __syncwarp();
+                }
+                if (!ok) break;
+            }
+        }
+    } else {
+        // ================= epilogue: warps 12-15, one lane quarter of tensor memory each =================
+        const int q = warp & 3;
+        constexpr int CHUNKS = NT / 32;
+        long long j = 0;
+        for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x, ++j) {
+            const int ocb = (int)(t % a.n_ocb);
+            const long long g0 = (t / a.n_ocb) * (MT * M_TILE);
+            bool ok = true;
+#pragma unroll 1
+            for (int mt = 0; mt < MT && ok; ++mt) {
+                // the position tiles of a CTA tile are handed over one by one: while this one is drained, the
+                // issuers of the others still run, and its own issuer may start on the next CTA tile
+                const int slot = (int)(j % nbuf) * MT + mt;
+                if (!mbar_wait(&tfull_bar[slot], (uint32_t)((j / nbuf) & 1))) { *abort_flag = 1; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const long long g = g0 + mt * M_TILE + q * 32 + lane;
+                long long out_off = -1;
+                if (g < a.total_pos) {
+                    const long long b = g / a.Lp;
+                    const int rem = (int)(g - b * a.Lp);
+                    const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
+                    if (yy < a.H && xx < a.W) out_off = b * a.K * HW + (long long)yy * a.W + xx;
+                }
+#pragma unroll 1
+                for (int chunk = 0; chunk < CHUNKS; ++chunk) {
+                    uint32_t r[32];
+                    load_chunk<NT>(a, tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * a.tile_cols + chunk * 32), r);
+                    if (chunk == CHUNKS - 1) {
+                        // everything of this slot is in registers: hand it back before the stores
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tempty_bar[slot])) : "memory");
+                    }
+                    store_chunk(a, r, out_off, ocb * NT + chunk * 32, HW);
+                }
+            }
+            if (!ok) break;
+        }
+    }
+
+    __syncwarp();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*abort_flag && tid == 0 && a.status) atomicCAS(a.status, 0, 1);
+    if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)a.tmem_cols) : "memory");
+}
+
+}  // namespace tdc_tc

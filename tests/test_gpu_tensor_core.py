@@ -103,3 +103,41 @@ def test_module_and_network_precisions(T):
         a = net(xin)
         b = net.set_precision("auto")(xin)
     assert rel_err(b.cpu().numpy(), a.cpu().numpy()) <= 1e-4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,Cc,K,H,W,R", [(1, 3, 5, 1, 1, 1), (2, 7, 9, 2, 3, 3), (5, 33, 130, 9, 13, 3), (70, 24, 40, 14, 14, 3),
+                                           (9, 64, 64, 56, 56, 3), (300, 16, 32, 7, 7, 3), (33, 40, 64, 15, 15, 1), (16, 32, 32, 28, 28, 1)])
+def test_persistent_and_one_tile_kernels_agree(T, B, Cc, K, H, W, R, monkeypatch):
+    """The launcher has two kernels (one tile per CTA; persistent CTAs walking a tile list with the accumulators
+    handed over tile by tile).  Both are forced in turn through the environment switch the launcher reads per call,
+    with and without the fused epilogue, on shapes with fewer tiles than SMs, several tiles per CTA, ragged channel
+    counts and one-pixel images: same arithmetic in the same order, so the outputs must be bit-identical, and the
+    persistent one is checked against the fp64 arbiter on sampled images."""
+    from tdc_b200 import tc
+    x, w = draw_core(900 + B + Cc + H, B, Cc, K, H, W, R)
+    g = torch.Generator().manual_seed(B + K)
+    scale, shift = (torch.rand(K, generator=g) + 0.5).cuda(), torch.randn(K, generator=g).cuda()
+    res = torch.randn(B, K, H, W, generator=g).cuda()
+    xd, wd = x.cuda(), w.cuda()
+    sel = sorted({0, B // 2, B - 1})
+    ref = O.conv2d_f64(x[sel].numpy(), w.numpy(), pad=(R - 1) // 2)
+    for mode, tol in ((3, FP32_TOL), (1, TF32_TOL)):
+        conv = T.TcConv(wd, mode=mode)
+        out = {}
+        for persist in ("0", "1"):
+            monkeypatch.setenv("TDC_TC_PERSIST", persist)
+            out[persist] = (conv(xd).clone(), conv(xd, scale, shift, res, True).clone())
+        assert torch.equal(out["0"][0], out["1"][0]) and torch.equal(out["0"][1], out["1"][1]), mode
+        assert rel_err(out["1"][0][sel].cpu().numpy(), ref) <= tol
+        want = np.maximum(ref * scale.cpu().numpy()[None, :, None, None] + shift.cpu().numpy()[None, :, None, None] + res[sel].cpu().numpy(), 0)
+        assert rel_err(out["1"][1][sel].cpu().numpy(), want) <= tol
+        if mode == 3:
+            y3 = out["1"][0]
+    for knobs in ({"TDC_TC_MT": "1"}, {"TDC_TC_MT": "2", "TDC_TC_NBUF": "1"}, {"TDC_TC_NS": "2", "TDC_TC_DEPTH": "2"}):
+        for k, v in knobs.items():
+            monkeypatch.setenv(k, v)
+        assert torch.equal(T.TcConv(wd, mode=3)(xd), y3), knobs      # tile count, buffers and ring depth change no bit
+        for k in knobs:
+            monkeypatch.delenv(k)
+    assert tc.status() == 0
