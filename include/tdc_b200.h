@@ -242,7 +242,9 @@ TDC_API int tdc_tk_block_f32_static(const float* x, const float* w1, const float
  * counterpart in the reference, whose kernel and whose cuDNN calls are fp32 FMA code
  * (template_benchmark_cudnn.template:365-402; inference/TKConv.py:92-93).  Same result
  * definition as tdc_conv2d_epi_f32 for "same" convolutions: R = S in {1, 3}, stride 1,
- * pad = (R-1)/2.
+ * pad = (R-1)/2; a 1x1 filter may also be strided (the down-sampling shortcut of a residual
+ * stage, inference/resnet_inet_tt.py:27-29,363-366): `flags` carries stride - 1 in its low four bits,
+ * H and W are the input image, y is [B][K][(H-1)/stride+1][(W-1)/stride+1].
  *   mode 3  "3xTF32": operands split into hi + lo TF32 parts, three MMAs per product;
  *           fp32-level accuracy (held to the same 1e-5 bar as the fp32 kernels)
  *   mode 1  plain TF32: one MMA per product; 5e-3 bar; reported separately
@@ -263,8 +265,9 @@ typedef struct tdc_tc_plan {
 TDC_API const char* tdc_tc_last_error_string(void);
 TDC_API int tdc_tc_plan_make(int C, int K, int R, int S, int mode, tdc_tc_plan* out);
 TDC_API int tdc_tc_prepare_weights(const tdc_tc_plan* plan, const float* w, int w_layout, void* wt, void* stream);
+#define TDC_TC_STRIDE_MASK 0xF   /* flags & mask = stride - 1 (1x1 filters only); other bits must be 0 */
 TDC_API int tdc_conv2d_tc(const tdc_tc_plan* plan, const float* x, const void* wt, float* y,
-                          int B, int H, int W, const tdc_epilogue* epi, int flags /* 0 */, void* stream);
+                          int B, int H, int W, const tdc_epilogue* epi, int flags, void* stream);
 TDC_API int tdc_tc_status(int* out);
 
 /*

@@ -49,7 +49,9 @@ struct Args {
     float*       y;        // [B][K][H][W]
     const float* scale; const float* bias; const float* residual;
     int relu;
-    int B, C, H, W, K;
+    int B, C, H, W, K;     // H, W: the OUTPUT image (equal to the input image unless a 1x1 filter is strided)
+    int stride, Win;       // input step per output position and input row length
+    long long HWin;        // input image size (channel pitch of x)
     int taps_r;            // R (= S): 1 or 3
     int Wp, Lp;            // row pitch and positions per image of the padded position space
     int P;                 // patch rows staged per CTA (multiple of 8)
@@ -226,26 +228,48 @@ __device__ __forceinline__ void load_chunk(const Args& a, uint32_t taddr, uint32
 
 // ... and registers -> y (NCHW: the lanes of a warp hold consecutive positions, so every
 // store instruction writes one contiguous run).  `out_off` < 0: the position is padding.
+// Called by whole warps.  With the fused options, lane k fetches scale and bias of channel
+// oc0 + k once and the others get them by shuffle, and the 32 residual values are loaded
+// before the first store (y and the residual may be the same buffer as far as the compiler
+// knows, so loads placed between the stores would each wait out a memory round trip).
 __device__ __forceinline__ void store_chunk(const Args& a, const uint32_t (&r)[32], long long out_off, int oc0, long long HW) {
-    if (out_off < 0) return;
-    const long long o0 = out_off + (long long)oc0 * HW;
+    const int lane = threadIdx.x & 31;
+    const bool live = out_off >= 0;
+    const long long o0 = (live ? out_off : 0) + (long long)oc0 * HW;
     float* yp = a.y + o0;
     const int n = a.K - oc0;                      // channels of this chunk that exist
     if (n >= 32 && !a.scale && !a.bias && !a.residual && !a.relu) {
+        if (live) {
 #pragma unroll
-        for (int k = 0; k < 32; ++k) { *yp = __uint_as_float(r[k]); yp += HW; }
-    } else {
-        const float* rp = a.residual ? a.residual + o0 : nullptr;
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-            if (k < n) {
-                float val = __uint_as_float(r[k]);
-                if (a.scale) val *= __ldg(a.scale + oc0 + k);
-                if (a.bias) val += __ldg(a.bias + oc0 + k);
-                if (rp) val += rp[k * HW];
-                yp[k * HW] = a.relu ? fmaxf(val, 0.f) : val;
-            }
+            for (int k = 0; k < 32; ++k) { *yp = __uint_as_float(r[k]); yp += HW; }
         }
+        return;
+    }
+    const float sc = (a.scale && lane < n) ? __ldg(a.scale + oc0 + lane) : 1.f;
+    const float bi = (a.bias && lane < n) ? __ldg(a.bias + oc0 + lane) : 0.f;
+    float v[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) v[k] = __uint_as_float(r[k]);
+    if (a.scale) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v[k] *= __shfl_sync(0xffffffffu, sc, k);
+    }
+    if (a.bias) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v[k] += __shfl_sync(0xffffffffu, bi, k);
+    }
+    if (a.residual && live) {
+        const float* rp = a.residual + o0;
+        float rv[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) rv[k] = k < n ? rp[k * HW] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v[k] += rv[k];
+    }
+    if (live) {
+#pragma unroll
+        for (int k = 0; k < 32; ++k)
+            if (k < n) yp[k * HW] = a.relu ? fmaxf(v[k], 0.f) : v[k];
     }
 }
 
@@ -396,7 +420,7 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
                         const long long b = g / a.Lp;
                         const int rem = (int)(g - b * a.Lp);
                         const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
-                        if (yy < a.H && xx < a.W) src_off[i] = b * a.C * HW + (long long)yy * a.W + xx;
+                        if (yy < a.H && xx < a.W) src_off[i] = b * a.C * a.HWin + (long long)(yy * a.stride) * a.Win + xx * a.stride;
                     }
                 }
             }
@@ -407,7 +431,7 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
                 for (int i = 0; i < PPT; ++i)
 #pragma unroll
                     for (int j = 0; j < CB; ++j)
-                        v[i][j] = (src_off[i] >= 0 && c0 + j < a.C) ? __ldg(a.x + src_off[i] + (long long)(c0 + j) * HW) : 0.f;
+                        v[i][j] = (src_off[i] >= 0 && c0 + j < a.C) ? __ldg(a.x + src_off[i] + (long long)(c0 + j) * a.HWin) : 0.f;
             };
             auto stage = [&](int kb, float (&v)[PPT][CB]) -> bool {
                 float* A = open_stage(kb);
@@ -569,11 +593,16 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
                   const tdc_epilogue* epi, int flags, void* stream) {
     if (!p || !x || !wt || !y) return tc_fail(TDC_ERR_NULL, "plan, x, wt and y must be non-NULL");
     if (B <= 0 || H <= 0 || W <= 0) return tc_fail(TDC_ERR_SHAPE, "B=%d H=%d W=%d", B, H, W);
-    if (flags != 0) return tc_fail(TDC_ERR_UNSUPPORTED, "flags must be 0");
+    const int stride = (flags & TDC_TC_STRIDE_MASK) + 1;
+    if (flags & ~TDC_TC_STRIDE_MASK) return tc_fail(TDC_ERR_UNSUPPORTED, "unknown flag bits %#x", flags & ~TDC_TC_STRIDE_MASK);
+    if (stride > 1 && p->R != 1) return tc_fail(TDC_ERR_UNSUPPORTED, "a stride is taken for 1x1 filters only");
     using namespace tdc_tc;
     Args a{};
     a.x = x; a.wt = (const float*)wt; a.y = y;
     if (epi) { a.scale = epi->scale; a.bias = epi->bias; a.residual = epi->residual; a.relu = epi->relu ? 1 : 0; }
+    // from here on H and W are the output image; the input image is only an address pattern of the loaders
+    a.stride = stride; a.Win = W; a.HWin = (long long)H * W;
+    H = (H - 1) / stride + 1; W = (W - 1) / stride + 1;
     a.B = B; a.C = p->C; a.H = H; a.W = W; a.K = p->K; a.taps_r = p->R;
     const int pad = (p->R - 1) / 2;
     a.Wp = W + pad;                       // one shared zero column per row when the filter has a halo
@@ -605,7 +634,7 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     int mt = 512 / a.tile_cols > 4 ? 4 : 512 / a.tile_cols, ns = 0, depth = 0, nbuf = 1;   // tensor memory: 512 columns
     if (env_mt && atoi(env_mt) >= 1) while (mt > atoi(env_mt)) mt /= 2;
     // 16-byte input loads: 1x1 filter, images a multiple of 4 positions long, 16-byte aligned base
-    const bool vec = taps == 1 && ((long long)H * W) % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
+    const bool vec = taps == 1 && stride == 1 && ((long long)H * W) % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
     const bool ring = persist && !vec;                       // input staged through the raw cp.async ring
     const char* env_depth = getenv("TDC_TC_DEPTH");
     size_t stage_bytes = 0, raw_bytes = 0;

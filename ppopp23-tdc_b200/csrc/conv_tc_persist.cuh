@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                                     const long long b = g / a.Lp;
                                     const int rem = (int)(g - b * a.Lp);
                                     const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
-                                    if (yy < a.H && xx < a.W) src_off[i] = b * a.C * HW + (long long)yy * a.W + xx;
+                                    if (yy < a.H && xx < a.W) src_off[i] = b * a.C * a.HWin + (long long)(yy * a.stride) * a.Win + xx * a.stride;
                                 }
                             }
                         }
@@ -178,11 +178,11 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     for (int i = 0; i < PPT; ++i) {
                         const int pp = tid + i * LOADERS;
                         if (pp < a.P) {
-                            const float* src = a.x + (src_off[i] >= 0 ? src_off[i] + (long long)c0 * HW : 0);
+                            const float* src = a.x + (src_off[i] >= 0 ? src_off[i] + (long long)c0 * a.HWin : 0);
 #pragma unroll
                             for (int j = 0; j < CB; ++j) {
                                 const bool real = src_off[i] >= 0 && c0 + j < a.C;
-                                cp_async4(R + j * a.P + pp, real ? src + (long long)j * HW : a.x, real);
+                                cp_async4(R + j * a.P + pp, real ? src + (long long)j * a.HWin : a.x, real);
                             }
                         }
                     }

@@ -72,14 +72,14 @@ def _fold_bn_now(bn):
 
 def _one_conv(owner, name, x, w_kcrs, w_crsk, scale, shift, residual, relu, stride, padding, precision):
     """One convolution with its epilogue on the kernel that suits it: tensor cores (3xTF32) for
-    stride-1 1x1 / 3x3 layers with enough work to fill the GPU when `precision` allows, the fp32
+    stride-1 3x3 and any 1x1 layers with enough work to fill the GPU when `precision` allows, the fp32
     kernel with a table tile otherwise."""
     from . import tc
     B, Cc, H, W = x.shape
     K, _, R, S = w_kcrs.shape
     if precision != "fp32" and tc.supported(R, S, stride, padding, W) and \
-            (precision != "auto" or tc.worthwhile(B, Cc, H, W, K, R)):
-        return tc.cached(owner, name, w_kcrs, 1 if precision == "tf32" else 3)(x, scale, shift, residual, relu)
+            (precision != "auto" or tc.worthwhile(B, Cc, (H - 1) // stride + 1, (W - 1) // stride + 1, K, R)):
+        return tc.cached(owner, name, w_kcrs, 1 if precision == "tf32" else 3)(x, scale, shift, residual, relu, stride=stride)
     tile = tiles.table_tile(B, Cc, H, W, K, R, S, padding, stride)
     if w_crsk is not None:
         return ops.conv2d_epi(x, w_crsk, scale, shift, residual, relu, stride, padding, w_layout=W_CRSK, tile=tile)

@@ -34,12 +34,16 @@ class TcConv:
             _check(lib.tdc_tc_prepare_weights(C.byref(self.plan), _dev_f32(weight, "weight"), w_layout,
                                               self.wt.data_ptr(), _stream()))
 
-    def __call__(self, x, scale=None, bias=None, residual=None, relu=False, out=None, flags=0):
+    def __call__(self, x, scale=None, bias=None, residual=None, relu=False, out=None, stride=1):
+        """`stride` > 1 is taken for 1x1 filters only (the down-sampling shortcut of a residual stage)."""
         B, Cc, H, W = x.shape
         if Cc != self.C:
             raise TdcError(_lib.ERR_SHAPE, "x has %d channels, the filter expects %d" % (Cc, self.C))
+        if not 1 <= stride <= 16:
+            raise TdcError(_lib.ERR_UNSUPPORTED, "stride %d" % stride)
+        flags = stride - 1
         if out is None:
-            out = torch.empty((B, self.K, H, W), device=x.device, dtype=torch.float32)
+            out = torch.empty((B, self.K, (H - 1) // stride + 1, (W - 1) // stride + 1), device=x.device, dtype=torch.float32)
         e = _epilogue(scale, bias, residual, relu)
         with torch.cuda.device(x.device):
             _check(lib.tdc_conv2d_tc(C.byref(self.plan), _dev_f32(x, "x"), self.wt.data_ptr(), _dev_f32(out, "out"),
@@ -49,7 +53,7 @@ class TcConv:
 
 def supported(R, S, stride, padding, W):
     """True when the tensor-core variant is built for this convolution."""
-    return R == S and R in (1, 3) and stride == 1 and padding == (R - 1) // 2 and W <= 256
+    return R == S and R in (1, 3) and (stride == 1 or (R == 1 and 1 <= stride <= 16)) and padding == (R - 1) // 2 and W <= 256 * stride
 
 
 def worthwhile(B, C, H, W, K, R):

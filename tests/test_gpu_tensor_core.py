@@ -141,3 +141,28 @@ def test_persistent_and_one_tile_kernels_agree(T, B, Cc, K, H, W, R, monkeypatch
         for k in knobs:
             monkeypatch.delenv(k)
     assert tc.status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,Cc,K,H,W,stride", [(4, 64, 128, 56, 56, 2), (3, 24, 40, 15, 13, 2), (2, 16, 32, 9, 9, 3), (70, 128, 256, 28, 28, 2)])
+def test_strided_1x1_shortcut(T, B, Cc, K, H, W, stride, monkeypatch):
+    """The down-sampling shortcut of a residual stage (a 1x1 filter with a stride): both kernels, both modes,
+    with the folded-BatchNorm epilogue, against the fp64 arbiter."""
+    from tdc_b200 import tc
+    x, w = draw_core(1300 + B + Cc + H, B, Cc, K, H, W, 1)
+    g = torch.Generator().manual_seed(K)
+    scale, shift = (torch.rand(K, generator=g) + 0.5).cuda(), torch.randn(K, generator=g).cuda()
+    sel = sorted({0, B // 2, B - 1})
+    ref = O.conv2d_f64(x[sel].numpy(), w.numpy(), pad=0, stride=stride)
+    want = ref * scale.cpu().numpy()[None, :, None, None] + shift.cpu().numpy()[None, :, None, None]
+    assert tc.supported(1, 1, stride, 0, W) and not tc.supported(3, 3, stride, 1, W)
+    for mode, tol in ((3, FP32_TOL), (1, TF32_TOL)):
+        conv = T.TcConv(w.cuda(), mode=mode)
+        for persist in ("0", "1"):
+            monkeypatch.setenv("TDC_TC_PERSIST", persist)
+            y = conv(x.cuda(), scale, shift, stride=stride)
+            assert tuple(y.shape) == (B, K, (H - 1) // stride + 1, (W - 1) // stride + 1)
+            assert rel_err(y[sel].cpu().numpy(), want) <= tol, (mode, persist)
+    with pytest.raises(T.TdcError):
+        T.TcConv(torch.zeros(8, 8, 3, 3).cuda())(x.cuda()[:, :8], stride=2)
+    assert tc.status() == 0
