@@ -259,16 +259,37 @@ typedef struct tdc_tc_plan {
     int    cb;            /* channels per stage (one K step = 8)          */
     int    nkb, n_ocb;    /* channel blocks, output-channel blocks        */
     int    hl;            /* 2 when operands are split (mode 3), else 1   */
+    int    general;       /* 1: made by tdc_tc_plan_make_general          */
     size_t weights_bytes; /* size of the pre-arranged filter              */
 } tdc_tc_plan;
 
 TDC_API const char* tdc_tc_last_error_string(void);
 TDC_API int tdc_tc_plan_make(int C, int K, int R, int S, int mode, tdc_tc_plan* out);
+/* A plan for ANY filter size, stride and padding (the 7x7 stride-2 stem, the 3x3 stride-2 cores of the
+ * down-sampling blocks: inference/resnet_inet_tt.py:319-320,32-38): the contraction runs over
+ * (channel, filter row, filter column) triples gathered by the loaders, i.e. a classic implicit GEMM
+ * that re-reads the input R*S/stride^2 times from cache.  Stride and padding come with the call. */
+TDC_API int tdc_tc_plan_make_general(int C, int K, int R, int S, int mode, tdc_tc_plan* out);
 TDC_API int tdc_tc_prepare_weights(const tdc_tc_plan* plan, const float* w, int w_layout, void* wt, void* stream);
-#define TDC_TC_STRIDE_MASK 0xF   /* flags & mask = stride - 1 (1x1 filters only); other bits must be 0 */
+#define TDC_TC_STRIDE_MASK 0x0F  /* flags & mask = stride - 1 (1x1 filters and general plans)         */
+#define TDC_TC_PAD_MASK    0xF0  /* (flags & mask) >> 4 = padding (general plans); other bits must be 0 */
+#define TDC_TC_PAD_SHIFT   4
 TDC_API int tdc_conv2d_tc(const tdc_tc_plan* plan, const float* x, const void* wt, float* y,
                           int B, int H, int W, const tdc_epilogue* epi, int flags, void* stream);
 TDC_API int tdc_tc_status(int* out);
+
+/*
+ * Pooling layer of the end-to-end skeleton: Pool::initialize(b,c,h,w,pad,windowH,windowW,mode,stride) /
+ * Pool::forward (A100-evaluation/EndToEnd/resnet18-tk/src/Pool.cu:8-48, a cudnnPoolingForward call; the
+ * nn.MaxPool2d(3,2,1) of inference/resnet_inet_tt.py:323).  x [B][C][H][W] -> y [B][C][Ho][Wo] with
+ * Ho = (H - window_h + 2*pad)/stride + 1; padding never wins a maximum; NaNs are not propagated
+ * (CUDNN_NOT_PROPAGATE_NAN there).  Needs 2*pad <= window so that no window is all padding.
+ */
+#define TDC_POOL_MAX              0
+#define TDC_POOL_AVG_INCLUDE_PAD  1
+#define TDC_POOL_AVG_EXCLUDE_PAD  2
+TDC_API int tdc_pool2d_f32(const float* x, float* y, int B, int C, int H, int W, int window_h, int window_w,
+                           int pad, int stride, int mode, void* stream);
 
 /*
  * Layer objects with the surface of the reference's end-to-end classes:

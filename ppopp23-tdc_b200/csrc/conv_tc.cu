@@ -52,6 +52,7 @@ struct Args {
     int B, C, H, W, K;     // H, W: the OUTPUT image (equal to the input image unless a 1x1 filter is strided)
     int stride, Win;       // input step per output position and input row length
     long long HWin;        // input image size (channel pitch of x)
+    int gather, gR, gS, gpad, Hin;   // general plan: the channels the MMAs see are (input channel, filter row, filter column) triples
     int taps_r;            // R (= S): 1 or 3
     int Wp, Lp;            // row pitch and positions per image of the padded position space
     int P;                 // patch rows staged per CTA (multiple of 8)
@@ -313,9 +314,9 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
     const long long HW = (long long)a.H * a.W;
 
     if (tid == 0) {
-        // full: every loader thread arrives once, plus the arrive that announces the filter's bytes;
+        // full: every loader warp arrives once (lane 0, after the warp's stores), plus the arrive that announces the filter's bytes;
         // empty / done: one commit per issuing thread
-        for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], LOADERS + 1); mbar_init(&empty_bar[s], MT); }
+        for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], LOADERS / 32 + 1); mbar_init(&empty_bar[s], MT); }
         mbar_init(done_bar, MT);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -347,7 +348,8 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
         };
         auto close_stage = [&](int kb) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[kb % a.ns])) : "memory");
+            __syncwarp();                                                  // one arrival per warp: 8 instead of 256 updates of one barrier
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[kb % a.ns])) : "memory");
         };
         auto put = [&](float* A, int q, int pp, float c0, float c1, float c2, float c3) {   // 4 channels of one patch row
             float4 hi;
@@ -563,19 +565,32 @@ extern "C" {
 
 const char* tdc_tc_last_error_string(void) { return g_tc_err; }
 
-int tdc_tc_plan_make(int C, int K, int R, int S, int mode, tdc_tc_plan* out) {
+static int plan_fill(int C, int K, int R, int S, int mode, int general, tdc_tc_plan* out) {
     if (!out) return tc_fail(TDC_ERR_NULL, "out is NULL");
     if (C <= 0 || K <= 0) return tc_fail(TDC_ERR_SHAPE, "C=%d K=%d", C, K);
-    if (R != S || (R != 1 && R != 3)) return tc_fail(TDC_ERR_UNSUPPORTED, "the tensor-core path is built for 1x1 and 3x3 filters, not %dx%d", R, S);
     if (mode != 1 && mode != 3) return tc_fail(TDC_ERR_UNSUPPORTED, "mode %d (1 = TF32, 3 = 3xTF32)", mode);
     out->C = C; out->K = K; out->R = R; out->S = S; out->mode = mode;
     out->nt = pick_nt(K);
     out->cb = tdc_tc::CB;
-    out->nkb = cdiv(C, tdc_tc::CB);
+    // a general plan contracts over (channel, filter row, filter column) triples, one tap
+    out->nkb = cdiv(general ? C * R * S : C, tdc_tc::CB);
     out->n_ocb = cdiv(K, out->nt);
     out->hl = mode == 3 ? 2 : 1;
-    out->weights_bytes = sizeof(float) * (size_t)out->hl * R * S * tdc_tc::CB * out->nt * out->nkb * out->n_ocb;
+    out->general = general;
+    out->weights_bytes = sizeof(float) * (size_t)out->hl * (general ? 1 : R * S) * tdc_tc::CB * out->nt * out->nkb * out->n_ocb;
     return TDC_OK;
+}
+
+int tdc_tc_plan_make(int C, int K, int R, int S, int mode, tdc_tc_plan* out) {
+    if (R != S || (R != 1 && R != 3))
+        return tc_fail(TDC_ERR_UNSUPPORTED, "this plan is built for 1x1 and 3x3 filters, not %dx%d (tdc_tc_plan_make_general takes any)", R, S);
+    return plan_fill(C, K, R, S, mode, 0, out);
+}
+
+int tdc_tc_plan_make_general(int C, int K, int R, int S, int mode, tdc_tc_plan* out) {
+    if (R <= 0 || S <= 0 || R > 15 || S > 15) return tc_fail(TDC_ERR_SHAPE, "filter %dx%d", R, S);
+    if ((long long)C * R * S > (1 << 20)) return tc_fail(TDC_ERR_SHAPE, "C*R*S = %lld is too long a contraction", (long long)C * R * S);
+    return plan_fill(C, K, R, S, mode, 1, out);
 }
 
 int tdc_tc_prepare_weights(const tdc_tc_plan* p, const float* w, int w_layout, void* wt, void* stream) {
@@ -583,8 +598,11 @@ int tdc_tc_prepare_weights(const tdc_tc_plan* p, const float* w, int w_layout, v
     if (w_layout != TDC_W_KCRS && w_layout != TDC_W_CRSK) return tc_fail(TDC_ERR_UNSUPPORTED, "w_layout %d", w_layout);
     long long n = (long long)(p->weights_bytes / sizeof(float));
     int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-    tdc_tc::prepare_weights_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(w, w_layout == TDC_W_KCRS, (float*)wt, p->C, p->K,
-                                                                           p->R * p->S, p->nt, p->nkb, p->n_ocb, p->hl);
+    // a general plan: the filter is a 1x1 filter over C*R*S channels; in both layouts channel, row and column are
+    // adjacent index digits, so the flattened filter is addressed exactly as a 1x1 one
+    const int Cw = p->general ? p->C * p->R * p->S : p->C, taps = p->general ? 1 : p->R * p->S;
+    tdc_tc::prepare_weights_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(w, w_layout == TDC_W_KCRS, (float*)wt, Cw, p->K,
+                                                                           taps, p->nt, p->nkb, p->n_ocb, p->hl);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "prepare launch: %s", cudaGetErrorString(e));
 }
@@ -593,24 +611,33 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
                   const tdc_epilogue* epi, int flags, void* stream) {
     if (!p || !x || !wt || !y) return tc_fail(TDC_ERR_NULL, "plan, x, wt and y must be non-NULL");
     if (B <= 0 || H <= 0 || W <= 0) return tc_fail(TDC_ERR_SHAPE, "B=%d H=%d W=%d", B, H, W);
-    const int stride = (flags & TDC_TC_STRIDE_MASK) + 1;
-    if (flags & ~TDC_TC_STRIDE_MASK) return tc_fail(TDC_ERR_UNSUPPORTED, "unknown flag bits %#x", flags & ~TDC_TC_STRIDE_MASK);
-    if (stride > 1 && p->R != 1) return tc_fail(TDC_ERR_UNSUPPORTED, "a stride is taken for 1x1 filters only");
+    const int stride = (flags & TDC_TC_STRIDE_MASK) + 1, gpad = (flags & TDC_TC_PAD_MASK) >> TDC_TC_PAD_SHIFT;
+    if (flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK)) return tc_fail(TDC_ERR_UNSUPPORTED, "unknown flag bits %#x", flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK));
+    if (!p->general && stride > 1 && p->R != 1) return tc_fail(TDC_ERR_UNSUPPORTED, "a stride is taken for 1x1 filters and general plans only");
+    if (!p->general && gpad != 0) return tc_fail(TDC_ERR_UNSUPPORTED, "a padding is taken for general plans only (the others pad (R-1)/2)");
     using namespace tdc_tc;
     Args a{};
     a.x = x; a.wt = (const float*)wt; a.y = y;
     if (epi) { a.scale = epi->scale; a.bias = epi->bias; a.residual = epi->residual; a.relu = epi->relu ? 1 : 0; }
     // from here on H and W are the output image; the input image is only an address pattern of the loaders
-    a.stride = stride; a.Win = W; a.HWin = (long long)H * W;
-    H = (H - 1) / stride + 1; W = (W - 1) / stride + 1;
-    a.B = B; a.C = p->C; a.H = H; a.W = W; a.K = p->K; a.taps_r = p->R;
-    const int pad = (p->R - 1) / 2;
+    a.stride = stride; a.Win = W; a.HWin = (long long)H * W; a.Hin = H;
+    if (p->general) {
+        a.gather = 1; a.gR = p->R; a.gS = p->S; a.gpad = gpad;
+        if (H + 2 * gpad < p->R || W + 2 * gpad < p->S) return tc_fail(TDC_ERR_SHAPE, "the %dx%d filter does not fit the padded %dx%d image", p->R, p->S, H, W);
+        H = (H + 2 * gpad - p->R) / stride + 1; W = (W + 2 * gpad - p->S) / stride + 1;
+        if ((long long)p->C * a.HWin >= (1ll << 31)) return tc_fail(TDC_ERR_SHAPE, "channels x image = %lld elements is too large for a general plan", (long long)p->C * a.HWin);
+    } else {
+        H = (H - 1) / stride + 1; W = (W - 1) / stride + 1;
+    }
+    const int taps_r = p->general ? 1 : p->R;     // filter size as the MMAs see it
+    a.B = B; a.C = p->general ? p->C * p->R * p->S : p->C; a.H = H; a.W = W; a.K = p->K; a.taps_r = taps_r;
+    const int pad = (taps_r - 1) / 2;
     a.Wp = W + pad;                       // one shared zero column per row when the filter has a halo
     a.Lp = (H + pad) * a.Wp;              // and one zero row after the image
     a.total_pos = (long long)B * a.Lp;
     if (W > 256) return tc_fail(TDC_ERR_UNSUPPORTED, "image width %d is too large for the tensor-core path (max 256)", W);
     a.nkb = p->nkb; a.n_ocb = p->n_ocb; a.hl = p->hl;
-    const int taps = p->R * p->S;
+    const int taps = taps_r * taps_r;
     int device;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return tc_fail(TDC_ERR_NO_DEVICE, "cudaGetDevice: %s", cudaGetErrorString(e));
@@ -630,11 +657,11 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     // output channels per block: prologue and epilogue would otherwise show).  With 128-channel blocks the
     // one-tile kernel, which drains tensor memory with all its warps, measured faster, and with plain TF32
     // operands two one-tile CTAs share an SM and overlap by themselves.  TDC_TC_PERSIST=0/1 forces either.
-    const bool persist = env_persist ? atoi(env_persist) != 0 : (p->nt <= 64 && a.hl == 2);
+    const bool persist = p->general || (env_persist ? atoi(env_persist) != 0 : (p->nt <= 64 && a.hl == 2));   // general plans: the persistent kernel only
     int mt = 512 / a.tile_cols > 4 ? 4 : 512 / a.tile_cols, ns = 0, depth = 0, nbuf = 1;   // tensor memory: 512 columns
     if (env_mt && atoi(env_mt) >= 1) while (mt > atoi(env_mt)) mt /= 2;
     // 16-byte input loads: 1x1 filter, images a multiple of 4 positions long, 16-byte aligned base
-    const bool vec = taps == 1 && stride == 1 && ((long long)H * W) % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
+    const bool vec = taps == 1 && !p->general && stride == 1 && ((long long)H * W) % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
     const bool ring = persist && !vec;                       // input staged through the raw cp.async ring
     const char* env_depth = getenv("TDC_TC_DEPTH");
     size_t stage_bytes = 0, raw_bytes = 0;

@@ -42,8 +42,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     const long long ntiles = a.ntiles;          // position tiles x output-channel blocks
 
     if (tid == 0) {
-        for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], LOADERS + 1); mbar_init(&empty_bar[s], MT); }
-        for (int b = 0; b < 8; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 128); }
+        for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], LOADERS / 32 + 1); mbar_init(&empty_bar[s], MT); }   // one arrival per loader warp + the filter's bytes
+        for (int b = 0; b < 8; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }             // one per issuer; one per epilogue warp
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -72,7 +72,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
         };
         auto close_stage = [&]() {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[it % a.ns])) : "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[it % a.ns])) : "memory");
             ++it;
         };
         auto put = [&](float* A, int q, int pp, float c0, float c1, float c2, float c3) {
@@ -153,36 +154,82 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             long long src_off[PPT];              // of the tile being copied: offset of channel 0 of each owned row, -1 = zeros
             long long l_tile = blockIdx.x;       // copy side: tile and channel block of the next block to issue
             int l_kb = 0;
+            // general plan (TAPS == 1 only): a "channel" is an (input channel, filter row, filter column) triple
+            // and a patch row is an output position, whose window starts at input (iy0, ix0), possibly outside
+            const float* rbase[PPT];             // x at (image, channel 0, iy0, ix0) of each owned row (only formed, never read, when outside)
+            int rmask[PPT];                      // bit dy: input row iy0 + dy exists; bit 16 + dx: input column ix0 + dx exists; 0 = no such position
+            int g_ci = 0, g_dy = 0, g_dx = 0;    // the triple of the next channel to copy
+            const int g_cin = (TAPS == 1 && a.gather) ? a.C / (a.gR * a.gS) : 0;
             auto issue = [&](long long li) {
                 if (li < total) {
-                    if (l_kb == 0) {
-                        const long long gp0 = (l_tile / a.n_ocb) * (MT * M_TILE) - (long long)pad * (a.Wp + 1);
+                    if (TAPS == 1 && a.gather) {
+                        if (l_kb == 0) {
+                            const long long g0 = (l_tile / a.n_ocb) * (MT * M_TILE);
 #pragma unroll
-                        for (int i = 0; i < PPT; ++i) {
-                            const int pp = tid + i * LOADERS;
-                            src_off[i] = -1;
-                            if (pp < a.P) {
-                                const long long g = gp0 + pp;
-                                if (g >= 0 && g < a.total_pos) {
+                            for (int i = 0; i < PPT; ++i) {
+                                const int pp = tid + i * LOADERS;
+                                rmask[i] = 0; rbase[i] = a.x;
+                                const long long g = g0 + pp;
+                                if (pp < a.P && g < a.total_pos) {
                                     const long long b = g / a.Lp;
                                     const int rem = (int)(g - b * a.Lp);
-                                    const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
-                                    if (yy < a.H && xx < a.W) src_off[i] = b * a.C * a.HWin + (long long)(yy * a.stride) * a.Win + xx * a.stride;
+                                    const int oy = rem / a.Wp, ox = rem - oy * a.Wp;
+                                    const int iy0 = oy * a.stride - a.gpad, ix0 = ox * a.stride - a.gpad;
+                                    int m = 0;
+                                    for (int d = 0; d < a.gR; ++d) m |= ((unsigned)(iy0 + d) < (unsigned)a.Hin) << d;
+                                    for (int d = 0; d < a.gS; ++d) m |= ((unsigned)(ix0 + d) < (unsigned)a.Win) << (16 + d);
+                                    rmask[i] = m;
+                                    rbase[i] = a.x + (b * g_cin * a.HWin + (long long)iy0 * a.Win + ix0);
+                                }
+                            }
+                            g_ci = g_dy = g_dx = 0;
+                        }
+                        const uint32_t dst0 = smem_u32(raw0 + (li % depth) * raw_floats) + (uint32_t)tid * 4u;
+#pragma unroll
+                        for (int j = 0; j < CB; ++j) {
+                            const int delta = g_ci * (int)a.HWin + g_dy * a.Win + g_dx;     // the host keeps channels x image below 2^31
+                            const int sel = g_ci < g_cin ? ((1 << g_dy) | (0x10000 << g_dx)) : -1;   // -1 never matches a mask
+#pragma unroll
+                            for (int i = 0; i < PPT; ++i) {
+                                if (tid + i * LOADERS < a.P) {
+                                    const bool real = (rmask[i] & sel) == sel;
+                                    const float* src = real ? rbase[i] + delta : a.x;
+                                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;"
+                                                 ::"r"(dst0 + (uint32_t)((j * a.P + i * LOADERS) * 4)), "l"(src), "r"(real ? 4u : 0u) : "memory");
+                                }
+                            }
+                            if (++g_dx == a.gS) { g_dx = 0; if (++g_dy == a.gR) { g_dy = 0; ++g_ci; } }
+                        }
+                    } else {
+                        if (l_kb == 0) {
+                            const long long gp0 = (l_tile / a.n_ocb) * (MT * M_TILE) - (long long)pad * (a.Wp + 1);
+#pragma unroll
+                            for (int i = 0; i < PPT; ++i) {
+                                const int pp = tid + i * LOADERS;
+                                src_off[i] = -1;
+                                if (pp < a.P) {
+                                    const long long g = gp0 + pp;
+                                    if (g >= 0 && g < a.total_pos) {
+                                        const long long b = g / a.Lp;
+                                        const int rem = (int)(g - b * a.Lp);
+                                        const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
+                                        if (yy < a.H && xx < a.W) src_off[i] = b * a.C * a.HWin + (long long)(yy * a.stride) * a.Win + xx * a.stride;
+                                    }
                                 }
                             }
                         }
-                    }
-                    float* R = raw0 + (li % depth) * raw_floats;
-                    const int c0 = l_kb * CB;
+                        float* R = raw0 + (li % depth) * raw_floats;
+                        const int c0 = l_kb * CB;
 #pragma unroll
-                    for (int i = 0; i < PPT; ++i) {
-                        const int pp = tid + i * LOADERS;
-                        if (pp < a.P) {
-                            const float* src = a.x + (src_off[i] >= 0 ? src_off[i] + (long long)c0 * a.HWin : 0);
+                        for (int i = 0; i < PPT; ++i) {
+                            const int pp = tid + i * LOADERS;
+                            if (pp < a.P) {
+                                const float* src = a.x + (src_off[i] >= 0 ? src_off[i] + (long long)c0 * a.HWin : 0);
 #pragma unroll
-                            for (int j = 0; j < CB; ++j) {
-                                const bool real = src_off[i] >= 0 && c0 + j < a.C;
-                                cp_async4(R + j * a.P + pp, real ? src + (long long)j * a.HWin : a.x, real);
+                                for (int j = 0; j < CB; ++j) {
+                                    const bool real = src_off[i] >= 0 && c0 + j < a.C;
+                                    cp_async4(R + j * a.P + pp, real ? src + (long long)j * a.HWin : a.x, real);
+                                }
                             }
                         }
                     }
@@ -273,7 +320,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     if (chunk == CHUNKS - 1) {
                         // everything of this slot is in registers: hand it back before the stores
                         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tempty_bar[slot])) : "memory");
+                        __syncwarp();
+                        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tempty_bar[slot])) : "memory");
                     }
                     store_chunk(a, r, out_off, ocb * NT + chunk * 32, HW);
                 }

@@ -37,7 +37,7 @@ class Epilogue(C.Structure):
 
 class TcPlan(C.Structure):
     """tdc_tc_plan: layer-shape facts of the tensor-core variant."""
-    _fields_ = [(n, C.c_int) for n in ("C", "K", "R", "S", "mode", "nt", "cb", "nkb", "n_ocb", "hl")] + \
+    _fields_ = [(n, C.c_int) for n in ("C", "K", "R", "S", "mode", "nt", "cb", "nkb", "n_ocb", "hl", "general")] + \
                [("weights_bytes", C.c_size_t)]
 
 
@@ -65,7 +65,9 @@ _PROTOTYPES = {
     "tdc_tk_block_epi_f32": (_i, [_p] * 5 + [_i] * 12 + [C.POINTER(Epilogue), C.POINTER(Tile), _p, _sz, _p]),
     "tdc_permute_weights": (_i, [_p, _p, _i, _i, _i, _i, _p]),
     "tdc_tc_last_error_string": (C.c_char_p, []),
+    "tdc_pool2d_f32": (_i, [_p, _p] + [_i] * 9 + [_p]),
     "tdc_tc_plan_make": (_i, [_i] * 5 + [C.POINTER(TcPlan)]),
+    "tdc_tc_plan_make_general": (_i, [_i] * 5 + [C.POINTER(TcPlan)]),
     "tdc_tc_prepare_weights": (_i, [C.POINTER(TcPlan), _p, _i, _p, _p]),
     "tdc_conv2d_tc": (_i, [C.POINTER(TcPlan), _p, _p, _p, _i, _i, _i, C.POINTER(Epilogue), _i, _p]),
     "tdc_tc_status": (_i, [C.POINTER(_i)]),

@@ -127,6 +127,27 @@ def _epilogue(scale, bias, residual, relu):
     return e
 
 
+POOL_MAX, POOL_AVG_INCLUDE_PAD, POOL_AVG_EXCLUDE_PAD = 0, 1, 2
+
+
+def pool2d(x, kernel_size, stride=None, padding=0, mode=POOL_MAX, out=None):
+    """The pooling layer of the end-to-end skeleton (Pool::initialize / Pool::forward,
+    A100-evaluation/EndToEnd/resnet18-tk/src/Pool.cu:8-48; nn.MaxPool2d(3, 2, 1) in
+    inference/resnet_inet_tt.py:323): x [B][C][H][W] -> [B][C][Ho][Wo]."""
+    kh, kw = (int(v) for v in kernel_size) if isinstance(kernel_size, (tuple, list)) else (int(kernel_size),) * 2
+    stride = kh if stride is None else _pair(stride)
+    padding = _pair(padding)
+    B, Cc, H, W = x.shape
+    Ho, Wo = (H - kh + 2 * padding) // stride + 1, (W - kw + 2 * padding) // stride + 1
+    if out is None:
+        out = torch.empty((B, Cc, Ho, Wo), device=x.device, dtype=torch.float32)
+    with torch.cuda.device(x.device):
+        code = lib.tdc_pool2d_f32(_dev_f32(x, "x"), _dev_f32(out, "out"), B, Cc, H, W, kh, kw, padding, stride, mode, _stream())
+    if code != _lib.OK:
+        raise TdcError(code, "tdc_pool2d_f32: window %dx%d stride %d padding %d on %dx%d" % (kh, kw, stride, padding, H, W))
+    return out
+
+
 def conv2d_epi(x, w, scale=None, bias=None, residual=None, relu=False, stride=1, padding=0, w_layout=W_KCRS,
                tile=None, out=None):
     """y = relu?(conv(x, w) * scale[k] + bias[k] + residual): a conv with a folded inference-mode

@@ -80,6 +80,12 @@ def _one_conv(owner, name, x, w_kcrs, w_crsk, scale, shift, residual, relu, stri
     if precision != "fp32" and tc.supported(R, S, stride, padding, W) and \
             (precision != "auto" or tc.worthwhile(B, Cc, (H - 1) // stride + 1, (W - 1) // stride + 1, K, R)):
         return tc.cached(owner, name, w_kcrs, 1 if precision == "tf32" else 3)(x, scale, shift, residual, relu, stride=stride)
+    Ho, Wo = (H + 2 * padding - R) // stride + 1, (W + 2 * padding - S) // stride + 1
+    if precision != "fp32" and tc.general_supported(R, S, stride, padding, Wo) and \
+            (precision != "auto" or 2.0 * B * Ho * Wo * Cc * K * R * S >= 0.5e9):
+        # strided 3x3 cores, the 7x7 stem: the gathering plan
+        return tc.cached(owner, name, w_kcrs, 1 if precision == "tf32" else 3, general=True)(
+            x, scale, shift, residual, relu, stride=stride, padding=padding)
     tile = tiles.table_tile(B, Cc, H, W, K, R, S, padding, stride)
     if w_crsk is not None:
         return ops.conv2d_epi(x, w_crsk, scale, shift, residual, relu, stride, padding, w_layout=W_CRSK, tile=tile)
@@ -192,7 +198,8 @@ class TKResNet(nn.Module):
         x = x.contiguous().float()
         s, b = _fold_bn(self.bn1)
         x = _tk_or_dense(self.conv1, x, s, b, None, True, self.precision)
-        x = self.maxpool(x)
+        mp = self.maxpool      # nn.MaxPool2d kept as the module (state-dict and repr parity); computed by the pooling kernel
+        x = ops.pool2d(x, mp.kernel_size, mp.stride, mp.padding)
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         x = torch.flatten(self.avgpool(x), 1)
         return self.fc(x)

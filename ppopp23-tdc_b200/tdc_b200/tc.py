@@ -2,8 +2,9 @@
 
 `TcConv` holds what the C ABI needs per layer: the plan (tdc_tc_plan_make) and the filter
 pre-arranged for the kernel (tdc_tc_prepare_weights).  mode 3 ("3xTF32") gives fp32-level
-results; mode 1 is plain TF32.  Only "same" convolutions with 1x1 or 3x3 filters and stride 1
-are built; anything else raises.
+results; mode 1 is plain TF32.  The default plan serves "same" convolutions with 1x1 or 3x3 filters
+and stride 1 (1x1 filters also strided) and reads the input once; `general=True` makes the plan that
+takes any filter size, stride and padding by gathering (channel, row, column) triples.
 """
 import ctypes as C
 
@@ -20,30 +21,41 @@ def _check(code):
 
 
 class TcConv:
-    def __init__(self, weight, mode=3, w_layout=_lib.W_KCRS):
+    def __init__(self, weight, mode=3, w_layout=_lib.W_KCRS, general=False):
         """weight: [K][C][R][S] (or [C][R][S][K] with w_layout=W_CRSK), fp32 CUDA tensor."""
         if w_layout == _lib.W_KCRS:
             K, Cc, R, S = weight.shape
         else:
             Cc, R, S, K = weight.shape
         self.plan = TcPlan()
-        _check(lib.tdc_tc_plan_make(Cc, K, R, S, mode, C.byref(self.plan)))
-        self.C, self.K, self.R, self.mode = Cc, K, R, mode
+        _check((lib.tdc_tc_plan_make_general if general else lib.tdc_tc_plan_make)(Cc, K, R, S, mode, C.byref(self.plan)))
+        self.C, self.K, self.R, self.S, self.mode, self.general = Cc, K, R, S, mode, bool(general)
         self.wt = torch.empty(self.plan.weights_bytes, dtype=torch.uint8, device=weight.device)
         with torch.cuda.device(weight.device):
             _check(lib.tdc_tc_prepare_weights(C.byref(self.plan), _dev_f32(weight, "weight"), w_layout,
                                               self.wt.data_ptr(), _stream()))
 
-    def __call__(self, x, scale=None, bias=None, residual=None, relu=False, out=None, stride=1):
-        """`stride` > 1 is taken for 1x1 filters only (the down-sampling shortcut of a residual stage)."""
+    def __call__(self, x, scale=None, bias=None, residual=None, relu=False, out=None, stride=1, padding=None):
+        """`stride` > 1 is taken for 1x1 filters (the down-sampling shortcut of a residual stage) and by general
+        plans, which also take any `padding` (the others pad (R-1)/2)."""
         B, Cc, H, W = x.shape
         if Cc != self.C:
             raise TdcError(_lib.ERR_SHAPE, "x has %d channels, the filter expects %d" % (Cc, self.C))
         if not 1 <= stride <= 16:
             raise TdcError(_lib.ERR_UNSUPPORTED, "stride %d" % stride)
         flags = stride - 1
+        if self.general:
+            padding = 0 if padding is None else padding
+            if not 0 <= padding <= 15:
+                raise TdcError(_lib.ERR_UNSUPPORTED, "padding %d" % padding)
+            flags |= padding << 4
+            Ho, Wo = (H + 2 * padding - self.R) // stride + 1, (W + 2 * padding - self.S) // stride + 1
+        else:
+            if padding is not None and padding != (self.R - 1) // 2:
+                raise TdcError(_lib.ERR_UNSUPPORTED, "this plan pads (R-1)/2; make it with general=True for padding %d" % padding)
+            Ho, Wo = (H - 1) // stride + 1, (W - 1) // stride + 1
         if out is None:
-            out = torch.empty((B, self.K, (H - 1) // stride + 1, (W - 1) // stride + 1), device=x.device, dtype=torch.float32)
+            out = torch.empty((B, self.K, Ho, Wo), device=x.device, dtype=torch.float32)
         e = _epilogue(scale, bias, residual, relu)
         with torch.cuda.device(x.device):
             _check(lib.tdc_conv2d_tc(C.byref(self.plan), _dev_f32(x, "x"), self.wt.data_ptr(), _dev_f32(out, "out"),
@@ -56,6 +68,11 @@ def supported(R, S, stride, padding, W):
     return R == S and R in (1, 3) and (stride == 1 or (R == 1 and 1 <= stride <= 16)) and padding == (R - 1) // 2 and W <= 256 * stride
 
 
+def general_supported(R, S, stride, padding, Wo):
+    """True when a general plan (any filter, stride, padding) can run this convolution."""
+    return 1 <= R <= 15 and 1 <= S <= 15 and 1 <= stride <= 16 and 0 <= padding <= 15 and Wo <= 256
+
+
 def worthwhile(B, C, H, W, K, R):
     """The tensor-core kernel works on tiles of 128 positions x up to 128 channels; below about
     half a GFLOP there are too few tiles to fill 148 SMs and the fp32 kernel with its channel
@@ -63,16 +80,16 @@ def worthwhile(B, C, H, W, K, R):
     return 2.0 * B * H * W * C * K * R * R >= 0.5e9
 
 
-def cached(owner, name, weight, mode, w_layout=_lib.W_KCRS):
+def cached(owner, name, weight, mode, w_layout=_lib.W_KCRS, general=False):
     """TcConv for `weight`, kept on the module that owns the weight (`owner`) under `name`, and
     rebuilt when the tensor is written to or replaced (version / storage check).  Keeping it on the
     owner — not in a table keyed by address — means a freed network's entries can never be taken
     for those of a new network whose weights happen to land on the same addresses."""
     store = owner.__dict__.setdefault("_tc_convs", {})
     key = (weight._version, weight.data_ptr(), tuple(weight.shape))
-    hit = store.get((name, mode, w_layout))
+    hit = store.get((name, mode, w_layout, general))
     if hit is None or hit[0] != key:
-        hit = store[(name, mode, w_layout)] = (key, TcConv(weight.detach(), mode, w_layout))
+        hit = store[(name, mode, w_layout, general)] = (key, TcConv(weight.detach(), mode, w_layout, general))
     return hit[1]
 
 

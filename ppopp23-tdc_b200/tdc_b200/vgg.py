@@ -12,6 +12,7 @@ assembly in torch on the CPU.
 import torch
 import torch.nn as nn
 
+from . import ops
 from ._lib import ERR_UNSUPPORTED, TdcError
 from .resnet import Conv2dB200, _fold_bn, _tk_or_dense, round8
 from .tkconv import TKConv2dC_B200
@@ -87,7 +88,7 @@ class TKVGG(nn.Module):
         while i < len(mods):
             m = mods[i]
             if isinstance(m, nn.MaxPool2d):
-                x = m(x)
+                x = ops.pool2d(x, m.kernel_size, m.stride, m.padding)
                 i += 1
                 continue
             # conv [+ BatchNorm] + ReLU in the conv's own launch chain

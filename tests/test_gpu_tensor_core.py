@@ -26,6 +26,9 @@ def test_plan_is_made_on_the_host(T):
     assert T.lib.tdc_tc_plan_make(20, 200, 1, 1, 1, C.byref(p)) == 0
     assert (p.nt, p.nkb, p.n_ocb, p.hl) == (128, 3, 2, 1)
     assert T.lib.tdc_tc_plan_make(64, 64, 5, 5, 3, C.byref(p)) == _lib.ERR_UNSUPPORTED
+    assert T.lib.tdc_tc_plan_make_general(3, 64, 7, 7, 3, C.byref(p)) == 0          # the stem: 147 "channels" in 19 blocks of 8
+    assert (p.general, p.nt, p.nkb, p.n_ocb, p.hl) == (1, 64, 19, 1, 2) and p.weights_bytes == 4 * 2 * 1 * 8 * 64 * 19
+    assert T.lib.tdc_tc_plan_make_general(3, 64, 0, 7, 3, C.byref(p)) == _lib.ERR_SHAPE
     assert T.lib.tdc_tc_plan_make(64, 64, 3, 3, 2, C.byref(p)) == _lib.ERR_UNSUPPORTED
     assert T.lib.tdc_tc_plan_make(0, 64, 3, 3, 3, C.byref(p)) == _lib.ERR_SHAPE
     assert b"mode" in T.lib.tdc_tc_last_error_string() or b"C=" in T.lib.tdc_tc_last_error_string()
@@ -165,4 +168,34 @@ def test_strided_1x1_shortcut(T, B, Cc, K, H, W, stride, monkeypatch):
             assert rel_err(y[sel].cpu().numpy(), want) <= tol, (mode, persist)
     with pytest.raises(T.TdcError):
         T.TcConv(torch.zeros(8, 8, 3, 3).cuda())(x.cuda()[:, :8], stride=2)
+    assert tc.status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,Cc,K,H,W,R,stride,pad", [(2, 3, 64, 32, 32, 7, 2, 3), (3, 16, 24, 15, 13, 3, 2, 1), (2, 8, 16, 9, 9, 5, 1, 2),
+                                                      (1, 4, 8, 6, 7, 3, 3, 0), (40, 64, 64, 28, 28, 3, 2, 1), (3, 5, 130, 8, 8, 3, 1, 1),
+                                                      (2, 32, 32, 12, 12, 1, 1, 0)])
+def test_general_plan(T, B, Cc, K, H, W, R, stride, pad):
+    """The gathering plan (any filter size, stride, padding; the stem and the strided cores of the residual
+    networks): both modes and both filter layouts against the fp64 arbiter, and bit-identical to the
+    one-pass plan where that one applies (the same products summed in a different channel order would not be;
+    here the order is the same only for 1x1 filters)."""
+    from tdc_b200 import tc
+    x, w = draw_core(1700 + B + Cc + H + R, B, Cc, K, H, W, R)
+    sel = sorted({0, B // 2, B - 1})
+    ref = O.conv2d_f64(x[sel].numpy(), w.numpy(), pad=pad, stride=stride)
+    g = torch.Generator().manual_seed(K + R)
+    scale, shift = (torch.rand(K, generator=g) + 0.5).cuda(), torch.randn(K, generator=g).cuda()
+    for mode, tol in ((3, FP32_TOL), (1, TF32_TOL)):
+        conv = T.TcConv(w.cuda(), mode=mode, general=True)
+        y = conv(x.cuda(), stride=stride, padding=pad)
+        assert tuple(y.shape[1:]) == ref.shape[1:] and rel_err(y[sel].cpu().numpy(), ref) <= tol, (mode, rel_err(y[sel].cpu().numpy(), ref))
+        y = conv(x.cuda(), scale, shift, None, True, stride=stride, padding=pad)
+        want = np.maximum(ref * scale.cpu().numpy()[None, :, None, None] + shift.cpu().numpy()[None, :, None, None], 0)
+        assert rel_err(y[sel].cpu().numpy(), want) <= tol
+    crsk = torch.from_numpy(np.ascontiguousarray(w.numpy().transpose(1, 2, 3, 0))).cuda()
+    y2 = T.TcConv(crsk, mode=3, w_layout=T.W_CRSK, general=True)(x.cuda(), stride=stride, padding=pad)
+    assert torch.equal(y2, T.TcConv(w.cuda(), mode=3, general=True)(x.cuda(), stride=stride, padding=pad))
+    if R == 1:
+        assert torch.equal(y2, T.TcConv(w.cuda(), mode=3)(x.cuda(), stride=stride))
     assert tc.status() == 0
