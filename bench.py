@@ -219,8 +219,28 @@ def bench_tk_block(torch, T, dev, time_layer, peaks):
                 err = float((m(x)[:2].double() - y64).abs().max() / y64.abs().max())
             flops = 2.0 * B * H * H * (Cc * R + 9 * R * R + R * Cc)
             by = 4.0 * (2 * B * Cc * H * H + 2 * Cc * R + 9 * R * R)
-            rows.append(dict(C=Cc, H=H, R=R, B=B, us=us, cudnn_us=cud, rel_err_fp64=err, tflops=flops / us / 1e6,
-                             hbm_floor_us=by / peaks["hbm_gbs"] / 1e3, gbs=by / us / 1e3))
+            row = dict(C=Cc, H=H, R=R, B=B, us=us, cudnn_us=cud, rel_err_fp64=err, tflops=flops / us / 1e6,
+                       hbm_floor_us=by / peaks["hbm_gbs"] / 1e3, gbs=by / us / 1e3)
+            if B == 1:
+                # batch-1 latency without host launch gaps on either side: the three launches replayed from a CUDA graph
+                for key, fn in (("graph_us", lambda: m(x)), ("cudnn_graph_us", lambda: ref(x))):
+                    side = torch.cuda.Stream()
+                    side.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(side), torch.no_grad():
+                        for _ in range(3):
+                            fn()
+                    torch.cuda.current_stream().wait_stream(side)
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph), torch.no_grad():
+                        fn()
+                    for _ in range(3):
+                        graph.replay()
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(); [graph.replay() for _ in range(50)]; e1.record()
+                    torch.cuda.synchronize()
+                    row[key] = e0.elapsed_time(e1) * 1e3 / 50
+            rows.append(row)
     return rows
 
 
@@ -436,7 +456,7 @@ def main():
     # DRAM bytes (read + write) of each launch of the step from one ncu capture of this command
     # (dram__bytes_read.sum + dram__bytes_write.sum per launch, batch 64); the summary and the command
     # are in profiles/launch_list_bench.md.  Outputs stay in L2 within a launch, so this is input + filter.
-    NCU_DRAM_MB = {(56, 32): 25.9, (56, 64): 52.7, (28, 64): 13.2, (28, 128): 27.0, (14, 128): 7.7, (14, 256): 17.6,
+    NCU_DRAM_MB = {(56, 32): 25.8, (56, 64): 53.0, (28, 64): 13.2, (28, 128): 27.0, (14, 128): 7.7, (14, 256): 17.6,
                    (7, 256): 8.0, (7, 512): 25.4}
     roofline = {
         "bound": "tensor", "achieved": tot_fl / tot_tc3 / 1e6, "peak": tf32_peak / 3.0, "unit": "TFLOP/s",
@@ -446,7 +466,7 @@ def main():
                          "algorithmic_bytes": conv_bytes(BATCH, dom["H"], dom["R1"], dom["R2"]),
                          "source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the dominant launch, "
                                    "profiles/launch_list_bench.md; the output is still in L2 when the launch ends"},
-        "kernel": "conv_tc_kernel (tcgen05 kind::tf32, 3xTF32), the 8 launches of a step, L2 flushed before each",
+        "kernel": "conv_tc_persist_kernel / conv_tc_kernel (tcgen05 kind::tf32, 3xTF32), the 8 launches of a step, L2 flushed before each",
         "peak_source": "algorithmic FLOPs against (bf16_tflops/2)/3: dense TF32 taken as half the measured cuBLAS bf16 rate of "
                        "MEASURED_PEAKS.json (%s), divided by the three TF32 products each fp32-level product costs" % peaks["source"],
         "dominant_launch": {k: dom[k] for k in ("H", "R1", "R2", "tc3_us", "tc3_tflops")},

@@ -1,0 +1,33 @@
+"""Which kernel runs one convolution: shared by the network assemblies and the Tucker module.
+
+`precision`: "fp32" = the fp32 FMA kernel always (bit-reproducible); "tf32x3" / "tf32" = tensor cores wherever a
+plan exists (split operands, fp32-level results / plain TF32); "auto" = tensor cores with split operands where the
+layer has enough work to fill the GPU, the fp32 FMA kernel with its measured-table tile otherwise.
+"""
+from . import ops, tiles
+from ._lib import W_CRSK
+
+
+def one_conv(owner, name, x, w_kcrs, w_crsk, scale, shift, residual, relu, stride, padding, precision):
+    """One convolution with its epilogue on the kernel that suits it: tensor cores (3xTF32) for
+    stride-1 3x3 and any 1x1 layers with enough work to fill the GPU when `precision` allows, the fp32
+    kernel with a table tile otherwise."""
+    from . import tc
+    B, Cc, H, W = x.shape
+    K, _, R, S = w_kcrs.shape
+    one_pass = tc.supported(R, S, stride, padding, W)
+    if precision != "fp32" and one_pass and \
+            (precision != "auto" or tc.worthwhile(B, Cc, (H - 1) // stride + 1, (W - 1) // stride + 1, K, R)):
+        return tc.cached(owner, name, w_kcrs, 1 if precision == "tf32" else 3)(x, scale, shift, residual, relu, stride=stride)
+    Ho, Wo = (H + 2 * padding - R) // stride + 1, (W + 2 * padding - S) // stride + 1
+    if precision != "fp32" and not one_pass and tc.general_supported(R, S, stride, padding, Wo) and \
+            (precision != "auto" or 2.0 * B * Ho * Wo * Cc * K * R * S >= 0.5e9):
+        # strided 3x3 cores, the 7x7 stem: the gathering plan
+        return tc.cached(owner, name, w_kcrs, 1 if precision == "tf32" else 3, general=True)(
+            x, scale, shift, residual, relu, stride=stride, padding=padding)
+    tile = tiles.table_tile(B, Cc, H, W, K, R, S, padding, stride)
+    if w_crsk is not None:
+        if callable(w_crsk):          # made (and cached by the owner) only when this path is taken
+            w_crsk = w_crsk()
+        return ops.conv2d_epi(x, w_crsk, scale, shift, residual, relu, stride, padding, w_layout=W_CRSK, tile=tile)
+    return ops.conv2d_epi(x, w_kcrs.detach(), scale, shift, residual, relu, stride, padding, tile=tile)

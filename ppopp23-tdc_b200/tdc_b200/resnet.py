@@ -19,6 +19,7 @@ import torch.nn as nn
 
 from . import ops, tiles
 from ._lib import ERR_UNSUPPORTED, W_CRSK, TdcError
+from .dispatch import one_conv as _one_conv
 from .tkconv import TKConv2dC_B200
 
 
@@ -70,28 +71,6 @@ def _fold_bn_now(bn):
     return scale.float().contiguous(), (b - mean * scale).float().contiguous()
 
 
-def _one_conv(owner, name, x, w_kcrs, w_crsk, scale, shift, residual, relu, stride, padding, precision):
-    """One convolution with its epilogue on the kernel that suits it: tensor cores (3xTF32) for
-    stride-1 3x3 and any 1x1 layers with enough work to fill the GPU when `precision` allows, the fp32
-    kernel with a table tile otherwise."""
-    from . import tc
-    B, Cc, H, W = x.shape
-    K, _, R, S = w_kcrs.shape
-    if precision != "fp32" and tc.supported(R, S, stride, padding, W) and \
-            (precision != "auto" or tc.worthwhile(B, Cc, (H - 1) // stride + 1, (W - 1) // stride + 1, K, R)):
-        return tc.cached(owner, name, w_kcrs, 1 if precision == "tf32" else 3)(x, scale, shift, residual, relu, stride=stride)
-    Ho, Wo = (H + 2 * padding - R) // stride + 1, (W + 2 * padding - S) // stride + 1
-    if precision != "fp32" and tc.general_supported(R, S, stride, padding, Wo) and \
-            (precision != "auto" or 2.0 * B * Ho * Wo * Cc * K * R * S >= 0.5e9):
-        # strided 3x3 cores, the 7x7 stem: the gathering plan
-        return tc.cached(owner, name, w_kcrs, 1 if precision == "tf32" else 3, general=True)(
-            x, scale, shift, residual, relu, stride=stride, padding=padding)
-    tile = tiles.table_tile(B, Cc, H, W, K, R, S, padding, stride)
-    if w_crsk is not None:
-        return ops.conv2d_epi(x, w_crsk, scale, shift, residual, relu, stride, padding, w_layout=W_CRSK, tile=tile)
-    return ops.conv2d_epi(x, w_kcrs.detach(), scale, shift, residual, relu, stride, padding, tile=tile)
-
-
 def _tk_or_dense(conv, x, scale, shift, residual, relu, precision="fp32"):
     """One conv module + folded BN (+ residual) (+ ReLU): a Tucker conv as its three launches with
     the epilogue on the last, a dense conv as one."""
@@ -99,10 +78,10 @@ def _tk_or_dense(conv, x, scale, shift, residual, relu, precision="fp32"):
         b = conv.bias.detach() if scale is None else conv.bias.detach() * scale
         shift = b if shift is None else shift + b
     if isinstance(conv, TKConv2dC_B200):
-        z1 = _one_conv(conv, "first", x, conv.first_kernel, None, None, None, None, False, 1, 0, precision)
-        z2 = _one_conv(conv, "core", z1, conv.core_kernel, conv._core_channel_last(), None, None, None, False,
+        z1 = _one_conv(conv, "first", x, conv.first_kernel, lambda: conv._factor_channel_last("first_kernel"), None, None, None, False, 1, 0, precision)
+        z2 = _one_conv(conv, "core", z1, conv.core_kernel, conv._core_channel_last, None, None, None, False,
                        conv.stride[0], conv.padding[0], precision)
-        return _one_conv(conv, "last", z2, conv.last_kernel, None, scale, shift, residual, relu, 1, 0, precision)
+        return _one_conv(conv, "last", z2, conv.last_kernel, lambda: conv._factor_channel_last("last_kernel"), scale, shift, residual, relu, 1, 0, precision)
     return _one_conv(conv, "weight", x, conv.weight, None, scale, shift, residual, relu, conv.stride[0], conv.padding[0], precision)
 
 

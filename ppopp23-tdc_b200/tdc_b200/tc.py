@@ -74,10 +74,12 @@ def general_supported(R, S, stride, padding, Wo):
 
 
 def worthwhile(B, C, H, W, K, R):
-    """The tensor-core kernel works on tiles of 128 positions x up to 128 channels; below about
-    half a GFLOP there are too few tiles to fill 148 SMs and the fp32 kernel with its channel
-    slices and clusters is the faster one (batch-1 layers)."""
-    return 2.0 * B * H * W * C * K * R * R >= 0.5e9
+    """The tensor-core kernel works on tiles of 128 positions x up to 128 channels.  With fewer than about 16
+    position tiles, or below about 0.2 GFLOP, there is too little to fill 148 SMs and the fp32 kernel with its
+    channel slices and clusters is the faster one (batch-1 layers, 7x7 images at small batch): measured on the
+    Tucker blocks C = 64..512 at batch 32, where it loses only the 1x1 steps of the 7x7 block."""
+    pad = (R - 1) // 2
+    return 2.0 * B * H * W * C * K * R * R >= 0.2e9 and B * (H + pad) * (W + pad) >= 16 * 128
 
 
 def cached(owner, name, weight, mode, w_layout=_lib.W_KCRS, general=False):

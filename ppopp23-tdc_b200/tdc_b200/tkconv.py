@@ -91,6 +91,16 @@ class TKConv2dC_B200(nn.Module):
             self._core_crsk = (key, ops.permute_weights(w.detach().contiguous()))
         return self._core_crsk[1]
 
+    def _factor_channel_last(self, name):
+        """[C][1][1][K] copy of a 1x1 factor (`first_kernel` / `last_kernel`), rebuilt when the parameter changes."""
+        w = getattr(self, name)
+        key = (w._version, w.data_ptr())
+        store = self.__dict__.setdefault("_factor_crsk", {})
+        hit = store.get(name)
+        if hit is None or hit[0] != key:
+            hit = store[name] = (key, ops.permute_weights(w.detach().contiguous()))
+        return hit[1]
+
     def _ws(self, x, shared=False):
         """Workspace for the block's two intermediates: this module's own, or (shared=True) one
         buffer per device that all blocks of a network reuse — they run one after another on one
@@ -108,32 +118,35 @@ class TKConv2dC_B200(nn.Module):
             ws = self._workspace = torch.empty(need, device=x.device, dtype=torch.uint8)
         return ws
 
-    def _use_tc(self, x):
-        from . import tc
-        if self.precision == "fp32":
-            return 0
-        R, S = self.kernel_size
-        B, _, H, W = x.shape
-        if not tc.supported(R, S, self.stride[0], self.padding[0], W) or self.stride[0] != self.stride[1]:
-            return 0
-        if self.precision == "auto":
-            return 3 if tc.worthwhile(B, self.in_rank, H, W, self.out_rank, R) else 0
-        return 3 if self.precision == "tf32x3" else 1
-
     def forward(self, x):
         x = self._check(x)
-        mode = self._use_tc(x)
-        if mode:
-            from . import tc
-            z1 = tc.cached(self, "first", self.first_kernel, mode)(x)
-            z2 = tc.cached(self, "core", self.core_kernel, mode)(z1)
-            return tc.cached(self, "last", self.last_kernel, mode)(z2, bias=None if self.bias is None else self.bias.detach())
+        if self.precision != "fp32" and self.stride[0] == self.stride[1] and self.padding[0] == self.padding[1]:
+            # each of the three steps on the kernel that suits it (tensor cores where a plan exists and, under
+            # "auto", the step is large enough; the fp32 FMA kernel with its table tile otherwise)
+            from .dispatch import one_conv
+            p = self.precision
+            bias = None if self.bias is None else self.bias.detach()
+            z1 = one_conv(self, "first", x, self.first_kernel, lambda: self._factor_channel_last("first_kernel"),
+                          None, None, None, False, 1, 0, p)
+            z2 = one_conv(self, "core", z1, self.core_kernel, self._core_channel_last, None, None, None, False,
+                          self.stride[0], self.padding[0], p)
+            return one_conv(self, "last", z2, self.last_kernel, lambda: self._factor_channel_last("last_kernel"),
+                            None, bias, None, False, 1, 0, p)
         B, _, H, W = x.shape
         tile = tiles.table_tile(B, self.in_rank, H, W, self.out_rank, self.kernel_size[0], self.kernel_size[1],
                                 self.padding[0], self.stride[0])     # measured table first, model otherwise
+        bias = None if self.bias is None else self.bias.detach()
+        Ho, Wo = ops.out_hw(H, W, self.kernel_size[0], self.kernel_size[1], self.padding[0], self.stride[0])
+        t1 = tiles.table_tile(B, self.in_channels, H, W, self.in_rank, 1, 1, 0, 1)
+        t3 = tiles.table_tile(B, self.out_rank, Ho, Wo, self.out_channels, 1, 1, 0, 1)
+        if t1 is not None or t3 is not None:
+            # measured tiles exist for the 1x1 steps: the same three launches, each with its table tile and its
+            # channel-last filter copy (tdc_tk_block_f32 takes a tile for the core only)
+            z1 = ops.conv2d(x, self._factor_channel_last("first_kernel"), w_layout=W_CRSK, tile=t1)
+            z2 = ops.core_conv2d(z1, self._core_channel_last(), self.stride, self.padding, w_layout=W_CRSK, tile=tile)
+            return ops.conv2d(z2, self._factor_channel_last("last_kernel"), bias, w_layout=W_CRSK, tile=t3)
         return ops.tk_block(x, self.first_kernel.detach(), self._core_channel_last(), self.last_kernel.detach(),
-                            None if self.bias is None else self.bias.detach(), self.stride, self.padding,
-                            core_layout=W_CRSK, workspace=self._ws(x), core_tile=tile)
+                            bias, self.stride, self.padding, core_layout=W_CRSK, workspace=self._ws(x), core_tile=tile)
 
     def forward_features(self, x):
         x = self._check(x)

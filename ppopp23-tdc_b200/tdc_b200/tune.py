@@ -61,6 +61,16 @@ def sweep_shapes():
     return [(R1, R2, H, H, 3, 1, 1) for (H, R1, R2) in SWEEP]
 
 
+def tkblock_shapes():
+    """The three convolutions of the Tucker blocks C = K in {64@56, 128@28, 256@14, 512@7}, R1 = R2 = C/2
+    (the middles of the ResNet-50 bottlenecks): 1x1 C->R, 3x3 R->R, 1x1 R->C."""
+    out = []
+    for C, H in ((64, 56), (128, 28), (256, 14), (512, 7)):
+        R = C // 2
+        out += [(C, R, H, H, 1, 1, 0), (R, R, H, H, 3, 1, 1), (R, C, H, H, 1, 1, 0)]
+    return out
+
+
 def candidates(B, C, H, W, K, R=3, S=3, pad=1, stride=1):
     """Every tile of the compiled thread-tile set that can be launched for the shape."""
     Ho, Wo = (H + 2 * pad - R) // stride + 1, (W + 2 * pad - S) // stride + 1
@@ -117,7 +127,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--out", default="tile_table.csv")
-    ap.add_argument("--shapes", default="sweep", choices=["sweep", "resnet18"])
+    ap.add_argument("--shapes", default="sweep", choices=["sweep", "resnet18", "tkblock"])
     ap.add_argument("--max-per-shape", type=int, default=300)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--seed", type=int, default=0)
@@ -128,7 +138,7 @@ def main(argv=None):
     stream = torch.cuda.current_stream()
     cover = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
     reps = 1 if a.batch >= 16 else 8
-    shapes = sweep_shapes() if a.shapes == "sweep" else resnet18_shapes()
+    shapes = {"sweep": sweep_shapes, "resnet18": resnet18_shapes, "tkblock": tkblock_shapes}[a.shapes]()
     with open(a.out, "w", newline="") as f:
         wr = csv.writer(f)
         wr.writerow(COLUMNS)
