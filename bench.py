@@ -331,6 +331,89 @@ def bench_resnet(torch, T, dev, dist, world, rank, stream):
     return out
 
 
+def bench_vgg(torch, T, dev, dist, world, rank, stream):
+    """TK-compressed VGG-16 (every 3x3 conv but the first Tucker with R = round8(0.5*channels), random init, eval),
+    224x224 N(0,1) images: the batch-2048 job sharded over the GPUs, each rank running its 2048/world images as
+    chunks of 128 through the same forward (activations of a 2048-image chunk would not be a sensible working set),
+    logits gathered once at the end.  Strong scaling by construction: total work is fixed."""
+    from tdc_b200.parallel import gather_slices
+    F = torch.nn.functional
+    model = T.tkc_vgg16(precision="auto").eval().to(dev)
+    TOTAL, CHUNK = 2048, 128
+    mine = TOTAL // world
+    x = torch.randn(CHUNK, 3, 224, 224, generator=torch.Generator().manual_seed(5001 + rank)).to(dev)
+
+    def job():
+        outs = [model(x) for _ in range(mine // CHUNK)]
+        y = torch.cat(outs)
+        return gather_slices(y, TOTAL) if dist is not None else y
+
+    def torch_forward(t):
+        for m in model.features:
+            if hasattr(m, "first_kernel"):
+                t = F.conv2d(F.conv2d(F.conv2d(t, m.first_kernel), m.core_kernel, None, m.stride, m.padding), m.last_kernel, m.bias)
+            elif isinstance(m, torch.nn.Conv2d):
+                t = F.conv2d(t, m.weight, m.bias, m.stride, m.padding)
+            else:
+                t = m(t)
+        return model.head.fc(torch.flatten(F.adaptive_avg_pool2d(t, 1), 1))
+    out = {}
+    with torch.no_grad():
+        for _ in range(2):
+            y1 = model(x)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        y = job()
+        e1.record(stream)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        out = {"b2048_ms": ms, "images_per_s": TOTAL / (ms * 1e-3), "chunk": CHUNK, "images_per_gpu": mine}
+        if world == 1:
+            torch.backends.cudnn.benchmark = True
+            torch.backends.cudnn.allow_tf32 = False
+            for _ in range(2):
+                yr = torch_forward(x)
+            torch.cuda.synchronize()
+            e0.record(stream)
+            for _ in range(2):
+                yr = torch_forward(x)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            out["cudnn_chunk_ms"] = e0.elapsed_time(e1) / 2
+            out["chunk_ms"] = ms / (mine // CHUNK)
+            y64 = torch_forward_double(torch, model, x[:2])
+            out["rel_err_fp64"] = float((y1[:2].double() - y64).abs().max() / y64.abs().max())
+            out["cudnn_rel_err_fp64"] = float((yr[:2].double() - y64).abs().max() / y64.abs().max())
+    out["config"] = "VGG-16 cfg D, twelve of thirteen 3x3 convs Tucker with R=round8(0.5*ch), 224x224 N(0,1) images, fp32, eval; 2048 images over all GPUs"
+    return out
+
+
+def torch_forward_double(torch, model, x):
+    """The same VGG forward in fp64 through torch (the arbiter for the end-to-end error)."""
+    F = torch.nn.functional
+    t = x.double()
+    for m in model.features:
+        if hasattr(m, "first_kernel"):
+            b = None if m.bias is None else m.bias.double()
+            t = F.conv2d(F.conv2d(F.conv2d(t, m.first_kernel.double()), m.core_kernel.double(), None, m.stride, m.padding), m.last_kernel.double(), b)
+        elif isinstance(m, torch.nn.Conv2d):
+            t = F.conv2d(t, m.weight.double(), None if m.bias is None else m.bias.double(), m.stride, m.padding)
+        elif isinstance(m, torch.nn.ReLU):
+            t = F.relu(t)
+        else:
+            t = m(t)
+    return F.linear(torch.flatten(F.adaptive_avg_pool2d(t, 1), 1), model.head.fc.weight.double(), model.head.fc.bias.double())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -542,6 +625,7 @@ def main():
     # ---- TK-compressed ResNet-18 forward (every rank its own batch; one gather of the logits) --
     if not args.no_extras:
         line["tk_resnet18"] = bench_resnet(torch, T, dev, dist, world, rank, stream)
+        line["tk_vgg16"] = bench_vgg(torch, T, dev, dist, world, rank, stream)
         if rank == 0 and world == 1:
             line["tk_block"] = bench_tk_block(torch, T, dev, time_layer, peaks)
 
