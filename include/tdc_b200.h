@@ -314,6 +314,10 @@ TDC_API int  tdc_conv_set_tile(tdc_conv* l, const tdc_tile* tile);
 TDC_API int  tdc_conv_set_precision(tdc_conv* l, int mode);
 TDC_API int  tdc_conv_forward(tdc_conv* l, const float* dev_in, float** dev_out, void* stream);
 TDC_API int  tdc_conv_forward_host(tdc_conv* l, const float* host_in, float* host_out);
+/* The same without the final synchronise, on `stream`: independent layers (the per-shape drivers of a sweep) run
+ * on streams of their own, so the copy in of one overlaps the copy out of another.  Host buffers must be pinned
+ * for the copies to be asynchronous; the caller synchronises the stream before reading host_out. */
+TDC_API int  tdc_conv_forward_host_async(tdc_conv* l, const float* host_in, float* host_out, void* stream);
 TDC_API void tdc_conv_destroy(tdc_conv* l);
 
 TDC_API int  tdc_tkconv_create(tdc_tkconv** out, int b, int C, int N1, int N2, int N3, int h, int w,

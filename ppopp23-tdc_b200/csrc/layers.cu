@@ -128,19 +128,25 @@ int tdc_conv_forward(tdc_conv* l, const float* dev_in, float** dev_out, void* st
     return TDC_OK;
 }
 
-int tdc_conv_forward_host(tdc_conv* l, const float* host_in, float* host_out) {
+int tdc_conv_forward_host_async(tdc_conv* l, const float* host_in, float* host_out, void* stream) {
     if (!l || !host_in || !host_out) return TDC_ERR_NULL;
     size_t in_bytes = (size_t)l->b * l->c * l->h * l->w * sizeof(float);
+    cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
     if (!l->staging_in && (e = cudaMalloc((void**)&l->staging_in, in_bytes)) != cudaSuccess) return cuda_fail("cudaMalloc", e);
-    if ((e = cudaMemcpyAsync(l->staging_in, host_in, in_bytes, cudaMemcpyHostToDevice, nullptr)) != cudaSuccess)
+    if ((e = cudaMemcpyAsync(l->staging_in, host_in, in_bytes, cudaMemcpyHostToDevice, st)) != cudaSuccess)
         return cuda_fail("copy in", e);
     float* o;
-    int rc = tdc_conv_forward(l, l->staging_in, &o, nullptr);
+    int rc = tdc_conv_forward(l, l->staging_in, &o, stream);
     if (rc) return rc;
-    e = cudaMemcpyAsync(host_out, o, (size_t)l->b * l->n * l->ho * l->wo * sizeof(float), cudaMemcpyDeviceToHost, nullptr);
-    if (e != cudaSuccess) return cuda_fail("copy out", e);
-    e = cudaStreamSynchronize(nullptr);
+    e = cudaMemcpyAsync(host_out, o, (size_t)l->b * l->n * l->ho * l->wo * sizeof(float), cudaMemcpyDeviceToHost, st);
+    return e == cudaSuccess ? TDC_OK : cuda_fail("copy out", e);
+}
+
+int tdc_conv_forward_host(tdc_conv* l, const float* host_in, float* host_out) {
+    int rc = tdc_conv_forward_host_async(l, host_in, host_out, nullptr);
+    if (rc) return rc;
+    cudaError_t e = cudaStreamSynchronize(nullptr);
     return e == cudaSuccess ? TDC_OK : cuda_fail("synchronize", e);
 }
 

@@ -83,6 +83,7 @@ _PROTOTYPES = {
     "tdc_conv_set_precision": (_i, [_p, _i]),
     "tdc_conv_forward": (_i, [_p, _p, C.POINTER(_p), _p]),
     "tdc_conv_forward_host": (_i, [_p, _p, _p]),
+    "tdc_conv_forward_host_async": (_i, [_p, _p, _p, _p]),
     "tdc_conv_destroy": (None, [_p]),
     "tdc_tkconv_create": (_i, [C.POINTER(_p)] + [_i] * 11 + [_p] * 4),
     "tdc_tkconv_forward": (_i, [_p, _p, C.POINTER(_p), _p]),

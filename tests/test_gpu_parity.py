@@ -197,6 +197,12 @@ def test_layer_objects_with_host_buffers(T):
     out = np.empty((2, 12, 14, 14), np.float32)
     assert lib.tdc_conv_forward_host(h, fp(z1), fp(out)) == 0
     assert rel_err(out, O.conv2d_f64(z1, wn, pad=1)) <= FP32_TOL
+    # the variant that leaves the synchronise to the caller, on a stream of the caller's: pinned buffers, same bits
+    side = torch.cuda.Stream()
+    zin, zout = torch.from_numpy(z1).pin_memory(), torch.empty(2, 12, 14, 14).pin_memory()
+    assert lib.tdc_conv_forward_host_async(h, C.c_void_p(zin.data_ptr()), C.c_void_p(zout.data_ptr()), C.c_void_p(side.cuda_stream)) == 0
+    side.synchronize()
+    assert np.array_equal(zout.numpy(), out)
     lib.tdc_conv_destroy(h)
     # all-ones weights when none are given, as the reference fills them (Conv.cu:88-91)
     assert lib.tdc_conv_create(C.byref(h), 1, 4, 6, 6, 5, 1, 3, 3, 1, None, None) == 0
