@@ -10,7 +10,7 @@ from ._lib import B200, EPI_NONE, EPI_RELU, LIB_PATH, W_CRSK, W_KCRS, DevInfo, L
 from .ops import (conv2d, conv2d_epi, pool2d, tk_block_epi, core_conv2d, out_hw, permute_weights, query_device, select_tile, tile_cost, tile_info,
                   tk_block, tk_block_workspace_bytes)
 from .tiles import best_tile, load_tables, table_tile
-from .resnet import HalfRanks, TKBasicBlock, TKResNet, fill_deterministic, tkc_resnet18
+from .resnet import HalfRanks, HalfRanksBottleneck, TKBasicBlock, TKBottleneck, TKResNet, fill_deterministic, tkc_resnet18, tkc_resnet50
 from .tc import TcConv
 from .tkconv import TKConv2dC_B200
 from .tkconv_variants import TKConv2dM_B200, TKConv2dR_B200
@@ -21,6 +21,6 @@ __all__ = [
     "B200", "DevInfo", "EPI_NONE", "EPI_RELU", "LIB_PATH", "LaunchInfo", "TKConv2dC_B200", "TKConv2dM_B200", "TKConv2dR_B200", "TKVGG", "HalfRanksVGG", "tkc_vgg16", "partial_tucker_hosvd",
     "tucker_to_dense", "TcConv", "TdcError", "Tile",
     "W_CRSK", "W_KCRS", "best_tile", "conv2d", "conv2d_epi", "pool2d", "tk_block_epi", "HalfRanks", "TKBasicBlock", "TKResNet",
-    "fill_deterministic", "tkc_resnet18", "core_conv2d", "lib", "out_hw", "permute_weights", "query_device",
+    "fill_deterministic", "tkc_resnet18", "tkc_resnet50", "TKBottleneck", "HalfRanksBottleneck", "core_conv2d", "lib", "out_hw", "permute_weights", "query_device",
     "select_tile", "table_tile", "load_tables", "tile_cost", "tile_info", "tk_block", "tk_block_workspace_bytes",
 ]

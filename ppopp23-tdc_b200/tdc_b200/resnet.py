@@ -42,6 +42,18 @@ class HalfRanks:
             inplanes = planes
 
 
+class HalfRanksBottleneck:
+    """hp_dict for a bottleneck ResNet: the 3x3 conv of every block (`layer{s}.{i}.conv2.weight`, width -> width)
+    Tucker with R1 = R2 = round8(ratio*width); the 1x1 convs stay dense (inference/resnet_inet_tt.py:185-212 makes a
+    conv Tucker only when its key is in `ranks`)."""
+
+    def __init__(self, layers=(3, 4, 6, 3), ratio=0.5):
+        self.ranks = {}
+        for s, (planes, n) in enumerate(zip((64, 128, 256, 512), layers), start=1):
+            for i in range(n):
+                self.ranks["layer%d.%d.conv2.weight" % (s, i)] = [round8(ratio * planes), round8(ratio * planes)]
+
+
 class Conv2dB200(nn.Conv2d):
     """nn.Conv2d parameters (`weight`, `bias`), forward on the B200 kernel."""
 
@@ -121,12 +133,56 @@ class TKBasicBlock(nn.Module):
         return _tk_or_dense(self.conv2, out, s2, b2, identity, True, prec)
 
 
-class TKResNet(nn.Module):
-    """inference/resnet_inet_tt.py:287-394 (TTResNet) for basic blocks."""
+class TKBottleneck(nn.Module):
+    """inference/resnet_inet_tt.py:155-237 (TTBottleneck, the v1.5 form: the stride sits on the 3x3 conv) with
+    conv = TKConv2dC_B200 for the convs named in `hp_dict.ranks`, dense 1x1 / 3x3 otherwise."""
+    expansion = 4
 
-    def __init__(self, layers=(2, 2, 2, 2), num_classes=1000, hp_dict=None, precision="fp32"):
+    def __init__(self, inplanes, planes, stride=1, downsample=None, stage=1, id=0, hp_dict=None):
         super().__init__()
-        hp_dict = hp_dict if hp_dict is not None else HalfRanks(layers)
+        width = planes
+
+        def make(name, cin, cout, k, st):
+            key = "layer%d.%d.%s.weight" % (stage, id, name)
+            if key in hp_dict.ranks:
+                return TKConv2dC_B200(cin, cout, k, stride=st, padding=k // 2, bias=False, hp_dict=hp_dict, name=key)
+            return Conv2dB200(cin, cout, k, stride=st, padding=k // 2, bias=False)
+        self.conv1 = make("conv1", inplanes, width, 1, 1)
+        self.bn1 = nn.BatchNorm2d(width)
+        self.conv2 = make("conv2", width, width, 3, stride)
+        self.bn2 = nn.BatchNorm2d(width)
+        self.conv3 = make("conv3", width, planes * self.expansion, 1, 1)
+        self.bn3 = nn.BatchNorm2d(planes * self.expansion)
+        self.relu = nn.ReLU(inplace=True)
+        self.downsample = downsample
+        self.stride = stride
+
+    def forward(self, x):
+        if self.training:
+            raise TdcError(ERR_UNSUPPORTED, "training-mode BatchNorm is not built; call .eval()")
+        prec = getattr(self, "precision", "fp32")
+        s1, b1 = _fold_bn(self.bn1)
+        s2, b2 = _fold_bn(self.bn2)
+        s3, b3 = _fold_bn(self.bn3)
+        out = _tk_or_dense(self.conv1, x, s1, b1, None, True, prec)
+        out = _tk_or_dense(self.conv2, out, s2, b2, None, True, prec)
+        identity = x
+        if self.downsample is not None:
+            sd, bd = _fold_bn(self.downsample[1])
+            identity = _tk_or_dense(self.downsample[0], x, sd, bd, None, False, prec)
+        return _tk_or_dense(self.conv3, out, s3, b3, identity, True, prec)
+
+
+class TKResNet(nn.Module):
+    """inference/resnet_inet_tt.py:287-394 (TTResNet) for basic blocks (`block=TKBasicBlock`) and bottleneck
+    blocks (`block=TKBottleneck`)."""
+
+    def __init__(self, layers=(2, 2, 2, 2), num_classes=1000, hp_dict=None, precision="fp32", block=None):
+        super().__init__()
+        block = block if block is not None else TKBasicBlock
+        if hp_dict is None:
+            hp_dict = HalfRanks(layers) if block is TKBasicBlock else HalfRanksBottleneck(layers)
+        self.block = block
         self.inplanes = 64
         self.conv1 = Conv2dB200(3, 64, kernel_size=7, stride=2, padding=3, bias=False)
         self.bn1 = nn.BatchNorm2d(64)
@@ -137,7 +193,7 @@ class TKResNet(nn.Module):
         self.layer3 = self._make_layer(256, layers[2], 2, 3, hp_dict)
         self.layer4 = self._make_layer(512, layers[3], 2, 4, hp_dict)
         self.avgpool = nn.AdaptiveAvgPool2d((1, 1))
-        self.fc = nn.Linear(512, num_classes)
+        self.fc = nn.Linear(512 * block.expansion, num_classes)
         for m in self.modules():        # the reference's init loop, resnet_inet_tt.py:335-340
             if isinstance(m, nn.Conv2d):
                 nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")
@@ -154,19 +210,19 @@ class TKResNet(nn.Module):
             raise ValueError("precision %r" % (precision,))
         self.precision = precision
         for m in self.modules():
-            if isinstance(m, TKBasicBlock):
+            if isinstance(m, (TKBasicBlock, TKBottleneck)):
                 m.precision = precision
         return self
 
     def _make_layer(self, planes, blocks, stride, stage, hp_dict):
-        downsample = None
-        if stride != 1 or self.inplanes != planes:
-            downsample = nn.Sequential(Conv2dB200(self.inplanes, planes, 1, stride=stride, bias=False),
-                                       nn.BatchNorm2d(planes))
-        layers = [TKBasicBlock(self.inplanes, planes, stride, downsample, stage=stage, id=0, hp_dict=hp_dict)]
-        self.inplanes = planes
+        block, downsample = self.block, None
+        if stride != 1 or self.inplanes != planes * block.expansion:
+            downsample = nn.Sequential(Conv2dB200(self.inplanes, planes * block.expansion, 1, stride=stride, bias=False),
+                                       nn.BatchNorm2d(planes * block.expansion))
+        layers = [block(self.inplanes, planes, stride, downsample, stage=stage, id=0, hp_dict=hp_dict)]
+        self.inplanes = planes * block.expansion
         for i in range(1, blocks):
-            layers.append(TKBasicBlock(planes, planes, stage=stage, id=i, hp_dict=hp_dict))
+            layers.append(block(self.inplanes, planes, stage=stage, id=i, hp_dict=hp_dict))
         return nn.Sequential(*layers)
 
     def forward(self, x):
@@ -187,6 +243,12 @@ class TKResNet(nn.Module):
 def tkc_resnet18(hp_dict=None, num_classes=1000, precision="fp32"):
     """inference/resnet_inet_tt.py:483-496 without the checkpoint load."""
     return TKResNet((2, 2, 2, 2), num_classes, hp_dict, precision)
+
+
+def tkc_resnet50(hp_dict=None, num_classes=1000, precision="fp32"):
+    """inference/resnet_inet_tt.py:614-627 without the checkpoint load: bottleneck blocks [3, 4, 6, 3]; by default
+    the 3x3 conv of every block is a Tucker conv with R = round8(0.5*width)."""
+    return TKResNet((3, 4, 6, 3), num_classes, hp_dict, precision, block=TKBottleneck)
 
 
 def fill_deterministic(module, seed=0):

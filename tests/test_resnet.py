@@ -67,3 +67,40 @@ def test_fused_epilogue_against_separate_ops(built):
     assert rel_err(y.cpu().numpy(), ref.cpu().numpy()) <= 1e-5
     with pytest.raises(T.TdcError):
         T.conv2d_epi(x, w, scale, shift, res[:, :, :7], True, 1, 1)
+
+
+Z50 = np.load(os.path.join(GOLDEN, "tk_resnet50.npz"))
+
+
+def test_resnet50_keys_and_ranks_match_the_reference(built):
+    """Bottleneck assembly (reference: TTBottleneck / tkc_resnet50): state-dict keys equal to those of the reference's
+    own TTResNet(TTBottleneck, [3,4,6,3], conv=TKConv2dC) (tests/golden/make_golden_resnet50.py), the 3x3 conv of every
+    block Tucker, the stride on that conv."""
+    import tdc_b200 as T
+    m = T.tkc_resnet50()
+    assert sorted(m.state_dict().keys()) == list(Z50["keys"])
+    hp = T.HalfRanksBottleneck()
+    assert len(hp.ranks) == 16 and hp.ranks["layer3.5.conv2.weight"] == [128, 128]
+    b = m.layer2[0]
+    assert isinstance(b.conv2, T.TKConv2dC_B200) and b.conv2.stride == (2, 2) and tuple(b.conv2.core_kernel.shape) == (64, 64, 3, 3)
+    assert isinstance(b.conv1, torch.nn.Conv2d) and tuple(b.conv1.weight.shape) == (128, 256, 1, 1)
+    assert tuple(b.downsample[0].weight.shape) == (512, 256, 1, 1) and m.fc.in_features == 2048
+    assert sum(p.numel() for p in m.parameters()) == 18326568
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("precision", ["fp32", "auto"])
+def test_resnet50_logits_match_the_reference_network(built, precision):
+    import tdc_b200 as T
+    m = T.fill_deterministic(T.tkc_resnet50(precision=precision).eval(), seed=0).cuda()
+    x = torch.randn(2, 3, 128, 128, generator=torch.Generator().manual_seed(4050)).cuda()
+    feats = {}
+    m.layer1.register_forward_hook(lambda mod, i, o: feats.__setitem__("layer1", o))
+    m.layer4.register_forward_hook(lambda mod, i, o: feats.__setitem__("layer4", o))
+    with torch.no_grad():
+        logits = m(x)
+    # 53 chained convolutions: the end-to-end bar of the residual networks, 1e-4 of the largest logit
+    assert rel_err(feats["layer1"][0].mean((1, 2)).cpu().numpy(), Z50["layer1_mean"]) <= 1e-5
+    assert rel_err(feats["layer4"][0].mean((1, 2)).cpu().numpy(), Z50["layer4_mean"]) <= 1e-4
+    assert rel_err(logits.cpu().numpy(), Z50["logits"]) <= 1e-4
+    assert (logits.argmax(1).cpu().numpy() == Z50["logits"].argmax(1)).all()
