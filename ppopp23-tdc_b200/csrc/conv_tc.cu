@@ -66,6 +66,7 @@ struct Args {
     long long total_pos;   // B * Lp
     int nbuf;              // persistent kernel: accumulator buffers in tensor memory (1 or 2)
     int depth;             // persistent kernel: slots of the raw-input ring (cp.async groups in flight)
+    int kps;               // persistent kernel: channel blocks per shared-memory stage
     long long ntiles;      // persistent kernel: position tiles x output-channel blocks
     int* status;           // device status word: 0 ok, else first failure code
 };
@@ -79,13 +80,17 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 // Bounded wait: true when the phase with `parity` has completed, false after ~1 s.
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try(bar, parity)) return true;          // the common case costs no clock read
     const long long t0 = clock64();
     for (;;) {
-        uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-        if (ok) return true;
+        if (mbar_try(bar, parity)) return true;
         if (clock64() - t0 > 2000000000ll) return false;
     }
 }
@@ -336,10 +341,13 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
         // ================= loaders =================
         // Two channel blocks of input are always in flight in registers (blocks kb and kb+1 are
         // loaded while kb-1 is being split and stored), and the filter copies run `ns` stages ahead.
+        // ring positions are counters that wrap, not kb % ns: these loops are bound by instruction latency
+        int st_idx = 0, st_use = 0;                     // stage to fill next, parity of its use count
         auto open_stage = [&](int kb) -> float* {       // wait until the stage is free, start its filter copy
-            const int s = kb % a.ns;
+            const int s = st_idx;
             float* A = stage0 + (long long)s * stage_floats;
-            if (kb >= a.ns && !mbar_wait(&empty_bar[s], (uint32_t)((kb / a.ns - 1) & 1))) { *abort_flag = 1; return nullptr; }
+            // use number u of a stage waits for the MMAs of use u-1; the first use passes at once
+            if (!mbar_wait(&empty_bar[s], (uint32_t)(st_use ^ 1))) { *abort_flag = 1; return nullptr; }
             if (tid == 0) {
                 mbar_expect_tx(&full_bar[s], b_bytes);
                 bulk_g2s(A + a_floats, wt_cta + (long long)kb * b_floats, b_bytes, &full_bar[s]);
@@ -349,7 +357,8 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
         auto close_stage = [&](int kb) {
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
             __syncwarp();                                                  // one arrival per warp: 8 instead of 256 updates of one barrier
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[kb % a.ns])) : "memory");
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[st_idx])) : "memory");
+            if (++st_idx == a.ns) { st_idx = 0; st_use ^= 1; }
         };
         auto put = [&](float* A, int q, int pp, float c0, float c1, float c2, float c3) {   // 4 channels of one patch row
             float4 hi;
@@ -465,9 +474,11 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
         const int mt = __shfl_sync(0xffffffffu, warp - 8, 0);
         if (mt < MT) {
             const uint32_t d_main = tmem + (uint32_t)(mt * a.tile_cols);
+            int st_idx = 0, st_use = 0;
             for (int kb = 0; kb < a.nkb; ++kb) {
-                const int s = kb % a.ns;
-                if (!mbar_wait(&full_bar[s], (uint32_t)((kb / a.ns) & 1))) { *abort_flag = 1; break; }
+                const int s = st_idx;
+                if (!mbar_wait(&full_bar[s], (uint32_t)st_use)) { *abort_flag = 1; break; }
+                if (++st_idx == a.ns) { st_idx = 0; st_use ^= 1; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const float* A = stage0 + (long long)s * stage_floats;
                 if (elect_one()) {
@@ -697,6 +708,18 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     a.P = ((mt * M_TILE + 2 * pad * (a.Wp + 1)) + 7) / 8 * 8;
     stage_bytes = sizeof(float) * ((size_t)a.hl * CB * a.P + (size_t)a.hl * taps * CB * p->nt);
     raw_bytes = ring ? sizeof(float) * (size_t)CB * a.P : 0;
+    // One-tap filters (1x1, general plans) do one or two MMAs per channel block and position tile: a stage of one
+    // block would be all hand-over.  Their stages take up to four blocks (what leaves room for two stages and,
+    // with the ring, two raw slots); TDC_TC_KPS overrides.
+    a.kps = 1;
+    if (persist && taps == 1) {
+        const char* env_kps = getenv("TDC_TC_KPS");
+        int want = env_kps && atoi(env_kps) >= 1 && atoi(env_kps) <= 8 ? atoi(env_kps) : 4;
+        if (want > a.nkb) want = a.nkb;
+        while (want > 1 && 2 * want * stage_bytes + 2 * raw_bytes > room) --want;
+        a.kps = want;
+        stage_bytes *= want;
+    }
     if (ring) {
         // three operand stages when at least four raw slots still fit beside them, else two; then as many raw slots as fit
         ns = 3 * stage_bytes + 4 * raw_bytes <= room ? 3 : 2;

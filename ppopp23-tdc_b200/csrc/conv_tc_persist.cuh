@@ -33,7 +33,9 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     float*    stage0     = reinterpret_cast<float*>(smem_raw + P_HEADER);
 
     constexpr int PPT = 3;
-    const int a_floats = a.hl * CB * a.P, b_floats = a.hl * TAPS * CB * NT, stage_floats = a_floats + b_floats;
+    // a stage holds a.kps channel blocks (one for 3x3 filters; several for one-tap filters, whose stages would
+    // otherwise be all hand-over and no work): [kps input blocks][kps filter blocks]
+    const int a_floats = a.hl * CB * a.P, b_floats = a.hl * TAPS * CB * NT, stage_floats = a.kps * (a_floats + b_floats);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int pad = (a.taps_r - 1) / 2;
     const long long HW = (long long)a.H * a.W;
@@ -58,23 +60,36 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
 
     if (warp < 8) {
         // ================= loaders =================
-        long long it = 0;                        // channel blocks staged so far, over all tiles: stage = it % ns
+        // no division in these loops: the loaders are bound by instruction latency (two warps per scheduler), so the
+        // ring positions are counters that wrap, not quotients of a running index
+        int st_idx = 0, st_use = 0, st_k = 0;    // stage being filled, parity of its use count, blocks stored in it
+        float* stage_A = nullptr;                // the stage being filled
+        // where channel block kb of the current tile goes; its first block of a stage waits for the stage and starts
+        // the copy of the stage's filter blocks
         auto open_stage = [&](const float* wt_tile, int kb) -> float* {
-            const int s = (int)(it % a.ns);
-            float* A = stage0 + (long long)s * stage_floats;
-            // use number u of this stage waits for the MMAs of use u-1; the first use passes at once
-            if (!mbar_wait(&empty_bar[s], (uint32_t)(((it / a.ns) & 1) ^ 1))) { *abort_flag = 1; return nullptr; }
-            if (tid == 0) {
-                mbar_expect_tx(&full_bar[s], b_bytes);
-                bulk_g2s(A + a_floats, wt_tile + (long long)kb * b_floats, b_bytes, &full_bar[s]);
+            const int k = st_k;
+            if (k == 0) {
+                const int s = st_idx;
+                stage_A = stage0 + (long long)s * stage_floats;
+                // use number u of this stage waits for the MMAs of use u-1; the first use passes at once
+                if (!mbar_wait(&empty_bar[s], (uint32_t)(st_use ^ 1))) { *abort_flag = 1; return nullptr; }
+                if (tid == 0) {
+                    const uint32_t bytes = (uint32_t)(a.nkb - kb < a.kps ? a.nkb - kb : a.kps) * b_bytes;
+                    mbar_expect_tx(&full_bar[s], bytes);
+                    bulk_g2s(stage_A + a.kps * a_floats, wt_tile + (long long)kb * b_floats, bytes, &full_bar[s]);
+                }
             }
-            return A;
+            return stage_A + k * a_floats;
         };
-        auto close_stage = [&]() {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[it % a.ns])) : "memory");
-            ++it;
+        // after channel block kb is stored: the last block of a stage hands the stage over
+        auto close_stage = [&](int kb) {
+            if (++st_k == a.kps || kb == a.nkb - 1) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&full_bar[st_idx])) : "memory");
+                st_k = 0;
+                if (++st_idx == a.ns) { st_idx = 0; st_use ^= 1; }
+            }
         };
         auto put = [&](float* A, int q, int pp, float c0, float c1, float c2, float c3) {
             float4 hi;
@@ -126,7 +141,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                             put(A, q, pp + 3, v[i][0].w, v[i][1].w, v[i][2].w, v[i][3].w);
                         }
                     }
-                    close_stage();
+                    close_stage(kb);
                     return true;
                 };
                 load(0, va);
@@ -152,8 +167,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             const long long my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
             const long long total = my_tiles * a.nkb;
             long long src_off[PPT];              // of the tile being copied: offset of channel 0 of each owned row, -1 = zeros
-            long long l_tile = blockIdx.x;       // copy side: tile and channel block of the next block to issue
-            int l_kb = 0;
+            long long l_tile = blockIdx.x;       // copy side: tile, channel block and raw slot of the next block to issue
+            int l_kb = 0, l_slot = 0;
             // general plan (TAPS == 1 only): a "channel" is an (input channel, filter row, filter column) triple
             // and a patch row is an output position, whose window starts at input (iy0, ix0), possibly outside
             const float* rbase[PPT];             // x at (image, channel 0, iy0, ix0) of each owned row (only formed, never read, when outside)
@@ -184,7 +199,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                             }
                             g_ci = g_dy = g_dx = 0;
                         }
-                        const uint32_t dst0 = smem_u32(raw0 + (li % depth) * raw_floats) + (uint32_t)tid * 4u;
+                        const uint32_t dst0 = smem_u32(raw0 + l_slot * raw_floats) + (uint32_t)tid * 4u;
 #pragma unroll
                         for (int j = 0; j < CB; ++j) {
                             const int delta = g_ci * (int)a.HWin + g_dy * a.Win + g_dx;     // the host keeps channels x image below 2^31
@@ -218,7 +233,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                                 }
                             }
                         }
-                        float* R = raw0 + (li % depth) * raw_floats;
+                        float* R = raw0 + l_slot * raw_floats;
                         const int c0 = l_kb * CB;
 #pragma unroll
                         for (int i = 0; i < PPT; ++i) {
@@ -234,18 +249,20 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                         }
                     }
                     if (++l_kb == a.nkb) { l_kb = 0; l_tile += gridDim.x; }
+                    if (++l_slot == depth) l_slot = 0;
                 }
                 asm volatile("cp.async.commit_group;" ::: "memory");      // an empty group past the end keeps the count uniform
             };
             for (int d = 0; d < depth; ++d) issue(d);
             long long c_tile = blockIdx.x;
-            int c_kb = 0;
+            int c_kb = 0, c_slot = 0;
+            const float* wt_tile = a.wt + (c_tile % a.n_ocb) * a.nkb * b_floats;
             for (long long ci = 0; ci < total && !*abort_flag; ++ci) {
-                const float* wt_tile = a.wt + (c_tile % a.n_ocb) * a.nkb * b_floats;
                 float* A = open_stage(wt_tile, c_kb);
                 if (!A) break;
                 cp_async_wait_pending(depth - 1);                         // block ci has landed (this thread's part)
-                const float* R = raw0 + (ci % depth) * raw_floats;
+                const float* R = raw0 + c_slot * raw_floats;
+                if (++c_slot == depth) c_slot = 0;
 #pragma unroll
                 for (int i = 0; i < PPT; ++i) {
                     const int pp = tid + i * LOADERS;
@@ -255,9 +272,9 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                             put(A, q, pp, R[(4 * q) * a.P + pp], R[(4 * q + 1) * a.P + pp], R[(4 * q + 2) * a.P + pp], R[(4 * q + 3) * a.P + pp]);
                     }
                 }
-                close_stage();
+                close_stage(c_kb);
                 issue(ci + depth);                                         // the slot just read is free again
-                if (++c_kb == a.nkb) { c_kb = 0; c_tile += gridDim.x; }
+                if (++c_kb == a.nkb) { c_kb = 0; c_tile += gridDim.x; wt_tile = a.wt + (c_tile % a.n_ocb) * a.nkb * b_floats; }
             }
             asm volatile("cp.async.wait_all;" ::: "memory");
         }
@@ -266,7 +283,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
         // ================= MMA issuers: warp 8+mt owns position tile mt =================
         const int mt = __shfl_sync(0xffffffffu, warp - 8, 0);
         if (mt < MT) {
-            long long it = 0, j = 0;            // channel blocks consumed so far; tiles done by this CTA
+            long long j = 0;                    // tiles done by this CTA
+            int st_idx = 0, st_use = 0;         // stage to consume next, parity of its use count
             for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x, ++j) {
                 const int slot = (int)(j % nbuf) * MT + mt;
                 // the epilogue must have emptied this accumulator slot (its previous use); the first use passes at once
@@ -274,15 +292,19 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_main = tmem + (uint32_t)(slot * a.tile_cols);
                 bool ok = true;
-                for (int kb = 0; kb < a.nkb; ++kb, ++it) {
-                    const int s = (int)(it % a.ns);
-                    if (!mbar_wait(&full_bar[s], (uint32_t)((it / a.ns) & 1))) { *abort_flag = 1; ok = false; break; }
+                for (int kb0 = 0; kb0 < a.nkb; kb0 += a.kps) {
+                    const int s = st_idx;
+                    if (!mbar_wait(&full_bar[s], (uint32_t)st_use)) { *abort_flag = 1; ok = false; break; }
+                    if (++st_idx == a.ns) { st_idx = 0; st_use ^= 1; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const float* A = stage0 + (long long)s * stage_floats;
+                    const int kend = kb0 + a.kps < a.nkb ? kb0 + a.kps : a.nkb;
                     if (elect_one()) {
-                        issue_block<NT, TAPS>(a, d_main, smem_u32(A), smem_u32(A + a_floats), (uint32_t)(mt * M_TILE), kb & 1, kb < 2 && (kb == 0 || a.nmain == 2));
+                        for (int kb = kb0; kb < kend; ++kb)
+                            issue_block<NT, TAPS>(a, d_main, smem_u32(A + (kb - kb0) * a_floats), smem_u32(A + a.kps * a_floats + (kb - kb0) * b_floats),
+                                                  (uint32_t)(mt * M_TILE), kb & 1, kb < 2 && (kb == 0 || a.nmain == 2));
                         mma_commit(&empty_bar[s]);                        // the stage may be refilled when these MMAs are done
-                        if (kb + 1 == a.nkb) mma_commit(&tfull_bar[slot]); // and this position tile's accumulators are complete
+                        if (kend == a.nkb) mma_commit(&tfull_bar[slot]);  // and this position tile's accumulators are complete
                     }
                     __syncwarp();
                 }
