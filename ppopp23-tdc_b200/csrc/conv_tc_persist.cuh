@@ -18,7 +18,7 @@
 
 namespace tdc_tc {
 
-constexpr int P_THREADS = 512;   // 8 loader warps, 4 issuer warps (one lane each), 4 epilogue warps
+constexpr int P_THREADS = 640;   // 8 loader warps, 4 issuer warps (one lane each), 2 groups of 4 epilogue warps
 constexpr int P_HEADER  = 256;   // bytes of barriers and flags in front of the stages
 
 template <int NT, int MT, int TAPS, bool VEC>
@@ -312,7 +312,10 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             }
         }
     } else {
-        // ================= epilogue: warps 12-15, one lane quarter of tensor memory each =================
+        // ================= epilogue: warps 12-19, two groups of four (one lane quarter of tensor memory per warp);
+        // group g drains the position tiles mt = g, g+2: the epilogue is a latency chain (tensor memory -> registers
+        // -> residual loads -> stores), and two chains in flight hide more of it than one =================
+        const int grp = (warp - 12) >> 2;
         const int q = warp & 3;
         constexpr int CHUNKS = NT / 32;
         long long j = 0;
@@ -321,7 +324,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             const long long g0 = (t / a.n_ocb) * (MT * M_TILE);
             bool ok = true;
 #pragma unroll 1
-            for (int mt = 0; mt < MT && ok; ++mt) {
+            for (int mt = grp; mt < MT && ok; mt += 2) {
                 // the position tiles of a CTA tile are handed over one by one: while this one is drained, the
                 // issuers of the others still run, and its own issuer may start on the next CTA tile
                 const int slot = (int)(j % nbuf) * MT + mt;
