@@ -4,14 +4,15 @@
 // One CTA per SM walks a list of tiles (tile = MT x 128 positions x NT output channels).
 // What a one-tile-per-CTA launch pays per tile — tensor-memory allocation, barrier set-up, a
 // cold first load, and an epilogue during which the tensor core idles — is paid once or hidden:
-//   * loaders (warps 0-7) never stop: the shared-memory stages are a ring that runs across tile
-//     boundaries, so the first channel blocks of the next tile are staged while the MMAs of
-//     this one finish;
-//   * the accumulators are double-buffered in tensor memory (when 2 x MT x columns-per-tile
-//     fits in 512 columns): issuers (lane 0 of warps 8..8+MT-1) start the next tile in the
-//     other buffer while the epilogue warps (12-15) drain this one;
-//   * the epilogue releases its buffer as soon as the values are in registers and only then
-//     does its global stores.
+//   * loaders (warps 0-7) never stop: the shared-memory stages and the raw-input ring behind them
+//     run across tile boundaries, so the first channel blocks of the next tile are staged while
+//     the MMAs of this one finish;
+//   * the accumulators of a CTA tile are handed over one 128-position tile at a time: warp 8+mt
+//     issues the MMAs of position tile mt and may start the next CTA tile as soon as ITS
+//     accumulators have been read, while the other issuers still work on this one (and tensor
+//     memory holds two CTA tiles outright when 2 x MT x columns-per-tile fits in 512 columns);
+//   * two groups of four epilogue warps (12-15, 16-19; group g drains the position tiles g, g+2)
+//     release an accumulator as soon as its values are in registers and only then store.
 // Every mbarrier wait is bounded; a wait that runs out raises the CTA's abort flag, every
 // role leaves its loop at the next check, the status word is set and tensor memory is freed.
 #pragma once
