@@ -664,11 +664,14 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     const char* env_ns = getenv("TDC_TC_NS");
     const char* env_nbuf = getenv("TDC_TC_NBUF");
     const char* env_persist = getenv("TDC_TC_PERSIST");
-    // The persistent kernel wins where one CTA per SM fits and a CTA tile is short (split operands, up to 64
-    // output channels per block: prologue and epilogue would otherwise show).  With 128-channel blocks the
-    // one-tile kernel, which drains tensor memory with all its warps, measured faster, and with plain TF32
-    // operands two one-tile CTAs share an SM and overlap by themselves.  TDC_TC_PERSIST=0/1 forces either.
-    const bool persist = p->general || (env_persist ? atoi(env_persist) != 0 : (p->nt <= 64 && a.hl == 2));   // general plans: the persistent kernel only
+    // The persistent kernel wins where a CTA tile is short and its prologue and epilogue would otherwise show: split
+    // operands with up to 64 output channels per block, and one-tap filters with 128-channel blocks when there are
+    // enough positions for two position tiles per CTA.  For 3x3 filters with 128-channel blocks the one-tile
+    // kernel, which drains tensor memory with all its warps, measured faster, and with plain TF32 operands two
+    // one-tile CTAs share an SM and overlap by themselves.  TDC_TC_PERSIST=0/1 forces either.
+    const long long tiles_mt2 = ((a.total_pos + 2 * M_TILE - 1) / (2 * M_TILE)) * a.n_ocb;
+    const bool persist = p->general || (env_persist ? atoi(env_persist) != 0
+                                                    : (a.hl == 2 && (p->nt <= 64 || (taps == 1 && tiles_mt2 >= sms))));
     int mt = 512 / a.tile_cols > 4 ? 4 : 512 / a.tile_cols, ns = 0, depth = 0, nbuf = 1;   // tensor memory: 512 columns
     if (env_mt && atoi(env_mt) >= 1) while (mt > atoi(env_mt)) mt /= 2;
     // 16-byte input loads: 1x1 filter, images a multiple of 4 positions long, 16-byte aligned base
