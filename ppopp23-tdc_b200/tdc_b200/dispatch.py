@@ -21,8 +21,9 @@ def one_conv(owner, name, x, w_kcrs, w_crsk, scale, shift, residual, relu, strid
         return tc.cached(owner, name, w_kcrs, 1 if precision == "tf32" else 3)(x, scale, shift, residual, relu, stride=stride)
     Ho, Wo = (H + 2 * padding - R) // stride + 1, (W + 2 * padding - S) // stride + 1
     if precision != "fp32" and not one_pass and tc.general_supported(R, S, stride, padding, Wo) and \
-            (precision != "auto" or 2.0 * B * Ho * Wo * Cc * K * R * S >= 0.5e9):
-        # strided 3x3 cores, the 7x7 stem: the gathering plan
+            (precision != "auto" or (2.0 * B * Ho * Wo * Cc * K * R * S >= 0.5e9 and B * Ho * Wo >= 256 * 128)):
+        # strided 3x3 cores, the 7x7 stem: the gathering plan (under "auto" only with at least 256 position tiles:
+        # it pays per channel block and tile, and with few tiles the fp32 kernel's slices and clusters win)
         return tc.cached(owner, name, w_kcrs, 1 if precision == "tf32" else 3, general=True)(
             x, scale, shift, residual, relu, stride=stride, padding=padding)
     tile = tiles.table_tile(B, Cc, H, W, K, R, S, padding, stride)
