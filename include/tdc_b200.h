@@ -270,6 +270,12 @@ TDC_API int tdc_tc_plan_make(int C, int K, int R, int S, int mode, tdc_tc_plan* 
  * (channel, filter row, filter column) triples gathered by the loaders, i.e. a classic implicit GEMM
  * that re-reads the input R*S/stride^2 times from cache.  Stride and padding come with the call. */
 TDC_API int tdc_tc_plan_make_general(int C, int K, int R, int S, int mode, tdc_tc_plan* out);
+/* Output channels per block are 128 / 64 / 32 by K in the plans above, which suits layers with many output positions.
+ * tdc_tc_pick_nt gives the block size for a layer with `positions` output positions (B x padded image; smaller blocks
+ * mean more CTAs when the positions alone do not fill `sm_count` SMs), tdc_tc_plan_make_nt makes a plan (general or
+ * not) with that block size; its prepared filter differs, so a caller keeps one per block size it uses. */
+TDC_API int tdc_tc_pick_nt(int K, int mode, long long positions, int sm_count);
+TDC_API int tdc_tc_plan_make_nt(int C, int K, int R, int S, int mode, int general, int nt, tdc_tc_plan* out);
 TDC_API int tdc_tc_prepare_weights(const tdc_tc_plan* plan, const float* w, int w_layout, void* wt, void* stream);
 #define TDC_TC_STRIDE_MASK 0x0F  /* flags & mask = stride - 1 (1x1 filters and general plans)         */
 #define TDC_TC_PAD_MASK    0xF0  /* (flags & mask) >> 4 = padding (general plans); other bits must be 0 */

@@ -576,12 +576,12 @@ extern "C" {
 
 const char* tdc_tc_last_error_string(void) { return g_tc_err; }
 
-static int plan_fill(int C, int K, int R, int S, int mode, int general, tdc_tc_plan* out) {
+static int plan_fill(int C, int K, int R, int S, int mode, int general, tdc_tc_plan* out, int nt = 0) {
     if (!out) return tc_fail(TDC_ERR_NULL, "out is NULL");
     if (C <= 0 || K <= 0) return tc_fail(TDC_ERR_SHAPE, "C=%d K=%d", C, K);
     if (mode != 1 && mode != 3) return tc_fail(TDC_ERR_UNSUPPORTED, "mode %d (1 = TF32, 3 = 3xTF32)", mode);
     out->C = C; out->K = K; out->R = R; out->S = S; out->mode = mode;
-    out->nt = pick_nt(K);
+    out->nt = nt ? nt : pick_nt(K);
     out->cb = tdc_tc::CB;
     // a general plan contracts over (channel, filter row, filter column) triples, one tap
     out->nkb = cdiv(general ? C * R * S : C, tdc_tc::CB);
@@ -596,6 +596,38 @@ int tdc_tc_plan_make(int C, int K, int R, int S, int mode, tdc_tc_plan* out) {
     if (R != S || (R != 1 && R != 3))
         return tc_fail(TDC_ERR_UNSUPPORTED, "this plan is built for 1x1 and 3x3 filters, not %dx%d (tdc_tc_plan_make_general takes any)", R, S);
     return plan_fill(C, K, R, S, mode, 0, out);
+}
+
+int tdc_tc_pick_nt(int K, int mode, long long positions, int sm_count) {
+    // Output channels per block for a layer with `positions` output positions (padding included): the default
+    // (128 / 64 / 32 by K) serves layers whose tiles fill the SMs; with fewer tiles, smaller blocks give more CTAs.
+    // Estimate per candidate: rounds of tiles over the SMs x clocks of one tap of one position tile and channel
+    // block (the slower of the MMA pair's math and its operand reads from shared memory at 128 bytes per clock).
+    if (K <= 0 || positions <= 0 || sm_count <= 0) return pick_nt(K > 0 ? K : 1);
+    const int base = pick_nt(K);
+    const long long ptiles = (positions + tdc_tc::M_TILE - 1) / tdc_tc::M_TILE;
+    int best = base;
+    double best_cost = 0.0;
+    if (ptiles * ((K + base - 1) / base) >= sm_count) return base;      // every SM has a tile already
+    for (int nt = base; nt >= 32; nt /= 2) {
+        const double math = mode == 3 ? 96.0 * nt / 64.0 : 32.0 * nt / 64.0;
+        const double smem = mode == 3 ? ((4096.0 + 64.0 * nt) + (4096.0 + 32.0 * nt)) / 128.0 : (4096.0 + 32.0 * nt) / 128.0;
+        const long long tiles = ptiles * ((K + nt - 1) / nt);
+        const double cost = (double)((tiles + sm_count - 1) / sm_count) * (math > smem ? math : smem);
+        if (nt == base || cost < best_cost * 0.95) { best = nt; best_cost = cost; }      // a smaller block must win clearly
+    }
+    return best;
+}
+
+int tdc_tc_plan_make_nt(int C, int K, int R, int S, int mode, int general, int nt, tdc_tc_plan* out) {
+    if (nt != 32 && nt != 64 && nt != 128) return tc_fail(TDC_ERR_UNSUPPORTED, "nt %d (32, 64 or 128)", nt);
+    if (general) {
+        if (R <= 0 || S <= 0 || R > 15 || S > 15) return tc_fail(TDC_ERR_SHAPE, "filter %dx%d", R, S);
+        if ((long long)C * R * S > (1 << 20)) return tc_fail(TDC_ERR_SHAPE, "C*R*S = %lld is too long a contraction", (long long)C * R * S);
+    } else if (R != S || (R != 1 && R != 3)) {
+        return tc_fail(TDC_ERR_UNSUPPORTED, "this plan is built for 1x1 and 3x3 filters, not %dx%d", R, S);
+    }
+    return plan_fill(C, K, R, S, mode, general ? 1 : 0, out, nt);
 }
 
 int tdc_tc_plan_make_general(int C, int K, int R, int S, int mode, tdc_tc_plan* out) {

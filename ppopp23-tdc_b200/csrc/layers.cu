@@ -63,7 +63,12 @@ int tdc_conv_set_precision(tdc_conv* l, int mode) {
     if (mode == 0) { l->tc_mode = 0; return TDC_OK; }
     if (l->stride != 1 || l->r != l->s || l->pad != (l->r - 1) / 2) return TDC_ERR_UNSUPPORTED;
     tdc_tc_plan p;
-    int rc = tdc_tc_plan_make(l->c, l->n, l->r, l->s, mode, &p);
+    // the layer's shape is fixed, so the output-channel block size that suits its position count is known here
+    int sms = 148, device = 0;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int halo = (l->r - 1) / 2;
+    const int nt = tdc_tc_pick_nt(l->n, mode, (long long)l->b * (l->h + halo) * (l->w + halo), sms);
+    int rc = tdc_tc_plan_make_nt(l->c, l->n, l->r, l->s, mode, 0, nt, &p);
     if (rc) return rc;
     void* wt = nullptr;
     cudaError_t e = cudaMalloc(&wt, p.weights_bytes);

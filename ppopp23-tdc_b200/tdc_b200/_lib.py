@@ -68,6 +68,8 @@ _PROTOTYPES = {
     "tdc_pool2d_f32": (_i, [_p, _p] + [_i] * 9 + [_p]),
     "tdc_tc_plan_make": (_i, [_i] * 5 + [C.POINTER(TcPlan)]),
     "tdc_tc_plan_make_general": (_i, [_i] * 5 + [C.POINTER(TcPlan)]),
+    "tdc_tc_pick_nt": (_i, [_i, _i, C.c_longlong, _i]),
+    "tdc_tc_plan_make_nt": (_i, [_i] * 7 + [C.POINTER(TcPlan)]),
     "tdc_tc_prepare_weights": (_i, [C.POINTER(TcPlan), _p, _i, _p, _p]),
     "tdc_conv2d_tc": (_i, [C.POINTER(TcPlan), _p, _p, _p, _i, _i, _i, C.POINTER(Epilogue), _i, _p]),
     "tdc_tc_status": (_i, [C.POINTER(_i)]),

@@ -27,6 +27,25 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+class _on_device:
+    """`with _on_device(t.device):` — torch.cuda.device() only when the tensor's GPU is not the current one (the
+    context manager costs more host time than a small launch)."""
+    __slots__ = ("ctx",)
+
+    def __init__(self, device):
+        idx = device.index
+        self.ctx = None if idx is None or idx == torch.cuda.current_device() else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            return self.ctx.__exit__(*exc)
+        return False
+
+
 def out_hw(H, W, R, S, pad, stride):
     return (H + 2 * pad - R) // stride + 1, (W + 2 * pad - S) // stride + 1
 
@@ -57,7 +76,7 @@ def conv2d(x, w, bias=None, stride=1, padding=0, w_layout=W_KCRS, relu=False, ti
     if out is None:
         out = torch.empty((B, K, max(Ho, 0), max(Wo, 0)), device=x.device, dtype=torch.float32)
     tp = C.byref(tile) if tile is not None else None
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         check(lib.tdc_conv2d_f32(_dev_f32(x, "x"), _dev_f32(w, "w"),
                                  _dev_f32(bias, "bias") if bias is not None else None, _dev_f32(out, "out"),
                                  B, Cc, H, W, K, R, S, padding, stride, w_layout,
@@ -79,7 +98,7 @@ def core_conv2d(x, w, stride=1, padding=0, w_layout=W_KCRS, tile=None, out=None)
     if out is None:
         out = torch.empty((B, K, max(Ho, 0), max(Wo, 0)), device=x.device, dtype=torch.float32)
     tp = C.byref(tile) if tile is not None else None
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         check(lib.tdc_core_conv2d_f32(_dev_f32(x, "x"), _dev_f32(w, "w"), _dev_f32(out, "out"),
                                       B, Cc, H, W, K, R, S, padding, stride, w_layout, tp, _stream()))
     return out
@@ -109,7 +128,7 @@ def tk_block(x, first, core, last, bias=None, stride=1, padding=0, core_layout=W
         workspace = torch.empty(need, device=x.device, dtype=torch.uint8)
     if out is None:
         out = torch.empty((B, K, Ho, Wo), device=x.device, dtype=torch.float32)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         check(lib.tdc_tk_block_f32(_dev_f32(x, "x"), _dev_f32(first, "first"), _dev_f32(core, "core"),
                                    _dev_f32(last, "last"), _dev_f32(bias, "bias") if bias is not None else None,
                                    _dev_f32(out, "out"), B, Cc, H, W, R1, R2, K, R, S, padding, stride,
@@ -141,7 +160,7 @@ def pool2d(x, kernel_size, stride=None, padding=0, mode=POOL_MAX, out=None):
     Ho, Wo = (H - kh + 2 * padding) // stride + 1, (W - kw + 2 * padding) // stride + 1
     if out is None:
         out = torch.empty((B, Cc, Ho, Wo), device=x.device, dtype=torch.float32)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         code = lib.tdc_pool2d_f32(_dev_f32(x, "x"), _dev_f32(out, "out"), B, Cc, H, W, kh, kw, padding, stride, mode, _stream())
     if code != _lib.OK:
         raise TdcError(code, "tdc_pool2d_f32: window %dx%d stride %d padding %d on %dx%d" % (kh, kw, stride, padding, H, W))
@@ -167,7 +186,7 @@ def conv2d_epi(x, w, scale=None, bias=None, residual=None, relu=False, stride=1,
     if residual is not None and tuple(residual.shape) != tuple(out.shape):
         raise TdcError(_lib.ERR_SHAPE, "residual %s does not match the output %s" % (tuple(residual.shape), tuple(out.shape)))
     e = _epilogue(scale, bias, residual, relu)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         check(lib.tdc_conv2d_epi_f32(_dev_f32(x, "x"), _dev_f32(w, "w"), _dev_f32(out, "out"), B, Cc, H, W, K, R, S,
                                      padding, stride, w_layout, C.byref(e), C.byref(tile) if tile is not None else None,
                                      _stream()))
@@ -196,7 +215,7 @@ def tk_block_epi(x, first, core, last, scale=None, bias=None, residual=None, rel
     if residual is not None and tuple(residual.shape) != tuple(out.shape):
         raise TdcError(_lib.ERR_SHAPE, "residual %s does not match the output %s" % (tuple(residual.shape), tuple(out.shape)))
     e = _epilogue(scale, bias, residual, relu)
-    with torch.cuda.device(x.device):
+    with _on_device(x.device):
         check(lib.tdc_tk_block_epi_f32(_dev_f32(x, "x"), _dev_f32(first, "first"), _dev_f32(core, "core"),
                                        _dev_f32(last, "last"), _dev_f32(out, "out"), B, Cc, H, W, R1, R2, K, R, S,
                                        padding, stride, core_layout, C.byref(e),

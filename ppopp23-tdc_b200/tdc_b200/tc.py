@@ -12,7 +12,7 @@ import torch
 
 from . import _lib
 from ._lib import TcPlan, TdcError, lib
-from .ops import _dev_f32, _epilogue, _stream
+from .ops import _dev_f32, _epilogue, _on_device, _stream
 
 
 def _check(code):
@@ -30,10 +30,31 @@ class TcConv:
         self.plan = TcPlan()
         _check((lib.tdc_tc_plan_make_general if general else lib.tdc_tc_plan_make)(Cc, K, R, S, mode, C.byref(self.plan)))
         self.C, self.K, self.R, self.S, self.mode, self.general = Cc, K, R, S, mode, bool(general)
-        self.wt = torch.empty(self.plan.weights_bytes, dtype=torch.uint8, device=weight.device)
-        with torch.cuda.device(weight.device):
-            _check(lib.tdc_tc_prepare_weights(C.byref(self.plan), _dev_f32(weight, "weight"), w_layout,
-                                              self.wt.data_ptr(), _stream()))
+        self._weight, self._w_layout = weight, w_layout
+        self.wt = self._prepare(self.plan)
+        self._by_nt = {self.plan.nt: (self.plan, self.wt)}       # output-channel block size -> (plan, prepared filter)
+        self._sms = torch.cuda.get_device_properties(weight.device).multi_processor_count
+        self._nt_of = {}                                         # positions -> block size (the rule is a library call)
+
+    def _prepare(self, plan):
+        wt = torch.empty(plan.weights_bytes, dtype=torch.uint8, device=self._weight.device)
+        with torch.cuda.device(self._weight.device):
+            _check(lib.tdc_tc_prepare_weights(C.byref(plan), _dev_f32(self._weight, "weight"), self._w_layout,
+                                              wt.data_ptr(), _stream()))
+        return wt
+
+    def _for_positions(self, positions):
+        """(plan, prepared filter) with the output-channel block size that suits `positions` output positions: the
+        default for layers with many position tiles, smaller blocks (more CTAs) for few; prepared on first use."""
+        nt = self._nt_of.get(positions)
+        if nt is None:
+            nt = self._nt_of[positions] = lib.tdc_tc_pick_nt(self.K, self.mode, positions, self._sms)
+        hit = self._by_nt.get(nt)
+        if hit is None:
+            plan = TcPlan()
+            _check(lib.tdc_tc_plan_make_nt(self.C, self.K, self.R, self.S, self.mode, int(self.general), nt, C.byref(plan)))
+            hit = self._by_nt[nt] = (plan, self._prepare(plan))
+        return hit
 
     def __call__(self, x, scale=None, bias=None, residual=None, relu=False, out=None, stride=1, padding=None):
         """`stride` > 1 is taken for 1x1 filters (the down-sampling shortcut of a residual stage) and by general
@@ -57,8 +78,10 @@ class TcConv:
         if out is None:
             out = torch.empty((B, self.K, Ho, Wo), device=x.device, dtype=torch.float32)
         e = _epilogue(scale, bias, residual, relu)
-        with torch.cuda.device(x.device):
-            _check(lib.tdc_conv2d_tc(C.byref(self.plan), _dev_f32(x, "x"), self.wt.data_ptr(), _dev_f32(out, "out"),
+        halo = 0 if self.general else (self.R - 1) // 2
+        plan, wt = self._for_positions(B * (Ho + halo) * (Wo + halo))
+        with _on_device(x.device):
+            _check(lib.tdc_conv2d_tc(C.byref(plan), _dev_f32(x, "x"), wt.data_ptr(), _dev_f32(out, "out"),
                                      B, H, W, C.byref(e), flags, _stream()))
         return out
 

@@ -30,3 +30,22 @@ def test_tensor_cores_only_where_they_fill_the_gpu(tc):
     assert not tc.worthwhile(32, 512, 7, 7, 256, 1) and not tc.worthwhile(32, 256, 7, 7, 512, 1)
     # many positions but hardly any arithmetic
     assert not tc.worthwhile(64, 3, 56, 56, 8, 1)
+
+
+def test_block_size_by_position_count(built):
+    """tdc_tc_pick_nt: the default block (128 / 64 / 32 output channels by K) for layers with many position tiles,
+    smaller blocks where the positions alone leave SMs idle — a host-side rule, no GPU."""
+    import ctypes as C
+    import tdc_b200 as T
+    from tdc_b200 import _lib
+    pick = lambda K, pos, mode=3: T.lib.tdc_tc_pick_nt(K, mode, pos, 148)
+    assert pick(64, 64 * 57 * 57) == 64 and pick(128, 64 * 29 * 29) == 128 and pick(32, 64 * 57 * 57) == 32
+    assert pick(128, 32 * 29 * 29) == 128        # 211 tiles fill 148 SMs: the default stays
+    assert pick(512, 64 * 8 * 8) == 128          # 7x7x512 at batch 64: 128 tiles of 128-channel blocks already
+    assert pick(256, 64 * 8 * 8) == 64           # 7x7x256 at batch 64: 64 tiles -> 128 tiles of 64-channel blocks
+    assert pick(256, 32 * 8 * 8) == 32           # the core of the 7x7 Tucker block at batch 32
+    p = _lib.TcPlan()
+    assert T.lib.tdc_tc_plan_make_nt(256, 256, 3, 3, 3, 0, 64, C.byref(p)) == 0
+    assert (p.nt, p.n_ocb, p.nkb) == (64, 4, 32) and p.weights_bytes == 4 * 2 * 9 * 8 * 64 * 32 * 4
+    assert T.lib.tdc_tc_plan_make_nt(256, 256, 3, 3, 3, 0, 48, C.byref(p)) == _lib.ERR_UNSUPPORTED
+    assert T.lib.tdc_tc_plan_make_nt(3, 64, 7, 7, 3, 1, 32, C.byref(p)) == 0 and (p.general, p.nt, p.n_ocb) == (1, 32, 2)
