@@ -199,3 +199,51 @@ def test_general_plan(T, B, Cc, K, H, W, R, stride, pad):
     if R == 1:
         assert torch.equal(y2, T.TcConv(w.cuda(), mode=3)(x.cuda(), stride=stride))
     assert tc.status() == 0
+
+
+@pytest.mark.gpu
+def test_random_shapes_against_fp64(T):
+    """Sixty seeded random layers (ragged channel counts, tiny and odd images, batch sizes around the tile and SM
+    counts, one-pass and gathering plans, random epilogue options) against the same convolution in fp64 on the GPU:
+    the launcher's choices (kernel, tiles per CTA, channels per block, blocks per stage) must never change a result
+    beyond the split-operand bar."""
+    import random
+    from tdc_b200 import tc
+    F = torch.nn.functional
+    rnd = random.Random(20231)
+    worst = 0.0
+    for case in range(60):
+        general = rnd.random() < 0.35
+        R = rnd.choice((1, 3, 5, 7)) if general else rnd.choice((1, 3))
+        stride = rnd.choice((1, 2, 3)) if (general or R == 1) else 1
+        pad = rnd.randint(0, R // 2 + 1) if general else (R - 1) // 2
+        Cc, K = rnd.choice((1, 3, 8, 20, 33, 64, 72, 130)), rnd.choice((1, 5, 32, 40, 64, 96, 130, 200))
+        H, W = rnd.choice((1, 2, 7, 9, 14, 28, 31)), rnd.choice((1, 3, 7, 12, 14, 28, 40))
+        if H + 2 * pad < R or W + 2 * pad < R:
+            continue
+        B = rnd.choice((1, 2, 5, 37, 150))
+        if B * Cc * H * W > 6e6 or B * K * H * W > 6e6:
+            B = 2
+        g = torch.Generator().manual_seed(case)
+        x = torch.randn(B, Cc, H, W, generator=g).cuda()
+        w = (torch.randn(K, Cc, R, R, generator=g) * (2.0 / (K * R * R)) ** 0.5).cuda()
+        scale = (torch.rand(K, generator=g) + 0.5).cuda() if rnd.random() < 0.5 else None
+        shift = torch.randn(K, generator=g).cuda() if rnd.random() < 0.5 else None
+        relu = rnd.random() < 0.5
+        ref = F.conv2d(x.double(), w.double(), None, stride, pad)
+        res = torch.randn(ref.shape, generator=g).cuda() if rnd.random() < 0.4 else None
+        if scale is not None:
+            ref = ref * scale.double().view(1, -1, 1, 1)
+        if shift is not None:
+            ref = ref + shift.double().view(1, -1, 1, 1)
+        if res is not None:
+            ref = ref + res.double()
+        if relu:
+            ref = ref.relu()
+        conv = T.TcConv(w, mode=3, general=general)
+        y = conv(x, scale, shift, res, relu, stride=stride, padding=pad if general else None)
+        assert y.shape == ref.shape, (case, y.shape, ref.shape)
+        err = float((y.double() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+        worst = max(worst, err)
+        assert err <= FP32_TOL, (case, general, B, Cc, K, H, W, R, stride, pad, err)
+    assert tc.status() == 0 and worst > 0.0
