@@ -67,6 +67,8 @@ struct Args {
     int nbuf;              // persistent kernel: accumulator buffers in tensor memory (1 or 2)
     int depth;             // persistent kernel: slots of the raw-input ring (cp.async groups in flight)
     int kps;               // persistent kernel: channel blocks per shared-memory stage
+    long long full_groups, tail_first_pt, pt_total;   // persistent kernel: tile list (see tile_of)
+    int tail_cnt;
     long long ntiles;      // persistent kernel: position tiles x output-channel blocks
     int* status;           // device status word: 0 ok, else first failure code
 };
@@ -702,8 +704,10 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     // kernel, which drains tensor memory with all its warps, measured faster, and with plain TF32 operands two
     // one-tile CTAs share an SM and overlap by themselves.  TDC_TC_PERSIST=0/1 forces either.
     const long long tiles_mt2 = ((a.total_pos + 2 * M_TILE - 1) / (2 * M_TILE)) * a.n_ocb;
+    // ... and for 3x3 filters with one 128-channel block when the tile list has complete rounds plus a rest: the
+    // persistent kernel spreads the rest over all SMs as smaller tiles (28x28x128 at batch 64: 88 -> 76 us).
     const bool persist = p->general || (env_persist ? atoi(env_persist) != 0
-                                                    : (a.hl == 2 && (p->nt <= 64 || (taps == 1 && tiles_mt2 >= sms))));
+                                                    : (a.hl == 2 && (p->nt <= 64 || (tiles_mt2 >= sms && (taps == 1 || (a.n_ocb == 1 && tiles_mt2 % sms != 0))))));
     int mt = 512 / a.tile_cols > 4 ? 4 : 512 / a.tile_cols, ns = 0, depth = 0, nbuf = 1;   // tensor memory: 512 columns
     if (env_mt && atoi(env_mt) >= 1) while (mt > atoi(env_mt)) mt /= 2;
     // 16-byte input loads: 1x1 filter, images a multiple of 4 positions long, 16-byte aligned base
@@ -779,7 +783,20 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     e = cudaGetSymbolAddress(&status_ptr, g_tc_status);
     if (e != cudaSuccess) return tc_fail(TDC_ERR_CUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
     a.status = (int*)status_ptr;
-    const long long tiles = (a.total_pos + (long long)mt * M_TILE - 1) / ((long long)mt * M_TILE);
+    long long tiles = (a.total_pos + (long long)mt * M_TILE - 1) / ((long long)mt * M_TILE);
+    a.pt_total = (a.total_pos + M_TILE - 1) / M_TILE;
+    a.full_groups = tiles; a.tail_first_pt = 0; a.tail_cnt = mt;          // every tile holds mt position tiles ...
+    const char* env_tail = getenv("TDC_TC_TAIL");
+    if (persist && a.n_ocb == 1 && mt > 1 && !(env_tail && atoi(env_tail) == 0)) {
+        // ... except that the position tiles left for the last, partial round are spread over all SMs as smaller tiles
+        const long long rounds = (a.pt_total / mt) / sms, full = rounds * sms, rest = a.pt_total - full * mt;
+        if (rounds >= 1 && rest > 0) {          // (with no complete round the choice of mt above already weighed SMs against filter traffic)
+            a.full_groups = full;
+            a.tail_first_pt = full * mt;
+            a.tail_cnt = (int)((rest + sms - 1) / sms);
+            tiles = full + (rest + a.tail_cnt - 1) / a.tail_cnt;
+        }
+    }
     a.ntiles = tiles * a.n_ocb;
     if (a.ntiles >= (1ll << 31)) return tc_fail(TDC_ERR_TILE, "grid too large");
     const long long ctas = persist ? (a.ntiles < sms ? a.ntiles : sms) : a.ntiles;

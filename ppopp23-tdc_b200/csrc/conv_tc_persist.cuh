@@ -22,6 +22,21 @@ namespace tdc_tc {
 constexpr int P_THREADS = 640;   // 8 loader warps, 4 issuer warps (one lane each), 2 groups of 4 epilogue warps
 constexpr int P_HEADER  = 256;   // bytes of barriers and flags in front of the stages
 
+// Tile t of the list -> first output position, position tiles it holds (`cnt` <= MT), output-channel block.
+// Tiles of the complete rounds hold MT position tiles; what is left for the last, partial round is spread over
+// all CTAs as smaller tiles (with one output-channel block; a.full_groups covers every tile otherwise), so the
+// launch ends after a part of a round instead of a whole one.
+template <int MT>
+__device__ __forceinline__ void tile_of(const Args& a, long long t, long long& g0, int& cnt, int& ocb) {
+    long long tg = t;
+    ocb = 0;
+    if (a.n_ocb > 1) { tg = t / a.n_ocb; ocb = (int)(t - tg * a.n_ocb); }
+    if (tg < a.full_groups) { g0 = tg * (MT * M_TILE); cnt = MT; return; }
+    const long long first = a.tail_first_pt + (tg - a.full_groups) * a.tail_cnt, left = a.pt_total - first;
+    g0 = first * M_TILE;
+    cnt = left < a.tail_cnt ? (int)left : a.tail_cnt;
+}
+
 template <int NT, int MT, int TAPS, bool VEC>
 __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -39,6 +54,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     const int a_floats = a.hl * CB * a.P, b_floats = a.hl * TAPS * CB * NT, stage_floats = a.kps * (a_floats + b_floats);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int pad = (a.taps_r - 1) / 2;
+    const int halo_rows = 2 * pad * (a.Wp + 1);                  // patch rows beyond the positions of a tile
     const long long HW = (long long)a.H * a.W;
     const uint32_t b_bytes = (uint32_t)b_floats * 4u;
     const int nbuf = a.nbuf;
@@ -103,8 +119,10 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             // 1x1 filter, H*W a multiple of 4: a thread owns 4 consecutive positions x 4 channels of a block;
             // four 16-byte loads (one per channel), transposed in registers into four 16-byte stores
             for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x) {
-                const int ocb = (int)(t % a.n_ocb);
-                const long long g0 = (t / a.n_ocb) * (MT * M_TILE);
+                long long g0;
+                int cnt, ocb;
+                tile_of<MT>(a, t, g0, cnt, ocb);
+                const int rows = cnt * M_TILE;                           // a one-tap filter has no halo
                 const float* wt_tile = a.wt + (long long)ocb * a.nkb * b_floats;
                 bool ok = true;
                 constexpr int NI = (MT * M_TILE / 2 + LOADERS - 1) / LOADERS;
@@ -113,7 +131,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 for (int i = 0; i < NI; ++i) {
                     const int quad = (tid + i * LOADERS) >> 1;
                     off[i] = -1;
-                    if (quad * 4 < a.P) {
+                    if (quad * 4 < rows) {
                         const long long g = g0 + quad * 4;
                         if (g < a.total_pos) { const long long b = g / a.Lp; off[i] = b * a.C * HW + (g - b * a.Lp); }
                     }
@@ -135,7 +153,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
 #pragma unroll
                     for (int i = 0; i < NI; ++i) {
                         const int item = tid + i * LOADERS, q = item & 1, pp = (item >> 1) * 4;
-                        if (pp < a.P) {
+                        if (pp < rows) {
                             put(A, q, pp + 0, v[i][0].x, v[i][1].x, v[i][2].x, v[i][3].x);
                             put(A, q, pp + 1, v[i][0].y, v[i][1].y, v[i][2].y, v[i][3].y);
                             put(A, q, pp + 2, v[i][0].z, v[i][1].z, v[i][2].z, v[i][3].z);
@@ -169,7 +187,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             const long long total = my_tiles * a.nkb;
             long long src_off[PPT];              // of the tile being copied: offset of channel 0 of each owned row, -1 = zeros
             long long l_tile = blockIdx.x;       // copy side: tile, channel block and raw slot of the next block to issue
-            int l_kb = 0, l_slot = 0;
+            int l_kb = 0, l_slot = 0, l_rows = 0, c_rows = 0;   // rows of the tile being copied / converted
             // general plan (TAPS == 1 only): a "channel" is an (input channel, filter row, filter column) triple
             // and a patch row is an output position, whose window starts at input (iy0, ix0), possibly outside
             const float* rbase[PPT];             // x at (image, channel 0, iy0, ix0) of each owned row (only formed, never read, when outside)
@@ -180,13 +198,16 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 if (li < total) {
                     if (TAPS == 1 && a.gather) {
                         if (l_kb == 0) {
-                            const long long g0 = (l_tile / a.n_ocb) * (MT * M_TILE);
+                            long long g0;
+                            int cnt, ocb;
+                            tile_of<MT>(a, l_tile, g0, cnt, ocb);
+                            l_rows = cnt * M_TILE;
 #pragma unroll
                             for (int i = 0; i < PPT; ++i) {
                                 const int pp = tid + i * LOADERS;
                                 rmask[i] = 0; rbase[i] = a.x;
                                 const long long g = g0 + pp;
-                                if (pp < a.P && g < a.total_pos) {
+                                if (pp < l_rows && g < a.total_pos) {
                                     const long long b = g / a.Lp;
                                     const int rem = (int)(g - b * a.Lp);
                                     const int oy = rem / a.Wp, ox = rem - oy * a.Wp;
@@ -207,7 +228,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                             const int sel = g_ci < g_cin ? ((1 << g_dy) | (0x10000 << g_dx)) : -1;   // -1 never matches a mask
 #pragma unroll
                             for (int i = 0; i < PPT; ++i) {
-                                if (tid + i * LOADERS < a.P) {
+                                if (tid + i * LOADERS < l_rows) {
                                     const bool real = (rmask[i] & sel) == sel;
                                     const float* src = real ? rbase[i] + delta : a.x;
                                     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;"
@@ -218,12 +239,16 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                         }
                     } else {
                         if (l_kb == 0) {
-                            const long long gp0 = (l_tile / a.n_ocb) * (MT * M_TILE) - (long long)pad * (a.Wp + 1);
+                            long long g0;
+                            int cnt, ocb;
+                            tile_of<MT>(a, l_tile, g0, cnt, ocb);
+                            l_rows = cnt * M_TILE + halo_rows;
+                            const long long gp0 = g0 - (long long)pad * (a.Wp + 1);
 #pragma unroll
                             for (int i = 0; i < PPT; ++i) {
                                 const int pp = tid + i * LOADERS;
                                 src_off[i] = -1;
-                                if (pp < a.P) {
+                                if (pp < l_rows) {
                                     const long long g = gp0 + pp;
                                     if (g >= 0 && g < a.total_pos) {
                                         const long long b = g / a.Lp;
@@ -239,7 +264,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
 #pragma unroll
                         for (int i = 0; i < PPT; ++i) {
                             const int pp = tid + i * LOADERS;
-                            if (pp < a.P) {
+                            if (pp < l_rows) {
                                 const float* src = a.x + (src_off[i] >= 0 ? src_off[i] + (long long)c0 * a.HWin : 0);
 #pragma unroll
                                 for (int j = 0; j < CB; ++j) {
@@ -257,7 +282,15 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             for (int d = 0; d < depth; ++d) issue(d);
             long long c_tile = blockIdx.x;
             int c_kb = 0, c_slot = 0;
-            const float* wt_tile = a.wt + (c_tile % a.n_ocb) * a.nkb * b_floats;
+            const float* wt_tile = a.wt;
+            auto enter_tile = [&]() {                      // convert side: rows and filter block of tile c_tile
+                long long g0;
+                int cnt, ocb;
+                tile_of<MT>(a, c_tile, g0, cnt, ocb);
+                c_rows = cnt * M_TILE + halo_rows;
+                wt_tile = a.wt + (long long)ocb * a.nkb * b_floats;
+            };
+            if (total > 0) enter_tile();
             for (long long ci = 0; ci < total && !*abort_flag; ++ci) {
                 float* A = open_stage(wt_tile, c_kb);
                 if (!A) break;
@@ -267,7 +300,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
 #pragma unroll
                 for (int i = 0; i < PPT; ++i) {
                     const int pp = tid + i * LOADERS;
-                    if (pp < a.P) {
+                    if (pp < c_rows) {
 #pragma unroll
                         for (int q = 0; q < CB / 4; ++q)
                             put(A, q, pp, R[(4 * q) * a.P + pp], R[(4 * q + 1) * a.P + pp], R[(4 * q + 2) * a.P + pp], R[(4 * q + 3) * a.P + pp]);
@@ -275,7 +308,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 }
                 close_stage(c_kb);
                 issue(ci + depth);                                         // the slot just read is free again
-                if (++c_kb == a.nkb) { c_kb = 0; c_tile += gridDim.x; wt_tile = a.wt + (c_tile % a.n_ocb) * a.nkb * b_floats; }
+                if (++c_kb == a.nkb) { c_kb = 0; c_tile += gridDim.x; if (ci + 1 < total) enter_tile(); }
             }
             asm volatile("cp.async.wait_all;" ::: "memory");
         }
@@ -288,6 +321,21 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             int st_idx = 0, st_use = 0;         // stage to consume next, parity of its use count
             for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x, ++j) {
                 const int slot = (int)(j % nbuf) * MT + mt;
+                long long g0_unused;
+                int cnt, ocb_unused;
+                tile_of<MT>(a, t, g0_unused, cnt, ocb_unused);
+                if (mt >= cnt) {
+                    // a smaller tile of the last round (always a CTA's last tile) has no position tile for this warp:
+                    // it only keeps the stages' hand-over in step, one arrival per stage use
+                    bool fine = true;
+                    for (int kb0 = 0; kb0 < a.nkb && fine; kb0 += a.kps) {
+                        fine = mbar_wait(&full_bar[st_idx], (uint32_t)st_use);
+                        if (fine && lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty_bar[st_idx])) : "memory");
+                        if (++st_idx == a.ns) { st_idx = 0; st_use ^= 1; }
+                    }
+                    if (!fine) { *abort_flag = 1; break; }
+                    continue;
+                }
                 // the epilogue must have emptied this accumulator slot (its previous use); the first use passes at once
                 if (!mbar_wait(&tempty_bar[slot], (uint32_t)(((j / nbuf) & 1) ^ 1))) { *abort_flag = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -321,11 +369,12 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
         constexpr int CHUNKS = NT / 32;
         long long j = 0;
         for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x, ++j) {
-            const int ocb = (int)(t % a.n_ocb);
-            const long long g0 = (t / a.n_ocb) * (MT * M_TILE);
+            long long g0;
+            int cnt, ocb;
+            tile_of<MT>(a, t, g0, cnt, ocb);
             bool ok = true;
 #pragma unroll 1
-            for (int mt = grp; mt < MT && ok; mt += 2) {
+            for (int mt = grp; mt < cnt && ok; mt += 2) {
                 // the position tiles of a CTA tile are handed over one by one: while this one is drained, the
                 // issuers of the others still run, and its own issuer may start on the next CTA tile
                 const int slot = (int)(j % nbuf) * MT + mt;

@@ -110,7 +110,8 @@ def test_module_and_network_precisions(T):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("B,Cc,K,H,W,R", [(1, 3, 5, 1, 1, 1), (2, 7, 9, 2, 3, 3), (5, 33, 130, 9, 13, 3), (70, 24, 40, 14, 14, 3),
-                                           (9, 64, 64, 56, 56, 3), (300, 16, 32, 7, 7, 3), (33, 40, 64, 15, 15, 1), (16, 32, 32, 28, 28, 1)])
+                                           (9, 64, 64, 56, 56, 3), (300, 16, 32, 7, 7, 3), (33, 40, 64, 15, 15, 1), (16, 32, 32, 28, 28, 1),
+                                           (100, 24, 128, 28, 28, 3), (47, 16, 64, 56, 56, 1)])
 def test_persistent_and_one_tile_kernels_agree(T, B, Cc, K, H, W, R, monkeypatch):
     """The launcher has two kernels (one tile per CTA; persistent CTAs walking a tile list with the accumulators
     handed over tile by tile).  Both are forced in turn through the environment switch the launcher reads per call,
@@ -137,7 +138,7 @@ def test_persistent_and_one_tile_kernels_agree(T, B, Cc, K, H, W, R, monkeypatch
         assert rel_err(out["1"][1][sel].cpu().numpy(), want) <= tol
         if mode == 3:
             y3 = out["1"][0]
-    for knobs in ({"TDC_TC_MT": "1"}, {"TDC_TC_MT": "2", "TDC_TC_NBUF": "1"}, {"TDC_TC_NS": "2", "TDC_TC_DEPTH": "2"}):
+    for knobs in ({"TDC_TC_MT": "1"}, {"TDC_TC_MT": "2", "TDC_TC_NBUF": "1"}, {"TDC_TC_NS": "2", "TDC_TC_DEPTH": "2"}, {"TDC_TC_TAIL": "0"}, {"TDC_TC_KPS": "1"}):
         for k, v in knobs.items():
             monkeypatch.setenv(k, v)
         assert torch.equal(T.TcConv(wd, mode=3)(xd), y3), knobs      # tile count, buffers and ring depth change no bit
