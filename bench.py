@@ -539,7 +539,7 @@ def main():
     # DRAM bytes (read + write) of each launch of the step from one ncu capture of this command
     # (dram__bytes_read.sum + dram__bytes_write.sum per launch, batch 64); the summary and the command
     # are in profiles/launch_list_bench.md.  Outputs stay in L2 within a launch, so this is input + filter.
-    NCU_DRAM_MB = {(56, 32): 25.8, (56, 64): 53.0, (28, 64): 13.2, (28, 128): 27.0, (14, 128): 7.7, (14, 256): 17.6,
+    NCU_DRAM_MB = {(56, 32): 25.8, (56, 64): 51.9, (28, 64): 13.2, (28, 128): 26.9, (14, 128): 7.7, (14, 256): 17.6,
                    (7, 256): 8.0, (7, 512): 25.4}
     roofline = {
         "bound": "tensor", "achieved": tot_fl / tot_tc3 / 1e6, "peak": tf32_peak / 3.0, "unit": "TFLOP/s",
