@@ -729,7 +729,7 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
         const int P = ((m * M_TILE + 2 * pad * (a.Wp + 1)) + 7) / 8 * 8;
         const size_t sb = sizeof(float) * ((size_t)a.hl * CB * P + (size_t)a.hl * taps * CB * p->nt);
         const size_t rb = ring ? sizeof(float) * (size_t)CB * P : 0;
-        if (2 * sb + 2 * rb > room || P > 3 * LOADERS) continue;
+        if (2 * sb + 2 * rb > room || P > (persist && m > 1 ? 4 : 3) * LOADERS) continue;     // rows per loader thread the kernels are built for
         const double ntl = (double)((a.total_pos + (long long)m * M_TILE - 1) / ((long long)m * M_TILE)) * a.n_ocb;
         const double rounds = (double)(((long long)ntl + sms - 1) / sms);
         const double tile_clk = a.nkb * (m * taps * op_bytes + (double)sb + 2.0 * rb) / 128.0 + 2000.0 * m * (p->nt / 32);

@@ -48,7 +48,9 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float*    stage0     = reinterpret_cast<float*>(smem_raw + P_HEADER);
 
-    constexpr int PPT = 3;
+    // patch rows per loader thread: MT x 128 positions, plus two image rows of halo for a 3x3 filter (the host keeps
+    // the patch within PPT x 256 rows; images up to 256 wide)
+    constexpr int PPT = TAPS == 1 ? (MT >= 2 ? MT / 2 : 1) : (MT == 1 ? 3 : 4);
     // a stage holds a.kps channel blocks (one for 3x3 filters; several for one-tap filters, whose stages would
     // otherwise be all hand-over and no work): [kps input blocks][kps filter blocks]
     const int a_floats = a.hl * CB * a.P, b_floats = a.hl * TAPS * CB * NT, stage_floats = a.kps * (a_floats + b_floats);

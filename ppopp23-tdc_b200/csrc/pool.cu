@@ -60,6 +60,23 @@ __global__ void maxpool_3x3s2_kernel(const float* __restrict__ x, float* __restr
     }
 }
 
+// 2x2 window, stride 2, no padding, max (the pooling of the VGG feature stack, inference/vgg_tt.py:116-123), H even,
+// W a multiple of 8: a thread makes 4 neighbouring outputs from two aligned 16-byte loads in each of two rows.
+__global__ void maxpool_2x2s2_kernel(const float* __restrict__ x, float* __restrict__ y, long long planes, int H, int W, int Ho, int Wo) {
+    const int q = Wo / 4;
+    const long long n = planes * Ho * q;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i % q), oy = (int)((i / q) % Ho);
+        const long long plane = i / ((long long)q * Ho);
+        const float* row = x + plane * H * W + (long long)(2 * oy) * W + 8 * t;
+        const float4 a0 = __ldg(reinterpret_cast<const float4*>(row)), b0 = __ldg(reinterpret_cast<const float4*>(row + 4));
+        const float4 a1 = __ldg(reinterpret_cast<const float4*>(row + W)), b1 = __ldg(reinterpret_cast<const float4*>(row + W + 4));
+        *reinterpret_cast<float4*>(y + (plane * Ho + oy) * Wo + 4 * t) =
+            make_float4(fmaxf(fmaxf(a0.x, a0.y), fmaxf(a1.x, a1.y)), fmaxf(fmaxf(a0.z, a0.w), fmaxf(a1.z, a1.w)),
+                        fmaxf(fmaxf(b0.x, b0.y), fmaxf(b1.x, b1.y)), fmaxf(fmaxf(b0.z, b0.w), fmaxf(b1.z, b1.w)));
+    }
+}
+
 }  // namespace
 
 extern "C" int tdc_pool2d_f32(const float* x, float* y, int B, int C, int H, int W, int window_h, int window_w, int pad,
@@ -74,11 +91,14 @@ extern "C" int tdc_pool2d_f32(const float* x, float* y, int B, int C, int H, int
     cudaStream_t st = (cudaStream_t)stream;
     const bool fast = mode == TDC_POOL_MAX && window_h == 3 && window_w == 3 && stride == 2 && pad == 1 && W % 8 == 0 &&
                       reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0;
-    const long long n = fast ? planes * Ho * (Wo / 4) : planes * Ho * Wo;
+    const bool fast2 = mode == TDC_POOL_MAX && window_h == 2 && window_w == 2 && stride == 2 && pad == 0 && W % 8 == 0 && H % 2 == 0 &&
+                       reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0;
+    const long long n = (fast || fast2) ? planes * Ho * (Wo / 4) : planes * Ho * Wo;
     const int threads = 256;
     long long blocks = (n + threads - 1) / threads;
     if (blocks > 148ll * 64) blocks = 148ll * 64;
     if (fast) maxpool_3x3s2_kernel<<<(unsigned)blocks, threads, 0, st>>>(x, y, planes, H, W, Ho, Wo);
+    else if (fast2) maxpool_2x2s2_kernel<<<(unsigned)blocks, threads, 0, st>>>(x, y, planes, H, W, Ho, Wo);
     else pool_generic_kernel<<<(unsigned)blocks, threads, 0, st>>>(x, y, planes, H, W, Ho, Wo, window_h, window_w, pad, stride, mode);
     return cudaGetLastError() == cudaSuccess ? TDC_OK : TDC_ERR_CUDA;
 }

@@ -14,7 +14,7 @@ def T(built):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("B,C,H,W,k,s,p", [(2, 3, 16, 16, 3, 2, 1), (3, 5, 112, 112, 3, 2, 1), (2, 5, 15, 13, 3, 2, 1), (1, 4, 8, 8, 2, 2, 0),
-                                            (2, 2, 9, 24, 3, 2, 1), (1, 1, 1, 1, 1, 1, 0), (2, 3, 7, 7, 7, 1, 0), (1, 2, 10, 10, 3, 1, 1)])
+                                            (2, 2, 9, 24, 3, 2, 1), (3, 5, 56, 56, 2, 2, 0), (2, 3, 6, 24, 2, 2, 0), (1, 2, 7, 8, 2, 2, 0), (1, 1, 1, 1, 1, 1, 0), (2, 3, 7, 7, 7, 1, 0), (1, 2, 10, 10, 3, 1, 1)])
 def test_pooling_matches_torch(T, B, C, H, W, k, s, p):
     x = torch.randn(B, C, H, W, generator=torch.Generator().manual_seed(H * W + k))
     xd = x.cuda()
