@@ -49,6 +49,7 @@ struct Args {
     float*       y;        // [B][K][H][W]
     const float* scale; const float* bias; const float* residual;
     int relu;
+    int epi_vec;           // scale and bias are 16-byte aligned (or absent): whole chunks read them as 16-byte words
     int B, C, H, W, K;     // H, W: the OUTPUT image (equal to the input image unless a 1x1 filter is strided)
     int stride, Win;       // input step per output position and input row length
     long long HWin;        // input image size (channel pitch of x)
@@ -253,18 +254,38 @@ __device__ __forceinline__ void store_chunk(const Args& a, const uint32_t (&r)[3
         }
         return;
     }
-    const float sc = (a.scale && lane < n) ? __ldg(a.scale + oc0 + lane) : 1.f;
-    const float bi = (a.bias && lane < n) ? __ldg(a.bias + oc0 + lane) : 0.f;
     float v[32];
 #pragma unroll
     for (int k = 0; k < 32; ++k) v[k] = __uint_as_float(r[k]);
-    if (a.scale) {
+    if (n >= 32 && a.epi_vec) {
+        // a whole chunk, 16-byte aligned scale / bias: eight warp-uniform 16-byte loads each instead of 32 shuffles
+        if (a.scale) {
+            const float4* sp = reinterpret_cast<const float4*>(a.scale + oc0);
 #pragma unroll
-        for (int k = 0; k < 32; ++k) v[k] *= __shfl_sync(0xffffffffu, sc, k);
-    }
-    if (a.bias) {
+            for (int k4 = 0; k4 < 8; ++k4) {
+                const float4 t = __ldg(sp + k4);
+                v[4 * k4] *= t.x; v[4 * k4 + 1] *= t.y; v[4 * k4 + 2] *= t.z; v[4 * k4 + 3] *= t.w;
+            }
+        }
+        if (a.bias) {
+            const float4* bp = reinterpret_cast<const float4*>(a.bias + oc0);
 #pragma unroll
-        for (int k = 0; k < 32; ++k) v[k] += __shfl_sync(0xffffffffu, bi, k);
+            for (int k4 = 0; k4 < 8; ++k4) {
+                const float4 t = __ldg(bp + k4);
+                v[4 * k4] += t.x; v[4 * k4 + 1] += t.y; v[4 * k4 + 2] += t.z; v[4 * k4 + 3] += t.w;
+            }
+        }
+    } else {
+        const float sc = (a.scale && lane < n) ? __ldg(a.scale + oc0 + lane) : 1.f;
+        const float bi = (a.bias && lane < n) ? __ldg(a.bias + oc0 + lane) : 0.f;
+        if (a.scale) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] *= __shfl_sync(0xffffffffu, sc, k);
+        }
+        if (a.bias) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] += __shfl_sync(0xffffffffu, bi, k);
+        }
     }
     if (a.residual && live) {
         const float* rp = a.residual + o0;
@@ -274,10 +295,19 @@ __device__ __forceinline__ void store_chunk(const Args& a, const uint32_t (&r)[3
 #pragma unroll
         for (int k = 0; k < 32; ++k) v[k] += rv[k];
     }
-    if (live) {
+    if (a.relu) {
 #pragma unroll
-        for (int k = 0; k < 32; ++k)
-            if (k < n) yp[k * HW] = a.relu ? fmaxf(v[k], 0.f) : v[k];
+        for (int k = 0; k < 32; ++k) v[k] = fmaxf(v[k], 0.f);
+    }
+    if (live) {
+        if (n >= 32) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) { *yp = v[k]; yp += HW; }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+                if (k < n) yp[k * HW] = v[k];
+        }
     }
 }
 
@@ -664,6 +694,7 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     Args a{};
     a.x = x; a.wt = (const float*)wt; a.y = y;
     if (epi) { a.scale = epi->scale; a.bias = epi->bias; a.residual = epi->residual; a.relu = epi->relu ? 1 : 0; }
+    a.epi_vec = reinterpret_cast<uintptr_t>(a.scale) % 16 == 0 && reinterpret_cast<uintptr_t>(a.bias) % 16 == 0;
     // from here on H and W are the output image; the input image is only an address pattern of the loaders
     a.stride = stride; a.Win = W; a.HWin = (long long)H * W; a.Hin = H;
     if (p->general) {
