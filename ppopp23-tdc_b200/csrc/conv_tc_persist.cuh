@@ -19,7 +19,11 @@
 
 namespace tdc_tc {
 
-constexpr int P_THREADS = 640;   // 8 loader warps, 4 issuer warps (one lane each), 2 groups of 4 epilogue warps
+#ifndef TDC_TC_EPI_GROUPS
+#define TDC_TC_EPI_GROUPS 2
+#endif
+constexpr int P_GROUPS  = TDC_TC_EPI_GROUPS;          // groups of four epilogue warps
+constexpr int P_THREADS = 384 + 128 * P_GROUPS;     // 8 loader warps, 4 issuer warps (one lane each), the epilogue groups
 constexpr int P_HEADER  = 256;   // bytes of barriers and flags in front of the stages
 
 // Tile t of the list -> first output position, position tiles it holds (`cnt` <= MT), output-channel block.
@@ -64,7 +68,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
 
     if (tid == 0) {
         for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], LOADERS / 32 + 1); mbar_init(&empty_bar[s], MT); }   // one arrival per loader warp + the filter's bytes
-        for (int b = 0; b < 8; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }             // one per issuer; one per epilogue warp
+        for (int b = 0; b < 8; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4 * (NT / 32)); }   // one per issuer; one per epilogue warp and 32-channel chunk
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -363,9 +367,10 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             }
         }
     } else {
-        // ================= epilogue: warps 12-19, two groups of four (one lane quarter of tensor memory per warp);
-        // group g drains the position tiles mt = g, g+2: the epilogue is a latency chain (tensor memory -> registers
-        // -> residual loads -> stores), and two chains in flight hide more of it than one =================
+        // ================= epilogue: P_GROUPS groups of four warps (one lane quarter of tensor memory per warp).
+        // The work items of a CTA tile are (position tile, 32-channel chunk) pairs, dealt to the groups in turn: the
+        // epilogue is a latency chain (tensor memory -> registers -> residual loads -> stores), and several chains in
+        // flight hide more of it than one; all groups start on the first position tile, whose issuer is released first.
         const int grp = (warp - 12) >> 2;
         const int q = warp & 3;
         constexpr int CHUNKS = NT / 32;
@@ -376,7 +381,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             tile_of<MT>(a, t, g0, cnt, ocb);
             bool ok = true;
 #pragma unroll 1
-            for (int mt = grp; mt < cnt && ok; mt += 2) {
+            for (int item = grp; item < cnt * CHUNKS && ok; item += P_GROUPS) {
+                const int mt = item / CHUNKS, chunk = item - mt * CHUNKS;
                 // the position tiles of a CTA tile are handed over one by one: while this one is drained, the
                 // issuers of the others still run, and its own issuer may start on the next CTA tile
                 const int slot = (int)(j % nbuf) * MT + mt;
@@ -390,18 +396,14 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
                     if (yy < a.H && xx < a.W) out_off = b * a.K * HW + (long long)yy * a.W + xx;
                 }
-#pragma unroll 1
-                for (int chunk = 0; chunk < CHUNKS; ++chunk) {
-                    uint32_t r[32];
-                    load_chunk<NT>(a, tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * a.tile_cols + chunk * 32), r);
-                    if (chunk == CHUNKS - 1) {
-                        // everything of this slot is in registers: hand it back before the stores
-                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tempty_bar[slot])) : "memory");
-                    }
-                    store_chunk(a, r, out_off, ocb * NT + chunk * 32, HW);
-                }
+                uint32_t r[32];
+                load_chunk<NT>(a, tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * a.tile_cols + chunk * 32), r);
+                // this chunk of the slot is in registers: one arrival per warp and chunk hands the slot back when
+                // all of its chunks have been read, before the stores
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tempty_bar[slot])) : "memory");
+                store_chunk(a, r, out_off, ocb * NT + chunk * 32, HW);
             }
             if (!ok) break;
         }
