@@ -11,8 +11,9 @@
 //     issues the MMAs of position tile mt and may start the next CTA tile as soon as ITS
 //     accumulators have been read, while the other issuers still work on this one (and tensor
 //     memory holds two CTA tiles outright when 2 x MT x columns-per-tile fits in 512 columns);
-//   * two groups of four epilogue warps (12-15, 16-19; group g drains the position tiles g, g+2)
-//     release an accumulator as soon as its values are in registers and only then store.
+//   * two groups of four epilogue warps (12-15, 16-19) take the (position tile, 32-channel chunk)
+//     items of a CTA tile in turn; an accumulator is handed back as soon as all its chunks are in
+//     registers, before the stores.
 // Every mbarrier wait is bounded; a wait that runs out raises the CTA's abort flag, every
 // role leaves its loop at the next check, the status word is set and tensor memory is freed.
 #pragma once
