@@ -97,12 +97,15 @@ def general_supported(R, S, stride, padding, Wo):
 
 
 def worthwhile(B, C, H, W, K, R):
-    """The tensor-core kernel works on tiles of 128 positions x up to 128 channels.  With fewer than about 16
-    position tiles, or below about 0.2 GFLOP, there is too little to fill 148 SMs and the fp32 kernel with its
-    channel slices and clusters is the faster one (batch-1 layers, 7x7 images at small batch): measured on the
-    Tucker blocks C = 64..512 at batch 32, where it loses only the 1x1 steps of the 7x7 block."""
+    """The tensor-core kernel works on tiles of 128 positions x up to 128 channels; with too few position tiles or too
+    little arithmetic the fp32 kernel with its channel slices and clusters is the faster one.  Measured crossovers
+    (sweep shapes at batch 1..8, Tucker blocks at batch 32): a 3x3 layer wants about 4 position tiles and 0.1 GFLOP,
+    a 1x1 layer (little work per channel block, so the hand-overs dominate) about 16 tiles and 0.2 GFLOP."""
     pad = (R - 1) // 2
-    return 2.0 * B * H * W * C * K * R * R >= 0.2e9 and B * (H + pad) * (W + pad) >= 16 * 128
+    flops, positions = 2.0 * B * H * W * C * K * R * R, B * (H + pad) * (W + pad)
+    if R == 1:
+        return flops >= 0.2e9 and positions >= 16 * 128
+    return flops >= 0.1e9 and positions >= 4 * 128
 
 
 def cached(owner, name, weight, mode, w_layout=_lib.W_KCRS, general=False):

@@ -20,8 +20,12 @@ def test_one_pass_plan_covers_same_convs_and_strided_1x1(tc):
 
 def test_tensor_cores_only_where_they_fill_the_gpu(tc):
     # batch-1 layers: the fp32 kernel with clusters (too few positions or too little arithmetic for 128-position tiles)
-    for H, R in ((56, 32), (28, 64), (28, 128), (14, 256), (7, 512)):
+    for H, R in ((56, 32), (28, 64), (14, 128), (14, 256), (7, 512)):
         assert not tc.worthwhile(1, R, H, H, R, 3)
+    assert tc.worthwhile(1, 64, 56, 56, 64, 3)                       # 26 position tiles, 0.23 GFLOP: measured 16 vs 19 us
+    # a few images are enough for the 3x3 layers with at least four position tiles
+    assert tc.worthwhile(2, 32, 56, 56, 32, 3) and tc.worthwhile(4, 128, 14, 14, 128, 3) and tc.worthwhile(8, 512, 7, 7, 512, 3)
+    assert not tc.worthwhile(2, 256, 7, 7, 256, 3) and not tc.worthwhile(4, 512, 7, 7, 512, 3)
     # batch 64: tensor cores for every sweep shape
     for H, R in ((56, 32), (28, 64), (14, 128), (7, 256), (7, 512)):
         assert tc.worthwhile(64, R, H, H, R, 3)
