@@ -34,6 +34,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <map>
+#include <mutex>
+#include <utility>
 #include "../../include/tdc_b200.h"
 
 namespace tdc_tc {
@@ -600,6 +603,13 @@ int tc_fail(int code, const char* fmt, ...) {
 __device__ int g_tc_status;   // 0 = every wait of every launch so far completed
 
 int pick_nt(int K) { return K > 64 ? 128 : (K > 32 ? 64 : 32); }
+
+// What a launch would otherwise ask the runtime every time: per device the shared-memory limit, the SM count and
+// the address of the status word; per (device, kernel) the dynamic shared-memory size already opted in.
+struct DevFacts { int smem_max = 0, sms = 0; int* status = nullptr; };
+std::mutex g_tc_mu;
+std::map<int, DevFacts> g_tc_dev;
+std::map<std::pair<int, const void*>, size_t> g_tc_smem_set;
 int cdiv(int a, int b) { return (a + b - 1) / b; }
 
 }  // namespace
@@ -717,9 +727,23 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     int device;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return tc_fail(TDC_ERR_NO_DEVICE, "cudaGetDevice: %s", cudaGetErrorString(e));
-    int smem_max = 0, sms = 148;
-    cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    DevFacts facts;
+    {
+        std::lock_guard<std::mutex> lk(g_tc_mu);
+        auto it = g_tc_dev.find(device);
+        if (it == g_tc_dev.end()) {
+            DevFacts f;
+            void* sp = nullptr;
+            if ((e = cudaDeviceGetAttribute(&f.smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, device)) != cudaSuccess ||
+                (e = cudaDeviceGetAttribute(&f.sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess ||
+                (e = cudaGetSymbolAddress(&sp, g_tc_status)) != cudaSuccess)
+                return tc_fail(TDC_ERR_CUDA, "device query: %s", cudaGetErrorString(e));
+            f.status = (int*)sp;
+            it = g_tc_dev.emplace(device, f).first;
+        }
+        facts = it->second;
+    }
+    const int smem_max = facts.smem_max, sms = facts.sms;
     // long reductions get two main accumulators per tile (4*NT columns per tile instead of 2*NT)
     a.nmain = (a.hl == 2 && (long long)p->nkb * taps > 320) ? 2 : 1;
     a.tile_cols = (a.nmain == 2 ? 4 : 2) * p->nt;
@@ -811,10 +835,7 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     a.tmem_cols = 32;
     while (a.tmem_cols < nbuf * mt * a.tile_cols) a.tmem_cols *= 2;
     const size_t smem = header + ns * stage_bytes + depth * raw_bytes;
-    void* status_ptr = nullptr;
-    e = cudaGetSymbolAddress(&status_ptr, g_tc_status);
-    if (e != cudaSuccess) return tc_fail(TDC_ERR_CUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-    a.status = (int*)status_ptr;
+    a.status = facts.status;
     long long tiles = (a.total_pos + (long long)mt * M_TILE - 1) / ((long long)mt * M_TILE);
     a.pt_total = (a.total_pos + M_TILE - 1) / M_TILE;
     a.full_groups = tiles; a.tail_first_pt = 0; a.tail_cnt = mt;          // every tile holds mt position tiles ...
@@ -842,8 +863,15 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     else fn = mt == 4 ? TDC_TC_PICK(32, 4) : (mt == 2 ? TDC_TC_PICK(32, 2) : TDC_TC_PICK(32, 1));
 #undef TDC_TC_PICK
 #undef TDC_TC_PICK3
-    e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return tc_fail(TDC_ERR_CUDA, "cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(e));
+    {
+        std::lock_guard<std::mutex> lk(g_tc_mu);
+        size_t& have = g_tc_smem_set[{device, fn}];
+        if (smem > have) {
+            e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return tc_fail(TDC_ERR_CUDA, "cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(e));
+            have = smem;
+        }
+    }
     void* args[] = {&a};
     e = cudaLaunchKernel(fn, dim3((unsigned)ctas), dim3(threads), args, smem, (cudaStream_t)stream);
     return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "launch: %s", cudaGetErrorString(e));
