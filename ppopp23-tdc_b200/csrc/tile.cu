@@ -176,10 +176,31 @@ double tile_cost(const Shape& s, const tdc_tile& t, const Geometry& g, const tdc
         double lsu = lsu_per_warp * resident * warps / 0.6;
         return std::max(issue, lsu) + 0.25 * std::min(issue, lsu);
     };
+    // Latency of one CTA, which bounds a wave from below however few warps share the SM.  Each chunk is a dependent
+    // step — copy issued, copy landed, barrier, arithmetic — and on a GPU that the grid barely fills (the batch-1
+    // layers) nothing else hides it: the sweeps there give about 12,000 cycles a chunk plus its bytes at 20 B/clk,
+    // with 0.7 of the chunk's arithmetic on top (the rest runs under the next copy), and 70 cycles per accumulator
+    // for every further rank of a cluster whose partial sums the leader adds over distributed shared memory.
+    // Without this term the model kept few CTAs walking many chunks where a cluster that splits them is 2x faster.
+    // Constants fitted on six measured sweeps (batch 1 to 256, 78 shapes): mean loss of the model's pick against
+    // the measured best 6.6 %, against 37 % without the term.
+    // Latency of one CTA, which bounds a wave from below however few warps share the SM.  Each chunk is a dependent
+    // step — copy issued, copy landed, barrier, arithmetic — and on a GPU that the grid barely fills (the batch-1
+    // layers) nothing else hides it: 6,000 cycles a chunk plus its bytes at 20 B/clk, 0.7 of the chunk's arithmetic
+    // on top (the rest runs under the next copy), and 70 cycles per accumulator for every further rank of a cluster
+    // whose partial sums the leader adds over distributed shared memory.  Without this term the model kept few CTAs
+    // walking many chunks where a cluster that splits them is 2x faster.  Constants chosen on a B200 by timing the
+    // model's own pick for the 78 shapes of the measured tables (batch 1 to 256): it is 1.19x slower than the
+    // table's tile on average (geometric mean over the six tables), against 1.37x without the term.
+    const double chunk_bytes = 4.0 * ((double)t.tc * g.patch + (double)t.tc * RS * ocb);
+    const double chunk_copy = 6000.0 + chunk_bytes / 20.0;
+    const double chunk_math = (ch_per_thread / std::max(nchunks, 1)) * per_ch * std::max(warps / 4.0, 1.0) / issue_eff(warps / 4.0);
+    const double cta_latency = nchunks * (chunk_copy + 0.7 * chunk_math) + fixed + (t.ks > 1 ? 2.5 * nacc * (t.ks - 1) : 0.0) +
+                               (t.kc > 1 ? 70.0 * nacc * (t.kc - 1) : 0.0);
     long long slots = (long long)dev.sm_count * cps;
     long long full = g.ctas / slots, rem = g.ctas % slots;
-    double cycles = full * batch_time(cps);
-    if (rem) cycles += batch_time((int)cdiv((int)rem, dev.sm_count));
+    double cycles = full * std::max(batch_time(cps), cta_latency);
+    if (rem) cycles += std::max(batch_time((int)cdiv((int)rem, dev.sm_count)), cta_latency);
     if (vols) {
         vols[0] = (double)g.ctas * s.C * RS * ocb;                 // filter words staged
         vols[1] = (double)g.ctas * s.C * g.patch;                  // input words staged

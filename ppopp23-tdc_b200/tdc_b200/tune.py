@@ -129,6 +129,9 @@ def main(argv=None):
     ap.add_argument("--out", default="tile_table.csv")
     ap.add_argument("--shapes", default="sweep", choices=["sweep", "resnet18", "tkblock"])
     ap.add_argument("--max-per-shape", type=int, default=300)
+    ap.add_argument("--model-top", type=int, default=60,
+                    help="candidates the analytical model ranks best are always measured, beside the random sample")
+    ap.add_argument("--keep", default=None, help="an earlier table: its tile for a shape is measured again beside the new candidates")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--best-out", default=None, help="also write the fastest row per shape to this CSV")
@@ -139,6 +142,7 @@ def main(argv=None):
     cover = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
     reps = 1 if a.batch >= 16 else 8
     shapes = {"sweep": sweep_shapes, "resnet18": resnet18_shapes, "tkblock": tkblock_shapes}[a.shapes]()
+    kept = best_rows(a.keep) if a.keep else {}
     with open(a.out, "w", newline="") as f:
         wr = csv.writer(f)
         wr.writerow(COLUMNS)
@@ -154,9 +158,20 @@ def main(argv=None):
             cands = candidates(B, Cc, H, W, N, R, R, pad, stride)
             model_pick = ops.select_tile(*shape).as_tuple()
             if len(cands) > a.max_per_shape:
-                cands = rnd.sample(cands, a.max_per_shape)
+                def modelled(c):
+                    try:
+                        return ops.tile_cost(shape, Tile(*c))[0]
+                    except TdcError:
+                        return float("inf")
+                ranked = sorted(cands, key=modelled)[:a.model_top]
+                cands = ranked + [c for c in rnd.sample(cands, a.max_per_shape) if c not in ranked]
             if model_pick not in cands:
                 cands.append(model_pick)
+            old = kept.get((Cc, N, H, W, B, R, stride))
+            if old is not None:
+                old = tuple(int(old[k]) for k in ("th", "tw", "tc", "tn", "nog", "gy", "gx", "imgs", "ks", "kc"))
+                if old not in cands:
+                    cands.append(old)
             n_ok = 0
             for c in cands:
                 t = Tile(*c)
