@@ -298,6 +298,19 @@ TDC_API int tdc_pool2d_f32(const float* x, float* y, int B, int C, int H, int W,
                            int pad, int stride, int mode, void* stream);
 
 /*
+ * Per-channel scale, shift and ReLU with image strides: y[b][c][i] = relu?(x[b][c][i]*scale[c] + shift[c]) for
+ * i < HW, image b of x at x + b*x_image_stride and of y at y + b*y_image_stride (strides in elements,
+ * >= C*HW).  One call stands for the reference's BatchNorm::forward in its inference form followed by
+ * Activation::forward (A100-evaluation/EndToEnd/densenet121-tk/src/BatchNorm.cu:58-80, src/Activation.cu:38-41)
+ * ahead of each conv of a dense layer (src/TenDense.cu:44-53; norm1 / norm2 of
+ * inference/densenet_inet_tt.py:36-60), reading the first C channels of the block's feature buffer in place;
+ * with scale = shift = NULL and relu = 0 it is the strided copy that appends a layer's new features to that
+ * buffer (Concate::forward, inc/common.h:165-177).  scale / shift NULL = 1 / 0.
+ */
+TDC_API int tdc_affine_relu_f32(const float* x, float* y, const float* scale, const float* shift, int B, int C, int HW,
+                                long long x_image_stride, long long y_image_stride, int relu, void* stream);
+
+/*
  * Layer objects with the surface of the reference's end-to-end classes:
  * Conv::initialize(b,c,h,w,n,pad,r,s,stride,weightFile,use_bias) / float* Conv::forward(float*)
  * (A100-evaluation/EndToEnd/resnet18-tk/inc/common.h:38-69, src/Conv.cu:2-125) and

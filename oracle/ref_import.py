@@ -59,6 +59,69 @@ def import_resnet():
     return resnet_inet_tt
 
 
+def import_svdconv():
+    """Returns the reference's SVDConv module (SVDConv2dC, SVDConv2dM, SVDConv2dR); it needs torch and numpy only."""
+    if not available():
+        raise ImportError("reference tree not found at %s" % REFERENCE_ROOT)
+    inf = os.path.join(REFERENCE_ROOT, "inference")
+    if inf not in sys.path:
+        sys.path.insert(0, inf)
+    import SVDConv   # noqa: the reference's module name
+    return SVDConv
+
+
+def import_densenet():
+    """Returns the reference's densenet_inet_tt module (TenDenseNet, ...), unmodified.  It takes four things from
+    timm, which is not installed here (inference/densenet_inet_tt.py:5,14-18): the model registry decorator (an
+    identity stub), `build_model_with_cfg` / `create_norm_act` / `BlurPool2d` (imported, never used by the default
+    configuration: stubs that raise), and two building blocks that the default network does use and that are restated
+    here from timm's documented behaviour — `BatchNormAct2d` = nn.BatchNorm2d followed by ReLU under BatchNorm2d's
+    parameter names, and `create_classifier(num_features, num_classes, pool_type='avg')` = (global average pool +
+    flatten, nn.Linear).  Everything else — the dense layers, blocks, transitions, the Tucker and SVD convs — is the
+    reference's code."""
+    import torch
+    import torch.nn as nn
+    import_tkconv()
+
+    class BatchNormAct2d(nn.BatchNorm2d):
+        def forward(self, x):
+            return torch.relu(super().forward(x))
+
+    class _GlobalAvgFlatten(nn.Module):
+        def forward(self, x):
+            return x.mean((2, 3))
+
+    def create_classifier(num_features, num_classes, pool_type='avg'):
+        assert pool_type == 'avg'
+        return _GlobalAvgFlatten(), nn.Linear(num_features, num_classes)
+
+    reg = _stub("timm.models.registry", register_model=lambda f: f)
+    helpers = _stub("timm.models.helpers", build_model_with_cfg=_unavailable)
+    layers = _stub("timm.models.layers", BatchNormAct2d=BatchNormAct2d, create_norm_act=_unavailable,
+                   BlurPool2d=_unavailable, create_classifier=create_classifier)
+    for name, val in (("BatchNormAct2d", BatchNormAct2d), ("create_norm_act", _unavailable), ("BlurPool2d", _unavailable),
+                      ("create_classifier", create_classifier)):
+        if not hasattr(layers, name):
+            setattr(layers, name, val)
+    models = _stub("timm.models", registry=reg)
+    models.helpers, models.layers = helpers, layers
+    data = _stub("timm.data", IMAGENET_DEFAULT_MEAN=(0.485, 0.456, 0.406), IMAGENET_DEFAULT_STD=(0.229, 0.224, 0.225))
+    timm = _stub("timm", models=models, create_model=_unavailable)
+    timm.data = data
+    import densenet_inet_tt   # noqa: the reference's module name
+    return densenet_inet_tt
+
+
+def import_hp_dict(module_name):
+    """A module of the reference's inference/hp_dicts (e.g. "tk_densenet121_hp"): plain Python dictionaries."""
+    import importlib.util
+    path = os.path.join(REFERENCE_ROOT, "inference", "hp_dicts", module_name + ".py")
+    spec = importlib.util.spec_from_file_location("tdc_ref_" + module_name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 class Ranks:
     """Stand-in for the hp_dict objects of inference/hp_dicts/*.py: `.ranks[name] -> [R2, R1]`."""
 

@@ -66,6 +66,7 @@ _PROTOTYPES = {
     "tdc_permute_weights": (_i, [_p, _p, _i, _i, _i, _i, _p]),
     "tdc_tc_last_error_string": (C.c_char_p, []),
     "tdc_pool2d_f32": (_i, [_p, _p] + [_i] * 9 + [_p]),
+    "tdc_affine_relu_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, C.c_longlong, C.c_longlong, _i, _p]),
     "tdc_tc_plan_make": (_i, [_i] * 5 + [C.POINTER(TcPlan)]),
     "tdc_tc_plan_make_general": (_i, [_i] * 5 + [C.POINTER(TcPlan)]),
     "tdc_tc_pick_nt": (_i, [_i, _i, C.c_longlong, _i]),

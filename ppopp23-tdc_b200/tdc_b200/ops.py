@@ -167,6 +167,39 @@ def pool2d(x, kernel_size, stride=None, padding=0, mode=POOL_MAX, out=None):
     return out
 
 
+def _image_view(t, name):
+    """(pointer, image stride) of a [B][C][H][W] fp32 CUDA tensor whose images are dense [C][H][W] blocks that may be
+    spaced apart — a channel slice `buf[:, :C]` of a larger NCHW buffer."""
+    B, Cc, H, W = t.shape
+    if t.dtype != torch.float32 or not t.is_cuda:
+        raise TdcError(_lib.ERR_UNSUPPORTED, "%s must be a float32 CUDA tensor" % name)
+    sb, sc, sh, sw = t.stride()
+    if (sc, sh, sw) != (H * W, W, 1) or (B > 1 and sb < Cc * H * W):
+        raise TdcError(_lib.ERR_UNSUPPORTED, "%s: images must be dense [C][H][W] blocks (strides %s)" % (name, t.stride()))
+    return t.data_ptr(), (sb if B > 1 else Cc * H * W)
+
+
+def affine_relu(x, scale=None, shift=None, relu=True, out=None):
+    """y = relu?(x*scale[c] + shift[c]) per channel — inference BatchNorm + ReLU ahead of a conv (norm1 / norm2 of a
+    dense layer, inference/densenet_inet_tt.py:36-60; BatchNorm::forward + Activation::forward of the end-to-end
+    skeleton).  `x` and `out` may be channel slices of larger NCHW buffers; with no scale, shift or ReLU this is the
+    copy that appends new features to a dense block's feature buffer."""
+    B, Cc, H, W = x.shape
+    if out is None:
+        out = torch.empty((B, Cc, H, W), device=x.device, dtype=torch.float32)
+    elif tuple(out.shape) != (B, Cc, H, W):
+        raise TdcError(_lib.ERR_SHAPE, "out has shape %s, expected %s" % (tuple(out.shape), (B, Cc, H, W)))
+    xp, xs = _image_view(x, "x")
+    yp, ys = _image_view(out, "out")
+    with _on_device(x.device):
+        code = lib.tdc_affine_relu_f32(xp, yp, _dev_f32(scale, "scale") if scale is not None else None,
+                                       _dev_f32(shift, "shift") if shift is not None else None, B, Cc, H * W, xs, ys,
+                                       1 if relu else 0, _stream())
+    if code != _lib.OK:
+        raise TdcError(code, "tdc_affine_relu_f32")
+    return out
+
+
 def conv2d_epi(x, w, scale=None, bias=None, residual=None, relu=False, stride=1, padding=0, w_layout=W_KCRS,
                tile=None, out=None):
     """y = relu?(conv(x, w) * scale[k] + bias[k] + residual): a conv with a folded inference-mode

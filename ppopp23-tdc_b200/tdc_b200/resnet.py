@@ -251,10 +251,10 @@ def tkc_resnet50(hp_dict=None, num_classes=1000, precision="fp32"):
     return TKResNet((3, 4, 6, 3), num_classes, hp_dict, precision, block=TKBottleneck)
 
 
-def fill_deterministic(module, seed=0):
+def fill_deterministic(module, seed=0, gain=1.0):
     """Every parameter and buffer from a generator seeded by (seed, its name): two models with
     the same state-dict keys — this one and the reference's — get identical values whatever their
-    construction order.  Conv/Tucker kernels Kaiming-normal (fan_out), BatchNorm affine ~ (1, 0)
+    construction order.  Conv/Tucker kernels Kaiming-normal (fan_out) times `gain`, BatchNorm affine ~ (1, 0)
     +- 0.1, running mean ~ N(0, 0.1), running var in [0.5, 1.5], classifier ~ N(0, 0.01)."""
     import zlib
     sd = module.state_dict()
@@ -265,7 +265,7 @@ def fill_deterministic(module, seed=0):
         g = torch.Generator().manual_seed((zlib.crc32(name.encode()) + seed) & 0x7FFFFFFF)
         if t.dim() == 4:
             fan_out = t.shape[0] * t.shape[2] * t.shape[3]
-            v = torch.empty(t.shape).normal_(0.0, (2.0 / fan_out) ** 0.5, generator=g)
+            v = torch.empty(t.shape).normal_(0.0, gain * (2.0 / fan_out) ** 0.5, generator=g)
         elif name.endswith("running_var"):
             v = torch.rand(t.shape, generator=g) + 0.5
         elif name.endswith("running_mean"):

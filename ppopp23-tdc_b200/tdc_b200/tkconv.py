@@ -101,6 +101,24 @@ class TKConv2dC_B200(nn.Module):
             hit = store[name] = (key, ops.permute_weights(w.detach().contiguous()))
         return hit[1]
 
+    def fold_pays(self):
+        """True when the core and the last 1x1 step, multiplied into ONE kh x kw conv R1 -> K, cost no more
+        multiply-adds than the two steps apart (K <= R2, roughly: the dense layers of TK-DenseNet, 32 -> 32 -> 32)."""
+        rs = self.kernel_size[0] * self.kernel_size[1]
+        return rs * self.in_rank * self.out_channels <= rs * self.in_rank * self.out_rank + self.out_rank * self.out_channels
+
+    def _core_last(self):
+        """(KCRS, channel-last) copies of last o core: w[k][c][i][j] = sum_r last[k][r] * core[r][c][i][j], summed in
+        fp64 and rounded once; rebuilt when either parameter changes.  The same linear map as the two steps, one
+        launch and one intermediate fewer; results differ from the two-step chain by fp32 rounding only."""
+        key = (self.core_kernel._version, self.core_kernel.data_ptr(), self.last_kernel._version, self.last_kernel.data_ptr())
+        hit = self.__dict__.get("_core_last_cache")
+        if hit is None or hit[0] != key:
+            w = torch.einsum("kr,rcij->kcij", self.last_kernel.detach().double()[:, :, 0, 0], self.core_kernel.detach().double())
+            w = w.float().contiguous()
+            hit = self.__dict__["_core_last_cache"] = (key, w, ops.permute_weights(w))
+        return hit[1], hit[2]
+
     def _ws(self, x, shared=False):
         """Workspace for the block's two intermediates: this module's own, or (shared=True) one
         buffer per device that all blocks of a network reuse — they run one after another on one

@@ -71,6 +71,24 @@ def tkblock_shapes():
     return out
 
 
+def densenet121_shapes(block_config=(6, 12, 24, 16), growth=32, bn_size=4):
+    """Every convolution of TK-DenseNet-121 with the reference's shipped ranks (inference/hp_dicts/tk_densenet121_hp.py):
+    the stem, per dense layer the 1x1 bottleneck conv (C0 + i*growth -> 128) and the Tucker conv's three steps
+    (128 -> 32 1x1, 32 -> 32 3x3, 32 -> 32 1x1), and the three transition convs."""
+    shapes = [(3, 2 * growth, 224, 224, 7, 2, 3)]
+    c, H = 2 * growth, 56
+    mid = bn_size * growth
+    for s, n in enumerate(block_config):
+        for i in range(n):
+            shapes.append((c + i * growth, mid, H, H, 1, 1, 0))
+        shapes += [(mid, growth, H, H, 1, 1, 0), (growth, growth, H, H, 3, 1, 1), (growth, growth, H, H, 1, 1, 0)]
+        c += n * growth
+        if s != len(block_config) - 1:
+            shapes.append((c, c // 2, H, H, 1, 1, 0))
+            c, H = c // 2, H // 2
+    return shapes
+
+
 def candidates(B, C, H, W, K, R=3, S=3, pad=1, stride=1):
     """Every tile of the compiled thread-tile set that can be launched for the shape."""
     Ho, Wo = (H + 2 * pad - R) // stride + 1, (W + 2 * pad - S) // stride + 1
@@ -127,7 +145,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--out", default="tile_table.csv")
-    ap.add_argument("--shapes", default="sweep", choices=["sweep", "resnet18", "tkblock"])
+    ap.add_argument("--shapes", default="sweep", choices=["sweep", "resnet18", "tkblock", "densenet121"])
     ap.add_argument("--max-per-shape", type=int, default=300)
     ap.add_argument("--model-top", type=int, default=60,
                     help="candidates the analytical model ranks best are always measured, beside the random sample")
@@ -141,7 +159,7 @@ def main(argv=None):
     stream = torch.cuda.current_stream()
     cover = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
     reps = 1 if a.batch >= 16 else 8
-    shapes = {"sweep": sweep_shapes, "resnet18": resnet18_shapes, "tkblock": tkblock_shapes}[a.shapes]()
+    shapes = {"sweep": sweep_shapes, "resnet18": resnet18_shapes, "tkblock": tkblock_shapes, "densenet121": densenet121_shapes}[a.shapes]()
     kept = best_rows(a.keep) if a.keep else {}
     with open(a.out, "w", newline="") as f:
         wr = csv.writer(f)

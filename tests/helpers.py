@@ -6,6 +6,7 @@ import numpy as np
 import torch
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 # The fp32 bar: max|y - y_ref| / max|y_ref| <= 1e-5 per tensor (the hot path's stated
 # tolerance). Both sides are fp32 sums of up to 4608 products in different orders, so
