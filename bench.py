@@ -331,6 +331,81 @@ def bench_resnet(torch, T, dev, dist, world, rank, stream):
     return out
 
 
+def torch_densenet_forward(torch, m, x):
+    """The reference's GPU path for the TK-DenseNet: torch.cat of all earlier features per layer, BatchNorm + ReLU,
+    the bottleneck conv, BatchNorm + ReLU, the three F.conv2d calls of the Tucker conv
+    (inference/densenet_inet_tt.py:56-60,103-108,134-139; TKConv.py:90-95), i.e. cuDNN through torch.  A reported
+    baseline; none of the product's kernels run here."""
+    F = torch.nn.functional
+
+    def conv(c, t):
+        if hasattr(c, "first_kernel"):
+            t = F.conv2d(t, c.first_kernel)
+            t = F.conv2d(t, c.core_kernel, None, c.stride, c.padding)
+            return F.conv2d(t, c.last_kernel, c.bias)
+        return F.conv2d(t, c.weight, c.bias, c.stride, c.padding)
+
+    def bn_relu(b, t):
+        return F.relu(F.batch_norm(t, b.running_mean, b.running_var, b.weight, b.bias, False, 0.0, b.eps))
+
+    f = m.features
+    x = F.max_pool2d(bn_relu(f.norm0, conv(f.conv0, x)), 3, 2, 1)
+    for name, mod in f.named_children():
+        if name.startswith("denseblock"):
+            feats = [x]
+            for layer in mod.values():
+                z = conv(layer.conv1, bn_relu(layer.norm1, torch.cat(feats, 1)))
+                feats.append(conv(layer.conv2, bn_relu(layer.norm2, z)))
+            x = torch.cat(feats, 1)
+        elif name.startswith("transition"):
+            x = F.avg_pool2d(conv(mod.conv, bn_relu(mod.norm, x)), 2, 2)
+    x = bn_relu(f.norm5, x)
+    return m.classifier(torch.flatten(F.adaptive_avg_pool2d(x, 1), 1))
+
+
+def bench_densenet(torch, T, dev):
+    """TK-DenseNet-121 (the reference's shipped ranks: every 3x3 conv Tucker [32, 32]) at batch 1 and 32, each forward
+    captured as a CUDA graph — the network is ~300 launches, launch-bound from the interpreter — with the cuDNN path on
+    the same weights, also as a graph, beside it."""
+    model = T.fill_deterministic(T.tkc_densenet121(precision="auto").eval(), seed=0, gain=0.7).to(dev)
+    torch.backends.cudnn.benchmark = True
+    torch.backends.cudnn.allow_tf32 = False
+    out = {}
+
+    class Ref:
+        def eval(self):
+            return self
+
+        def __call__(self, t):
+            return torch_densenet_forward(torch, model, t)
+    with torch.no_grad():
+        for B, iters in ((1, 20), (32, 10)):
+            x = torch.randn(B, 3, 224, 224, generator=torch.Generator().manual_seed(121)).to(dev)
+            row = {}
+            for key, net in (("graph_ms", model), ("cudnn_graph_ms", Ref())):
+                g = T.GraphedForward(net, x)
+                for _ in range(3):
+                    g(x)
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(iters):
+                    y = g(x)
+                e1.record()
+                torch.cuda.synchronize()
+                row[key] = e0.elapsed_time(e1) / iters
+                row["y_" + key] = y[:2].double().clone()
+            y64 = torch_densenet_forward(torch, model.double(), x[:2].double())
+            model.float()
+            row["rel_err_fp64"] = float((row.pop("y_graph_ms") - y64).abs().max() / y64.abs().max())
+            row["cudnn_rel_err_fp64"] = float((row.pop("y_cudnn_graph_ms") - y64).abs().max() / y64.abs().max())
+            row["images_per_s"] = B / (row["graph_ms"] * 1e-3)
+            out["b%d" % B] = row
+    out["config"] = ("DenseNet-121 (growth 32, blocks 6/12/24/16), the 3x3 conv of all 58 dense layers Tucker with ranks "
+                     "[32, 32], 224x224 N(0,1) images, fp32-level results, eval, CUDA graph on both sides")
+    return out
+
+
 def bench_vgg(torch, T, dev, dist, world, rank, stream):
     """TK-compressed VGG-16 (every 3x3 conv but the first Tucker with R = round8(0.5*channels), random init, eval),
     224x224 N(0,1) images: the batch-2048 job sharded over the GPUs, each rank running its 2048/world images as
@@ -646,6 +721,7 @@ def main():
         line["tk_vgg16"] = bench_vgg(torch, T, dev, dist, world, rank, stream)
         if rank == 0 and world == 1:
             line["tk_block"] = bench_tk_block(torch, T, dev, time_layer, peaks)
+            line["tk_densenet121"] = bench_densenet(torch, T, dev)
 
     # ---- extras on rank 0 of a single-GPU run: batch-1 latency, cuDNN, CPU baseline ---------
     if rank == 0 and world == 1 and not args.no_extras:
