@@ -70,7 +70,31 @@ def build(force=False, verbose=False):
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
+    build_baseline_tool(force)
     return LIB
+
+
+BASELINE_SRC = os.path.join(HERE, "baselines", "cudnn_layer.cpp")
+BASELINE_EXE = os.path.join(HERE, "tdc_b200", "cudnn_layer_baseline")
+
+
+def build_baseline_tool(force=False):
+    """The cuDNN algorithm baselines of the layer driver (a measurement tool, a process of its own; not part of the
+    library).  Skipped with a note when the cuDNN headers are not installed."""
+    inc = next((d for d in ("/usr/include/x86_64-linux-gnu", "/usr/include", "/usr/local/cuda/include")
+                if os.path.exists(os.path.join(d, "cudnn.h"))), None)
+    if inc is None:
+        sys.stderr.write("cudnn.h not found: cudnn_layer_baseline not built\n")
+        return None
+    if not force and os.path.exists(BASELINE_EXE) and os.path.getmtime(BASELINE_EXE) >= os.path.getmtime(BASELINE_SRC):
+        return BASELINE_EXE
+    cmd = [_nvcc(), "-O2", "-std=c++17", "-Wno-deprecated-gpu-targets", "-I", inc, BASELINE_SRC, "-o", BASELINE_EXE,
+           "-lcudnn", "-lcudart"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write("cudnn_layer_baseline not built:\n%s\n" % r.stderr)
+        return None
+    return BASELINE_EXE
 
 
 if __name__ == "__main__":

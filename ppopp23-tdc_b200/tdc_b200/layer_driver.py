@@ -13,10 +13,36 @@ compile loop at compile_run.py:14-52).  Here shape and tile are arguments:
 conv).  Output row: N,C,H,W,B,cudnn_ms,tdc_first_ms,tdc_ms,speedup,frac_fp32,diff — `diff` is
 the reference's L1 check (exact integers expected: 0), `tdc_first_ms` its protocol (first
 launch, no warm-up), `tdc_ms` the warmed median.
+
+`--reference-row` prints (and appends to `--csv`) the reference's own row instead,
+`N,C,H,W,FFT,WINO,GEMM,TVM,TDC,FFT/TDC,WINO/TDC,GEMM/TDC,TVM/TDC,diff` (template_benchmark_cudnn.template:500-512;
+times in ms): the three cuDNN algorithm classes are timed by `cudnn_layer_baseline` (baselines/cudnn_layer.cpp, a
+process of its own), TDC is the warmed median of this build's kernel, TVM is `nan` (the AutoTVM baseline is not
+reproduced).  `tdc_b200.end2end` reads these rows.
 """
 import argparse
 import statistics
 import sys
+
+
+def cudnn_algorithm_times(B, C, H, W, K, R, S, pad, stride, iters=20):
+    """(fft_ms, winograd_ms, gemm_ms) of cuDNN's three legacy algorithm classes for one layer, from the
+    `cudnn_layer_baseline` tool run as a child process; NaN where cuDNN refuses an algorithm or the tool is not
+    built."""
+    import os
+    import subprocess
+    exe = os.path.join(os.path.dirname(os.path.abspath(__file__)), "cudnn_layer_baseline")
+    nan = float("nan")
+    if not os.path.exists(exe):
+        print("cudnn_layer_baseline is not built (python ppopp23-tdc_b200/build.py): cuDNN columns are nan", file=sys.stderr)
+        return nan, nan, nan
+    r = subprocess.run([exe] + [str(v) for v in (B, C, H, W, K, R, S, pad, stride, iters)], capture_output=True, text=True,
+                       timeout=600)
+    if r.returncode != 0:
+        print("cudnn_layer_baseline failed: %s" % r.stderr.strip(), file=sys.stderr)
+        return nan, nan, nan
+    fft, wino, gemm = (float(v) for v in r.stdout.strip().split(",")[:3])
+    return fft, wino, gemm
 
 
 def main(argv=None):
@@ -35,6 +61,8 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-cudnn", action="store_true")
     ap.add_argument("--csv", default=None)
+    ap.add_argument("--reference-row", action="store_true",
+                    help="print the reference's CSV row with the cuDNN FFT / Winograd / implicit-GEMM times")
     ap.add_argument("--tc", type=int, default=0, choices=[0, 1, 3],
                     help="run the tensor-core variant instead: 3 = 3xTF32 (fp32-level), 1 = plain TF32")
     a = ap.parse_args(argv)
@@ -78,6 +106,11 @@ def main(argv=None):
     flops = 2.0 * B * N * Cc * k * k * Ho * Wo
     frac = flops / (tdc * 1e-3) / (sm * 128 * 2 * 1.965e9)
     row = "%d,%d,%d,%d,%d,%f,%f,%f,%f,%f,%g" % (N, Cc, H, W, B, cud, first, tdc, cud / tdc, frac, diff)
+    if a.reference_row:
+        fft, wino, gemm = cudnn_algorithm_times(B, Cc, H, W, N, k, k, a.pad, a.stride, a.iters)
+        tvm = float("nan")
+        row = "%d,%d,%d,%d,%f,%f,%f,%f,%f,%f,%f,%f,%f,%g" % (N, Cc, H, W, fft, wino, gemm, tvm, tdc, fft / tdc, wino / tdc,
+                                                             gemm / tdc, tvm / tdc, diff)
     print(row)
     print("tile", tile, file=sys.stderr)
     if a.csv:

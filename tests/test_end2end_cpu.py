@@ -28,3 +28,26 @@ def test_core_conv_counts_of_tk_resnet18(built):
     assert c[(32, 32, 56, 56)] == 4 and c[(32, 64, 56, 56)] == 1 and c[(64, 64, 28, 28)] == 3 and c[(256, 256, 7, 7)] == 3
     v = end2end.core_conv_counts(T.tkc_vgg16(), torch.zeros(1, 3, 224, 224))
     assert sum(v.values()) == 12 and v[(32, 32, 224, 224)] == 1 and v[(256, 256, 14, 14)] == 3
+
+
+def test_reference_row_of_the_layer_driver_is_read_back(built, tmp_path):
+    """`layer_driver --reference-row` writes the reference's row (N,C,H,W,FFT,WINO,GEMM,TVM,TDC,ratios,diff) with nan
+    for what was not measured; the aggregator reads it like the reference's own CSVs."""
+    from tdc_b200 import end2end
+    p = tmp_path / "B200-layers-eval.csv"
+    p.write_text("64,64,56,56,0.115488,nan,0.046656,nan,0.036976,3.123323,nan,1.261791,nan,0\n"
+                 "512,512,7,7,0.350688,nan,0.702912,nan,0.046000,7.623652,nan,15.280696,nan,0\n")
+    rows = end2end.read_layer_csv(str(p))
+    assert rows[(64, 64, 56, 56)]["gemm"] == 0.046656 and rows[(512, 512, 7, 7)]["tdc"] == 0.046
+    assert rows[(64, 64, 56, 56)]["wino"] != rows[(64, 64, 56, 56)]["wino"]          # nan
+    assert abs(end2end.derived_time(2.0, {(64, 64, 56, 56): 2, (512, 512, 7, 7): 1}, rows)
+               - (2.0 - 2 * (0.046656 - 0.036976) - (0.702912 - 0.046))) < 1e-12
+
+
+def test_cudnn_baseline_tool_is_built_where_cudnn_headers_exist(built):
+    import os
+    import tdc_b200
+    have_headers = any(os.path.exists(os.path.join(d, "cudnn.h")) for d in
+                       ("/usr/include/x86_64-linux-gnu", "/usr/include", "/usr/local/cuda/include"))
+    exe = os.path.join(os.path.dirname(tdc_b200.__file__), "cudnn_layer_baseline")
+    assert os.path.exists(exe) == have_headers
