@@ -1,0 +1,58 @@
+"""Times one memory-bound kernel of the library alone and prints its bandwidth.
+
+    python -m tdc_b200.kernel_bench affine  --batch 32 --channels 224 --of 256 --size 56
+    python -m tdc_b200.kernel_bench maxpool --batch 256 --channels 64 --size 112      # 3x3 / stride 2 / pad 1
+    python -m tdc_b200.kernel_bench maxpool2 --batch 128 --channels 64 --size 224     # 2x2 / stride 2
+
+`affine`: scale, shift and ReLU over the first `--channels` channels of a [batch][--of][size][size] buffer, the
+pre-activation of a DenseNet layer.  Algorithmic bytes = input read once + output written once; the L2 is flushed
+before every timed launch (a 256 MB memset), times are CUDA events on the launching stream, median of `--iters`.
+"""
+import argparse
+import statistics
+
+
+def main(argv=None):
+    import torch
+    from . import ops
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["affine", "maxpool", "maxpool2"])
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--channels", type=int, default=224)
+    ap.add_argument("--of", type=int, default=None, help="channels of the buffer the input is a prefix of (affine)")
+    ap.add_argument("--size", type=int, default=56)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--peak-gbs", type=float, default=None, help="measured copy bandwidth to quote the fraction of")
+    a = ap.parse_args(argv)
+    dev = torch.device("cuda")
+    stream = torch.cuda.current_stream()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    B, C, H = a.batch, a.channels, a.size
+    if a.kernel == "affine":
+        buf = torch.randn(B, a.of or C, H, H, device=dev)
+        scale, shift = torch.rand(C, device=dev) + 0.5, torch.randn(C, device=dev)
+        out = torch.empty(B, C, H, H, device=dev)
+        run = lambda: ops.affine_relu(buf[:, :C], scale, shift, relu=True, out=out)
+        nbytes = 2 * out.numel() * 4
+    else:
+        x = torch.randn(B, C, H, H, device=dev)
+        k, s, p = (3, 2, 1) if a.kernel == "maxpool" else (2, 2, 0)
+        out = ops.pool2d(x, k, s, p)
+        run = lambda: ops.pool2d(x, k, s, p, out=out)
+        nbytes = (x.numel() + out.numel()) * 4
+    for _ in range(3):
+        run()
+    ts = []
+    for _ in range(a.iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream); run(); e1.record(stream); e1.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e-3)
+    t = statistics.median(ts)
+    gbs = nbytes / t / 1e9
+    frac = "" if a.peak_gbs is None else "  %.2f of %.1f GB/s" % (gbs / a.peak_gbs, a.peak_gbs)
+    print("%s: %.1f us, %.1f MB, %.1f GB/s%s" % (a.kernel, t * 1e6, nbytes / 1e6, gbs, frac))
+
+
+if __name__ == "__main__":
+    main()
