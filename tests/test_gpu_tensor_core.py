@@ -138,12 +138,40 @@ def test_persistent_and_one_tile_kernels_agree(T, B, Cc, K, H, W, R, monkeypatch
         assert rel_err(out["1"][1][sel].cpu().numpy(), want) <= tol
         if mode == 3:
             y3 = out["1"][0]
-    for knobs in ({"TDC_TC_MT": "1"}, {"TDC_TC_MT": "2", "TDC_TC_NBUF": "1"}, {"TDC_TC_NS": "2", "TDC_TC_DEPTH": "2"}, {"TDC_TC_TAIL": "0"}, {"TDC_TC_KPS": "1"}):
+    for knobs in ({"TDC_TC_MT": "1"}, {"TDC_TC_MT": "2", "TDC_TC_NBUF": "1"}, {"TDC_TC_NS": "2", "TDC_TC_DEPTH": "2"}, {"TDC_TC_TAIL": "0"}, {"TDC_TC_KPS": "1"},
+                  {"TDC_TC_VEC": "0"}, {"TDC_TC_VEC": "1"}):
         for k, v in knobs.items():
             monkeypatch.setenv(k, v)
         assert torch.equal(T.TcConv(wd, mode=3)(xd), y3), knobs      # tile count, buffers and ring depth change no bit
         for k in knobs:
             monkeypatch.delenv(k)
+    assert tc.status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,Cc,K,H,W", [(128, 64, 128, 56, 56), (64, 32, 64, 56, 56), (32, 224, 128, 28, 28), (32, 256, 128, 14, 14),
+                                         (40, 96, 32, 28, 28), (3, 520, 256, 12, 12)])
+def test_one_tap_loaders_agree(T, B, Cc, K, H, W, monkeypatch):
+    """A 1x1 filter on images of a multiple of 4 pixels can be staged by 16-byte loads or through the cp.async ring;
+    the launcher picks by layer size.  Both forced in turn, in the persistent kernel with and without the smaller
+    tiles of the last round and in the one-tile kernel: the operands are the same values in the same places, so every
+    output bit agrees, and the first and last images are checked against fp64."""
+    from tdc_b200 import tc
+    g = torch.Generator().manual_seed(B + Cc + K)
+    x = torch.randn(B, Cc, H, W, generator=g).cuda()
+    w = (torch.randn(K, Cc, 1, 1, generator=g) * 0.1).cuda()
+    conv = T.TcConv(w, mode=3)
+    y = conv(x).clone()
+    for knobs in ({"TDC_TC_VEC": "0"}, {"TDC_TC_VEC": "1"}, {"TDC_TC_VEC": "0", "TDC_TC_TAIL": "0"}, {"TDC_TC_VEC": "0", "TDC_TC_PERSIST": "1"},
+                  {"TDC_TC_VEC": "1", "TDC_TC_PERSIST": "1"}, {"TDC_TC_VEC": "0", "TDC_TC_PERSIST": "0"}, {"TDC_TC_VEC": "0", "TDC_TC_MT": "1"}):
+        for k, v in knobs.items():
+            monkeypatch.setenv(k, v)
+        assert torch.equal(conv(x), y), knobs
+        for k in knobs:
+            monkeypatch.delenv(k)
+    for sel in (slice(0, 2), slice(B - 2, B)):
+        ref = torch.nn.functional.conv2d(x[sel].double(), w.double())
+        assert float((y[sel].double() - ref).abs().max() / ref.abs().max()) <= FP32_TOL
     assert tc.status() == 0
 
 
