@@ -754,14 +754,15 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     const char* env_nbuf = getenv("TDC_TC_NBUF");
     const char* env_persist = getenv("TDC_TC_PERSIST");
     // The persistent kernel wins where a CTA tile is short and its prologue and epilogue would otherwise show: split
-    // operands with up to 64 output channels per block, and one-tap filters with 128-channel blocks when there are
-    // enough positions for two position tiles per CTA.  For 3x3 filters with 128-channel blocks the one-tile
+    // operands with up to 64 output channels per block, and one-tap filters of any block size (with few tiles too:
+    // its cp.async ring has all loader threads and several channel blocks in flight, 20 % faster than the one-tile
+    // kernel on nine layers of 25..200 tiles).  For 3x3 filters with 128-channel blocks the one-tile
     // kernel, which drains tensor memory with all its warps, measured faster.  TDC_TC_PERSIST=0/1 forces either.
     const long long tiles_mt2 = ((a.total_pos + 2 * M_TILE - 1) / (2 * M_TILE)) * a.n_ocb;
     // ... and for 3x3 filters with one 128-channel block when the tile list has complete rounds plus a rest: the
     // persistent kernel spreads the rest over all SMs as smaller tiles (28x28x128 at batch 64: 88 -> 76 us).
     const bool persist = p->general || (env_persist ? atoi(env_persist) != 0
-                                                    : (a.hl == 2 ? (p->nt <= 64 || (tiles_mt2 >= sms && (taps == 1 || (a.n_ocb == 1 && tiles_mt2 % sms != 0))))
+                                                    : (a.hl == 2 ? (p->nt <= 64 || taps == 1 || (tiles_mt2 >= sms && a.n_ocb == 1 && tiles_mt2 % sms != 0))
                                                                  // plain TF32: two one-tile CTAs share an SM for short launches; long ones measured faster persistent
                                                                  : 2.0 * a.total_pos * p->C * p->K * taps >= 8e9));
     int mt = 512 / a.tile_cols > 4 ? 4 : 512 / a.tile_cols, ns = 0, depth = 0, nbuf = 1;   // tensor memory: 512 columns
