@@ -29,9 +29,13 @@ def test_tensor_cores_only_where_they_fill_the_gpu(tc):
     # batch 64: tensor cores for every sweep shape
     for H, R in ((56, 32), (28, 64), (14, 128), (7, 256), (7, 512)):
         assert tc.worthwhile(64, R, H, H, R, 3)
-    # the Tucker blocks at batch 32: every step but the 1x1 steps of the 7x7 block (1568 positions)
+    # the Tucker blocks at batch 32: every step (the first 1x1 step of the 7x7 block, 12 tiles and 512 channels to walk, is a tie)
     assert tc.worthwhile(32, 64, 56, 56, 32, 1) and tc.worthwhile(32, 128, 14, 14, 128, 3) and tc.worthwhile(32, 256, 7, 7, 256, 3)
-    assert not tc.worthwhile(32, 512, 7, 7, 256, 1) and not tc.worthwhile(32, 256, 7, 7, 512, 1)
+    assert tc.worthwhile(32, 256, 7, 7, 512, 1)                                                   # measured 46 vs 32 us
+    # 1x1 layers with few tiles: wide outputs pay from 3 tiles on, narrow ones need 24 tiles or real arithmetic
+    assert tc.worthwhile(8, 512, 7, 7, 2048, 1) and not tc.worthwhile(8, 2048, 7, 7, 512, 1)      # 79 vs 54 us, 118 vs 186 us
+    assert tc.worthwhile(16, 256, 14, 14, 128, 1) and not tc.worthwhile(8, 256, 14, 14, 128, 1)   # 44 vs 31 us, 26 vs 31 us
+    assert not tc.worthwhile(32, 768, 7, 7, 128, 1) and tc.worthwhile(32, 1024, 7, 7, 512, 1)     # 45 vs 75 us, 123 vs 99 us
     # many positions but hardly any arithmetic
     assert not tc.worthwhile(64, 3, 56, 56, 8, 1)
 
