@@ -763,20 +763,22 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     // persistent kernel spreads the rest over all SMs as smaller tiles (28x28x128 at batch 64: 88 -> 76 us).
     const bool persist = p->general || (env_persist ? atoi(env_persist) != 0
                                                     : (a.hl == 2 ? (p->nt <= 64 || taps == 1 || (tiles_mt2 >= sms && a.n_ocb == 1 && tiles_mt2 % sms != 0))
-                                                                 // plain TF32: two one-tile CTAs share an SM for short launches; long ones measured faster persistent
-                                                                 : 2.0 * a.total_pos * p->C * p->K * taps >= 8e9));
+                                                                 // plain TF32: one-tap filters likewise (14 layers: 20 % on 12, level on 2); 3x3: two one-tile
+                                                                 // CTAs share an SM for short launches, long ones measured faster persistent
+                                                                 : (taps == 1 || 2.0 * a.total_pos * p->C * p->K * taps >= 8e9)));
     int mt = 512 / a.tile_cols > 4 ? 4 : 512 / a.tile_cols, ns = 0, depth = 0, nbuf = 1;   // tensor memory: 512 columns
     if (env_mt && atoi(env_mt) >= 1) while (mt > atoi(env_mt)) mt /= 2;
     // 16-byte input loads: 1x1 filter, images a multiple of 4 positions long, 16-byte aligned base.  In the persistent
-    // kernel with split operands the cp.async ring is the faster loader all the same — it keeps all 256 loader threads
+    // kernel the cp.async ring is the faster loader all the same — it keeps all 256 loader threads
     // and `depth` channel blocks in flight where the 16-byte path has 64 threads per 128-position tile and two blocks
     // in registers — except for blocks of up to 64 channels with ten or more position tiles per SM (157 one-tap
     // layers, 64..1024 -> 32..512 channels at 14..112 pixels, batch 1..128, timed both ways: ring/16-byte = 0.71-0.89
-    // where the rule takes the ring, 1.06-1.14 where it does not; 0.88 geometric mean over all).  TDC_TC_VEC=0/1 forces.
+    // where the rule takes the ring, 1.06-1.14 where it does not; 0.88 geometric mean over all; plain TF32 on 14 of
+    // them: the same picture).  TDC_TC_VEC=0/1 forces.
     const char* env_vec = getenv("TDC_TC_VEC");
     const bool vec_ok = taps == 1 && !p->general && stride == 1 && ((long long)H * W) % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
     const long long ptiles = (a.total_pos + M_TILE - 1) / M_TILE;
-    const bool ring_wins = persist && a.hl == 2 && (p->nt > 64 || ptiles < 10ll * sms);
+    const bool ring_wins = persist && (p->nt > 64 || ptiles < 10ll * sms);
     const bool vec = vec_ok && (env_vec ? atoi(env_vec) != 0 : !ring_wins);
     const bool ring = persist && !vec;                       // input staged through the raw cp.async ring
     const char* env_depth = getenv("TDC_TC_DEPTH");
