@@ -57,6 +57,29 @@ def resnet18_shapes():
     return out
 
 
+def resnet50_shapes():
+    """(C, N, H, W, R, stride, pad) of every convolution of the TK-compressed ResNet-50 (bottleneck blocks [3,4,6,3], the
+    3x3 conv of every block Tucker with R1 = R2 = round8(0.5*width), the stride on that conv): stem, per block the 1x1
+    reduce, the Tucker conv's three steps, the 1x1 expand, and the 1x1 downsample convs."""
+    shapes = [(3, 64, 224, 224, 7, 2, 3)]
+    inpl, H = 64, 56
+    for planes, n, stride in ((64, 3, 1), (128, 4, 2), (256, 6, 2), (512, 3, 2)):
+        r = 8 * round(0.5 * planes / 8)
+        for blk in range(n):
+            s = stride if blk == 0 else 1
+            Ho = H // s
+            shapes += [(inpl, planes, H, H, 1, 1, 0), (planes, r, H, H, 1, 1, 0), (r, r, H, H, 3, s, 1), (r, planes, Ho, Ho, 1, 1, 0),
+                       (planes, 4 * planes, Ho, Ho, 1, 1, 0)]
+            if blk == 0:
+                shapes.append((inpl, 4 * planes, H, H, 1, s, 0))
+            inpl, H = 4 * planes, Ho
+    seen, out = set(), []
+    for sh in shapes:
+        if sh not in seen:
+            seen.add(sh); out.append(sh)
+    return out
+
+
 def sweep_shapes():
     return [(R1, R2, H, H, 3, 1, 1) for (H, R1, R2) in SWEEP]
 
@@ -145,7 +168,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--out", default="tile_table.csv")
-    ap.add_argument("--shapes", default="sweep", choices=["sweep", "resnet18", "tkblock", "densenet121"])
+    ap.add_argument("--shapes", default="sweep", choices=["sweep", "resnet18", "resnet50", "tkblock", "densenet121"])
     ap.add_argument("--max-per-shape", type=int, default=300)
     ap.add_argument("--model-top", type=int, default=60,
                     help="candidates the analytical model ranks best are always measured, beside the random sample")
@@ -159,7 +182,7 @@ def main(argv=None):
     stream = torch.cuda.current_stream()
     cover = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
     reps = 1 if a.batch >= 16 else 8
-    shapes = {"sweep": sweep_shapes, "resnet18": resnet18_shapes, "tkblock": tkblock_shapes, "densenet121": densenet121_shapes}[a.shapes]()
+    shapes = {"sweep": sweep_shapes, "resnet18": resnet18_shapes, "resnet50": resnet50_shapes, "tkblock": tkblock_shapes, "densenet121": densenet121_shapes}[a.shapes]()
     kept = best_rows(a.keep) if a.keep else {}
     with open(a.out, "w", newline="") as f:
         wr = csv.writer(f)
