@@ -247,6 +247,12 @@ TDC_API int tdc_tk_block_f32_static(const float* x, const float* w1, const float
  * H and W are the input image, y is [B][K][(H-1)/stride+1][(W-1)/stride+1].
  *   mode 3  "3xTF32": operands split into hi + lo TF32 parts, three MMAs per product;
  *           fp32-level accuracy (held to the same 1e-5 bar as the fp32 kernels)
+ *   mode 4  "3xFP16": the same split with fp16 parts (the lo part scaled by 2^11 to stay clear of fp16's
+ *           subnormals): the same 22 significant bits per operand at twice the MMA rate and half the
+ *           accumulations per output, so both faster and closer to fp64 than mode 3; the input and the filter
+ *           are scaled by powers of two into fp16's range (see tdc_conv2d_tc_ranged), so any finite fp32 data is
+ *           taken; the prepared filter carries a scratch tail that the call in flight uses, so calls sharing
+ *           one prepared filter must not overlap on the GPU
  *   mode 1  plain TF32: one MMA per product; 5e-3 bar; reported separately
  * Use: tdc_tc_plan_make once per layer shape, tdc_tc_prepare_weights once per weight load
  * into a caller-owned buffer of plan.weights_bytes, then tdc_conv2d_tc per call.  Every
@@ -256,9 +262,9 @@ TDC_API int tdc_tk_block_f32_static(const float* x, const float* w1, const float
 typedef struct tdc_tc_plan {
     int    C, K, R, S, mode;
     int    nt;            /* output channels per CTA (MMA N)              */
-    int    cb;            /* channels per stage (one K step = 8)          */
+    int    cb;            /* channels per K step: 8 (TF32), 16 (fp16)     */
     int    nkb, n_ocb;    /* channel blocks, output-channel blocks        */
-    int    hl;            /* 2 when operands are split (mode 3), else 1   */
+    int    hl;            /* 2 when operands are split (modes 3, 4), else 1 */
     int    general;       /* 1: made by tdc_tc_plan_make_general          */
     size_t weights_bytes; /* size of the pre-arranged filter              */
 } tdc_tc_plan;
@@ -282,6 +288,17 @@ TDC_API int tdc_tc_prepare_weights(const tdc_tc_plan* plan, const float* w, int 
 #define TDC_TC_PAD_SHIFT   4
 TDC_API int tdc_conv2d_tc(const tdc_tc_plan* plan, const float* x, const void* wt, float* y,
                           int B, int H, int W, const tdc_epilogue* epi, int flags, void* stream);
+/* Mode 4 scales the input by a power of two so that its largest magnitude lands just under 2^15 (fp16 ends at 65504),
+ * and undoes the scaling in the epilogue; for that it must know max|x|.  tdc_conv2d_tc finds it with a pass over x
+ * ahead of the convolution.  A caller that chains layers (the three steps of TKConv2dC.forward,
+ * inference/TKConv.py:90-95) can save that pass: y_absmax, when given, receives the partial maxima of |y|
+ * (TDC_TC_ABSMAX_FLOATS floats, every entry written), and the next call takes the same buffer as x_absmax.  Either
+ * pointer may be NULL; x_absmax must bound the x of THIS call (a maximum over more data only costs precision).
+ * Other modes ignore x_absmax and refuse y_absmax. */
+#define TDC_TC_ABSMAX_FLOATS 1024
+TDC_API int tdc_conv2d_tc_ranged(const tdc_tc_plan* plan, const float* x, const void* wt, float* y,
+                          int B, int H, int W, const tdc_epilogue* epi, int flags,
+                          const float* x_absmax, float* y_absmax, void* stream);
 TDC_API int tdc_tc_status(int* out);
 
 /*

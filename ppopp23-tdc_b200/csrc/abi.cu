@@ -10,14 +10,11 @@
 #include <map>
 #include <mutex>
 #include <tuple>
+#include "errors.h"
 #include "tile.h"
 
-using namespace tdc;
-
-namespace {
-
-thread_local char g_err[512] = "";
-
+namespace tdc {
+static thread_local char g_err[512] = "";
 int fail(int code, const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
@@ -25,6 +22,12 @@ int fail(int code, const char* fmt, ...) {
     va_end(ap);
     return code;
 }
+const char* last_error() { return g_err; }
+}  // namespace tdc
+
+using namespace tdc;
+
+namespace {
 
 std::mutex g_mu;
 std::map<int, tdc_devinfo> g_dev;                          // per device
@@ -173,7 +176,7 @@ __global__ void permute_kcrs_to_crsk(const float* __restrict__ in, float* __rest
 
 extern "C" {
 
-const char* tdc_last_error_string(void) { return g_err; }
+const char* tdc_last_error_string(void) { return tdc::last_error(); }
 int tdc_version(void) { return 100; }
 
 int tdc_query_device(int device, tdc_devinfo* out) {

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include "../../include/tdc_b200.h"
+#include "errors.h"
 
 namespace {
 
@@ -55,14 +56,18 @@ void launch_affine(const float* x, float* y, const float* scale, const float* sh
 
 extern "C" int tdc_affine_relu_f32(const float* x, float* y, const float* scale, const float* shift, int B, int C, int HW,
                                    long long x_image_stride, long long y_image_stride, int relu, void* stream) {
-    if (!x || !y) return TDC_ERR_NULL;
-    if (B <= 0 || C <= 0 || HW <= 0) return TDC_ERR_SHAPE;
-    if (x_image_stride < (long long)C * HW || y_image_stride < (long long)C * HW) return TDC_ERR_SHAPE;
+    using tdc::fail;
+    if (!x || !y) return fail(TDC_ERR_NULL, "tdc_affine_relu_f32: x and y must be non-NULL");
+    if (B <= 0 || C <= 0 || HW <= 0) return fail(TDC_ERR_SHAPE, "tdc_affine_relu_f32: B=%d C=%d HW=%d", B, C, HW);
+    if (x_image_stride < (long long)C * HW || y_image_stride < (long long)C * HW)
+        return fail(TDC_ERR_SHAPE, "tdc_affine_relu_f32: image strides %lld / %lld are shorter than an image of %lld elements",
+                    x_image_stride, y_image_stride, (long long)C * HW);
     const long long planes = (long long)B * C;
     const bool vec = HW % 4 == 0 && x_image_stride % 4 == 0 && y_image_stride % 4 == 0 &&
                      reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0;
     cudaStream_t st = (cudaStream_t)stream;
     if (vec) launch_affine<4>(x, y, scale, shift, C, HW / 4, x_image_stride, y_image_stride, planes * (HW / 4), relu, st);
     else launch_affine<1>(x, y, scale, shift, C, HW, x_image_stride, y_image_stride, planes * HW, relu, st);
-    return cudaGetLastError() == cudaSuccess ? TDC_OK : TDC_ERR_CUDA;
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? TDC_OK : fail(TDC_ERR_CUDA, "tdc_affine_relu_f32 launch: %s", cudaGetErrorString(e));
 }

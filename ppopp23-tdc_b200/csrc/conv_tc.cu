@@ -29,20 +29,28 @@
 //     (cp.async.bulk into this CTA's shared memory) that completes on an mbarrier.
 //   * Every wait on an mbarrier is bounded; a wait that runs out records a status word,
 //     the CTA skips to its clean-up (tensor memory is freed) and returns.
+#include <cuda.h>            // CUtensorMap and its enums (types only: the encoder is looked up at run time)
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <map>
 #include <mutex>
+#include <tuple>
 #include <utility>
 #include "../../include/tdc_b200.h"
 
 namespace tdc_tc {
 
 constexpr int M_TILE   = 128;   // positions per CTA = MMA M
-constexpr int CB       = 8;     // channels per stage = one K step of kind::tf32
+constexpr int CB       = 8;     // 4-byte words per operand row and K step (32 bytes): 8 TF32 channels, or 16 fp16 channels
+constexpr int BOXW     = 32;    // pixels per row of a bulk-tensor box (128 bytes)
+constexpr int BOXC     = 16;    // channels per box = one fp16 K step
+// channels of one K step: kind::tf32 contracts 8 per MMA, kind::f16 16 (the operand bytes are the same)
+template <bool F16> struct KStep { static constexpr int CH = F16 ? 16 : 8; };
 constexpr int LOADERS  = 256;   // threads of warps 0-7, which stage the input patch
 constexpr int THREADS  = 384;   // + warps 8-11: MMA issuers (lane 0 of each), everyone drains tensor memory
 
@@ -62,7 +70,7 @@ struct Args {
     int P;                 // patch rows staged per CTA (multiple of 8)
     int nkb;               // channel blocks
     int n_ocb;             // output-channel blocks
-    int hl;                // 2: hi/lo split (3xTF32), 1: plain TF32
+    int hl;                // 2: hi/lo split (3xTF32, 3xFP16), 1: plain TF32
     int ns;                // stages
     int nmain;             // 1 or 2 main accumulators per position tile (2: channel blocks alternate)
     int tile_cols;         // tensor-memory columns per position tile: 2*NT, or 4*NT with two mains
@@ -74,8 +82,44 @@ struct Args {
     long long full_groups, tail_first_pt, pt_total;   // persistent kernel: tile list (see tile_of)
     int tail_cnt;
     long long ntiles;      // persistent kernel: position tiles x output-channel blocks
+    int nseg, seg_blocks;  // persistent kernel: the channel blocks of a tile are accumulated in nseg runs of seg_blocks
+                           // blocks; each run starts fresh accumulators and is added to y in fp32 by the epilogue
+    int nbox_cap;          // bulk-tensor loader: boxes a raw slot holds
+    // fp16 operands: the input is scaled by a power of two that brings its largest magnitude just under 2^15 (fp16 ends
+    // at 65504), the filter likewise when it is prepared, and the epilogue undoes both.
+    const float* x_absmax; // [ABSMAX_SLOTS] partial maxima of |x| (every entry valid; the largest one counts)
+    const float* w_scale;  // [1] the power of two the prepared filter was multiplied by
+    float*       y_absmax; // [ABSMAX_SLOTS] or nullptr: partial maxima of |y| for the next layer (entry = CTA, rest zeroed)
     int* status;           // device status word: 0 ok, else first failure code
 };
+constexpr int ABSMAX_SLOTS = 1024;
+
+// The power of two that brings a tensor whose largest magnitude is m just under 2^15; 1 for an all-zero or non-finite m.
+__host__ __device__ __forceinline__ float range_scale(float m) {
+    if (!(m > 0.f) || !(m < 3.0e38f)) return 1.f;
+    int e;
+    frexpf(m, &e);                                  // m = f * 2^e, 0.5 <= f < 1
+    int k = 15 - e;
+    k = k < -60 ? -60 : (k > 60 ? 60 : k);
+    return ldexpf(1.f, k);
+}
+
+// The largest of the ABSMAX_SLOTS partial maxima, by the first 256 threads of a block (all threads must call it).
+__device__ __forceinline__ float absmax_of(const float* slots, unsigned int* scratch /* one shared word */) {
+    if (threadIdx.x == 0) *scratch = 0;
+    __syncthreads();
+    if (threadIdx.x < 256) {
+        unsigned int m = 0;
+#pragma unroll
+        for (int i = 0; i < ABSMAX_SLOTS / 256; ++i) m = max(m, __float_as_uint(slots[threadIdx.x + i * 256]) & 0x7fffffffu);
+        m = __reduce_max_sync(0xffffffffu, m);
+        if ((threadIdx.x & 31) == 0) atomicMax(scratch, m);
+    }
+    __syncthreads();
+    const float m = __uint_as_float(*scratch);
+    __syncthreads();                               // every thread has read the word: the caller may reuse it
+    return m;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -127,6 +171,42 @@ __device__ __forceinline__ float to_tf32(float v) {
     return __uint_as_float(r);
 }
 
+// One patch row of one channel block -> the operand layout of a stage: two 16-byte words (the two core matrices of a
+// K step) of the hi part at A + ((q*P + pp) << 2) and, with split operands, of the lo part 8*P words further on.
+// TF32: word q holds channels 4q..4q+3 as fp32 bit patterns with 10 mantissa bits; lo = c - hi.
+// FP16: word q holds channels 8q..8q+7 as halves; lo = (c - hi) * 2^11, which keeps it in fp16's normal range
+// for every c whose hi part is (the epilogue divides the small accumulator by 2^11 again).
+template <bool F16>
+__device__ __forceinline__ void store_row(float* A, int P, int hl, int pp, const float (&c)[KStep<F16>::CH], float xs = 1.f) {
+    if constexpr (F16) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            uint32_t h[4], l[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float c0 = c[8 * q + 2 * k] * xs, c1 = c[8 * q + 2 * k + 1] * xs;     // xs: the range scaling, a power of two
+                const __half2 hh = __floats2half2_rn(c0, c1);
+                const float2 hf = __half22float2(hh);
+                const __half2 ll = __floats2half2_rn((c0 - hf.x) * 2048.f, (c1 - hf.y) * 2048.f);
+                h[k] = *reinterpret_cast<const uint32_t*>(&hh);
+                l[k] = *reinterpret_cast<const uint32_t*>(&ll);
+            }
+            *reinterpret_cast<uint4*>(A + ((q * P + pp) << 2)) = make_uint4(h[0], h[1], h[2], h[3]);
+            if (hl == 2) *reinterpret_cast<uint4*>(A + CB * P + ((q * P + pp) << 2)) = make_uint4(l[0], l[1], l[2], l[3]);
+        }
+    } else {
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            float4 hi;
+            hi.x = to_tf32(c[4 * q]); hi.y = to_tf32(c[4 * q + 1]); hi.z = to_tf32(c[4 * q + 2]); hi.w = to_tf32(c[4 * q + 3]);
+            *reinterpret_cast<float4*>(A + ((q * P + pp) << 2)) = hi;
+            if (hl == 2)
+                *reinterpret_cast<float4*>(A + CB * P + ((q * P + pp) << 2)) =
+                    make_float4(c[4 * q] - hi.x, c[4 * q + 1] - hi.y, c[4 * q + 2] - hi.z, c[4 * q + 3] - hi.w);
+        }
+    }
+}
+
 // Shared-memory matrix descriptor: K-major, no swizzle.  lbo = bytes between the two core
 // matrices of one K step (channels 0-3 / 4-7), sbo = bytes between 8-row groups.
 __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -137,10 +217,16 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint3
     d |= 1ull << 46;                 // descriptor version of sm_100
     return d;                        // layout type 0 (no swizzle), base offset 0
 }
+template <bool F16>
 __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+    if constexpr (F16)
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+    else
+        asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                     "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                     ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -169,22 +255,24 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
-// Instruction descriptor: D fp32, A and B tf32, both K-major, M = 128, N = n.
+// Instruction descriptor: D fp32, A and B tf32 (format 2) or fp16 (format 0), both K-major, M = 128, N = n.
+template <bool F16>
 __device__ __forceinline__ uint32_t make_idesc(int n) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(M_TILE >> 4) << 24);
+    const uint32_t fmt = F16 ? 0u : 2u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(M_TILE >> 4) << 24);
 }
 
 // The MMAs of one channel block (stage) of one position tile.  `a_base` / `b_base`: shared
 // addresses of the stage's patch and filter; `row16`: first patch row of the tile (the unit
-// of a start-address step is 16 bytes = one patch row of 4 channels); `odd`: this block
-// is an odd channel block; `first`: it starts the accumulation of the accumulator it feeds.
-template <int NT, int TAPS>
+// of a start-address step is 16 bytes = one patch row of one core matrix); `odd`: this block
+// is an odd channel block of its run; `first`: it starts the accumulation of the accumulator it feeds.
+template <int NT, int TAPS, bool F16 = false>
 __device__ __forceinline__ void issue_block(const Args& a, uint32_t d_main, uint32_t a_base, uint32_t b_base, uint32_t row16,
                                             bool odd, bool first) {
-    // leading byte offset = distance between the two 4-channel core matrices of a K step,
-    // stride byte offset = distance between groups of 8 rows (verified on a B200 against the fp64 oracle)
+    // leading byte offset = distance between the two core matrices of a K step (the two 16-byte halves of an operand
+    // row), stride byte offset = distance between groups of 8 rows (verified on a B200 against the fp64 oracle)
     const uint32_t a_lbo = (uint32_t)a.P * 16u, b_lbo = (uint32_t)(a.hl * NT) * 16u, sbo = 128u;
-    const uint32_t idesc_n = make_idesc(NT), idesc_2n = make_idesc(2 * NT);
+    const uint32_t idesc_n = make_idesc<F16>(NT), idesc_2n = make_idesc<F16>(2 * NT);
     const uint64_t a_hi0 = make_desc(a_base, a_lbo, sbo) + row16;
     const uint64_t a_lo0 = make_desc(a_base + (uint32_t)(CB * a.P) * 4u, a_lbo, sbo) + row16;
     const uint64_t b_hi0 = make_desc(b_base, b_lbo, sbo);       // rows 0..NT-1 hi, NT..2NT-1 lo
@@ -193,7 +281,7 @@ __device__ __forceinline__ void issue_block(const Args& a, uint32_t d_main, uint
 #pragma unroll
         for (int tap = 0; tap < TAPS; ++tap) {
             const uint32_t a_off = (uint32_t)((tap / (TAPS == 9 ? 3 : 1)) * a.Wp + tap % (TAPS == 9 ? 3 : 1));
-            mma_tf32(d_main, a_hi0 + a_off, b_hi0 + tap * b_tap, idesc_n, (first && tap == 0) ? 0u : 1u);
+            mma_tf32<F16>(d_main, a_hi0 + a_off, b_hi0 + tap * b_tap, idesc_n, (first && tap == 0) ? 0u : 1u);
         }
     } else if (a.nmain == 2 && odd) {
         // odd channel block: second main accumulator; the lo rows of the filter start NT rows (NT x 16 bytes) in
@@ -201,37 +289,47 @@ __device__ __forceinline__ void issue_block(const Args& a, uint32_t d_main, uint
         for (int tap = 0; tap < TAPS; ++tap) {
             const uint32_t a_off = (uint32_t)((tap / (TAPS == 9 ? 3 : 1)) * a.Wp + tap % (TAPS == 9 ? 3 : 1));
             const uint64_t b_hi = b_hi0 + tap * b_tap;
-            mma_tf32(d_main + 2 * NT, a_hi0 + a_off, b_hi, idesc_n, (first && tap == 0) ? 0u : 1u);   // main1 += hi*hi
-            mma_tf32(d_main + NT, a_hi0 + a_off, b_hi + (uint64_t)NT, idesc_n, 1u);                   // small += hi*lo
-            mma_tf32(d_main + NT, a_lo0 + a_off, b_hi, idesc_n, 1u);                                  // small += lo*hi
+            mma_tf32<F16>(d_main + 2 * NT, a_hi0 + a_off, b_hi, idesc_n, (first && tap == 0) ? 0u : 1u);   // main1 += hi*hi
+            mma_tf32<F16>(d_main + NT, a_hi0 + a_off, b_hi + (uint64_t)NT, idesc_n, 1u);                   // small += hi*lo
+            mma_tf32<F16>(d_main + NT, a_lo0 + a_off, b_hi, idesc_n, 1u);                                  // small += lo*hi
         }
     } else {
 #pragma unroll
         for (int tap = 0; tap < TAPS; ++tap) {
             const uint32_t a_off = (uint32_t)((tap / (TAPS == 9 ? 3 : 1)) * a.Wp + tap % (TAPS == 9 ? 3 : 1));
             const uint64_t b_hi = b_hi0 + tap * b_tap;
-            mma_tf32(d_main, a_hi0 + a_off, b_hi, idesc_2n, (first && tap == 0) ? 0u : 1u);           // main += hi*hi, small += hi*lo
-            mma_tf32(d_main + NT, a_lo0 + a_off, b_hi, idesc_n, 1u);                                  // small += lo*hi
+            mma_tf32<F16>(d_main, a_hi0 + a_off, b_hi, idesc_2n, (first && tap == 0) ? 0u : 1u);           // main += hi*hi, small += hi*lo
+            mma_tf32<F16>(d_main + NT, a_lo0 + a_off, b_hi, idesc_n, 1u);                                  // small += lo*hi
         }
     }
 }
 
 // 32 output channels of this thread's position: tensor memory -> registers, with the
-// accumulators of the split (main + small, + second main) added in fp32.
-template <int NT>
-__device__ __forceinline__ void load_chunk(const Args& a, uint32_t taddr, uint32_t (&r)[32]) {
+// accumulators of the split (main + small, + second main) added in fp32.  `blocks`: channel
+// blocks of the run these accumulators hold (the second main exists from two blocks on).
+// With fp16 operands the lo halves were scaled by 2^11 on both sides (so that they stay
+// clear of fp16's subnormal range); the small accumulator carries that factor.
+template <int NT, bool F16 = false>
+__device__ __forceinline__ void load_chunk(const Args& a, uint32_t taddr, uint32_t (&r)[32], int blocks, float inv = 1.f) {
     tmem_ld32(taddr, r);
     if (a.hl == 2) {
         uint32_t r2[32];
         tmem_ld32(taddr + NT, r2);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if constexpr (F16) {
+            // `inv` undoes the range scaling of input and filter; the small accumulator also carries the 2^11 of the lo halves
+            const float inv_small = inv * (1.f / 2048.f);
 #pragma unroll
-        for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) + __uint_as_float(r2[k]));
-        if (a.nmain == 2 && a.nkb > 1) {          // second main accumulator (odd channel blocks)
+            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(fmaf(__uint_as_float(r2[k]), inv_small, __uint_as_float(r[k]) * inv));
+        } else {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) + __uint_as_float(r2[k]));
+        }
+        if (a.nmain == 2 && blocks > 1) {          // second main accumulator (odd channel blocks)
             tmem_ld32(taddr + 2 * NT, r2);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) + __uint_as_float(r2[k]));
+            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(fmaf(__uint_as_float(r2[k]), F16 ? inv : 1.f, __uint_as_float(r[k])));
         }
     } else {
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -244,22 +342,45 @@ __device__ __forceinline__ void load_chunk(const Args& a, uint32_t taddr, uint32
 // oc0 + k once and the others get them by shuffle, and the 32 residual values are loaded
 // before the first store (y and the residual may be the same buffer as far as the compiler
 // knows, so loads placed between the stores would each wait out a memory round trip).
-__device__ __forceinline__ void store_chunk(const Args& a, const uint32_t (&r)[32], long long out_off, int oc0, long long HW) {
+// `accum`: these accumulators are a later run of the tile's channel blocks: y already holds the sum of the
+// earlier runs (written by this same thread) and is added first.  `final`: this is the tile's last run, the
+// fused options apply; otherwise the bare partial sum is stored.
+__device__ __forceinline__ void store_chunk(const Args& a, const uint32_t (&r)[32], long long out_off, int oc0, long long HW,
+                                            bool accum = false, bool final = true, float* vmax = nullptr) {
     const int lane = threadIdx.x & 31;
     const bool live = out_off >= 0;
     const long long o0 = (live ? out_off : 0) + (long long)oc0 * HW;
     float* yp = a.y + o0;
     const int n = a.K - oc0;                      // channels of this chunk that exist
-    if (n >= 32 && !a.scale && !a.bias && !a.residual && !a.relu) {
+    if (n >= 32 && !accum && (!final || (!a.scale && !a.bias && !a.residual && !a.relu))) {
         if (live) {
 #pragma unroll
             for (int k = 0; k < 32; ++k) { *yp = __uint_as_float(r[k]); yp += HW; }
+            if (vmax) {                               // magnitudes compare like their bit patterns
+                unsigned int m = __float_as_uint(*vmax);
+#pragma unroll
+                for (int k = 0; k < 32; ++k) m = max(m, r[k] & 0x7fffffffu);
+                *vmax = __uint_as_float(m);
+            }
         }
         return;
     }
     float v[32];
 #pragma unroll
     for (int k = 0; k < 32; ++k) v[k] = __uint_as_float(r[k]);
+    if (accum && live) {
+        const float* q = yp;                       // one stepping pointer, not 32 addresses
+#pragma unroll
+        for (int k = 0; k < 32; ++k) { if (k < n) v[k] += *q; q += HW; }
+    }
+    if (!final) {
+        if (live) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+                if (k < n) yp[k * HW] = v[k];
+        }
+        return;
+    }
     if (n >= 32 && a.epi_vec) {
         // a whole chunk, 16-byte aligned scale / bias: eight warp-uniform 16-byte loads each instead of 32 shuffles
         if (a.scale) {
@@ -301,6 +422,12 @@ __device__ __forceinline__ void store_chunk(const Args& a, const uint32_t (&r)[3
     if (a.relu) {
 #pragma unroll
         for (int k = 0; k < 32; ++k) v[k] = fmaxf(v[k], 0.f);
+    }
+    if (vmax && live) {                              // largest stored magnitude, for the range scaling of the next layer
+        float m = *vmax;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) m = fmaxf(m, k < n ? fabsf(v[k]) : 0.f);
+        *vmax = m;
     }
     if (live) {
         if (n >= 32) {
@@ -548,7 +675,7 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
                 if (yy < a.H && xx < a.W) out_off = b * a.K * HW + (long long)yy * a.W + xx;
             }
             uint32_t r[32];
-            load_chunk<NT>(a, tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * a.tile_cols + chunk * 32), r);
+            load_chunk<NT>(a, tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * a.tile_cols + chunk * 32), r, a.nkb);
             store_chunk(a, r, out_off, ocb * NT + chunk * 32, HW);
         }
     }
@@ -564,42 +691,86 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
 namespace tdc_tc {
 
 // Filter [K][C][R][S] (or [C][R][S][K]) -> per (output block, channel block) the exact
-// shared-memory image of a stage's B part: [tap][CB/4][hl*NT][4] (rows 0..NT-1 the hi halves,
-// NT..2NT-1 the lo halves of the same channels), zero-filled past C and K.
-__global__ void prepare_weights_kernel(const float* __restrict__ w, int kcrs, float* __restrict__ wt, int C, int K, int taps,
-                                       int nt, int nkb, int n_ocb, int hl) {
-    const long long per_block = (long long)hl * taps * CB * nt;
+// shared-memory image of a stage's B part: [tap][2 words][hl*NT rows][16 bytes] (rows 0..NT-1 the hi halves,
+// NT..2NT-1 the lo halves of the same channels), zero-filled past C and K.  A 16-byte word holds 4 TF32 channels
+// or, with f16, 8 fp16 channels (lo scaled by 2^11 like the input's).
+// Largest magnitude of a tensor as ABSMAX_SLOTS partial maxima (no atomics, nothing to clear): block b writes entry
+// b, block 0 zeroes the entries beyond the grid.  Magnitudes are compared as unsigned bit patterns.
+__global__ void __launch_bounds__(256) absmax_kernel(const float* __restrict__ x, long long n, float* __restrict__ out) {
+    __shared__ unsigned int red[8];
+    unsigned int m = 0;
+    const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x, nthr = (long long)gridDim.x * blockDim.x;
+    if (reinterpret_cast<uintptr_t>(x) % 16 == 0) {
+        const long long n4 = n >> 2;
+        const uint4* x4 = reinterpret_cast<const uint4*>(x);
+        auto take = [&](const uint4 v) { m = max(max(m, v.x & 0x7fffffffu), max(max(v.y & 0x7fffffffu, v.z & 0x7fffffffu), v.w & 0x7fffffffu)); };
+        long long i = tid;
+        for (; i + 7 * nthr < n4; i += 8 * nthr) {          // eight independent 16-byte loads in flight per thread
+            uint4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = __ldg(x4 + i + k * nthr);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) take(v[k]);
+        }
+        for (; i < n4; i += nthr) take(__ldg(x4 + i));
+        for (long long i = (n4 << 2) + tid; i < n; i += nthr) m = max(m, __float_as_uint(__ldg(x + i)) & 0x7fffffffu);
+    } else {
+        for (long long i = tid; i < n; i += nthr) m = max(m, __float_as_uint(__ldg(x + i)) & 0x7fffffffu);
+    }
+    m = __reduce_max_sync(0xffffffffu, m);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < 8; ++i) m = max(m, red[i]);
+        out[blockIdx.x] = __uint_as_float(m);
+    }
+    if (blockIdx.x == 0)
+        for (int i = gridDim.x + threadIdx.x; i < ABSMAX_SLOTS; i += blockDim.x) out[i] = 0.f;
+}
+
+__global__ void __launch_bounds__(256) prepare_weights_kernel(const float* __restrict__ w, int kcrs, float* __restrict__ wt, int C, int K, int taps,
+                                       int nt, int nkb, int n_ocb, int hl, int f16, const float* __restrict__ w_absmax, float* __restrict__ w_scale) {
+    float ws = 1.f;                                           // fp16: the filter is scaled to the top of fp16's range
+    if (f16) {
+        __shared__ unsigned int word;
+        ws = range_scale(absmax_of(w_absmax, &word));
+        if (blockIdx.x == 0 && threadIdx.x == 0) *w_scale = ws;
+    }
+    const int epw = f16 ? 8 : 4;                              // elements per 16-byte word
+    const long long per_block = (long long)hl * taps * 2 * epw * nt;
     const long long n = per_block * nkb * n_ocb;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         long long t = i;
-        const int e = (int)(t % 4); t /= 4;
+        const int e = (int)(t % epw); t /= epw;
         const int nn = (int)(t % nt); t /= nt;
         const int h = (int)(t % hl); t /= hl;
-        const int chunk = (int)(t % (CB / 4)); t /= (CB / 4);
+        const int word = (int)(t % 2); t /= 2;
         const int tap = (int)(t % taps); t /= taps;
         const int kb = (int)(t % nkb); t /= nkb;
         const int ocb = (int)t;
-        const int oc = ocb * nt + nn, c = kb * CB + chunk * 4 + e;
+        const int oc = ocb * nt + nn, c = (kb * 2 + word) * epw + e;
         float val = 0.f;
         if (oc < K && c < C) val = kcrs ? w[((long long)oc * C + c) * taps + tap] : w[((long long)c * taps + tap) * K + oc];
-        const float hi = to_tf32(val);
-        wt[i] = (h == 0) ? hi : (val - hi);
+        if (f16) {
+            val *= ws;
+            const __half hi = __float2half_rn(val);
+            reinterpret_cast<__half*>(wt)[i] = (h == 0) ? hi : __float2half_rn((val - __half2float(hi)) * 2048.f);
+        } else {
+            const float hi = to_tf32(val);
+            wt[i] = (h == 0) ? hi : (val - hi);
+        }
     }
 }
 
 }  // namespace tdc_tc
 
 // ---------------------------------------------------------------------------------------------
+#include "errors.h"
+
 namespace {
 
-thread_local char g_tc_err[384] = "";
-int tc_fail(int code, const char* fmt, ...) {
-    va_list ap;
-    va_start(ap, fmt);
-    vsnprintf(g_tc_err, sizeof g_tc_err, fmt, ap);
-    va_end(ap);
-    return code;
-}
+using tdc::fail;
+#define tc_fail fail
 __device__ int g_tc_status;   // 0 = every wait of every launch so far completed
 
 int pick_nt(int K) { return K > 64 ? 128 : (K > 32 ? 64 : 32); }
@@ -612,25 +783,110 @@ std::map<int, DevFacts> g_tc_dev;
 std::map<std::pair<int, const void*>, size_t> g_tc_smem_set;
 int cdiv(int a, int b) { return (a + b - 1) / b; }
 
+// Scratch behind a prepared fp16 filter: [0, ABSMAX_SLOTS) floats = partial maxima of |x| written by the range pass of
+// the call in flight (calls that share a prepared filter must not overlap on the GPU), then one float = filter scale.
+constexpr size_t TC_TAIL_BYTES = (tdc_tc::ABSMAX_SLOTS + 64) * sizeof(float);
+float* tc_tail(const tdc_tc_plan* p, const void* wt) {
+    return reinterpret_cast<float*>(reinterpret_cast<uintptr_t>(wt) + p->weights_bytes - TC_TAIL_BYTES);
+}
+
+// Tuning overrides.  They are measurement aids, not part of the interface: the environment is looked at only when
+// TDC_TC_TUNING=1 was set before the first launch of the process, and then on every launch (tests switch them
+// between calls); otherwise a launch reads no environment and its configuration is cached per layer shape.
+//   TDC_TC_PERSIST 0/1 kernel, TDC_TC_MT cap on position tiles per CTA, TDC_TC_NS stages, TDC_TC_NBUF accumulator
+//   buffers, TDC_TC_VEC 0/1 16-byte register loader of one-tap filters, TDC_TC_DEPTH raw slots, TDC_TC_KPS channel
+//   blocks per stage (one-tap filters), TDC_TC_TAIL 0 = no smaller tiles in the last round, TDC_TC_CHAIN
+//   accumulations per run (0 = one run), TDC_TC_BULK 0/1 bulk-tensor loader.
+struct Tuning { int persist = -1, mt = -1, ns = -1, nbuf = -1, vec = -1, depth = -1, kps = -1, tail = -1, chain = -1, bulk = -1; };
+bool tuning_enabled() {
+    static const bool on = [] { const char* v = getenv("TDC_TC_TUNING"); return v && atoi(v) != 0; }();
+    return on;
+}
+Tuning read_tuning() {
+    Tuning t;
+    if (!tuning_enabled()) return t;
+    auto get = [](const char* name) { const char* v = getenv(name); return v ? atoi(v) : -1; };
+    t.persist = get("TDC_TC_PERSIST"); t.mt = get("TDC_TC_MT"); t.ns = get("TDC_TC_NS"); t.nbuf = get("TDC_TC_NBUF");
+    t.vec = get("TDC_TC_VEC"); t.depth = get("TDC_TC_DEPTH"); t.kps = get("TDC_TC_KPS"); t.tail = get("TDC_TC_TAIL");
+    t.chain = get("TDC_TC_CHAIN"); t.bulk = get("TDC_TC_BULK");
+    return t;
+}
+
+// A launch, complete but for the pointers of the call.
+struct Launch {
+    tdc_tc::Args a;
+    const void* fn = nullptr;
+    unsigned ctas = 0;
+    int threads = 0;
+    size_t smem = 0;
+    bool persist = false, bulk = false;
+};
+using LaunchKey = std::tuple<int, int, int, int, int, int, int, int, int, int, int, int, int>;
+std::map<LaunchKey, Launch> g_tc_launches;
+
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link against libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        return (EncodeTiledFn)p;
+    }();
+    return fn;
+}
+
+// Boxes the fullest raw slot of a launch needs: the patch of every position-tile start, with the rows of a full tile.
+int max_boxes(int H, int W, int Wp, int Lp, long long total_pos, int mt, int halo_rows, int pad) {
+    using namespace tdc_tc;
+    const long long ptiles = (total_pos + M_TILE - 1) / M_TILE;
+    // the pattern of image boundaries against tile starts repeats after lcm(Lp, 128) positions = Lp / gcd(Lp, 128) starts
+    int g = Lp, h = M_TILE;
+    while (h) { const int r = g % h; g = h; h = r; }
+    const long long period = Lp / g + mt + 1;
+    const long long scan = ptiles < period ? ptiles : period;
+    int worst = 0;
+    for (long long k = 0; k < scan; ++k) {
+        const long long g0 = k * M_TILE, left = ptiles - k;
+        const int rows = (int)(left < mt ? left : mt) * M_TILE + halo_rows;
+        const long long gp0 = g0 - (long long)pad * (Wp + 1);
+        const long long lo = gp0 < 0 ? 0 : gp0, hi = (gp0 + rows < total_pos ? gp0 + rows : total_pos) - 1;
+        int nb = 0;
+        for (long long b = lo / Lp; b <= hi / Lp; ++b) {
+            int pix4, nbox;
+            image_run(H, W, Wp, Lp, gp0, rows, b, pix4, nbox);
+            nb += nbox;
+        }
+        if (nb > worst) worst = nb;
+    }
+    return worst;
+}
+
 }  // namespace
 
 extern "C" {
 
-const char* tdc_tc_last_error_string(void) { return g_tc_err; }
+const char* tdc_tc_last_error_string(void) { return tdc::last_error(); }
 
 static int plan_fill(int C, int K, int R, int S, int mode, int general, tdc_tc_plan* out, int nt = 0) {
     if (!out) return tc_fail(TDC_ERR_NULL, "out is NULL");
     if (C <= 0 || K <= 0) return tc_fail(TDC_ERR_SHAPE, "C=%d K=%d", C, K);
-    if (mode != 1 && mode != 3) return tc_fail(TDC_ERR_UNSUPPORTED, "mode %d (1 = TF32, 3 = 3xTF32)", mode);
+    if (mode != 1 && mode != 3 && mode != 4) return tc_fail(TDC_ERR_UNSUPPORTED, "mode %d (1 = TF32, 3 = 3xTF32, 4 = 3xFP16)", mode);
     out->C = C; out->K = K; out->R = R; out->S = S; out->mode = mode;
     out->nt = nt ? nt : pick_nt(K);
-    out->cb = tdc_tc::CB;
+    out->cb = mode == 4 ? 16 : 8;
     // a general plan contracts over (channel, filter row, filter column) triples, one tap
-    out->nkb = cdiv(general ? C * R * S : C, tdc_tc::CB);
+    out->nkb = cdiv(general ? C * R * S : C, out->cb);
     out->n_ocb = cdiv(K, out->nt);
-    out->hl = mode == 3 ? 2 : 1;
+    out->hl = mode == 1 ? 1 : 2;
     out->general = general;
+    // per (output block, channel block, tap): 32 bytes (one K step) for each of the hl * nt operand rows
     out->weights_bytes = sizeof(float) * (size_t)out->hl * (general ? 1 : R * S) * tdc_tc::CB * out->nt * out->nkb * out->n_ocb;
+    // fp16 operands: a tail of scratch behind the filter holds the partial maxima of |x| of the call in flight and the
+    // power of two the filter was scaled by (see tc_tail)
+    if (mode == 4) out->weights_bytes += TC_TAIL_BYTES;
     return TDC_OK;
 }
 
@@ -652,8 +908,8 @@ int tdc_tc_pick_nt(int K, int mode, long long positions, int sm_count) {
     double best_cost = 0.0;
     if (ptiles * ((K + base - 1) / base) >= sm_count) return base;      // every SM has a tile already
     for (int nt = base; nt >= 32; nt /= 2) {
-        const double math = mode == 3 ? 96.0 * nt / 64.0 : 32.0 * nt / 64.0;
-        const double smem = mode == 3 ? ((4096.0 + 64.0 * nt) + (4096.0 + 32.0 * nt)) / 128.0 : (4096.0 + 32.0 * nt) / 128.0;
+        const double math = mode != 1 ? 96.0 * nt / 64.0 : 32.0 * nt / 64.0;
+        const double smem = mode != 1 ? ((4096.0 + 64.0 * nt) + (4096.0 + 32.0 * nt)) / 128.0 : (4096.0 + 32.0 * nt) / 128.0;
         const long long tiles = ptiles * ((K + nt - 1) / nt);
         const double cost = (double)((tiles + sm_count - 1) / sm_count) * (math > smem ? math : smem);
         if (nt == base || cost < best_cost * 0.95) { best = nt; best_cost = cost; }      // a smaller block must win clearly
@@ -681,32 +937,36 @@ int tdc_tc_plan_make_general(int C, int K, int R, int S, int mode, tdc_tc_plan* 
 int tdc_tc_prepare_weights(const tdc_tc_plan* p, const float* w, int w_layout, void* wt, void* stream) {
     if (!p || !w || !wt) return tc_fail(TDC_ERR_NULL, "plan, w and wt must be non-NULL");
     if (w_layout != TDC_W_KCRS && w_layout != TDC_W_CRSK) return tc_fail(TDC_ERR_UNSUPPORTED, "w_layout %d", w_layout);
-    long long n = (long long)(p->weights_bytes / sizeof(float));
+    if (reinterpret_cast<uintptr_t>(wt) % 16 != 0) return tc_fail(TDC_ERR_UNSUPPORTED, "wt must be 16-byte aligned (the kernels fetch it with bulk copies)");
+    const bool f16 = p->mode == 4;
+    long long n = (long long)((p->weights_bytes - (f16 ? TC_TAIL_BYTES : 0)) / (f16 ? 2 : 4));
     int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    float* tail = f16 ? tc_tail(p, wt) : nullptr;
+    if (f16) {      // the filter's largest magnitude first: the prepare kernel scales by the power of two that follows from it
+        const long long nw = (long long)p->C * p->K * p->R * p->S;
+        tdc_tc::absmax_kernel<<<(unsigned)(nw / 1024 + 1 < 256 ? nw / 1024 + 1 : 256), 256, 0, (cudaStream_t)stream>>>(w, nw, tail);
+    }
     // a general plan: the filter is a 1x1 filter over C*R*S channels; in both layouts channel, row and column are
     // adjacent index digits, so the flattened filter is addressed exactly as a 1x1 one
     const int Cw = p->general ? p->C * p->R * p->S : p->C, taps = p->general ? 1 : p->R * p->S;
     tdc_tc::prepare_weights_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(w, w_layout == TDC_W_KCRS, (float*)wt, Cw, p->K,
-                                                                           taps, p->nt, p->nkb, p->n_ocb, p->hl);
+                                                                           taps, p->nt, p->nkb, p->n_ocb, p->hl, f16 ? 1 : 0, tail,
+                                                                           tail ? tail + tdc_tc::ABSMAX_SLOTS : nullptr);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "prepare launch: %s", cudaGetErrorString(e));
 }
 
-int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y, int B, int H, int W,
-                  const tdc_epilogue* epi, int flags, void* stream) {
-    if (!p || !x || !wt || !y) return tc_fail(TDC_ERR_NULL, "plan, x, wt and y must be non-NULL");
-    if (B <= 0 || H <= 0 || W <= 0) return tc_fail(TDC_ERR_SHAPE, "B=%d H=%d W=%d", B, H, W);
-    const int stride = (flags & TDC_TC_STRIDE_MASK) + 1, gpad = (flags & TDC_TC_PAD_MASK) >> TDC_TC_PAD_SHIFT;
-    if (flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK)) return tc_fail(TDC_ERR_UNSUPPORTED, "unknown flag bits %#x", flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK));
-    if (!p->general && stride > 1 && p->R != 1) return tc_fail(TDC_ERR_UNSUPPORTED, "a stride is taken for 1x1 filters and general plans only");
-    if (!p->general && gpad != 0) return tc_fail(TDC_ERR_UNSUPPORTED, "a padding is taken for general plans only (the others pad (R-1)/2)");
+// Everything about a launch that follows from the plan, the image and the flags: kernel, grid, shared memory and the
+// argument block without its pointers.  `x_al16`: the input is 16-byte aligned (16-byte and bulk-tensor loads).
+static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, bool x_al16, const DevFacts& facts, const Tuning& tn, Launch* out) {
     using namespace tdc_tc;
+    const int stride = (flags & TDC_TC_STRIDE_MASK) + 1, gpad = (flags & TDC_TC_PAD_MASK) >> TDC_TC_PAD_SHIFT;
+    const bool f16 = p->mode == 4;
+    const int cbk = f16 ? 16 : 8;
     Args a{};
-    a.x = x; a.wt = (const float*)wt; a.y = y;
-    if (epi) { a.scale = epi->scale; a.bias = epi->bias; a.residual = epi->residual; a.relu = epi->relu ? 1 : 0; }
-    a.epi_vec = reinterpret_cast<uintptr_t>(a.scale) % 16 == 0 && reinterpret_cast<uintptr_t>(a.bias) % 16 == 0;
     // from here on H and W are the output image; the input image is only an address pattern of the loaders
     a.stride = stride; a.Win = W; a.HWin = (long long)H * W; a.Hin = H;
+    const int Hin = H, Win = W;
     if (p->general) {
         a.gather = 1; a.gR = p->R; a.gS = p->S; a.gpad = gpad;
         if (H + 2 * gpad < p->R || W + 2 * gpad < p->S) return tc_fail(TDC_ERR_SHAPE, "the %dx%d filter does not fit the padded %dx%d image", p->R, p->S, H, W);
@@ -724,6 +984,195 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
     if (W > 256) return tc_fail(TDC_ERR_UNSUPPORTED, "image width %d is too large for the tensor-core path (max 256)", W);
     a.nkb = p->nkb; a.n_ocb = p->n_ocb; a.hl = p->hl;
     const int taps = taps_r * taps_r;
+    const int smem_max = facts.smem_max, sms = facts.sms;
+    // TF32 operands: long reductions get two main accumulators per tile (4*NT columns per tile instead of 2*NT).
+    // fp16 operands: one main accumulator; long reductions are cut into runs instead (below).
+    a.nmain = (!f16 && a.hl == 2 && (long long)p->nkb * taps > 320) ? 2 : 1;
+    a.tile_cols = (a.nmain == 2 ? 4 : 2) * p->nt;
+    // The persistent kernel wins where a CTA tile is short and its prologue and epilogue would otherwise show: split
+    // operands with up to 64 output channels per block, and one-tap filters of any block size (with few tiles too:
+    // its cp.async ring has all loader threads and several channel blocks in flight, 20 % faster than the one-tile
+    // kernel on nine layers of 25..200 tiles).  For 3x3 filters with 128-channel blocks and TF32 operands the one-tile
+    // kernel, which drains tensor memory with all its warps, measured faster.  fp16 operands and general plans exist
+    // in the persistent kernel only.
+    const long long tiles_mt2 = ((a.total_pos + 2 * M_TILE - 1) / (2 * M_TILE)) * a.n_ocb;
+    // ... and for 3x3 filters with one 128-channel block when the tile list has complete rounds plus a rest: the
+    // persistent kernel spreads the rest over all SMs as smaller tiles (28x28x128 at batch 64: 88 -> 76 us).
+    const bool persist = p->general || f16 || (tn.persist >= 0 ? tn.persist != 0
+                                                    : (a.hl == 2 ? (p->nt <= 64 || taps == 1 || (tiles_mt2 >= sms && a.n_ocb == 1 && tiles_mt2 % sms != 0))
+                                                                 // plain TF32: one-tap filters likewise (14 layers: 20 % on 12, level on 2); 3x3: two one-tile
+                                                                 // CTAs share an SM for short launches, long ones measured faster persistent
+                                                                 : (taps == 1 || 2.0 * a.total_pos * p->C * p->K * taps >= 8e9)));
+    int mt = 512 / a.tile_cols > 4 ? 4 : 512 / a.tile_cols, ns = 0, depth = 0, nbuf = 1;   // tensor memory: 512 columns
+    if (tn.mt >= 1) while (mt > tn.mt) mt /= 2;
+    // 16-byte input loads: 1x1 filter, images a multiple of 4 positions long, 16-byte aligned base.  In the persistent
+    // kernel the cp.async ring is the faster loader all the same — it keeps all 256 loader threads
+    // and `depth` channel blocks in flight where the 16-byte path has 64 threads per 128-position tile and two blocks
+    // in registers — except for blocks of up to 64 channels with ten or more position tiles per SM (157 one-tap
+    // layers, 64..1024 -> 32..512 channels at 14..112 pixels, batch 1..128, timed both ways: ring/16-byte = 0.71-0.89
+    // where the rule takes the ring, 1.06-1.14 where it does not; 0.88 geometric mean over all; plain TF32 on 14 of
+    // them: the same picture).
+    const bool vec_ok = !f16 && taps == 1 && !p->general && stride == 1 && ((long long)H * W) % 4 == 0 && x_al16;
+    const long long ptiles = (a.total_pos + M_TILE - 1) / M_TILE;
+    const bool ring_wins = persist && (p->nt > 64 || ptiles < 10ll * sms);
+    const bool vec = vec_ok && (tn.vec >= 0 ? tn.vec != 0 : !ring_wins);
+    // Bulk-tensor loader: fp16 operands, unit stride, the input image a multiple of 4 pixels (the stride of the
+    // channel dimension of the tensor map must be a multiple of 16 bytes), 16-byte aligned input.
+    const bool bulk_ok = f16 && !p->general && stride == 1 && ((long long)Hin * Win) % 4 == 0 && x_al16 && encode_tiled() != nullptr;
+    bool bulk = bulk_ok && (tn.bulk >= 0 ? tn.bulk != 0 : true);
+    if (bulk && mt > 2) mt = 2;                                 // its producer is the fourth issuer warp
+    const size_t header = persist ? P_HEADER : 128;
+    const int halo_unit = 2 * pad * (a.Wp + 1);
+    // Position tiles per CTA: the largest candidate (4, 2, 1; what tensor memory and shared memory hold) that still
+    // gives every SM a tile.  One exception: when few position tiles share a large filter, streaming the filter
+    // from L2 once per tile is what bounds the launch; then a larger candidate is taken if the estimate below
+    // (shared-memory traffic at 128 bytes per clock per SM against filter bytes from L2) says it is faster.
+    const double op_bytes = a.hl == 2 ? (4096.0 + 64.0 * p->nt) + (4096.0 + 32.0 * p->nt) : 4096.0 + 32.0 * p->nt;   // per tap and position tile
+    const size_t room = (size_t)smem_max - header;
+    auto raw_bytes_of = [&](int m, int P, bool use_bulk, int* cap) -> size_t {
+        if (!persist || vec) return 0;
+        if (!use_bulk) return sizeof(float) * (size_t)cbk * P;
+        const int c = max_boxes(H, W, a.Wp, a.Lp, a.total_pos, m, halo_unit, pad);
+        if (cap) *cap = c;
+        return (size_t)c * BOXC * BOXW * sizeof(float);
+    };
+    int best_mt = 0, big_mt = 0;
+    double best_cost = 0.0, big_cost = 0.0;
+    bool best_l2_bound = false;
+    for (int attempt = 0; attempt < 2 && best_mt == 0; ++attempt) {
+        if (attempt == 1) { if (!bulk) break; bulk = false; }     // the bulk loader's slots did not fit: fall back to the ring
+        for (int m = mt; m >= 1; m /= 2) {
+            const int P = ((m * M_TILE + halo_unit) + 7) / 8 * 8;
+            const size_t sb = sizeof(float) * ((size_t)a.hl * CB * P + (size_t)a.hl * taps * CB * p->nt);
+            int cap = 0;
+            const size_t rb = raw_bytes_of(m, P, bulk, &cap);
+            if (2 * sb + 2 * rb > room || P > (persist && m > 1 ? 4 : 3) * LOADERS || (bulk && (cap > P_MAXBOX || cap == 0))) continue;   // rows per loader thread the kernels are built for
+            const double ntl = (double)((a.total_pos + (long long)m * M_TILE - 1) / ((long long)m * M_TILE)) * a.n_ocb;
+            const double rounds = (double)(((long long)ntl + sms - 1) / sms);
+            const double tile_clk = a.nkb * (m * taps * op_bytes + (double)sb + 2.0 * rb) / 128.0 + 2000.0 * m * (p->nt / 32);
+            const double l2_clk = ntl * a.nkb * (double)(sizeof(float) * a.hl * taps * CB * p->nt) / 2900.0;
+            const double cost = rounds * tile_clk > l2_clk ? rounds * tile_clk : l2_clk;
+            if (big_mt == 0 || cost < big_cost) { big_mt = m; big_cost = cost; }          // cheapest of the candidates seen so far (all larger or equal)
+            best_mt = m; best_cost = cost; best_l2_bound = l2_clk > rounds * tile_clk;
+            if (ntl >= sms) break;
+        }
+    }
+    if (best_mt != 0 && best_l2_bound && big_cost < best_cost) best_mt = big_mt;
+    if (best_mt == 0) return tc_fail(TDC_ERR_SMEM, "two stages of the %dx%d filter block do not fit in shared memory", p->R, p->S);
+    mt = best_mt;
+    const bool ring = persist && !vec && !bulk;              // input staged through the raw cp.async ring
+    // the persistent kernel double-buffers the accumulators when tensor memory has room for it
+    if (persist && 2 * mt * a.tile_cols <= 512 && tn.nbuf != 1) nbuf = 2;
+    a.P = ((mt * M_TILE + halo_unit) + 7) / 8 * 8;
+    size_t stage_bytes = sizeof(float) * ((size_t)a.hl * CB * a.P + (size_t)a.hl * taps * CB * p->nt);
+    int cap = 0;
+    const size_t raw_bytes = raw_bytes_of(mt, a.P, bulk, &cap);
+    a.nbox_cap = cap;
+    // One-tap filters (1x1, general plans) do one or two MMAs per channel block and position tile: a stage of one
+    // block would be all hand-over.  Their stages take up to four blocks (what leaves room for two stages and,
+    // with a raw ring, two raw slots).
+    a.kps = 1;
+    if (persist && taps == 1) {
+        int want = tn.kps >= 1 && tn.kps <= 8 ? tn.kps : 4;
+        if (want > a.nkb) want = a.nkb;
+        while (want > 1 && 2 * want * stage_bytes + 2 * raw_bytes > room) --want;
+        a.kps = want;
+        stage_bytes *= want;
+    }
+    if (ring || bulk) {
+        // three operand stages when at least four raw slots still fit beside them, else two; then as many raw slots as fit
+        ns = 3 * stage_bytes + 4 * raw_bytes <= room ? 3 : 2;
+        if (tn.ns >= 2 && tn.ns <= 4 && tn.ns * stage_bytes + 2 * raw_bytes <= room) ns = tn.ns;
+        depth = (int)((room - ns * stage_bytes) / raw_bytes);
+        if (depth > 8) depth = 8;
+        if (tn.depth >= 2 && tn.depth <= depth) depth = tn.depth;
+    } else {
+        const int ns_max = persist ? 4 : 3;
+        ns = 2;
+        while (ns < ns_max && (ns + 1) * stage_bytes <= room) ++ns;
+        if (tn.ns >= 2 && tn.ns <= ns) ns = tn.ns;
+    }
+    if (!persist && ns > a.nkb) ns = a.nkb > 0 ? a.nkb : 1;
+    a.ns = ns;
+    a.nbuf = nbuf;
+    a.depth = depth;
+    a.tmem_cols = 32;
+    while (a.tmem_cols < nbuf * mt * a.tile_cols) a.tmem_cols *= 2;
+    // Runs: at most `chain` MMAs feed one accumulator before the epilogue takes the partial sum over in fp32.  The
+    // error of the tensor core's running sum grows by about 2.5e-8 of the output scale per accumulation.
+    a.nseg = 1; a.seg_blocks = a.nkb;
+    const int chain = tn.chain >= 0 ? tn.chain : (f16 ? 144 : 0);
+    if (persist && chain > 0) {
+        const long long accs = ((long long)a.nkb * taps + a.nmain - 1) / a.nmain;
+        int nseg = (int)((accs + chain - 1) / chain);
+        if (nseg > 1) {
+            int sb = cdiv(a.nkb, nseg);
+            sb = cdiv(sb, a.kps) * a.kps;                   // a run ends with a stage
+            a.seg_blocks = sb;
+            a.nseg = cdiv(a.nkb, sb);
+        }
+    }
+    const size_t smem = header + ns * stage_bytes + depth * raw_bytes;
+    a.status = facts.status;
+    long long tiles = (a.total_pos + (long long)mt * M_TILE - 1) / ((long long)mt * M_TILE);
+    a.pt_total = (a.total_pos + M_TILE - 1) / M_TILE;
+    a.full_groups = tiles; a.tail_first_pt = 0; a.tail_cnt = mt;          // every tile holds mt position tiles ...
+    if (persist && a.n_ocb == 1 && mt > 1 && tn.tail != 0) {
+        // ... except that the position tiles left for the last, partial round are spread over all SMs as smaller tiles
+        const long long rounds = (a.pt_total / mt) / sms, full = rounds * sms, rest = a.pt_total - full * mt;
+        if (rounds >= 1 && rest > 0) {          // (with no complete round the choice of mt above already weighed SMs against filter traffic)
+            a.full_groups = full;
+            a.tail_first_pt = full * mt;
+            a.tail_cnt = (int)((rest + sms - 1) / sms);
+            tiles = full + (rest + a.tail_cnt - 1) / a.tail_cnt;
+        }
+    }
+    a.ntiles = tiles * a.n_ocb;
+    if (a.ntiles >= (1ll << 31)) return tc_fail(TDC_ERR_TILE, "grid too large");
+    const long long ctas = persist ? (a.ntiles < sms ? a.ntiles : sms) : a.ntiles;
+    const void* fn = nullptr;
+#define TDC_TC_ONE(NT_, MT_) (taps == 9 ? (const void*)&conv_tc_kernel<NT_, MT_, 9, false> : \
+                              (vec ? (const void*)&conv_tc_kernel<NT_, MT_, 1, true> : (const void*)&conv_tc_kernel<NT_, MT_, 1, false>))
+#define TDC_TC_PER(NT_, MT_) (f16 ? (taps == 9 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 9, LD_RING, true> \
+                                               : (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_RING, true>) \
+                                  : (taps == 9 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 9, LD_RING, false> \
+                                               : (vec ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_VEC, false> \
+                                                      : (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_RING, false>)))
+#define TDC_TC_BLK(NT_, MT_) (taps == 9 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 9, LD_BULK, true> \
+                                        : (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_BULK, true>)
+#define TDC_TC_PICK(NT_, MT_) (persist ? TDC_TC_PER(NT_, MT_) : TDC_TC_ONE(NT_, MT_))
+    if (bulk) {
+        if (p->nt == 128) fn = mt == 2 ? TDC_TC_BLK(128, 2) : TDC_TC_BLK(128, 1);
+        else if (p->nt == 64) fn = mt == 2 ? TDC_TC_BLK(64, 2) : TDC_TC_BLK(64, 1);
+        else fn = mt == 2 ? TDC_TC_BLK(32, 2) : TDC_TC_BLK(32, 1);
+    } else if (p->nt == 128) fn = mt == 2 ? TDC_TC_PICK(128, 2) : TDC_TC_PICK(128, 1);
+    else if (p->nt == 64) fn = mt == 4 ? TDC_TC_PICK(64, 4) : (mt == 2 ? TDC_TC_PICK(64, 2) : TDC_TC_PICK(64, 1));
+    else fn = mt == 4 ? TDC_TC_PICK(32, 4) : (mt == 2 ? TDC_TC_PICK(32, 2) : TDC_TC_PICK(32, 1));
+#undef TDC_TC_PICK
+#undef TDC_TC_BLK
+#undef TDC_TC_PER
+#undef TDC_TC_ONE
+    out->a = a; out->fn = fn; out->ctas = (unsigned)ctas; out->threads = persist ? P_THREADS : THREADS; out->smem = smem;
+    out->persist = persist; out->bulk = bulk;
+    return TDC_OK;
+}
+
+int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y, int B, int H, int W,
+                  const tdc_epilogue* epi, int flags, void* stream) {
+    return tdc_conv2d_tc_ranged(p, x, wt, y, B, H, W, epi, flags, nullptr, nullptr, stream);
+}
+
+int tdc_conv2d_tc_ranged(const tdc_tc_plan* p, const float* x, const void* wt, float* y, int B, int H, int W,
+                         const tdc_epilogue* epi, int flags, const float* x_absmax, float* y_absmax, void* stream) {
+    if (!p || !x || !wt || !y) return tc_fail(TDC_ERR_NULL, "plan, x, wt and y must be non-NULL");
+    if (y_absmax && p->mode != 4) return tc_fail(TDC_ERR_UNSUPPORTED, "y_absmax is written by mode 4 (fp16 operands) only");
+    if (B <= 0 || H <= 0 || W <= 0) return tc_fail(TDC_ERR_SHAPE, "B=%d H=%d W=%d", B, H, W);
+    const int stride = (flags & TDC_TC_STRIDE_MASK) + 1, gpad = (flags & TDC_TC_PAD_MASK) >> TDC_TC_PAD_SHIFT;
+    if (flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK)) return tc_fail(TDC_ERR_UNSUPPORTED, "unknown flag bits %#x", flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK));
+    if (!p->general && stride > 1 && p->R != 1) return tc_fail(TDC_ERR_UNSUPPORTED, "a stride is taken for 1x1 filters and general plans only");
+    if (!p->general && gpad != 0) return tc_fail(TDC_ERR_UNSUPPORTED, "a padding is taken for general plans only (the others pad (R-1)/2)");
+    if (reinterpret_cast<uintptr_t>(wt) % 16 != 0) return tc_fail(TDC_ERR_UNSUPPORTED, "wt must be 16-byte aligned (the kernels fetch it with bulk copies)");
+    using namespace tdc_tc;
     int device;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return tc_fail(TDC_ERR_NO_DEVICE, "cudaGetDevice: %s", cudaGetErrorString(e));
@@ -743,151 +1192,78 @@ int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y
         }
         facts = it->second;
     }
-    const int smem_max = facts.smem_max, sms = facts.sms;
-    // long reductions get two main accumulators per tile (4*NT columns per tile instead of 2*NT)
-    a.nmain = (a.hl == 2 && (long long)p->nkb * taps > 320) ? 2 : 1;
-    a.tile_cols = (a.nmain == 2 ? 4 : 2) * p->nt;
-    // tuning overrides (read per call): TDC_TC_PERSIST=0 selects the one-tile-per-CTA kernel, TDC_TC_MT caps the
-    // position tiles per CTA, TDC_TC_NS fixes the stage count, TDC_TC_NBUF the accumulator buffers
-    const char* env_mt = getenv("TDC_TC_MT");
-    const char* env_ns = getenv("TDC_TC_NS");
-    const char* env_nbuf = getenv("TDC_TC_NBUF");
-    const char* env_persist = getenv("TDC_TC_PERSIST");
-    // The persistent kernel wins where a CTA tile is short and its prologue and epilogue would otherwise show: split
-    // operands with up to 64 output channels per block, and one-tap filters of any block size (with few tiles too:
-    // its cp.async ring has all loader threads and several channel blocks in flight, 20 % faster than the one-tile
-    // kernel on nine layers of 25..200 tiles).  For 3x3 filters with 128-channel blocks the one-tile
-    // kernel, which drains tensor memory with all its warps, measured faster.  TDC_TC_PERSIST=0/1 forces either.
-    const long long tiles_mt2 = ((a.total_pos + 2 * M_TILE - 1) / (2 * M_TILE)) * a.n_ocb;
-    // ... and for 3x3 filters with one 128-channel block when the tile list has complete rounds plus a rest: the
-    // persistent kernel spreads the rest over all SMs as smaller tiles (28x28x128 at batch 64: 88 -> 76 us).
-    const bool persist = p->general || (env_persist ? atoi(env_persist) != 0
-                                                    : (a.hl == 2 ? (p->nt <= 64 || taps == 1 || (tiles_mt2 >= sms && a.n_ocb == 1 && tiles_mt2 % sms != 0))
-                                                                 // plain TF32: one-tap filters likewise (14 layers: 20 % on 12, level on 2); 3x3: two one-tile
-                                                                 // CTAs share an SM for short launches, long ones measured faster persistent
-                                                                 : (taps == 1 || 2.0 * a.total_pos * p->C * p->K * taps >= 8e9)));
-    int mt = 512 / a.tile_cols > 4 ? 4 : 512 / a.tile_cols, ns = 0, depth = 0, nbuf = 1;   // tensor memory: 512 columns
-    if (env_mt && atoi(env_mt) >= 1) while (mt > atoi(env_mt)) mt /= 2;
-    // 16-byte input loads: 1x1 filter, images a multiple of 4 positions long, 16-byte aligned base.  In the persistent
-    // kernel the cp.async ring is the faster loader all the same — it keeps all 256 loader threads
-    // and `depth` channel blocks in flight where the 16-byte path has 64 threads per 128-position tile and two blocks
-    // in registers — except for blocks of up to 64 channels with ten or more position tiles per SM (157 one-tap
-    // layers, 64..1024 -> 32..512 channels at 14..112 pixels, batch 1..128, timed both ways: ring/16-byte = 0.71-0.89
-    // where the rule takes the ring, 1.06-1.14 where it does not; 0.88 geometric mean over all; plain TF32 on 14 of
-    // them: the same picture).  TDC_TC_VEC=0/1 forces.
-    const char* env_vec = getenv("TDC_TC_VEC");
-    const bool vec_ok = taps == 1 && !p->general && stride == 1 && ((long long)H * W) % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0;
-    const long long ptiles = (a.total_pos + M_TILE - 1) / M_TILE;
-    const bool ring_wins = persist && (p->nt > 64 || ptiles < 10ll * sms);
-    const bool vec = vec_ok && (env_vec ? atoi(env_vec) != 0 : !ring_wins);
-    const bool ring = persist && !vec;                       // input staged through the raw cp.async ring
-    const char* env_depth = getenv("TDC_TC_DEPTH");
-    size_t stage_bytes = 0, raw_bytes = 0;
-    const size_t header = persist ? P_HEADER : 128;
-    // Position tiles per CTA: the largest candidate (4, 2, 1; what tensor memory and shared memory hold) that still
-    // gives every SM a tile.  One exception: when few position tiles share a large filter, streaming the filter
-    // from L2 once per tile is what bounds the launch; then a larger candidate is taken if the estimate below
-    // (shared-memory traffic at 128 bytes per clock per SM against filter bytes from L2) says it is faster.
-    const double op_bytes = a.hl == 2 ? (4096.0 + 64.0 * p->nt) + (4096.0 + 32.0 * p->nt) : 4096.0 + 32.0 * p->nt;   // per tap and position tile
-    const size_t room = (size_t)smem_max - header;
-    int best_mt = 0, big_mt = 0;
-    double best_cost = 0.0, big_cost = 0.0;
-    bool best_l2_bound = false;
-    for (int m = mt; m >= 1; m /= 2) {
-        const int P = ((m * M_TILE + 2 * pad * (a.Wp + 1)) + 7) / 8 * 8;
-        const size_t sb = sizeof(float) * ((size_t)a.hl * CB * P + (size_t)a.hl * taps * CB * p->nt);
-        const size_t rb = ring ? sizeof(float) * (size_t)CB * P : 0;
-        if (2 * sb + 2 * rb > room || P > (persist && m > 1 ? 4 : 3) * LOADERS) continue;     // rows per loader thread the kernels are built for
-        const double ntl = (double)((a.total_pos + (long long)m * M_TILE - 1) / ((long long)m * M_TILE)) * a.n_ocb;
-        const double rounds = (double)(((long long)ntl + sms - 1) / sms);
-        const double tile_clk = a.nkb * (m * taps * op_bytes + (double)sb + 2.0 * rb) / 128.0 + 2000.0 * m * (p->nt / 32);
-        const double l2_clk = ntl * a.nkb * (double)(sizeof(float) * a.hl * taps * CB * p->nt) / 2900.0;
-        const double cost = rounds * tile_clk > l2_clk ? rounds * tile_clk : l2_clk;
-        if (big_mt == 0 || cost < big_cost) { big_mt = m; big_cost = cost; }          // cheapest of the candidates seen so far (all larger or equal)
-        best_mt = m; best_cost = cost; best_l2_bound = l2_clk > rounds * tile_clk;
-        if (ntl >= sms) break;
-    }
-    if (best_mt != 0 && best_l2_bound && big_cost < best_cost) best_mt = big_mt;
-    if (best_mt == 0) return tc_fail(TDC_ERR_SMEM, "two stages of the %dx%d filter block do not fit in shared memory", p->R, p->S);
-    mt = best_mt;
-    // the persistent kernel double-buffers the accumulators when tensor memory has room for it
-    if (persist && 2 * mt * a.tile_cols <= 512 && !(env_nbuf && atoi(env_nbuf) == 1)) nbuf = 2;
-    a.P = ((mt * M_TILE + 2 * pad * (a.Wp + 1)) + 7) / 8 * 8;
-    stage_bytes = sizeof(float) * ((size_t)a.hl * CB * a.P + (size_t)a.hl * taps * CB * p->nt);
-    raw_bytes = ring ? sizeof(float) * (size_t)CB * a.P : 0;
-    // One-tap filters (1x1, general plans) do one or two MMAs per channel block and position tile: a stage of one
-    // block would be all hand-over.  Their stages take up to four blocks (what leaves room for two stages and,
-    // with the ring, two raw slots); TDC_TC_KPS overrides.
-    a.kps = 1;
-    if (persist && taps == 1) {
-        const char* env_kps = getenv("TDC_TC_KPS");
-        int want = env_kps && atoi(env_kps) >= 1 && atoi(env_kps) <= 8 ? atoi(env_kps) : 4;
-        if (want > a.nkb) want = a.nkb;
-        while (want > 1 && 2 * want * stage_bytes + 2 * raw_bytes > room) --want;
-        a.kps = want;
-        stage_bytes *= want;
-    }
-    if (ring) {
-        // three operand stages when at least four raw slots still fit beside them, else two; then as many raw slots as fit
-        ns = 3 * stage_bytes + 4 * raw_bytes <= room ? 3 : 2;
-        if (env_ns && atoi(env_ns) >= 2 && atoi(env_ns) <= 4 && atoi(env_ns) * stage_bytes + 2 * raw_bytes <= room) ns = atoi(env_ns);
-        depth = (int)((room - ns * stage_bytes) / raw_bytes);
-        if (depth > 8) depth = 8;
-        if (env_depth && atoi(env_depth) >= 2 && atoi(env_depth) <= depth) depth = atoi(env_depth);
+    const bool x_al16 = reinterpret_cast<uintptr_t>(x) % 16 == 0;
+    Launch L;
+    if (tuning_enabled()) {
+        const int rc = plan_launch(p, B, H, W, flags, x_al16, facts, read_tuning(), &L);
+        if (rc) return rc;
     } else {
-        const int ns_max = persist ? 4 : 3;
-        ns = 2;
-        while (ns < ns_max && (ns + 1) * stage_bytes <= room) ++ns;
-        if (env_ns && atoi(env_ns) >= 2 && atoi(env_ns) <= ns) ns = atoi(env_ns);
+        const LaunchKey key{device, p->C, p->K, p->R, p->S, p->mode, p->nt, p->general, B, H, W, flags, x_al16 ? 1 : 0};
+        std::lock_guard<std::mutex> lk(g_tc_mu);
+        auto it = g_tc_launches.find(key);
+        if (it == g_tc_launches.end()) {
+            const int rc = plan_launch(p, B, H, W, flags, x_al16, facts, Tuning{}, &L);
+            if (rc) return rc;
+            it = g_tc_launches.emplace(key, L).first;
+        }
+        L = it->second;
     }
-    if (!persist && ns > a.nkb) ns = a.nkb > 0 ? a.nkb : 1;
-    a.ns = ns;
-    a.nbuf = nbuf;
-    a.depth = depth;
-    a.tmem_cols = 32;
-    while (a.tmem_cols < nbuf * mt * a.tile_cols) a.tmem_cols *= 2;
-    const size_t smem = header + ns * stage_bytes + depth * raw_bytes;
-    a.status = facts.status;
-    long long tiles = (a.total_pos + (long long)mt * M_TILE - 1) / ((long long)mt * M_TILE);
-    a.pt_total = (a.total_pos + M_TILE - 1) / M_TILE;
-    a.full_groups = tiles; a.tail_first_pt = 0; a.tail_cnt = mt;          // every tile holds mt position tiles ...
-    const char* env_tail = getenv("TDC_TC_TAIL");
-    if (persist && a.n_ocb == 1 && mt > 1 && !(env_tail && atoi(env_tail) == 0)) {
-        // ... except that the position tiles left for the last, partial round are spread over all SMs as smaller tiles
-        const long long rounds = (a.pt_total / mt) / sms, full = rounds * sms, rest = a.pt_total - full * mt;
-        if (rounds >= 1 && rest > 0) {          // (with no complete round the choice of mt above already weighed SMs against filter traffic)
-            a.full_groups = full;
-            a.tail_first_pt = full * mt;
-            a.tail_cnt = (int)((rest + sms - 1) / sms);
-            tiles = full + (rest + a.tail_cnt - 1) / a.tail_cnt;
+    Args& a = L.a;
+    a.x = x; a.wt = (const float*)wt; a.y = y;
+    if (epi) { a.scale = epi->scale; a.bias = epi->bias; a.residual = epi->residual; a.relu = epi->relu ? 1 : 0; }
+    a.epi_vec = reinterpret_cast<uintptr_t>(a.scale) % 16 == 0 && reinterpret_cast<uintptr_t>(a.bias) % 16 == 0;
+    if (p->mode == 4) {
+        float* tail = tc_tail(p, wt);
+        a.w_scale = tail + ABSMAX_SLOTS;
+        a.y_absmax = y_absmax;
+        a.x_absmax = x_absmax;
+        if (!x_absmax) {
+            // nobody told us how large the input gets: one pass over it first (x then sits in L2 for the convolution)
+            const long long n = (long long)B * p->C * H * W;
+            const long long want = (n + 8191) / 8192;                      // 32 elements per thread at least
+            const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > 4 * facts.sms ? 4 * facts.sms : want));
+            absmax_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(x, n, tail);
+            if ((e = cudaGetLastError()) != cudaSuccess) return tc_fail(TDC_ERR_CUDA, "range pass launch: %s", cudaGetErrorString(e));
+            a.x_absmax = tail;
         }
     }
-    a.ntiles = tiles * a.n_ocb;
-    if (a.ntiles >= (1ll << 31)) return tc_fail(TDC_ERR_TILE, "grid too large");
-    const long long ctas = persist ? (a.ntiles < sms ? a.ntiles : sms) : a.ntiles;
-    const int threads = persist ? P_THREADS : THREADS;
-    const void* fn = nullptr;
-#define TDC_TC_PICK3(KERNEL, NT_, MT_) (taps == 9 ? (const void*)&KERNEL<NT_, MT_, 9, false> : \
-                                        (vec ? (const void*)&KERNEL<NT_, MT_, 1, true> : (const void*)&KERNEL<NT_, MT_, 1, false>))
-#define TDC_TC_PICK(NT_, MT_) (persist ? TDC_TC_PICK3(conv_tc_persist_kernel, NT_, MT_) : TDC_TC_PICK3(conv_tc_kernel, NT_, MT_))
-    if (p->nt == 128) fn = mt == 2 ? TDC_TC_PICK(128, 2) : TDC_TC_PICK(128, 1);
-    else if (p->nt == 64) fn = mt == 4 ? TDC_TC_PICK(64, 4) : (mt == 2 ? TDC_TC_PICK(64, 2) : TDC_TC_PICK(64, 1));
-    else fn = mt == 4 ? TDC_TC_PICK(32, 4) : (mt == 2 ? TDC_TC_PICK(32, 2) : TDC_TC_PICK(32, 1));
-#undef TDC_TC_PICK
-#undef TDC_TC_PICK3
+    CUtensorMap tmap;
+    memset(&tmap, 0, sizeof tmap);
+    if (L.bulk) {
+        // x as a 3-D tensor (pixels of an image, channels, images); a box is BOXW pixels of BOXC channels of one image
+        const cuuint64_t gdim[3] = {(cuuint64_t)H * W, (cuuint64_t)p->C, (cuuint64_t)B};
+        const cuuint64_t gstr[2] = {(cuuint64_t)H * W * sizeof(float), (cuuint64_t)p->C * H * W * sizeof(float)};
+        const cuuint32_t box[3] = {(cuuint32_t)BOXW, (cuuint32_t)BOXC, 1u}, estr[3] = {1u, 1u, 1u};
+        const CUresult r = encode_tiled()(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(x), gdim, gstr, box, estr,
+                                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return tc_fail(TDC_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    }
     {
         std::lock_guard<std::mutex> lk(g_tc_mu);
-        size_t& have = g_tc_smem_set[{device, fn}];
-        if (smem > have) {
-            e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return tc_fail(TDC_ERR_CUDA, "cudaFuncSetAttribute(%zu): %s", smem, cudaGetErrorString(e));
-            have = smem;
+        size_t& have = g_tc_smem_set[{device, L.fn}];
+        if (L.smem > have) {
+            e = cudaFuncSetAttribute(L.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.smem);
+            if (e != cudaSuccess) return tc_fail(TDC_ERR_CUDA, "cudaFuncSetAttribute(%zu): %s", L.smem, cudaGetErrorString(e));
+            have = L.smem;
         }
     }
-    void* args[] = {&a};
-    e = cudaLaunchKernel(fn, dim3((unsigned)ctas), dim3(threads), args, smem, (cudaStream_t)stream);
+    void* args[] = {&a, &tmap};
+    e = cudaLaunchKernel(L.fn, dim3(L.ctas), dim3(L.threads), args, L.smem, (cudaStream_t)stream);
     return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "launch: %s", cudaGetErrorString(e));
 }
+
+#ifdef TDC_TC_PROFILE
+// Measurement build only: the sixteen clock sums of the persistent kernel's roles (see conv_tc_persist.cuh); reset != 0 clears them.
+__attribute__((visibility("default"))) int tdc_tc_profile_read(unsigned long long* out, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, tdc_tc::g_tc_prof, sizeof(unsigned long long) * 16);
+    if (e == cudaSuccess && reset) {
+        unsigned long long z[16] = {};
+        e = cudaMemcpyToSymbol(tdc_tc::g_tc_prof, z, sizeof z);
+    }
+    return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "profile read: %s", cudaGetErrorString(e));
+}
+#endif
 
 int tdc_tc_status(int* out) {
     if (!out) return tc_fail(TDC_ERR_NULL, "out is NULL");

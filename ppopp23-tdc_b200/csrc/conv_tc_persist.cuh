@@ -14,6 +14,21 @@
 //   * two groups of four epilogue warps (12-15, 16-19) take the (position tile, 32-channel chunk)
 //     items of a CTA tile in turn; an accumulator is handed back as soon as all its chunks are in
 //     registers, before the stores.
+//
+// Runs.  The tensor core rounds its running sum at every accumulation, so the error of a tile grows with
+// the number of MMAs that feed one accumulator.  The host may therefore cut the channel blocks of a tile
+// into `nseg` runs: every run starts fresh accumulators, and the epilogue adds the runs to y in fp32 (the
+// thread that stored a partial sum is the one that reads it back).  Long contractions land on small
+// feature maps, where the extra pass over y is cheap.
+//
+// Input loaders (template parameter LD):
+//   0  ring:  global -> 4-byte cp.async -> raw fp32 slots -> registers -> split -> operand layout; a thread
+//             converts the rows it copied, so cp.async.wait_group is all the synchronisation the ring needs;
+//   1  vec:   1x1 filters, 16-byte global loads into registers (TF32 operands only);
+//   2  bulk:  a producer thread (warp 11) issues cp.async.bulk.tensor boxes of 32 pixels x 16 channels of
+//             this GPU's own input into raw slots, completion on an mbarrier per slot; warps 0-7 only convert.
+//             No load instruction is issued per element, which is what bounds loader 0 (fp16 operands,
+//             images of a multiple of 4 pixels, 16-byte aligned input).
 // Every mbarrier wait is bounded; a wait that runs out raises the CTA's abort flag, every
 // role leaves its loop at the next check, the status word is set and tensor memory is freed.
 #pragma once
@@ -25,7 +40,9 @@ namespace tdc_tc {
 #endif
 constexpr int P_GROUPS  = TDC_TC_EPI_GROUPS;          // groups of four epilogue warps
 constexpr int P_THREADS = 384 + 128 * P_GROUPS;     // 8 loader warps, 4 issuer warps (one lane each), the epilogue groups
-constexpr int P_HEADER  = 256;   // bytes of barriers and flags in front of the stages
+constexpr int P_HEADER  = 1024;  // bytes of barriers, flags and the producer's box table in front of the stages
+constexpr int P_MAXBOX  = 64;    // boxes one raw slot may hold (entries of the box table)
+constexpr int LD_RING = 0, LD_VEC = 1, LD_BULK = 2;
 
 // Tile t of the list -> first output position, position tiles it holds (`cnt` <= MT), output-channel block.
 // Tiles of the complete rounds hold MT position tiles; what is left for the last, partial round is spread over
@@ -42,15 +59,73 @@ __device__ __forceinline__ void tile_of(const Args& a, long long t, long long& g
     cnt = left < a.tail_cnt ? (int)left : a.tail_cnt;
 }
 
-template <int NT, int MT, int TAPS, bool VEC>
-__global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a) {
+// Image of padded position g (0 <= g < total_pos).  Position counts fit 32 bits for every layer of practical size, and a
+// 32-bit division is a fifth of the instructions of a 64-bit one: the per-tile index arithmetic of the loaders and
+// the epilogue is made of these.
+__device__ __forceinline__ long long image_of(const Args& a, long long g) {
+    return a.total_pos <= 0x7fffffffLL ? (long long)((unsigned)g / (unsigned)a.Lp) : g / a.Lp;
+}
+
+// The pixels of image b that the patch [gp0, gp0 + rows) of padded positions needs: the run starts at pixel
+// `pix4` (rounded down to a 16-byte boundary, which a bulk-tensor copy must start on) and takes `nbox` boxes
+// of BOXW pixels; nbox = 0 when the patch meets only padding of that image.  Producer and converters call
+// this with the same arguments, so they agree on where every pixel lands in a raw slot.
+__host__ __device__ __forceinline__ void image_run(int H, int W, int Wp, int Lp, long long gp0, int rows, long long b, int& pix4, int& nbox) {
+    const long long img0 = b * Lp;
+    const int ls = gp0 > img0 ? (int)(gp0 - img0) : 0;
+    const int le = gp0 + rows < img0 + Lp ? (int)(gp0 + rows - img0) : Lp;     // local padded positions [ls, le)
+    nbox = 0; pix4 = 0;
+    if (le <= ls) return;
+    int y0 = ls / Wp, x0 = ls - y0 * Wp;
+    if (x0 >= W) { ++y0; x0 = 0; }                                             // starts on the zero column
+    int y1 = (le - 1) / Wp, x1 = (le - 1) - y1 * Wp;
+    if (y1 >= H) { y1 = H - 1; x1 = W - 1; } else if (x1 >= W) x1 = W - 1;      // ends on the zero row / column
+    if (y0 >= H) return;
+    const int ps = y0 * W + x0, pe = y1 * W + x1 + 1;
+    if (pe <= ps) return;
+    pix4 = ps & ~3;
+    nbox = (pe - pix4 + BOXW - 1) / BOXW;
+}
+
+__device__ __forceinline__ void bulk_tensor_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+
+// Measurement build (-DTDC_TC_PROFILE): every role sums the clocks it spends in each kind of wait and in total; one
+// lane per warp adds them to g_tc_prof, which tdc_tc_profile_read hands to the host.  Not compiled otherwise.
+#ifdef TDC_TC_PROFILE
+__device__ unsigned long long g_tc_prof[16];   // [0, 12) kinds of wait or span, [12, 16) role totals
+#define TDC_PROF_DECL long long prof_t[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_start = clock64()
+#define TDC_PROF_WAIT(kind, call) ([&]() { const long long t0_ = clock64(); const bool ok_ = (call); prof_t[kind] += clock64() - t0_; return ok_; }())
+#define TDC_PROF_SPAN_BEGIN const long long span0_ = clock64()
+#define TDC_PROF_SPAN_END(kind) prof_t[kind] += clock64() - span0_
+#define TDC_PROF_FLUSH(role) do { if (lane == 0) { for (int k_ = 0; k_ < 12; ++k_) if (prof_t[k_]) atomicAdd(&g_tc_prof[k_], (unsigned long long)prof_t[k_]); \
+                                  atomicAdd(&g_tc_prof[12 + (role)], (unsigned long long)(clock64() - prof_start)); } } while (0)
+#else
+#define TDC_PROF_DECL
+#define TDC_PROF_WAIT(kind, call) (call)
+#define TDC_PROF_SPAN_BEGIN
+#define TDC_PROF_SPAN_END(kind)
+#define TDC_PROF_FLUSH(role)
+#endif
+
+template <int NT, int MT, int TAPS, int LD, bool F16>
+__global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a, const __grid_constant__ CUtensorMap tmap) {
+    static_assert(LD != LD_VEC || (TAPS == 1 && !F16), "the 16-byte register loader serves 1x1 filters with TF32 operands");
+    static_assert(LD != LD_BULK || (F16 && MT <= 2), "the bulk loader's producer is issuer warp 3, free when MT <= 2");
+    constexpr int CBK = KStep<F16>::CH;                               // channels per block
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint64_t* full_bar   = reinterpret_cast<uint64_t*>(smem_raw);    // [ns]  patch stored + filter landed
     uint64_t* empty_bar  = full_bar + 4;                              // [ns]  MMAs that read the stage are done
     uint64_t* tfull_bar  = empty_bar + 4;                             // [nbuf*MT] the accumulators of a 128-position tile are complete
     uint64_t* tempty_bar = tfull_bar + 8;                             // [nbuf*MT] the epilogue has read them
-    uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(tempty_bar + 8);
+    uint64_t* rfull_bar  = tempty_bar + 8;                            // [depth] bulk loader: the boxes of a raw slot have landed
+    uint64_t* rempty_bar = rfull_bar + 8;                             // [depth] ... and have been converted
+    uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(rempty_bar + 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    unsigned int* max_word = reinterpret_cast<unsigned int*>(tmem_slot + 2);   // block-wide maximum: of |x| at the start, of |y| at the end
+    int2*     box_tab    = reinterpret_cast<int2*>(smem_raw + 512);   // producer only: (first pixel, image) of each box
     float*    stage0     = reinterpret_cast<float*>(smem_raw + P_HEADER);
 
     // patch rows per loader thread: MT x 128 positions, plus two image rows of halo for a 3x3 filter (the host keeps
@@ -70,6 +145,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     if (tid == 0) {
         for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], LOADERS / 32 + 1); mbar_init(&empty_bar[s], MT); }   // one arrival per loader warp + the filter's bytes
         for (int b = 0; b < 8; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4 * (NT / 32)); }   // one per issuer; one per epilogue warp and 32-channel chunk
+        for (int d = 0; d < 8; ++d) { mbar_init(&rfull_bar[d], 1); mbar_init(&rempty_bar[d], LOADERS / 32); }    // the producer's arrive + bytes; one per converting warp
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -81,6 +157,15 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
+    TDC_PROF_DECL;
+    // fp16 operands: the power of two that brings the input just under 2^15, and the factor that undoes it (and the
+    // filter's, applied when it was prepared) in the epilogue
+    float xs = 1.f, inv = 1.f;
+    if constexpr (F16) {
+        xs = range_scale(absmax_of(a.x_absmax, max_word));
+        inv = 1.f / (xs * a.w_scale[0]);
+        if (tid == 0) *max_word = 0;                 // from here on: the largest |y| of this CTA (read after the last barrier)
+    }
 
     if (warp < 8) {
         // ================= loaders =================
@@ -96,7 +181,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 const int s = st_idx;
                 stage_A = stage0 + (long long)s * stage_floats;
                 // use number u of this stage waits for the MMAs of use u-1; the first use passes at once
-                if (!mbar_wait(&empty_bar[s], (uint32_t)(st_use ^ 1))) { *abort_flag = 1; return nullptr; }
+                if (!TDC_PROF_WAIT(0, mbar_wait(&empty_bar[s], (uint32_t)(st_use ^ 1)))) { *abort_flag = 1; return nullptr; }
                 if (tid == 0) {
                     const uint32_t bytes = (uint32_t)(a.nkb - kb < a.kps ? a.nkb - kb : a.kps) * b_bytes;
                     mbar_expect_tx(&full_bar[s], bytes);
@@ -115,14 +200,14 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 if (++st_idx == a.ns) { st_idx = 0; st_use ^= 1; }
             }
         };
-        auto put = [&](float* A, int q, int pp, float c0, float c1, float c2, float c3) {
-            float4 hi;
-            hi.x = to_tf32(c0); hi.y = to_tf32(c1); hi.z = to_tf32(c2); hi.w = to_tf32(c3);
-            *reinterpret_cast<float4*>(A + ((q * a.P + pp) << 2)) = hi;
-            if (a.hl == 2)
-                *reinterpret_cast<float4*>(A + CB * a.P + ((q * a.P + pp) << 2)) = make_float4(c0 - hi.x, c1 - hi.y, c2 - hi.z, c3 - hi.w);
-        };
-        if constexpr (VEC) {
+        if constexpr (LD == LD_VEC) {
+            auto put = [&](float* A, int q, int pp, float c0, float c1, float c2, float c3) {
+                float4 hi;
+                hi.x = to_tf32(c0); hi.y = to_tf32(c1); hi.z = to_tf32(c2); hi.w = to_tf32(c3);
+                *reinterpret_cast<float4*>(A + ((q * a.P + pp) << 2)) = hi;
+                if (a.hl == 2)
+                    *reinterpret_cast<float4*>(A + CB * a.P + ((q * a.P + pp) << 2)) = make_float4(c0 - hi.x, c1 - hi.y, c2 - hi.z, c3 - hi.w);
+            };
             // 1x1 filter, H*W a multiple of 4: a thread owns 4 consecutive positions x 4 channels of a block;
             // four 16-byte loads (one per channel), transposed in registers into four 16-byte stores
             for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x) {
@@ -140,7 +225,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     off[i] = -1;
                     if (quad * 4 < rows) {
                         const long long g = g0 + quad * 4;
-                        if (g < a.total_pos) { const long long b = g / a.Lp; off[i] = b * a.C * HW + (g - b * a.Lp); }
+                        if (g < a.total_pos) { const long long b = image_of(a, g); off[i] = b * a.C * HW + (g - b * a.Lp); }
                     }
                 }
                 float4 va[NI][4], vb[NI][4];
@@ -182,6 +267,75 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 }
                 if (!ok) break;
             }
+        } else if constexpr (LD == LD_BULK) {
+            // The raw slots are filled by the producer (below); these warps wait for a slot, pick their patch rows
+            // out of its boxes, split them and store the operand layout, then hand the slot back.
+            const float* raw0 = stage0 + (long long)a.ns * stage_floats;
+            const int slot_floats = a.nbox_cap * (BOXC * BOXW), depth = a.depth;
+            int r_slot = 0, r_use = 0;
+            for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x) {
+                long long g0;
+                int cnt, ocb;
+                tile_of<MT>(a, t, g0, cnt, ocb);
+                const int rows = cnt * M_TILE + halo_rows;
+                const long long gp0 = g0 - (long long)pad * (a.Wp + 1);
+                const float* wt_tile = a.wt + (long long)ocb * a.nkb * b_floats;
+                // offset of channel 0 of each owned patch row within a raw slot, -1 = a row of zeros
+                int roff[PPT];
+                TDC_PROF_SPAN_BEGIN;
+                {
+                    int g_img[PPT], g_pix[PPT];            // image and pixel of each owned row (-1: padding)
+#pragma unroll
+                    for (int i = 0; i < PPT; ++i) {
+                        const int pp = tid + i * LOADERS;
+                        roff[i] = -1; g_img[i] = -1; g_pix[i] = 0;
+                        const long long g = gp0 + pp;
+                        if (pp < rows && g >= 0 && g < a.total_pos) {
+                            const long long b = image_of(a, g);
+                            const int rem = (int)(g - b * a.Lp);
+                            const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
+                            if (yy < a.H && xx < a.W) { g_img[i] = (int)b; g_pix[i] = yy * a.W + xx; }
+                        }
+                    }
+                    const long long lo = gp0 < 0 ? 0 : gp0, hi = (gp0 + rows < a.total_pos ? gp0 + rows : a.total_pos) - 1;
+                    int box0 = 0;
+                    for (long long b = image_of(a, lo), b_last = image_of(a, hi); b <= b_last; ++b) {
+                        int pix4, nbox;
+                        image_run(a.H, a.W, a.Wp, a.Lp, gp0, rows, b, pix4, nbox);
+#pragma unroll
+                        for (int i = 0; i < PPT; ++i)
+                            if (g_img[i] == (int)b) {
+                                const int d = g_pix[i] - pix4;
+                                roff[i] = (box0 + d / BOXW) * (BOXC * BOXW) + (d & (BOXW - 1));
+                            }
+                        box0 += nbox;
+                    }
+                }
+                TDC_PROF_SPAN_END(6);
+                bool ok = true;
+                for (int kb = 0; kb < a.nkb; ++kb) {
+                    float* A = open_stage(wt_tile, kb);
+                    if (!A || !TDC_PROF_WAIT(1, mbar_wait(&rfull_bar[r_slot], (uint32_t)r_use))) { *abort_flag = 1; ok = false; break; }
+                    const float* R = raw0 + (long long)r_slot * slot_floats;
+                    TDC_PROF_SPAN_BEGIN;
+#pragma unroll
+                    for (int i = 0; i < PPT; ++i) {
+                        const int pp = tid + i * LOADERS;
+                        if (pp < rows) {
+                            float c[CBK];
+#pragma unroll
+                            for (int j = 0; j < CBK; ++j) c[j] = roff[i] >= 0 ? R[roff[i] + j * BOXW] : 0.f;
+                            store_row<F16>(A, a.P, a.hl, pp, c, xs);
+                        }
+                    }
+                    TDC_PROF_SPAN_END(8);
+                    __syncwarp();                                          // every lane has its values in registers
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&rempty_bar[r_slot])) : "memory");
+                    if (++r_slot == depth) { r_slot = 0; r_use ^= 1; }
+                    { TDC_PROF_SPAN_BEGIN; close_stage(kb); TDC_PROF_SPAN_END(9); }
+                }
+                if (!ok) break;
+            }
         } else {
             // The input goes global -> (cp.async, 4 bytes, zero-filled where the patch is padding) -> a ring of
             // raw fp32 slots in shared memory -> registers -> hi/lo split -> operand layout.  A thread copies and
@@ -189,7 +343,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             // `depth` channel blocks ahead and straight across tile boundaries, which keeps enough bytes in
             // flight to cover the memory latency and leaves no cold start at the beginning of a tile.
             float* raw0 = stage0 + (long long)a.ns * stage_floats;
-            const int raw_floats = CB * a.P, depth = a.depth;
+            const int raw_floats = CBK * a.P, depth = a.depth;
             const long long my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
             const long long total = my_tiles * a.nkb;
             long long src_off[PPT];              // of the tile being copied: offset of channel 0 of each owned row, -1 = zeros
@@ -215,7 +369,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                                 rmask[i] = 0; rbase[i] = a.x;
                                 const long long g = g0 + pp;
                                 if (pp < l_rows && g < a.total_pos) {
-                                    const long long b = g / a.Lp;
+                                    const long long b = image_of(a, g);
                                     const int rem = (int)(g - b * a.Lp);
                                     const int oy = rem / a.Wp, ox = rem - oy * a.Wp;
                                     const int iy0 = oy * a.stride - a.gpad, ix0 = ox * a.stride - a.gpad;
@@ -230,7 +384,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                         }
                         const uint32_t dst0 = smem_u32(raw0 + l_slot * raw_floats) + (uint32_t)tid * 4u;
 #pragma unroll
-                        for (int j = 0; j < CB; ++j) {
+                        for (int j = 0; j < CBK; ++j) {
                             const int delta = g_ci * (int)a.HWin + g_dy * a.Win + g_dx;     // the host keeps channels x image below 2^31
                             const int sel = g_ci < g_cin ? ((1 << g_dy) | (0x10000 << g_dx)) : -1;   // -1 never matches a mask
 #pragma unroll
@@ -258,7 +412,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                                 if (pp < l_rows) {
                                     const long long g = gp0 + pp;
                                     if (g >= 0 && g < a.total_pos) {
-                                        const long long b = g / a.Lp;
+                                        const long long b = image_of(a, g);
                                         const int rem = (int)(g - b * a.Lp);
                                         const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
                                         if (yy < a.H && xx < a.W) src_off[i] = b * a.C * a.HWin + (long long)(yy * a.stride) * a.Win + xx * a.stride;
@@ -267,14 +421,14 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                             }
                         }
                         float* R = raw0 + l_slot * raw_floats;
-                        const int c0 = l_kb * CB;
+                        const int c0 = l_kb * CBK;
 #pragma unroll
                         for (int i = 0; i < PPT; ++i) {
                             const int pp = tid + i * LOADERS;
                             if (pp < l_rows) {
                                 const float* src = a.x + (src_off[i] >= 0 ? src_off[i] + (long long)c0 * a.HWin : 0);
 #pragma unroll
-                                for (int j = 0; j < CB; ++j) {
+                                for (int j = 0; j < CBK; ++j) {
                                     const bool real = src_off[i] >= 0 && c0 + j < a.C;
                                     cp_async4(R + j * a.P + pp, real ? src + (long long)j * a.HWin : a.x, real);
                                 }
@@ -301,16 +455,17 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             for (long long ci = 0; ci < total && !*abort_flag; ++ci) {
                 float* A = open_stage(wt_tile, c_kb);
                 if (!A) break;
-                cp_async_wait_pending(depth - 1);                         // block ci has landed (this thread's part)
+                { TDC_PROF_SPAN_BEGIN; cp_async_wait_pending(depth - 1); TDC_PROF_SPAN_END(1); }   // block ci has landed (this thread's part)
                 const float* R = raw0 + c_slot * raw_floats;
                 if (++c_slot == depth) c_slot = 0;
 #pragma unroll
                 for (int i = 0; i < PPT; ++i) {
                     const int pp = tid + i * LOADERS;
                     if (pp < c_rows) {
+                        float c[CBK];
 #pragma unroll
-                        for (int q = 0; q < CB / 4; ++q)
-                            put(A, q, pp, R[(4 * q) * a.P + pp], R[(4 * q + 1) * a.P + pp], R[(4 * q + 2) * a.P + pp], R[(4 * q + 3) * a.P + pp]);
+                        for (int j = 0; j < CBK; ++j) c[j] = R[j * a.P + pp];
+                        store_row<F16>(A, a.P, a.hl, pp, c, xs);
                     }
                 }
                 close_stage(c_kb);
@@ -320,14 +475,59 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             asm volatile("cp.async.wait_all;" ::: "memory");
         }
     }
+    if (warp < 8) TDC_PROF_FLUSH(0);
+    if (warp < 8) {}
+    else if (LD == LD_BULK && warp == 11) {
+        // ================= producer of the bulk loader: one thread =================
+        // Per tile the list of boxes (first pixel, image) is the same for every channel block; a block's boxes go
+        // to one raw slot, whose mbarrier counts their bytes (a box is written whole, padding included).
+        if (lane == 0) {
+            float* raw0 = stage0 + (long long)a.ns * stage_floats;
+            const int slot_floats = a.nbox_cap * (BOXC * BOXW), depth = a.depth;
+            int p_slot = 0, p_use = 0;
+            for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x) {
+                long long g0;
+                int cnt, ocb;
+                tile_of<MT>(a, t, g0, cnt, ocb);
+                const int rows = cnt * M_TILE + halo_rows;
+                const long long gp0 = g0 - (long long)pad * (a.Wp + 1);
+                const long long lo = gp0 < 0 ? 0 : gp0, hi = (gp0 + rows < a.total_pos ? gp0 + rows : a.total_pos) - 1;
+                int nb = 0;
+                for (long long b = image_of(a, lo), b_last = image_of(a, hi); b <= b_last; ++b) {
+                    int pix4, nbox;
+                    image_run(a.H, a.W, a.Wp, a.Lp, gp0, rows, b, pix4, nbox);
+                    for (int k = 0; k < nbox; ++k, ++nb)
+                        if (nb < a.nbox_cap) box_tab[nb] = make_int2(pix4 + k * BOXW, (int)b);
+                }
+                if (nb > a.nbox_cap) { *abort_flag = 1; break; }      // the host sized the slots for fewer boxes: give up rather than drop pixels
+                bool ok = true;
+                for (int kb = 0; kb < a.nkb; ++kb) {
+                    if (!TDC_PROF_WAIT(2, mbar_wait(&rempty_bar[p_slot], (uint32_t)(p_use ^ 1)))) { *abort_flag = 1; ok = false; break; }
+                    float* dst = raw0 + (long long)p_slot * slot_floats;
+                    mbar_expect_tx(&rfull_bar[p_slot], (uint32_t)nb * (uint32_t)(BOXC * BOXW * 4));
+                    for (int i = 0; i < nb; ++i) {
+                        const int2 bx = box_tab[i];
+                        bulk_tensor_3d(dst + i * (BOXC * BOXW), &tmap, bx.x, kb * BOXC, bx.y, &rfull_bar[p_slot]);
+                    }
+                    if (++p_slot == depth) { p_slot = 0; p_use ^= 1; }
+                }
+                if (!ok) break;
+            }
+            // leaving early (another role gave up): no copy of this CTA may still be in flight when it exits, so
+            // wait (bounded) for the last copies issued into every slot; slots never used pass at once
+            if (*abort_flag)
+                for (int d = 0; d < depth; ++d) mbar_wait(&rfull_bar[d], (uint32_t)(d < p_slot ? p_use : p_use ^ 1));
+            TDC_PROF_FLUSH(1);
+        }
+        __syncwarp();
+    }
     else if (warp < 12) {
         // ================= MMA issuers: warp 8+mt owns position tile mt =================
         const int mt = __shfl_sync(0xffffffffu, warp - 8, 0);
         if (mt < MT) {
-            long long j = 0;                    // tiles done by this CTA
+            long long j = 0;                    // accumulator hand-overs so far: one per tile and run
             int st_idx = 0, st_use = 0;         // stage to consume next, parity of its use count
-            for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x, ++j) {
-                const int slot = (int)(j % nbuf) * MT + mt;
+            for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x) {
                 long long g0_unused;
                 int cnt, ocb_unused;
                 tile_of<MT>(a, t, g0_unused, cnt, ocb_unused);
@@ -341,31 +541,39 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                         if (++st_idx == a.ns) { st_idx = 0; st_use ^= 1; }
                     }
                     if (!fine) { *abort_flag = 1; break; }
+                    j += a.nseg;
                     continue;
                 }
-                // the epilogue must have emptied this accumulator slot (its previous use); the first use passes at once
-                if (!mbar_wait(&tempty_bar[slot], (uint32_t)(((j / nbuf) & 1) ^ 1))) { *abort_flag = 1; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t d_main = tmem + (uint32_t)(slot * a.tile_cols);
                 bool ok = true;
-                for (int kb0 = 0; kb0 < a.nkb; kb0 += a.kps) {
-                    const int s = st_idx;
-                    if (!mbar_wait(&full_bar[s], (uint32_t)st_use)) { *abort_flag = 1; ok = false; break; }
-                    if (++st_idx == a.ns) { st_idx = 0; st_use ^= 1; }
+                for (int seg = 0; seg < a.nseg && ok; ++seg, ++j) {
+                    const int slot = (int)(j % nbuf) * MT + mt;
+                    const int kb_lo = seg * a.seg_blocks, kb_hi = kb_lo + a.seg_blocks < a.nkb ? kb_lo + a.seg_blocks : a.nkb;
+                    // the epilogue must have emptied this accumulator slot (its previous use); the first use passes at once
+                    if (!TDC_PROF_WAIT(3, mbar_wait(&tempty_bar[slot], (uint32_t)(((j / nbuf) & 1) ^ 1)))) { *abort_flag = 1; ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const float* A = stage0 + (long long)s * stage_floats;
-                    const int kend = kb0 + a.kps < a.nkb ? kb0 + a.kps : a.nkb;
-                    if (elect_one()) {
-                        for (int kb = kb0; kb < kend; ++kb)
-                            issue_block<NT, TAPS>(a, d_main, smem_u32(A + (kb - kb0) * a_floats), smem_u32(A + a.kps * a_floats + (kb - kb0) * b_floats),
-                                                  (uint32_t)(mt * M_TILE), kb & 1, kb < 2 && (kb == 0 || a.nmain == 2));
-                        mma_commit(&empty_bar[s]);                        // the stage may be refilled when these MMAs are done
-                        if (kend == a.nkb) mma_commit(&tfull_bar[slot]);  // and this position tile's accumulators are complete
+                    const uint32_t d_main = tmem + (uint32_t)(slot * a.tile_cols);
+                    for (int kb0 = kb_lo; kb0 < kb_hi; kb0 += a.kps) {
+                        const int s = st_idx;
+                        if (!TDC_PROF_WAIT(4, mbar_wait(&full_bar[s], (uint32_t)st_use))) { *abort_flag = 1; ok = false; break; }
+                        if (++st_idx == a.ns) { st_idx = 0; st_use ^= 1; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const float* A = stage0 + (long long)s * stage_floats;
+                        const int kend = kb0 + a.kps < kb_hi ? kb0 + a.kps : kb_hi;
+                        if (elect_one()) {
+                            for (int kb = kb0; kb < kend; ++kb) {
+                                const int kr = kb - kb_lo;                    // block of this run
+                                issue_block<NT, TAPS, F16>(a, d_main, smem_u32(A + (kb - kb0) * a_floats), smem_u32(A + a.kps * a_floats + (kb - kb0) * b_floats),
+                                                           (uint32_t)(mt * M_TILE), kr & 1, kr < 2 && (kr == 0 || a.nmain == 2));
+                            }
+                            mma_commit(&empty_bar[s]);                        // the stage may be refilled when these MMAs are done
+                            if (kend == kb_hi) mma_commit(&tfull_bar[slot]);  // and this run's accumulators are complete
+                        }
+                        __syncwarp();
                     }
-                    __syncwarp();
                 }
                 if (!ok) break;
             }
+            TDC_PROF_FLUSH(2);
         }
     } else {
         // ================= epilogue: P_GROUPS groups of four warps (one lane quarter of tensor memory per warp).
@@ -376,44 +584,61 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
         const int q = warp & 3;
         constexpr int CHUNKS = NT / 32;
         long long j = 0;
-        for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x, ++j) {
+        float ymax = 0.f;                       // largest magnitude this thread stored (kept only when the caller asked for it)
+        float* const track = a.y_absmax ? &ymax : nullptr;
+        for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x) {
             long long g0;
             int cnt, ocb;
             tile_of<MT>(a, t, g0, cnt, ocb);
             bool ok = true;
+            for (int seg = 0; seg < a.nseg && ok; ++seg, ++j) {
+                const int kb_lo = seg * a.seg_blocks, blocks = (kb_lo + a.seg_blocks < a.nkb ? kb_lo + a.seg_blocks : a.nkb) - kb_lo;
 #pragma unroll 1
-            for (int item = grp; item < cnt * CHUNKS && ok; item += P_GROUPS) {
-                const int mt = item / CHUNKS, chunk = item - mt * CHUNKS;
-                // the position tiles of a CTA tile are handed over one by one: while this one is drained, the
-                // issuers of the others still run, and its own issuer may start on the next CTA tile
-                const int slot = (int)(j % nbuf) * MT + mt;
-                if (!mbar_wait(&tfull_bar[slot], (uint32_t)((j / nbuf) & 1))) { *abort_flag = 1; ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const long long g = g0 + mt * M_TILE + q * 32 + lane;
-                long long out_off = -1;
-                if (g < a.total_pos) {
-                    const long long b = g / a.Lp;
-                    const int rem = (int)(g - b * a.Lp);
-                    const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
-                    if (yy < a.H && xx < a.W) out_off = b * a.K * HW + (long long)yy * a.W + xx;
+                for (int item = grp; item < cnt * CHUNKS && ok; item += P_GROUPS) {
+                    const int mt = item / CHUNKS, chunk = item - mt * CHUNKS;
+                    // the position tiles of a CTA tile are handed over one by one: while this one is drained, the
+                    // issuers of the others still run, and its own issuer may start on the next run or CTA tile
+                    const int slot = (int)(j % nbuf) * MT + mt;
+                    if (!TDC_PROF_WAIT(5, mbar_wait(&tfull_bar[slot], (uint32_t)((j / nbuf) & 1)))) { *abort_flag = 1; ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const long long g = g0 + mt * M_TILE + q * 32 + lane;
+                    long long out_off = -1;
+                    if (g < a.total_pos) {
+                        const long long b = image_of(a, g);
+                        const int rem = (int)(g - b * a.Lp);
+                        const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
+                        if (yy < a.H && xx < a.W) out_off = b * a.K * HW + (long long)yy * a.W + xx;
+                    }
+                    uint32_t r[32];
+                    load_chunk<NT, F16>(a, tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * a.tile_cols + chunk * 32), r, blocks, inv);
+                    // this chunk of the slot is in registers: one arrival per warp and chunk hands the slot back when
+                    // all of its chunks have been read, before the stores
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tempty_bar[slot])) : "memory");
+                    { TDC_PROF_SPAN_BEGIN;
+                      store_chunk(a, r, out_off, ocb * NT + chunk * 32, HW, seg > 0, seg == a.nseg - 1, seg == a.nseg - 1 ? track : nullptr);
+                      TDC_PROF_SPAN_END(7); }
                 }
-                uint32_t r[32];
-                load_chunk<NT>(a, tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * a.tile_cols + chunk * 32), r);
-                // this chunk of the slot is in registers: one arrival per warp and chunk hands the slot back when
-                // all of its chunks have been read, before the stores
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tempty_bar[slot])) : "memory");
-                store_chunk(a, r, out_off, ocb * NT + chunk * 32, HW);
             }
             if (!ok) break;
         }
+        if (track) {
+            const unsigned int m = __reduce_max_sync(0xffffffffu, __float_as_uint(ymax));
+            if (lane == 0) atomicMax(max_word, m);
+        }
+        TDC_PROF_FLUSH(3);
     }
 
     __syncwarp();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (*abort_flag && tid == 0 && a.status) atomicCAS(a.status, 0, 1);
+    if (a.y_absmax) {                           // entry = CTA; CTA 0 clears the entries no CTA owns
+        if (tid == 0) a.y_absmax[blockIdx.x] = __uint_as_float(*max_word);
+        if (blockIdx.x == 0)
+            for (int i = gridDim.x + tid; i < ABSMAX_SLOTS; i += P_THREADS) a.y_absmax[i] = 0.f;
+    }
     if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)a.tmem_cols) : "memory");
 }
 

@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <vector>
 #include "../../include/tdc_b200.h"
+#include "errors.h"
 
 struct tdc_conv {
     int b, c, h, w, n, pad, r, s, stride, ho, wo;
@@ -18,6 +19,8 @@ struct tdc_conv {
     tdc_tc_plan plan{};
     void* tc_weights = nullptr;
     float* kcrs = nullptr;      // the filter as given, kept for tdc_conv_set_precision
+    cudaStream_t side[2] = {nullptr, nullptr};      // tdc_conv_forward_host_async: the chunks of a batch alternate between them
+    cudaEvent_t side_done[2] = {nullptr, nullptr}, start = nullptr;
 };
 
 struct tdc_tkconv {
@@ -30,11 +33,9 @@ struct tdc_tkconv {
 
 namespace {
 
-// Sets the library's error text through a failing call of its own (keeps one writer).
-int cuda_fail(const char* what, cudaError_t e) {
-    fprintf(stderr, "tdc_b200: %s: %s\n", what, cudaGetErrorString(e));
-    return TDC_ERR_CUDA;
-}
+using tdc::fail;
+
+int cuda_fail(const char* what, cudaError_t e) { return fail(TDC_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e)); }
 
 int upload(float** dst, const float* host, size_t n, float fill_if_null) {
     cudaError_t e = cudaMalloc((void**)dst, n * sizeof(float));
@@ -55,20 +56,28 @@ void tdc_conv_destroy(tdc_conv* l) {
     if (!l) return;
     cudaFree(l->kernel); cudaFree(l->bias); cudaFree(l->output); cudaFree(l->staging_in);
     cudaFree(l->tc_weights); cudaFree(l->kcrs);
+    for (int i = 0; i < 2; ++i) {
+        if (l->side[i]) cudaStreamDestroy(l->side[i]);
+        if (l->side_done[i]) cudaEventDestroy(l->side_done[i]);
+    }
+    if (l->start) cudaEventDestroy(l->start);
     delete l;
 }
 
 int tdc_conv_set_precision(tdc_conv* l, int mode) {
-    if (!l) return TDC_ERR_NULL;
+    if (!l) return fail(TDC_ERR_NULL, "tdc_conv_set_precision: layer is NULL");
     if (mode == 0) { l->tc_mode = 0; return TDC_OK; }
-    if (l->stride != 1 || l->r != l->s || l->pad != (l->r - 1) / 2) return TDC_ERR_UNSUPPORTED;
+    if (l->stride != 1 || l->r != l->s || (l->r != 1 && l->r != 3) || l->pad != (l->r - 1) / 2)
+        return fail(TDC_ERR_UNSUPPORTED, "tdc_conv_set_precision: the tensor-core path of a layer object takes 1x1 and 3x3 filters, "
+                                         "stride 1, padding (R-1)/2; this layer is %dx%d stride %d padding %d", l->r, l->s, l->stride, l->pad);
     tdc_tc_plan p;
     // the layer's shape is fixed, so the output-channel block size that suits its position count is known here
-    int sms = 148, device = 0;
-    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    tdc_devinfo dev;
+    int rc = tdc_query_device(-1, &dev);
+    if (rc) return rc;
     const int halo = (l->r - 1) / 2;
-    const int nt = tdc_tc_pick_nt(l->n, mode, (long long)l->b * (l->h + halo) * (l->w + halo), sms);
-    int rc = tdc_tc_plan_make_nt(l->c, l->n, l->r, l->s, mode, 0, nt, &p);
+    const int nt = tdc_tc_pick_nt(l->n, mode, (long long)l->b * (l->h + halo) * (l->w + halo), dev.sm_count);
+    rc = tdc_tc_plan_make_nt(l->c, l->n, l->r, l->s, mode, 0, nt, &p);
     if (rc) return rc;
     void* wt = nullptr;
     cudaError_t e = cudaMalloc(&wt, p.weights_bytes);
@@ -83,11 +92,11 @@ int tdc_conv_set_precision(tdc_conv* l, int mode) {
 
 int tdc_conv_create(tdc_conv** out, int b, int c, int h, int w, int n, int pad, int r, int s, int stride,
                     const float* host_w_kcrs, const float* host_bias) {
-    if (!out) return TDC_ERR_NULL;
+    if (!out) return fail(TDC_ERR_NULL, "tdc_conv_create: out is NULL");
     *out = nullptr;
     if (b <= 0 || c <= 0 || h <= 0 || w <= 0 || n <= 0 || r <= 0 || s <= 0 || stride <= 0 || pad < 0 ||
         h + 2 * pad < r || w + 2 * pad < s)
-        return TDC_ERR_SHAPE;
+        return fail(TDC_ERR_SHAPE, "tdc_conv_create: b=%d c=%d h=%d w=%d n=%d filter %dx%d pad=%d stride=%d", b, c, h, w, n, r, s, pad, stride);
     tdc_conv* l = new tdc_conv;
     l->b = b; l->c = c; l->h = h; l->w = w; l->n = n; l->pad = pad; l->r = r; l->s = s; l->stride = stride;
     l->ho = (h + 2 * pad - r) / stride + 1;
@@ -112,40 +121,74 @@ int tdc_conv_create(tdc_conv** out, int b, int c, int h, int w, int n, int pad, 
 }
 
 int tdc_conv_set_tile(tdc_conv* l, const tdc_tile* tile) {
-    if (!l) return TDC_ERR_NULL;
+    if (!l) return fail(TDC_ERR_NULL, "tdc_conv_set_tile: layer is NULL");
     l->has_tile = tile != nullptr;
     if (tile) l->tile = *tile;
     return TDC_OK;
 }
 
-int tdc_conv_forward(tdc_conv* l, const float* dev_in, float** dev_out, void* stream) {
-    if (!l || !dev_in || !dev_out) return TDC_ERR_NULL;
-    int rc;
+// Images [b0, b0 + nb) of the layer's batch: dev_in and the layer's output buffer are addressed at image b0.
+static int conv_forward_images(tdc_conv* l, const float* dev_in, int b0, int nb, void* stream) {
+    const float* x = dev_in + (size_t)b0 * l->c * l->h * l->w;
+    float* y = l->output + (size_t)b0 * l->n * l->ho * l->wo;
     if (l->tc_mode) {
         tdc_epilogue e{nullptr, l->bias, nullptr, 0};
-        rc = tdc_conv2d_tc(&l->plan, dev_in, l->tc_weights, l->output, l->b, l->h, l->w, &e, 0, stream);
-    } else {
-        rc = tdc_conv2d_f32(dev_in, l->kernel, l->bias, l->output, l->b, l->c, l->h, l->w, l->n, l->r, l->s, l->pad,
-                            l->stride, TDC_W_CRSK, TDC_EPI_NONE, l->has_tile ? &l->tile : nullptr, stream);
+        return tdc_conv2d_tc(&l->plan, x, l->tc_weights, y, nb, l->h, l->w, &e, 0, stream);
     }
+    return tdc_conv2d_f32(x, l->kernel, l->bias, y, nb, l->c, l->h, l->w, l->n, l->r, l->s, l->pad, l->stride, TDC_W_CRSK,
+                          TDC_EPI_NONE, (l->has_tile && nb == l->b) ? &l->tile : nullptr, stream);
+}
+
+int tdc_conv_forward(tdc_conv* l, const float* dev_in, float** dev_out, void* stream) {
+    if (!l || !dev_in || !dev_out) return fail(TDC_ERR_NULL, "tdc_conv_forward: layer, dev_in and dev_out must be non-NULL");
+    int rc = conv_forward_images(l, dev_in, 0, l->b, stream);
     if (rc) return rc;
     *dev_out = l->output;
     return TDC_OK;
 }
 
 int tdc_conv_forward_host_async(tdc_conv* l, const float* host_in, float* host_out, void* stream) {
-    if (!l || !host_in || !host_out) return TDC_ERR_NULL;
-    size_t in_bytes = (size_t)l->b * l->c * l->h * l->w * sizeof(float);
+    if (!l || !host_in || !host_out) return fail(TDC_ERR_NULL, "tdc_conv_forward_host_async: layer, host_in and host_out must be non-NULL");
+    const size_t in_img = (size_t)l->c * l->h * l->w, out_img = (size_t)l->n * l->ho * l->wo;
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
-    if (!l->staging_in && (e = cudaMalloc((void**)&l->staging_in, in_bytes)) != cudaSuccess) return cuda_fail("cudaMalloc", e);
-    if ((e = cudaMemcpyAsync(l->staging_in, host_in, in_bytes, cudaMemcpyHostToDevice, st)) != cudaSuccess)
-        return cuda_fail("copy in", e);
-    float* o;
-    int rc = tdc_conv_forward(l, l->staging_in, &o, stream);
-    if (rc) return rc;
-    e = cudaMemcpyAsync(host_out, o, (size_t)l->b * l->n * l->ho * l->wo * sizeof(float), cudaMemcpyDeviceToHost, st);
-    return e == cudaSuccess ? TDC_OK : cuda_fail("copy out", e);
+    if (!l->staging_in && (e = cudaMalloc((void**)&l->staging_in, l->b * in_img * sizeof(float))) != cudaSuccess) return cuda_fail("cudaMalloc", e);
+    // A batch of several images goes through in chunks on two streams of the layer's own, so that the copy in of one
+    // chunk, the kernel of another and the copy out of a third overlap; the caller's stream orders the whole
+    // (work queued on it before this call precedes the first copy, work queued after it follows the last).
+    const int chunks = (l->b >= 8 && l->b * (in_img + out_img) * sizeof(float) >= (4u << 20)) ? 4 : 1;
+    if (chunks == 1) {
+        if ((e = cudaMemcpyAsync(l->staging_in, host_in, l->b * in_img * sizeof(float), cudaMemcpyHostToDevice, st)) != cudaSuccess)
+            return cuda_fail("copy in", e);
+        int rc = conv_forward_images(l, l->staging_in, 0, l->b, stream);
+        if (rc) return rc;
+        e = cudaMemcpyAsync(host_out, l->output, l->b * out_img * sizeof(float), cudaMemcpyDeviceToHost, st);
+        return e == cudaSuccess ? TDC_OK : cuda_fail("copy out", e);
+    }
+    if (!l->side[0]) {
+        for (int i = 0; i < 2; ++i)
+            if ((e = cudaStreamCreateWithFlags(&l->side[i], cudaStreamNonBlocking)) != cudaSuccess ||
+                (e = cudaEventCreateWithFlags(&l->side_done[i], cudaEventDisableTiming)) != cudaSuccess)
+                return cuda_fail("side stream", e);
+        if ((e = cudaEventCreateWithFlags(&l->start, cudaEventDisableTiming)) != cudaSuccess) return cuda_fail("event", e);
+    }
+    if ((e = cudaEventRecord(l->start, st)) != cudaSuccess) return cuda_fail("event record", e);
+    for (int i = 0; i < 2; ++i)
+        if ((e = cudaStreamWaitEvent(l->side[i], l->start, 0)) != cudaSuccess) return cuda_fail("stream wait", e);
+    for (int k = 0; k < chunks; ++k) {
+        const int b0 = (int)((long long)l->b * k / chunks), nb = (int)((long long)l->b * (k + 1) / chunks) - b0;
+        cudaStream_t s = l->side[k & 1];
+        if ((e = cudaMemcpyAsync(l->staging_in + b0 * in_img, host_in + b0 * in_img, nb * in_img * sizeof(float), cudaMemcpyHostToDevice, s)) != cudaSuccess)
+            return cuda_fail("copy in", e);
+        int rc = conv_forward_images(l, l->staging_in, b0, nb, s);
+        if (rc) return rc;
+        if ((e = cudaMemcpyAsync(host_out + b0 * out_img, l->output + b0 * out_img, nb * out_img * sizeof(float), cudaMemcpyDeviceToHost, s)) != cudaSuccess)
+            return cuda_fail("copy out", e);
+    }
+    for (int i = 0; i < 2; ++i)
+        if ((e = cudaEventRecord(l->side_done[i], l->side[i])) != cudaSuccess || (e = cudaStreamWaitEvent(st, l->side_done[i], 0)) != cudaSuccess)
+            return cuda_fail("join", e);
+    return TDC_OK;
 }
 
 int tdc_conv_forward_host(tdc_conv* l, const float* host_in, float* host_out) {
@@ -165,11 +208,12 @@ void tdc_tkconv_destroy(tdc_tkconv* l) {
 int tdc_tkconv_create(tdc_tkconv** out, int b, int C, int N1, int N2, int N3, int h, int w, int r, int s, int pad,
                       int stride, const float* host_w1, const float* host_wcore_kcrs, const float* host_w3,
                       const float* host_bias) {
-    if (!out) return TDC_ERR_NULL;
+    if (!out) return fail(TDC_ERR_NULL, "tdc_tkconv_create: out is NULL");
     *out = nullptr;
     if (b <= 0 || C <= 0 || N1 <= 0 || N2 <= 0 || N3 <= 0 || h <= 0 || w <= 0 || r <= 0 || s <= 0 || stride <= 0 ||
         pad < 0 || h + 2 * pad < r || w + 2 * pad < s)
-        return TDC_ERR_SHAPE;
+        return fail(TDC_ERR_SHAPE, "tdc_tkconv_create: b=%d C=%d N1=%d N2=%d N3=%d h=%d w=%d filter %dx%d pad=%d stride=%d", b, C, N1, N2,
+                    N3, h, w, r, s, pad, stride);
     tdc_tkconv* l = new tdc_tkconv;
     l->b = b; l->C = C; l->N1 = N1; l->N2 = N2; l->N3 = N3; l->h = h; l->w = w; l->r = r; l->s = s;
     l->pad = pad; l->stride = stride;
@@ -199,7 +243,7 @@ int tdc_tkconv_create(tdc_tkconv** out, int b, int C, int N1, int N2, int N3, in
 }
 
 int tdc_tkconv_forward(tdc_tkconv* l, const float* dev_in, float** dev_out, void* stream) {
-    if (!l || !dev_in || !dev_out) return TDC_ERR_NULL;
+    if (!l || !dev_in || !dev_out) return fail(TDC_ERR_NULL, "tdc_tkconv_forward: layer, dev_in and dev_out must be non-NULL");
     int rc = tdc_tk_block_f32(dev_in, l->w1, l->wcore, l->w3, l->bias, l->output, l->b, l->C, l->h, l->w, l->N1,
                               l->N2, l->N3, l->r, l->s, l->pad, l->stride, TDC_W_CRSK, TDC_EPI_NONE, nullptr, l->workspace,
                               l->workspace_bytes, stream);
@@ -209,7 +253,7 @@ int tdc_tkconv_forward(tdc_tkconv* l, const float* dev_in, float** dev_out, void
 }
 
 int tdc_tkconv_forward_host(tdc_tkconv* l, const float* host_in, float* host_out) {
-    if (!l || !host_in || !host_out) return TDC_ERR_NULL;
+    if (!l || !host_in || !host_out) return fail(TDC_ERR_NULL, "tdc_tkconv_forward_host: layer, host_in and host_out must be non-NULL");
     size_t in_bytes = (size_t)l->b * l->C * l->h * l->w * sizeof(float);
     cudaError_t e;
     if (!l->staging_in && (e = cudaMalloc((void**)&l->staging_in, in_bytes)) != cudaSuccess) return cuda_fail("cudaMalloc", e);

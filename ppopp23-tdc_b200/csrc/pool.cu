@@ -6,6 +6,7 @@
 #include <float.h>
 #include <stdint.h>
 #include "../../include/tdc_b200.h"
+#include "errors.h"
 
 namespace {
 
@@ -81,11 +82,16 @@ __global__ void maxpool_2x2s2_kernel(const float* __restrict__ x, float* __restr
 
 extern "C" int tdc_pool2d_f32(const float* x, float* y, int B, int C, int H, int W, int window_h, int window_w, int pad,
                               int stride, int mode, void* stream) {
-    if (!x || !y) return TDC_ERR_NULL;
-    if (B <= 0 || C <= 0 || H <= 0 || W <= 0 || window_h <= 0 || window_w <= 0 || pad < 0 || stride <= 0) return TDC_ERR_SHAPE;
-    if (mode != TDC_POOL_MAX && mode != TDC_POOL_AVG_INCLUDE_PAD && mode != TDC_POOL_AVG_EXCLUDE_PAD) return TDC_ERR_UNSUPPORTED;
-    if (2 * pad > window_h || 2 * pad > window_w) return TDC_ERR_SHAPE;          // every window must hold at least one real element
-    if (H + 2 * pad < window_h || W + 2 * pad < window_w) return TDC_ERR_SHAPE;
+    using tdc::fail;
+    if (!x || !y) return fail(TDC_ERR_NULL, "tdc_pool2d_f32: x and y must be non-NULL");
+    if (B <= 0 || C <= 0 || H <= 0 || W <= 0 || window_h <= 0 || window_w <= 0 || pad < 0 || stride <= 0)
+        return fail(TDC_ERR_SHAPE, "tdc_pool2d_f32: B=%d C=%d H=%d W=%d window %dx%d pad=%d stride=%d", B, C, H, W, window_h, window_w, pad, stride);
+    if (mode != TDC_POOL_MAX && mode != TDC_POOL_AVG_INCLUDE_PAD && mode != TDC_POOL_AVG_EXCLUDE_PAD)
+        return fail(TDC_ERR_UNSUPPORTED, "tdc_pool2d_f32: mode %d", mode);
+    if (2 * pad > window_h || 2 * pad > window_w)          // every window must hold at least one real element
+        return fail(TDC_ERR_SHAPE, "tdc_pool2d_f32: padding %d leaves windows of %dx%d with no real element", pad, window_h, window_w);
+    if (H + 2 * pad < window_h || W + 2 * pad < window_w)
+        return fail(TDC_ERR_SHAPE, "tdc_pool2d_f32: window %dx%d larger than the padded %dx%d image", window_h, window_w, H, W);
     const int Ho = (H - window_h + 2 * pad) / stride + 1, Wo = (W - window_w + 2 * pad) / stride + 1;
     const long long planes = (long long)B * C;
     cudaStream_t st = (cudaStream_t)stream;
@@ -100,5 +106,6 @@ extern "C" int tdc_pool2d_f32(const float* x, float* y, int B, int C, int H, int
     if (fast) maxpool_3x3s2_kernel<<<(unsigned)blocks, threads, 0, st>>>(x, y, planes, H, W, Ho, Wo);
     else if (fast2) maxpool_2x2s2_kernel<<<(unsigned)blocks, threads, 0, st>>>(x, y, planes, H, W, Ho, Wo);
     else pool_generic_kernel<<<(unsigned)blocks, threads, 0, st>>>(x, y, planes, H, W, Ho, Wo, window_h, window_w, pad, stride, mode);
-    return cudaGetLastError() == cudaSuccess ? TDC_OK : TDC_ERR_CUDA;
+    const cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? TDC_OK : fail(TDC_ERR_CUDA, "tdc_pool2d_f32 launch: %s", cudaGetErrorString(e));
 }

@@ -5,7 +5,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libtdc_b200.so")
+# TDC_B200_LIB names another build of the same library (a measurement build, say); the default is the one build.py makes
+LIB_PATH = os.environ.get("TDC_B200_LIB") or os.path.join(_HERE, "libtdc_b200.so")
 
 OK, ERR_NULL, ERR_SHAPE, ERR_UNSUPPORTED, ERR_TILE, ERR_SMEM, ERR_CUDA, ERR_WORKSPACE, ERR_NO_DEVICE = range(9)
 W_KCRS, W_CRSK = 0, 1
@@ -73,6 +74,7 @@ _PROTOTYPES = {
     "tdc_tc_plan_make_nt": (_i, [_i] * 7 + [C.POINTER(TcPlan)]),
     "tdc_tc_prepare_weights": (_i, [C.POINTER(TcPlan), _p, _i, _p, _p]),
     "tdc_conv2d_tc": (_i, [C.POINTER(TcPlan), _p, _p, _p, _i, _i, _i, C.POINTER(Epilogue), _i, _p]),
+    "tdc_conv2d_tc_ranged": (_i, [C.POINTER(TcPlan), _p, _p, _p, _i, _i, _i, C.POINTER(Epilogue), _i, _p, _p, _p]),
     "tdc_tc_status": (_i, [C.POINTER(_i)]),
     "tdc_select_tile": (_i, [_i] * 9 + [C.POINTER(DevInfo), C.POINTER(Tile)]),
     "tdc_tile_info": (_i, [_i] * 9 + [C.POINTER(Tile), C.POINTER(LaunchInfo)]),

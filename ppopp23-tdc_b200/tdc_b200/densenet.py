@@ -195,7 +195,7 @@ class TKDenseNet(nn.Module):
     def set_precision(self, precision):
         """"fp32": every conv on the fp32 FMA kernels; "auto": large layers on tensor cores with split operands
         (fp32-level results); "tf32x3" / "tf32": every conv with a tensor-core plan on tensor cores."""
-        if precision not in ("fp32", "auto", "tf32x3", "tf32"):
+        if precision not in ("fp32", "auto", "fp16x3", "tf32x3", "tf32"):
             raise ValueError("precision %r" % (precision,))
         self.precision = precision
         for m in self.modules():

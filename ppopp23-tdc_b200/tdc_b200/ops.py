@@ -164,6 +164,9 @@ def pool2d(x, kernel_size, stride=None, padding=0, mode=POOL_MAX, out=None):
         code = lib.tdc_pool2d_f32(_dev_f32(x, "x"), _dev_f32(out, "out"), B, Cc, H, W, kh, kw, padding, stride, mode, _stream())
     if code != _lib.OK:
         raise TdcError(code, "tdc_pool2d_f32: window %dx%d stride %d padding %d on %dx%d" % (kh, kw, stride, padding, H, W))
+    bound = getattr(x, "_tdc_absmax", None)
+    if bound is not None:      # no pooling mode raises the largest magnitude: the input's bound holds for the output
+        out._tdc_absmax = bound
     return out
 
 

@@ -206,7 +206,7 @@ class TKResNet(nn.Module):
         """"fp32" (default): every conv on the fp32 FMA kernels; "auto": large layers on tensor cores
         with split operands (fp32-level results), small ones on the fp32 kernels; "tf32x3" / "tf32":
         every stride-1 1x1 / 3x3 conv on tensor cores."""
-        if precision not in ("fp32", "auto", "tf32x3", "tf32"):
+        if precision not in ("fp32", "auto", "fp16x3", "tf32x3", "tf32"):
             raise ValueError("precision %r" % (precision,))
         self.precision = precision
         for m in self.modules():

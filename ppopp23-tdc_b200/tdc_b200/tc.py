@@ -1,8 +1,11 @@
-"""Tensor-core variant of the core convolution (tcgen05, TF32 operands) — host side.
+"""Tensor-core variant of the core convolution (tcgen05, TF32 or fp16 operands) — host side.
 
 `TcConv` holds what the C ABI needs per layer: the plan (tdc_tc_plan_make) and the filter
-pre-arranged for the kernel (tdc_tc_prepare_weights).  mode 3 ("3xTF32") gives fp32-level
-results; mode 1 is plain TF32.  The default plan serves "same" convolutions with 1x1 or 3x3 filters
+pre-arranged for the kernel (tdc_tc_prepare_weights).  mode 3 ("3xTF32") and mode 4 ("3xFP16")
+give fp32-level results; mode 1 is plain TF32.  Mode 4 scales its input into fp16's range and needs
+the input's largest magnitude for that: every mode-4 output carries the partial maxima of its own
+magnitudes as the attribute `_tdc_absmax`, and a mode-4 call whose input carries one skips the pass
+over the input that would otherwise find it (the three steps of a Tucker conv chain this way).  The default plan serves "same" convolutions with 1x1 or 3x3 filters
 and stride 1 (1x1 filters also strided) and reads the input once; `general=True` makes the plan that
 takes any filter size, stride and padding by gathering (channel, row, column) triples.
 """
@@ -13,6 +16,9 @@ import torch
 from . import _lib
 from ._lib import TcPlan, TdcError, lib
 from .ops import _dev_f32, _epilogue, _on_device, _stream
+
+
+ABSMAX_FLOATS = 1024      # TDC_TC_ABSMAX_FLOATS
 
 
 def _check(code):
@@ -80,9 +86,18 @@ class TcConv:
         e = _epilogue(scale, bias, residual, relu)
         halo = 0 if self.general else (self.R - 1) // 2
         plan, wt = self._for_positions(B * (Ho + halo) * (Wo + halo))
+        if self.mode != 4:
+            with _on_device(x.device):
+                _check(lib.tdc_conv2d_tc(C.byref(plan), _dev_f32(x, "x"), wt.data_ptr(), _dev_f32(out, "out"),
+                                         B, H, W, C.byref(e), flags, _stream()))
+            return out
+        xmax = getattr(x, "_tdc_absmax", None)
+        ymax = torch.empty(ABSMAX_FLOATS, device=x.device, dtype=torch.float32)
         with _on_device(x.device):
-            _check(lib.tdc_conv2d_tc(C.byref(plan), _dev_f32(x, "x"), wt.data_ptr(), _dev_f32(out, "out"),
-                                     B, H, W, C.byref(e), flags, _stream()))
+            _check(lib.tdc_conv2d_tc_ranged(C.byref(plan), _dev_f32(x, "x"), wt.data_ptr(), _dev_f32(out, "out"),
+                                            B, H, W, C.byref(e), flags, xmax.data_ptr() if xmax is not None else None,
+                                            ymax.data_ptr(), _stream()))
+        out._tdc_absmax = ymax
         return out
 
 

@@ -24,9 +24,10 @@ _SHARED_WS = {}     # device -> uint8 tensor
 
 class TKConv2dC_B200(nn.Module):
     # "fp32": the fp32 FMA kernels (bit-reproducible, summation order documented);
-    # "tf32x3": tensor cores with split operands, fp32-level results (1e-5 bar);
+    # "fp16x3" / "tf32x3": tensor cores with operands split into two fp16 / TF32 parts, fp32-level results (1e-5 bar;
+    #     fp16 parts need |x| and |w| within fp16's range of 65504);
     # "tf32": tensor cores, plain TF32 (5e-3 bar);
-    # "auto": tf32x3 where the layer is large enough to fill the GPU, fp32 otherwise.
+    # "auto": split operands where the layer is large enough to fill the GPU, fp32 otherwise.
     precision = "fp32"
 
     def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1,

@@ -9,6 +9,10 @@ for p in (os.path.join(ROOT, "ppopp23-tdc_b200"), os.path.join(ROOT, "oracle"), 
         sys.path.insert(0, p)
 
 
+# the tensor-core launcher looks at its TDC_TC_* measurement switches only when this is set before its first launch
+os.environ.setdefault("TDC_TC_TUNING", "1")
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import GOLDEN, ROOT, rel_err
+from helpers import GOLDEN, NET_FP32_TOL, NET_TC_TOL, ROOT, rel_err
 
 Z = np.load(os.path.join(GOLDEN, "tk_densenet121.npz"))
 sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
@@ -159,11 +159,12 @@ def test_logits_match_the_reference_network(built, precision):
     with torch.no_grad():
         final = m.forward_features(x)
         logits = m(x)
-    # 120 chained convolutions with BatchNorm between them: the end-to-end bar of the other networks, 1e-4 of the
-    # largest value (each single convolution is held to 1e-5 in test_gpu_parity.py)
-    assert rel_err(feats["block1"][0].mean((1, 2)).cpu().numpy(), Z["block1_mean"]) <= 1e-5
-    assert rel_err(final[0].mean((1, 2)).cpu().numpy(), Z["final_mean"]) <= 1e-4
-    assert rel_err(logits.cpu().numpy(), Z["logits"]) <= 1e-4
+    # 120 chained convolutions with BatchNorm between them: the fp32 kernels at the single-layer bar, the tensor-core
+    # tier at its own
+    tol = NET_FP32_TOL if precision == "fp32" else NET_TC_TOL
+    assert rel_err(feats["block1"][0].mean((1, 2)).cpu().numpy(), Z["block1_mean"]) <= tol
+    assert rel_err(final[0].mean((1, 2)).cpu().numpy(), Z["final_mean"]) <= tol
+    assert rel_err(logits.cpu().numpy(), Z["logits"]) <= tol
     assert (logits.argmax(1).cpu().numpy() == Z["logits"].argmax(1)).all()
 
 

@@ -1,5 +1,6 @@
-"""The tensor-core variant (tcgen05, TF32 operands) against the fp64 arbiter, through the C ABI.
-mode 3 (split operands, "3xTF32") is held to the fp32 bar of 1e-5; mode 1 (plain TF32) to 5e-3."""
+"""The tensor-core variant (tcgen05, TF32 or fp16 operands) against the fp64 arbiter, through the C ABI.
+modes 3 and 4 (operands split into two TF32 / two fp16 parts) are held to the fp32 bar of 1e-5 per layer;
+mode 1 (plain TF32) to 5e-3."""
 import ctypes as C
 
 import numpy as np
@@ -7,7 +8,7 @@ import pytest
 import torch
 
 import oracle as O
-from helpers import FP32_TOL, SWEEP, draw_core, rel_err
+from helpers import FP32_TOL, NET_TC_TOL, SWEEP, draw_core, rel_err
 
 TF32_TOL = 5e-3
 
@@ -29,6 +30,8 @@ def test_plan_is_made_on_the_host(T):
     assert T.lib.tdc_tc_plan_make_general(3, 64, 7, 7, 3, C.byref(p)) == 0          # the stem: 147 "channels" in 19 blocks of 8
     assert (p.general, p.nt, p.nkb, p.n_ocb, p.hl) == (1, 64, 19, 1, 2) and p.weights_bytes == 4 * 2 * 1 * 8 * 64 * 19
     assert T.lib.tdc_tc_plan_make_general(3, 64, 0, 7, 3, C.byref(p)) == _lib.ERR_SHAPE
+    assert T.lib.tdc_tc_plan_make(64, 64, 3, 3, 4, C.byref(p)) == 0                   # fp16 parts: 16 channels per K step, a scratch tail
+    assert (p.nt, p.cb, p.nkb, p.n_ocb, p.hl) == (64, 16, 4, 1, 2) and p.weights_bytes == 4 * 2 * 9 * 8 * 64 * 4 + 4 * (1024 + 64)
     assert T.lib.tdc_tc_plan_make(64, 64, 3, 3, 2, C.byref(p)) == _lib.ERR_UNSUPPORTED
     assert T.lib.tdc_tc_plan_make(0, 64, 3, 3, 3, C.byref(p)) == _lib.ERR_SHAPE
     assert b"mode" in T.lib.tdc_tc_last_error_string() or b"C=" in T.lib.tdc_tc_last_error_string()
@@ -42,12 +45,13 @@ def test_against_arbiter(T, B, Cc, K, H, W, R):
     from tdc_b200 import tc
     x, w = draw_core(700 + B + Cc + H, B, Cc, K, H, W, R)
     ref = O.conv2d_f64(x.numpy(), w.numpy(), pad=(R - 1) // 2)
-    for mode, tol in ((3, FP32_TOL), (1, TF32_TOL)):
+    for mode, tol in ((4, FP32_TOL), (1, TF32_TOL), (3, FP32_TOL)):
         y = T.TcConv(w.cuda(), mode=mode)(x.cuda()).cpu().numpy()
         assert y.shape == ref.shape and rel_err(y, ref) <= tol, (mode, rel_err(y, ref))
     crsk = np.ascontiguousarray(w.numpy().transpose(1, 2, 3, 0))
-    y2 = T.TcConv(torch.from_numpy(crsk).cuda(), mode=3, w_layout=T.W_CRSK)(x.cuda()).cpu().numpy()
-    assert np.array_equal(y, y) and rel_err(y2, ref) <= FP32_TOL
+    for mode in (3, 4):          # the channel-last filter layout prepares the same operands: every bit agrees
+        y2 = T.TcConv(torch.from_numpy(crsk).cuda(), mode=mode, w_layout=T.W_CRSK)(x.cuda()).cpu().numpy()
+        assert rel_err(y2, ref) <= FP32_TOL and (mode != 3 or np.array_equal(y2, y))
     assert tc.status() == 0          # no bounded wait ran out
 
 
@@ -58,14 +62,17 @@ def test_sweep_shapes_meet_the_fp32_bar(T, H, R1, R2):
     with all-ones weights exactly (the reference drivers' own check)."""
     i = SWEEP.index((H, R1, R2))
     x, w = draw_core(2100 + i, 64, R1, R2, H, H)
-    conv = T.TcConv(w.cuda(), mode=3)
-    y = conv(x.cuda())
     sel = [0, 21, 42, 63]
-    assert rel_err(y[sel].cpu().numpy(), O.conv2d_f64(x[sel].numpy(), w.numpy(), pad=1)) <= FP32_TOL
+    ref = O.conv2d_f64(x[sel].numpy(), w.numpy(), pad=1)
     xi = torch.randint(0, 10, (2, R1, H, H), generator=torch.Generator().manual_seed(i)).float()
     ones = torch.ones(R2, R1, 3, 3)
-    yi = T.TcConv(ones.cuda(), mode=3)(xi.cuda()).cpu().numpy()
-    assert np.array_equal(yi, O.conv2d_f64(xi.numpy(), ones.numpy(), pad=1))
+    for mode in (3, 4):
+        y = T.TcConv(w.cuda(), mode=mode)(x.cuda())
+        assert rel_err(y[sel].cpu().numpy(), ref) <= FP32_TOL, mode
+        yi = T.TcConv(ones.cuda(), mode=mode)(xi.cuda()).cpu().numpy()
+        assert np.array_equal(yi, O.conv2d_f64(xi.numpy(), ones.numpy(), pad=1)), mode
+    # the fp16 mode is the closer of the two to fp64: half as many accumulations feed each running sum
+    assert rel_err(y[sel].cpu().numpy(), ref) <= 4e-6
 
 
 @pytest.mark.gpu
@@ -75,10 +82,11 @@ def test_epilogue_and_errors(T):
     w = (torch.randn(24, 16, 3, 3, generator=g) * 0.1).cuda()
     scale, shift = (torch.rand(24, generator=g) + 0.5).cuda(), torch.randn(24, generator=g).cuda()
     res = torch.randn(3, 24, 14, 14, generator=g).cuda()
-    y = T.TcConv(w, mode=3)(x, scale, shift, res, True)
     ref = torch.relu(torch.nn.functional.conv2d(x.double(), w.double(), padding=1) * scale.double().view(1, -1, 1, 1)
                      + shift.double().view(1, -1, 1, 1) + res.double())
-    assert rel_err(y.cpu().numpy(), ref.cpu().numpy()) <= FP32_TOL
+    for mode in (3, 4):
+        y = T.TcConv(w, mode=mode)(x, scale, shift, res, True)
+        assert rel_err(y.cpu().numpy(), ref.cpu().numpy()) <= FP32_TOL
     with pytest.raises(T.TdcError):
         T.TcConv(torch.zeros(4, 4, 5, 5).cuda())
     with pytest.raises(T.TdcError):
@@ -96,16 +104,18 @@ def test_module_and_network_precisions(T):
         y32 = m(x)
         m.precision = "tf32x3"
         y3 = m(x)
+        m.precision = "fp16x3"
+        y4 = m(x)
         m.precision = "tf32"
         y1 = m(x)
-    assert rel_err(y3.cpu().numpy(), y32.cpu().numpy()) <= FP32_TOL
+    assert rel_err(y3.cpu().numpy(), y32.cpu().numpy()) <= FP32_TOL and rel_err(y4.cpu().numpy(), y32.cpu().numpy()) <= FP32_TOL
     assert FP32_TOL < rel_err(y1.cpu().numpy(), y32.cpu().numpy()) <= TF32_TOL
     net = T.fill_deterministic(T.tkc_resnet18().eval(), 0).cuda()
     xin = torch.randn(8, 3, 224, 224, generator=torch.Generator().manual_seed(1)).cuda()
     with torch.no_grad():
         a = net(xin)
         b = net.set_precision("auto")(xin)
-    assert rel_err(b.cpu().numpy(), a.cpu().numpy()) <= 1e-4
+    assert rel_err(b.cpu().numpy(), a.cpu().numpy()) <= NET_TC_TOL
 
 
 @pytest.mark.gpu
@@ -188,7 +198,7 @@ def test_strided_1x1_shortcut(T, B, Cc, K, H, W, stride, monkeypatch):
     ref = O.conv2d_f64(x[sel].numpy(), w.numpy(), pad=0, stride=stride)
     want = ref * scale.cpu().numpy()[None, :, None, None] + shift.cpu().numpy()[None, :, None, None]
     assert tc.supported(1, 1, stride, 0, W) and not tc.supported(3, 3, stride, 1, W)
-    for mode, tol in ((3, FP32_TOL), (1, TF32_TOL)):
+    for mode, tol in ((3, FP32_TOL), (1, TF32_TOL), (4, FP32_TOL)):
         conv = T.TcConv(w.cuda(), mode=mode)
         for persist in ("0", "1"):
             monkeypatch.setenv("TDC_TC_PERSIST", persist)
@@ -215,7 +225,7 @@ def test_general_plan(T, B, Cc, K, H, W, R, stride, pad):
     ref = O.conv2d_f64(x[sel].numpy(), w.numpy(), pad=pad, stride=stride)
     g = torch.Generator().manual_seed(K + R)
     scale, shift = (torch.rand(K, generator=g) + 0.5).cuda(), torch.randn(K, generator=g).cuda()
-    for mode, tol in ((3, FP32_TOL), (1, TF32_TOL)):
+    for mode, tol in ((3, FP32_TOL), (1, TF32_TOL), (4, FP32_TOL)):
         conv = T.TcConv(w.cuda(), mode=mode, general=True)
         y = conv(x.cuda(), stride=stride, padding=pad)
         assert tuple(y.shape[1:]) == ref.shape[1:] and rel_err(y[sel].cpu().numpy(), ref) <= tol, (mode, rel_err(y[sel].cpu().numpy(), ref))
@@ -269,10 +279,51 @@ def test_random_shapes_against_fp64(T):
             ref = ref + res.double()
         if relu:
             ref = ref.relu()
-        conv = T.TcConv(w, mode=3, general=general)
+        conv = T.TcConv(w, mode=3 if case % 2 else 4, general=general)
         y = conv(x, scale, shift, res, relu, stride=stride, padding=pad if general else None)
         assert y.shape == ref.shape, (case, y.shape, ref.shape)
         err = float((y.double() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
         worst = max(worst, err)
         assert err <= FP32_TOL, (case, general, B, Cc, K, H, W, R, stride, pad, err)
     assert tc.status() == 0 and worst > 0.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,Cc,K,H,W,R", [(9, 64, 64, 56, 56, 3), (70, 24, 40, 14, 14, 3), (2, 256, 256, 14, 14, 3), (16, 32, 32, 28, 28, 1),
+                                           (3, 520, 256, 12, 12, 1), (5, 33, 130, 8, 10, 3)])
+def test_fp16_parts_loaders_runs_and_range(T, B, Cc, K, H, W, R, monkeypatch):
+    """Mode 4.  (1) Its two input loaders (bulk-tensor boxes filled by a producer thread; the cp.async ring) put
+    the same values in the same places: every output bit agrees, whatever the depth of the rings.  (2) Cutting
+    the channel blocks into runs that the epilogue adds in fp32 changes the rounding, not the result: within the
+    bar, and no farther from fp64 than one run.  (3) The power-of-two scaling into fp16's range makes the result
+    independent of the magnitude of input and filter: inputs of 1e-6 and 1e+20 times the same data give the
+    same relative error.  (4) The output's recorded largest magnitude is the true one, and a call that is handed
+    it skips its own pass over the input without changing a bit."""
+    from tdc_b200 import tc
+    x, w = draw_core(2500 + B + Cc + H, B, Cc, K, H, W, R)
+    xd, wd = x.cuda(), w.cuda()
+    ref = torch.nn.functional.conv2d(xd.double(), wd.double(), None, 1, (R - 1) // 2)
+    conv = T.TcConv(wd, mode=4)
+    y = conv(xd).clone()
+    err = rel_err(y.cpu().numpy(), ref.cpu().numpy())
+    assert err <= FP32_TOL
+    for knobs in ({"TDC_TC_BULK": "0"}, {"TDC_TC_BULK": "1"}, {"TDC_TC_BULK": "1", "TDC_TC_DEPTH": "2"}, {"TDC_TC_BULK": "0", "TDC_TC_MT": "1"},
+                  {"TDC_TC_BULK": "1", "TDC_TC_MT": "1", "TDC_TC_NBUF": "1"}, {"TDC_TC_NS": "2"}, {"TDC_TC_TAIL": "0"}):
+        for k, v in knobs.items():
+            monkeypatch.setenv(k, v)
+        assert torch.equal(conv(xd), y), knobs
+        for k in knobs:
+            monkeypatch.delenv(k)
+    for chain in ("9", "18", "0"):
+        monkeypatch.setenv("TDC_TC_CHAIN", chain)
+        e2 = rel_err(conv(xd).cpu().numpy(), ref.cpu().numpy())
+        assert e2 <= FP32_TOL and (chain == "0" or e2 <= 1.5 * err + 2e-7), (chain, e2, err)
+    monkeypatch.delenv("TDC_TC_CHAIN")
+    for sx, sw in ((1e-6, 1.0), (1e20, 1e-9), (3e4, 7e3)):
+        ys = T.TcConv(wd * sw, mode=4)(xd * sx)
+        assert rel_err(ys.cpu().numpy(), (ref * (sx * sw)).cpu().numpy()) <= max(2 * err, 2e-6), (sx, sw)
+    assert float(y._tdc_absmax.max()) == float(y.abs().max())
+    y_next = T.TcConv(torch.eye(K).view(K, K, 1, 1).cuda().contiguous(), mode=4)
+    plain = y.clone()                                     # no recorded magnitude: the call makes its own pass
+    assert torch.equal(y_next(y), y_next(plain))
+    assert tc.status() == 0

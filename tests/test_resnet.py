@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import GOLDEN, rel_err
+from helpers import GOLDEN, NET_FP32_TOL, NET_TC_TOL, rel_err
 
 Z = np.load(os.path.join(GOLDEN, "tk_resnet18.npz"))
 
@@ -44,12 +44,11 @@ def test_logits_match_the_reference_network(built):
     m.layer4.register_forward_hook(lambda mod, i, o: feats.__setitem__("layer4", o))
     with torch.no_grad():
         logits = m(x)
-    # sixteen Tucker blocks deep, BatchNorm folded into the convs: the error of ~50 chained fp32
-    # convolutions compounds, so the end-to-end bar is 1e-4 of the largest logit (each single
-    # convolution is held to 1e-5 in test_gpu_parity.py)
-    assert rel_err(feats["layer1"][0].mean((1, 2)).cpu().numpy(), Z["layer1_mean"]) <= 1e-5
-    assert rel_err(feats["layer4"][0].mean((1, 2)).cpu().numpy(), Z["layer4_mean"]) <= 1e-4
-    assert rel_err(logits.cpu().numpy(), Z["logits"]) <= 1e-4
+    # sixteen Tucker blocks deep, BatchNorm folded into the convs, on the fp32 FMA kernels: the whole network is held
+    # to the bar of a single layer (the golden logits are the reference network's own fp32 run on the CPU)
+    assert rel_err(feats["layer1"][0].mean((1, 2)).cpu().numpy(), Z["layer1_mean"]) <= NET_FP32_TOL
+    assert rel_err(feats["layer4"][0].mean((1, 2)).cpu().numpy(), Z["layer4_mean"]) <= NET_FP32_TOL
+    assert rel_err(logits.cpu().numpy(), Z["logits"]) <= NET_FP32_TOL
     assert (logits.argmax(1).cpu().numpy() == Z["logits"].argmax(1)).all()
 
 
@@ -99,8 +98,9 @@ def test_resnet50_logits_match_the_reference_network(built, precision):
     m.layer4.register_forward_hook(lambda mod, i, o: feats.__setitem__("layer4", o))
     with torch.no_grad():
         logits = m(x)
-    # 53 chained convolutions: the end-to-end bar of the residual networks, 1e-4 of the largest logit
-    assert rel_err(feats["layer1"][0].mean((1, 2)).cpu().numpy(), Z50["layer1_mean"]) <= 1e-5
-    assert rel_err(feats["layer4"][0].mean((1, 2)).cpu().numpy(), Z50["layer4_mean"]) <= 1e-4
-    assert rel_err(logits.cpu().numpy(), Z50["logits"]) <= 1e-4
+    # 53 chained convolutions: the fp32 kernels at the single-layer bar, the tensor-core tier at its own
+    tol = NET_FP32_TOL if precision == "fp32" else NET_TC_TOL
+    assert rel_err(feats["layer1"][0].mean((1, 2)).cpu().numpy(), Z50["layer1_mean"]) <= tol
+    assert rel_err(feats["layer4"][0].mean((1, 2)).cpu().numpy(), Z50["layer4_mean"]) <= tol
+    assert rel_err(logits.cpu().numpy(), Z50["logits"]) <= tol
     assert (logits.argmax(1).cpu().numpy() == Z50["logits"].argmax(1)).all()
