@@ -20,7 +20,8 @@ no collective on the data path).  Rank 0 prints ONE JSON line.
 
 `--impl reference` times the reference's CPU implementation of the path (the three
 F.conv2d calls of inference/TKConv.py:90-95 reduce to the core call for this step) on the
-host cores of the box, on a bounded batch sample.
+host cores of the box, on the same step: all eight shapes at batch 64.  It is one host whatever
+--gpus says (rank 0 runs it, the other ranks exit).
 """
 import argparse
 import ctypes as C
@@ -39,6 +40,7 @@ SWEEP = [(56, 32, 32), (56, 64, 64), (28, 64, 64), (28, 128, 128), (14, 128, 128
          (7, 256, 256), (7, 512, 512)]
 BATCH = 64
 METRIC, UNIT = "core_conv_sweep_throughput", "layer-images/s"
+WORKLOAD = "core-conv sweep: 8 shapes (H,R1=R2) 56/32 56/64 28/64 28/128 14/128 14/256 7/256 7/512, 3x3 s1 p1, batch 64 per GPU"
 
 
 def conv_flops(B, H, R1, R2):
@@ -109,6 +111,18 @@ class ClockSampler:
         return out
 
 
+def recorded_dram_bytes():
+    """{(H, R1): bytes} from the data file that sits beside the ncu summary of the step's launches: lines `H R1 bytes`."""
+    out = {}
+    path = os.path.join(ROOT, "profiles", "sweep_b64_dram_bytes.txt")
+    if os.path.exists(path):
+        for ln in open(path):
+            f = ln.split()
+            if len(f) >= 3 and not ln.startswith("#"):
+                out[(int(f[0]), int(f[1]))] = float(f[2])
+    return out
+
+
 def cpu_core_step(torch, batch, threads):
     """The reference's CPU path for one step at `batch` images per layer; returns seconds."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -135,7 +149,7 @@ def run_reference(args):
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    sample_b = 8
+    sample_b = BATCH                       # the whole step: a pass costs some tens of milliseconds on the host cores
     step = cpu_core_step(torch, sample_b, cores)
     for _ in range(max(args.warmup, 1)):
         step()
@@ -148,10 +162,11 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "core-conv sweep, 8 shapes, 3x3 s1 p1 fp32, batch %d per layer (sample of the batch-64 step)" % sample_b,
-                   "impl": "torch.nn.functional.conv2d on CPU, the call TKConv2dC.forward makes (inference/TKConv.py:92-93)"},
+        "config": {"workload": WORKLOAD,
+                   "impl": "torch.nn.functional.conv2d on CPU, the call TKConv2dC.forward makes (inference/TKConv.py:92-93); "
+                           "one host with all its cores, whatever --gpus says"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": "batch %d of 64 per layer, all 8 shapes, %d steps" % (sample_b, args.steps)},
+                         "sample": "the whole step: batch %d per layer, all 8 shapes, %d steps" % (sample_b, args.steps)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -527,15 +542,17 @@ def main():
         w = torch.randn(R2, R1, 3, 3, generator=g) * (2.0 / (R2 * 9)) ** 0.5
         xd, wk = x.to(dev), w.to(dev)
         layers.append(dict(H=H, R1=R1, R2=R2, x=xd, w=T.permute_weights(wk), wk=wk, y=torch.empty(BATCH, R2, H, H, device=dev),
-                           tile=T.best_tile(BATCH, R1, H, H, R2, 3, 3, 1, 1), tc3=T.TcConv(wk, mode=3), tc1=T.TcConv(wk, mode=1),
+                           tile=T.best_tile(BATCH, R1, H, H, R2, 3, 3, 1, 1), tc4=T.TcConv(wk, mode=4), tc3=T.TcConv(wk, mode=3), tc1=T.TcConv(wk, mode=1),
                            x_host=x, w_host=w))
 
     # The step the headline is quoted on: every layer on the fastest path that keeps fp32-level
-    # results (1e-5 bar) — at batch 64 that is the tensor-core kernel with split operands (3xTF32)
-    # for all eight shapes.  The fp32 FMA kernels and plain TF32 are timed beside it below.
+    # results (1e-5 bar) — at batch 64 that is the tensor-core kernel with operands split into two
+    # fp16 parts (3xFP16) for all eight shapes; each call is two launches, the pass that finds the
+    # input's largest magnitude (for the scaling into fp16's range) and the convolution.  Split TF32
+    # parts, the fp32 FMA kernels and plain TF32 are timed beside it below.
     def step():
         for L in layers:
-            L["tc3"](L["x"], out=L["y"])
+            L["tc4"](L["x"], out=L["y"])
 
     def step_simt():
         for L in layers:
@@ -598,38 +615,40 @@ def main():
         fl, by = conv_flops(BATCH, L["H"], L["R1"], L["R2"]), conv_bytes(BATCH, L["H"], L["R1"], L["R2"])
         ref = torch.nn.functional.conv2d(L["x"][:2].double(), L["wk"].double(), None, 1, 1)
         row = dict(H=L["H"], R1=L["R1"], R2=L["R2"], B=BATCH)
-        for name, fn in (("tc3", lambda L=L: L["tc3"](L["x"], out=L["y"])), ("tc1", lambda L=L: L["tc1"](L["x"], out=L["y"])),
+        for name, fn in (("tc4", lambda L=L: L["tc4"](L["x"], out=L["y"])), ("tc3", lambda L=L: L["tc3"](L["x"], out=L["y"])),
+                         ("tc1", lambda L=L: L["tc1"](L["x"], out=L["y"])),
                          ("simt", lambda L=L: T.core_conv2d(L["x"], L["w"], 1, 1, w_layout=T.W_CRSK, tile=L["tile"], out=L["y"]))):
             us = time_layer(fn)
             row[name + "_us"] = us
             row[name + "_tflops"] = fl / us / 1e6
             row[name + "_rel_err_fp64"] = float((L["y"][:2].double() - ref).abs().max() / ref.abs().max())
-        row["gbs_tc3"] = by / row["tc3_us"] / 1e3
+        row["gbs_tc4"] = by / row["tc4_us"] / 1e3
         row["tile_simt"] = list(L["tile"].as_tuple())
         per_layer.append(row)
     tot_fl = sum(conv_flops(BATCH, r["H"], r["R1"], r["R2"]) for r in per_layer)
     tot_by = sum(conv_bytes(BATCH, r["H"], r["R1"], r["R2"]) for r in per_layer)
-    dom = max(per_layer, key=lambda r: r["tc3_us"])
-    tot_tc3, tot_simt, tot_tc1 = (sum(r[k] for r in per_layer) for k in ("tc3_us", "simt_us", "tc1_us"))
-    # DRAM bytes (read + write) of each launch of the step from one ncu capture of this command
-    # (dram__bytes_read.sum + dram__bytes_write.sum per launch, batch 64); the summary and the command
-    # are in profiles/launch_list_bench.md.  Outputs stay in L2 within a launch, so this is input + filter.
-    NCU_DRAM_MB = {(56, 32): 25.8, (56, 64): 51.9, (28, 64): 13.2, (28, 128): 26.9, (14, 128): 7.7, (14, 256): 17.6,
-                   (7, 256): 8.0, (7, 512): 25.4}
+    dom = max(per_layer, key=lambda r: r["tc4_us"])
+    tot_tc4, tot_tc3, tot_simt, tot_tc1 = (sum(r[k] for r in per_layer) for k in ("tc4_us", "tc3_us", "simt_us", "tc1_us"))
+    f16_peak = peaks["bf16_tflops"]                                       # dense fp16 = the measured bf16 rate
+    # DRAM bytes (read + write) per launch as one ncu capture of this command recorded them (a data file beside the
+    # capture's summary; absent or without the shape: null).  Outputs stay in L2 within a launch.
+    recorded = recorded_dram_bytes()
     roofline = {
-        "bound": "tensor", "achieved": tot_fl / tot_tc3 / 1e6, "peak": tf32_peak / 3.0, "unit": "TFLOP/s",
-        "frac": tot_fl / tot_tc3 / 1e6 / (tf32_peak / 3.0),
-        "traffic": NCU_DRAM_MB[(dom["H"], dom["R1"])] * 1e6,
+        "bound": "tensor", "achieved": tot_fl / tot_tc4 / 1e6, "peak": f16_peak / 3.0, "unit": "TFLOP/s",
+        "frac": tot_fl / tot_tc4 / 1e6 / (f16_peak / 3.0),
+        "traffic": recorded.get((dom["H"], dom["R1"])),
         "traffic_note": {"launch": [dom["H"], dom["R1"], dom["R2"]], "unit": "bytes per launch",
                          "algorithmic_bytes": conv_bytes(BATCH, dom["H"], dom["R1"], dom["R2"]),
-                         "source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of the dominant launch, "
-                                   "profiles/launch_list_bench.md; the output is still in L2 when the launch ends"},
-        "kernel": "conv_tc_persist_kernel / conv_tc_kernel (tcgen05 kind::tf32, 3xTF32), the 8 launches of a step, L2 flushed before each",
-        "peak_source": "algorithmic FLOPs against (bf16_tflops/2)/3: dense TF32 taken as half the measured cuBLAS bf16 rate of "
-                       "MEASURED_PEAKS.json (%s), divided by the three TF32 products each fp32-level product costs" % peaks["source"],
-        "dominant_launch": {k: dom[k] for k in ("H", "R1", "R2", "tc3_us", "tc3_tflops")},
-        "hbm": {"achieved": tot_by / tot_tc3 / 1e3, "peak": peaks["hbm_gbs"], "unit": "GB/s"},
-        "vs_fp32_fma_peak": tot_fl / tot_tc3 / 1e6 / fp32_peak,
+                         "source": "recorded: dram__bytes_read.sum + dram__bytes_write.sum of the dominant launch in an earlier ncu "
+                                   "capture of this command (not measured by this run)"},
+        "kernel": "conv_tc_persist_kernel (tcgen05 kind::f16, operands split into two fp16 parts) + absmax_kernel, the 16 launches of a step, L2 flushed before each layer",
+        "peak_source": "algorithmic FLOPs against bf16_tflops/3: the measured cuBLAS bf16 rate of MEASURED_PEAKS.json (%s) as the dense "
+                       "fp16 rate, divided by the three fp16 products each fp32-level product costs" % peaks["source"],
+        "dominant_launch": {k: dom[k] for k in ("H", "R1", "R2", "tc4_us", "tc4_tflops")},
+        "hbm": {"achieved": tot_by / tot_tc4 / 1e3, "peak": peaks["hbm_gbs"], "unit": "GB/s"},
+        "vs_fp32_fma_peak": tot_fl / tot_tc4 / 1e6 / fp32_peak,
+        "tf32x3": {"achieved": tot_fl / tot_tc3 / 1e6, "peak": tf32_peak / 3.0, "frac": tot_fl / tot_tc3 / 1e6 / (tf32_peak / 3.0),
+                   "note": "the same step with TF32 parts (mode 3) against a third of the dense TF32 rate"},
     }
     simt = {
         "value": len(SWEEP) * BATCH * world / (ms_simt * 1e-3), "unit": UNIT, "ms_per_step": ms_simt,
@@ -646,14 +665,18 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "core-conv sweep: 8 shapes (H,R1=R2) 56/32 56/64 28/64 28/128 14/128 14/256 7/256 7/512, 3x3 s1 p1, batch 64 per GPU",
-                   "path": "fp32 in / fp32 out; products on tensor cores with operands split into two TF32 parts (3xTF32), fp32 accumulation; "
-                           "max rel. error vs fp64 over the sweep %.1e (bar 1e-5)" % max(r["tc3_rel_err_fp64"] for r in per_layer),
+        "config": {"workload": WORKLOAD,
+                   "path": "fp32 in / fp32 out; products on tensor cores with operands split into two fp16 parts (3xFP16, inputs scaled "
+                           "into fp16's range by a power of two found per call), fp32 accumulation; "
+                           "max rel. error vs fp64 over the sweep %.1e (bar 1e-5)" % max(r["tc4_rel_err_fp64"] for r in per_layer),
+                   "precision": "fp16x3",
                    "l2": "working set of a step (inputs+outputs 288 MB) exceeds the 126 MB L2; per-layer timings flush L2 explicitly",
                    "parallelism": "batch shards, no collective" if world > 1 else "single GPU"},
-        "clocks": clocks, "gpu_launches": len(SWEEP) * args.steps, "roofline": roofline,
+        "clocks": clocks, "gpu_launches": 2 * len(SWEEP) * args.steps, "roofline": roofline,
         "us_per_layer_b64": ms_step * 1e3 / len(SWEEP),
-        "fp32_fma_path": simt, "tf32_path": tf32, "per_layer_b64": per_layer,
+        "fp32_fma_path": simt, "tf32_path": tf32, "tf32x3_path": {"value": len(SWEEP) * BATCH * world / (tot_tc3 * 1e-6), "unit": UNIT,
+                                                                  "max_rel_err_fp64": max(r["tc3_rel_err_fp64"] for r in per_layer)},
+        "per_layer_b64": per_layer,
     }
 
     # ---- end to end through the layer objects with HOST buffers (pinned) -------------------
@@ -664,7 +687,7 @@ def main():
         wk = L["w_host"].contiguous()
         T._lib.check(lib.tdc_conv_create(C.byref(h), BATCH, L["R1"], L["H"], L["H"], L["R2"], 1, 3, 3, 1,
                                          C.c_void_p(wk.data_ptr()), None))
-        T._lib.check(lib.tdc_conv_set_precision(h, 3))
+        T._lib.check(lib.tdc_conv_set_precision(h, 4))
         xin = L["x_host"].pin_memory()
         yout = torch.empty(BATCH, L["R2"], L["H"], L["H"]).pin_memory()
         hosts.append((h, xin, yout))
@@ -705,12 +728,44 @@ def main():
     e2e_s = timings["async"]
     line["e2e"] = {"value": len(SWEEP) * BATCH * world / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d,
                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_s * 1e3,
-                   "api": "tdc_conv_forward_host_async per layer, each layer on its own stream (pinned host buffers; "
+                   "api": "tdc_conv_forward_host_async per layer, each layer on its own stream and, inside the call, in four batch "
+                          "chunks on two streams so that copy in, kernel and copy out overlap (pinned host buffers; "
                           "copies inside the timed region; the step ends when all streams have drained)",
                    "one_layer_at_a_time": {"value": len(SWEEP) * BATCH * world / timings["sync"], "ms_per_step": timings["sync"] * 1e3,
                                            "api": "tdc_conv_forward_host per layer (copy in, conv, copy out, synchronise)"}}
+    # what the host link allows: the same buffers copied in and out with no kernel between (copy in on one stream,
+    # copy out on another, so both directions run at once), as a ceiling for the end-to-end figure
+    dev_in = [torch.empty_like(x, device=dev) for _, x, _ in hosts]
+    dev_out = [torch.empty_like(y, device=dev) for _, _, y in hosts]
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def copies_only():
+        with torch.cuda.stream(s_in):
+            for d, (_, x, _) in zip(dev_in, hosts):
+                d.copy_(x, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            for d, (_, _, y) in zip(dev_out, hosts):
+                y.copy_(d, non_blocking=True)
+        s_in.synchronize(); s_out.synchronize()
+    for _ in range(2):
+        copies_only()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        copies_only()
+    barrier()
+    copy_s = (time.perf_counter() - t0) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([copy_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        copy_s = float(t.item())
+    line["e2e"]["copy_ceiling"] = {"ms_per_step": copy_s * 1e3, "value": len(SWEEP) * BATCH * world / copy_s, "unit": UNIT,
+                                   "gbs_each_way_per_gpu": h2d / copy_s / 1e9,
+                                   "note": "pinned-memory copies of the step's inputs and outputs alone, both directions at once, all ranks at once"}
+    line["e2e"]["frac_of_copy_ceiling"] = copy_s / e2e_s
+    del dev_in, dev_out
     # one parity probe of the end-to-end output against the resident path
-    e2e_ok = bool(torch.equal(hosts[0][2].to(dev), layers[0]["tc3"](layers[0]["x"])))
+    e2e_ok = bool(torch.equal(hosts[0][2].to(dev), layers[0]["tc4"](layers[0]["x"])))
     line["e2e"]["matches_resident_path"] = e2e_ok
     for h, _, _ in hosts:
         lib.tdc_conv_destroy(h)
@@ -741,28 +796,29 @@ def main():
             cud1 = time_layer(lambda: F.conv2d(x1, wk, None, 1, 1), iters=20)
             ref = F.conv2d(L["x"][:2].double(), wk.double(), None, 1, 1)
             cud_err = float((F.conv2d(L["x"], wk, None, 1, 1)[:2].double() - ref).abs().max() / ref.abs().max())
-            table.append(dict(H=H, R1=R1, R2=R2, us_b64=r64["tc3_us"], us_b64_fp32_fma=r64["simt_us"], us_b64_tf32=r64["tc1_us"],
-                              cudnn_us_b64=cud64, rel_err_fp64_b64=r64["tc3_rel_err_fp64"], cudnn_rel_err_fp64_b64=cud_err,
+            table.append(dict(H=H, R1=R1, R2=R2, us_b64=r64["tc4_us"], us_b64_tf32x3=r64["tc3_us"], us_b64_fp32_fma=r64["simt_us"], us_b64_tf32=r64["tc1_us"],
+                              cudnn_us_b64=cud64, rel_err_fp64_b64=r64["tc4_rel_err_fp64"], cudnn_rel_err_fp64_b64=cud_err,
+                              frac_b64=conv_flops(BATCH, H, R1, R2) / r64["tc4_us"] / 1e6 / (f16_peak / 3.0),
                               us_b1=us1, frac_fp32_b1=conv_flops(1, H, R1, R2) / us1 / 1e6 / fp32_peak, cudnn_us_b1=cud1,
                               tile_b1=list(t1.as_tuple())))
         line["layers"] = table
         gm = lambda v: float(torch.tensor(v).log().mean().exp())
         line["speedup_vs_cudnn_geomean"] = {"b64": gm([r["cudnn_us_b64"] / r["us_b64"] for r in table]),
+                                            "b64_tf32x3": gm([r["cudnn_us_b64"] / r["us_b64_tf32x3"] for r in table]),
                                             "b64_fp32_fma_kernels": gm([r["cudnn_us_b64"] / r["us_b64_fp32_fma"] for r in table]),
                                             "b64_tf32": gm([r["cudnn_us_b64"] / r["us_b64_tf32"] for r in table]),
                                             "b1": gm([r["cudnn_us_b1"] / r["us_b1"] for r in table]),
                                             "cudnn": "torch F.conv2d, cudnn.benchmark=True, allow_tf32=False, version %s" % torch.backends.cudnn.version()}
         cores = os.cpu_count() or 1
-        sample_b = 8
-        cstep = cpu_core_step(torch, sample_b, cores)
+        cstep = cpu_core_step(torch, BATCH, cores)
         cstep()
         t0 = time.perf_counter()
         n = 0
         while n < 3 or (time.perf_counter() - t0 < 10.0 and n < 50):
             cstep(); n += 1
         cdt = (time.perf_counter() - t0) / n
-        line["cpu_baseline"] = {"value": len(SWEEP) * sample_b / cdt, "unit": UNIT, "cores": cores, "kind": "port",
-                                "sample": "batch %d of 64 per layer, all 8 shapes, %d passes of torch F.conv2d on CPU" % (sample_b, n)}
+        line["cpu_baseline"] = {"value": len(SWEEP) * BATCH / cdt, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": "the whole step (batch %d per layer, all 8 shapes), %d passes of torch F.conv2d on CPU" % (BATCH, n)}
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:

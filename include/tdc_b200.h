@@ -9,6 +9,14 @@
  * Unless a comment says otherwise, pointers are DEVICE pointers to contiguous fp32
  * arrays that the caller owns.
  *
+ * Alignment.  x, w, y and the epilogue arrays need only the 4-byte alignment of a float:
+ * where a kernel would use 16-byte accesses it checks the pointer first and takes an
+ * element-wise path otherwise (slower, same results).  Two exceptions, both buffers the
+ * caller allocates for the library: the prepared filter of the tensor-core path (wt) must
+ * be 16-byte aligned, or tdc_tc_prepare_weights / tdc_conv2d_tc return
+ * TDC_ERR_UNSUPPORTED; tdc_pool2d_f32 and tdc_affine_relu_f32 likewise fall back to scalar
+ * accesses for unaligned x / y.
+ *
  * Naming.  The reference's CUDA drivers call the core conv's input channels C and its
  * output channels N, and hard-wire batch 1.  Here:  B = batch, C = input channels (R1
  * of the Tucker block), K = output channels (R2), H,W = input height/width, R,S =
@@ -212,9 +220,11 @@ TDC_API int tdc_tk_block_epi_f32(const float* x, const float* w1, const float* w
  * framework that owns the allocator and forbids side allocations, a step that may only
  * enqueue work on a stream.  tdc_tk_block_f32 asks such a caller for a workspace it has no
  * way to produce.  This variant keeps the two intermediates (z1, z2) in a fixed array that
- * is part of the library image instead: TDC_STATIC_WORKSPACE_BYTES of device memory that
- * every GPU holds from the moment it loads the library until the process exits, whether or
- * not this function is ever called.
+ * is part of the library image instead: TDC_STATIC_WORKSPACE_BYTES of device memory that a
+ * GPU holds from the moment the library's code is loaded onto it until the process exits.
+ * With CUDA's lazy module loading (the default) that moment is the first call of this
+ * library on the device; with CUDA_MODULE_LOADING=EAGER it is context creation.  Either
+ * way the memory is claimed by the driver when it loads the module, not by this function.
  *
  * Same arguments, results and status codes as tdc_tk_block_f32 minus the workspace pair; the
  * caller still passes x, the factors and y.  It returns TDC_ERR_WORKSPACE, with the needed and
@@ -223,7 +233,10 @@ TDC_API int tdc_tk_block_epi_f32(const float* x, const float* w1, const float* w
  * does.
  *
  * Set-up: the first call on each device looks up the array's device address (once, with that
- * device current).  Make that first call during start-up, before any stream capture begins.
+ * device current), which is also when a lazily loaded module lands on the device.  Make that
+ * first call during start-up — before any stream capture begins and before the host
+ * application's arena takes the rest of the device memory, or the module load itself can
+ * fail for lack of memory (reported as TDC_ERR_CUDA).
  *
  * Sharing: all calls on a device use the same array and it keeps whatever the previous call
  * left there; both intermediates are fully overwritten before they are read, so nothing needs

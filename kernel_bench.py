@@ -1,20 +1,24 @@
 """Times one memory-bound kernel of the library alone and prints its bandwidth.
 
-    python -m tdc_b200.kernel_bench affine  --batch 32 --channels 224 --of 256 --size 56
-    python -m tdc_b200.kernel_bench maxpool --batch 256 --channels 64 --size 112      # 3x3 / stride 2 / pad 1
-    python -m tdc_b200.kernel_bench maxpool2 --batch 128 --channels 64 --size 224     # 2x2 / stride 2
+    python kernel_bench.py affine  --batch 32 --channels 224 --of 256 --size 56
+    python kernel_bench.py maxpool --batch 256 --channels 64 --size 112      # 3x3 / stride 2 / pad 1
+    python kernel_bench.py maxpool2 --batch 128 --channels 64 --size 224     # 2x2 / stride 2
 
 `affine`: scale, shift and ReLU over the first `--channels` channels of a [batch][--of][size][size] buffer, the
 pre-activation of a DenseNet layer.  Algorithmic bytes = input read once + output written once; the L2 is flushed
 before every timed launch (a 256 MB memset), times are CUDA events on the launching stream, median of `--iters`.
 """
 import argparse
+import os
 import statistics
+import sys
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "ppopp23-tdc_b200"))
 
 
 def main(argv=None):
     import torch
-    from . import ops
+    from tdc_b200 import ops
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["affine", "maxpool", "maxpool2"])
     ap.add_argument("--batch", type=int, default=32)

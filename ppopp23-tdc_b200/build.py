@@ -71,7 +71,26 @@ def build(force=False, verbose=False):
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
     build_baseline_tool(force)
+    build_layer_driver(force)
     return LIB
+
+
+DRIVER_SRC = os.path.join(HERE, "drivers", "layer_driver.cu")
+DRIVER_EXE = os.path.join(HERE, "tdc_b200", "layer_driver")
+
+
+def build_layer_driver(force=False, defines=()):
+    """The native per-shape layer driver (drivers/layer_driver.cu): a C++ program that calls the library through its C
+    ABI only.  `defines` may carry the reference's compile-time macros, e.g. ("LAYER_C=64", "LAYER_N=64", "LAYER_H=56", "LAYER_W=56")."""
+    newest = max(os.path.getmtime(DRIVER_SRC), os.path.getmtime(LIB), os.path.getmtime(os.path.join(INCLUDE, "tdc_b200.h")))
+    if not force and not defines and os.path.exists(DRIVER_EXE) and os.path.getmtime(DRIVER_EXE) >= newest:
+        return DRIVER_EXE
+    cmd = [_nvcc(), "-O2", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", INCLUDE, DRIVER_SRC, "-o", DRIVER_EXE,
+           "-L", os.path.dirname(LIB), "-ltdc_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"] + ["-D" + d for d in defines]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("layer_driver failed to build:\n%s\n%s" % (r.stdout, r.stderr))
+    return DRIVER_EXE
 
 
 BASELINE_SRC = os.path.join(HERE, "baselines", "cudnn_layer.cpp")

@@ -129,6 +129,7 @@ int launch_conv_epi(const float* x, const float* w, const tdc_epilogue& epi, flo
     if (w_layout == TDC_W_KCRS) { a.ws_k = (long long)s.C * RS; a.ws_c = RS; a.ws_rs = 1; }
     else                        { a.ws_k = 1; a.ws_c = (long long)RS * s.K; a.ws_rs = s.K; }
     a.w_vec = (w_layout == TDC_W_CRSK && s.K % 4 == 0 && (reinterpret_cast<uintptr_t>(w) % 16 == 0)) ? 1 : 0;
+    a.y_vec = reinterpret_cast<uintptr_t>(y) % 16 == 0 ? 1 : 0;      // else the epilogue stores element by element
     a.relu = epi.relu ? 1 : 0;
     a.tc = t.tc; a.gy = t.gy; a.gx = t.gx; a.imgs = t.imgs; a.ks = t.ks;
     a.in_rows = g.in_rows; a.in_wp = g.in_wp; a.patch = g.patch;

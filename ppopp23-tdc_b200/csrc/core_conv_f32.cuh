@@ -44,6 +44,7 @@ struct ConvArgs {
     int R, S;            // filter size (used by the runtime-size variant only)
     long long ws_k, ws_c, ws_rs;
     int w_vec;           // 1: CRSK and K % 4 == 0 -> 16-byte weight copies
+    int y_vec;           // 1: y is 16-byte aligned -> rows of a multiple of 4 outputs may be stored as 16-byte words
     int relu;
     // runtime part of the tile
     int tc, gy, gx, imgs, ks;
@@ -356,7 +357,7 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
     const int b = b0 + iml;
     if (b >= a.B) return;
     const int oyb = oy0 + gyi * TH, oxb = ox0 + gxi * TW;
-    const bool vec_st = (a.Wo % 4 == 0);
+    const bool vec_st = a.y_vec && (a.Wo % 4 == 0);
 #pragma unroll
     for (int j = 0; j < TN; ++j) {
         const int oc = oc0 + ocg * TN + j;

@@ -178,14 +178,6 @@ double tile_cost(const Shape& s, const tdc_tile& t, const Geometry& g, const tdc
     };
     // Latency of one CTA, which bounds a wave from below however few warps share the SM.  Each chunk is a dependent
     // step — copy issued, copy landed, barrier, arithmetic — and on a GPU that the grid barely fills (the batch-1
-    // layers) nothing else hides it: the sweeps there give about 12,000 cycles a chunk plus its bytes at 20 B/clk,
-    // with 0.7 of the chunk's arithmetic on top (the rest runs under the next copy), and 70 cycles per accumulator
-    // for every further rank of a cluster whose partial sums the leader adds over distributed shared memory.
-    // Without this term the model kept few CTAs walking many chunks where a cluster that splits them is 2x faster.
-    // Constants fitted on six measured sweeps (batch 1 to 256, 78 shapes): mean loss of the model's pick against
-    // the measured best 6.6 %, against 37 % without the term.
-    // Latency of one CTA, which bounds a wave from below however few warps share the SM.  Each chunk is a dependent
-    // step — copy issued, copy landed, barrier, arithmetic — and on a GPU that the grid barely fills (the batch-1
     // layers) nothing else hides it: 6,000 cycles a chunk plus its bytes at 20 B/clk, 0.7 of the chunk's arithmetic
     // on top (the rest runs under the next copy), and 70 cycles per accumulator for every further rank of a cluster
     // whose partial sums the leader adds over distributed shared memory.  Without this term the model kept few CTAs

@@ -63,8 +63,8 @@ def main(argv=None):
     ap.add_argument("--csv", default=None)
     ap.add_argument("--reference-row", action="store_true",
                     help="print the reference's CSV row with the cuDNN FFT / Winograd / implicit-GEMM times")
-    ap.add_argument("--tc", type=int, default=0, choices=[0, 1, 3],
-                    help="run the tensor-core variant instead: 3 = 3xTF32 (fp32-level), 1 = plain TF32")
+    ap.add_argument("--tc", type=int, default=0, choices=[0, 1, 3, 4],
+                    help="run the tensor-core variant instead: 4 = 3xFP16, 3 = 3xTF32 (both fp32-level), 1 = plain TF32")
     a = ap.parse_args(argv)
     Cc, N, H, W = (int(v) for v in a.shape.split(","))
     B, k = a.batch, a.filter

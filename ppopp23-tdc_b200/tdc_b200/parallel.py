@@ -7,8 +7,23 @@ process per GPU, torch.distributed) holds a replica of the weights, runs the ide
 on its contiguous slice of the batch, and ONE collective at the end gathers the results
 (all_gather of equal, padded slices; NCCL over NVLink on GPUs, gloo in the CPU tests).  No
 collective and no remote access happens inside the forward.
+
+Failure.  A rank can only leave between steps (none of its kernels or collectives in flight).  The others notice
+at their next gather: the collective raises — at once when the peer's connection is gone, after the process
+group's timeout when the peer is merely silent — and `gather_slices` turns that into `ShardError`, so a driver loop
+catches one exception type, drops the step and decides whether to re-form the group with the ranks that are left.
+Nothing waits without a limit as long as the process group was created with a timeout.
 """
 import torch
+
+
+class ShardError(RuntimeError):
+    """The gather of a sharded step did not complete: a peer rank is gone or silent.  The local slice of the step is
+    in `.local` (it was computed before the collective), so the caller may still use or re-send it."""
+
+    def __init__(self, msg, local=None):
+        super().__init__(msg)
+        self.local = local
 
 
 def shard_bounds(batch, world, rank):
@@ -60,5 +75,8 @@ def gather_slices(local, batch, group=None, like=None):
     if local is not None and local.shape[0]:
         pad[: local.shape[0]] = local
     out = [torch.empty_like(pad) for _ in range(world)]
-    dist.all_gather(out, pad, group=group)
+    try:
+        dist.all_gather(out, pad, group=group)
+    except (RuntimeError, dist.DistBackendError) as e:       # peer gone (connection closed) or silent (group timeout)
+        raise ShardError("rank %d of %d: the gather of this step failed: %s" % (rank, world, str(e).splitlines()[0]), local) from e
     return torch.cat([o[:n] for o, n in zip(out, sizes)], dim=0)

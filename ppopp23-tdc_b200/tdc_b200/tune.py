@@ -169,6 +169,8 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--out", default="tile_table.csv")
     ap.add_argument("--shapes", default="sweep", choices=["sweep", "resnet18", "resnet50", "tkblock", "densenet121"])
+    ap.add_argument("--shape-list", default=None,
+                    help="shapes of one's own instead of a named set: C,N,H,W,R,stride,pad;C,N,H,W,R,stride,pad;...")
     ap.add_argument("--max-per-shape", type=int, default=300)
     ap.add_argument("--model-top", type=int, default=60,
                     help="candidates the analytical model ranks best are always measured, beside the random sample")
@@ -182,7 +184,12 @@ def main(argv=None):
     stream = torch.cuda.current_stream()
     cover = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
     reps = 1 if a.batch >= 16 else 8
-    shapes = {"sweep": sweep_shapes, "resnet18": resnet18_shapes, "resnet50": resnet50_shapes, "tkblock": tkblock_shapes, "densenet121": densenet121_shapes}[a.shapes]()
+    if a.shape_list:
+        shapes = [tuple(int(v) for v in item.split(",")) for item in a.shape_list.split(";") if item.strip()]
+        if any(len(sh) != 7 for sh in shapes):
+            ap.error("--shape-list items are C,N,H,W,R,stride,pad")
+    else:
+        shapes = {"sweep": sweep_shapes, "resnet18": resnet18_shapes, "resnet50": resnet50_shapes, "tkblock": tkblock_shapes, "densenet121": densenet121_shapes}[a.shapes]()
     kept = best_rows(a.keep) if a.keep else {}
     with open(a.out, "w", newline="") as f:
         wr = csv.writer(f)

@@ -57,6 +57,47 @@ def test_bad_arguments_are_status_codes_not_crashes(T):
     assert lib.tdc_tk_block_workspace_bytes(2, 8, 5, 5, 4, 6, 8, 3, 3, 1, 1) >= 4 * (2 * 4 * 25 + 2 * 6 * 25)
 
 
+def test_every_refusal_leaves_its_reason_in_the_one_error_string(T):
+    """All entry points share one thread-local message (tdc_last_error_string; tdc_tc_last_error_string is the same
+    text): each non-zero status below must leave a message of its own there, not the previous call's."""
+    from tdc_b200 import _lib
+    lib = T.lib
+    one = C.c_void_p(16)         # a non-NULL, 16-byte aligned stand-in that no check dereferences before refusing
+    odd = C.c_void_p(20)         # ... and one that is not 16-byte aligned
+    h = C.c_void_p()
+    plan = _lib.TcPlan()
+    assert lib.tdc_tc_plan_make(8, 8, 3, 3, 4, C.byref(plan)) == 0
+    cases = [
+        ("pool NULL", lambda: lib.tdc_pool2d_f32(None, None, 1, 1, 4, 4, 2, 2, 0, 2, 0, None), _lib.ERR_NULL, b"tdc_pool2d_f32"),
+        ("pool window", lambda: lib.tdc_pool2d_f32(one, one, 1, 1, 4, 4, 2, 2, 2, 2, 0, None), _lib.ERR_SHAPE, b"padding"),
+        ("pool mode", lambda: lib.tdc_pool2d_f32(one, one, 1, 1, 4, 4, 2, 2, 0, 2, 7, None), _lib.ERR_UNSUPPORTED, b"mode 7"),
+        ("affine NULL", lambda: lib.tdc_affine_relu_f32(None, None, None, None, 1, 1, 1, 1, 1, 0, None), _lib.ERR_NULL, b"tdc_affine_relu_f32"),
+        ("affine stride", lambda: lib.tdc_affine_relu_f32(one, one, None, None, 2, 4, 9, 8, 36, 0, None), _lib.ERR_SHAPE, b"strides"),
+        ("conv create", lambda: lib.tdc_conv_create(C.byref(h), 0, 1, 1, 1, 1, 0, 1, 1, 1, None, None), _lib.ERR_SHAPE, b"tdc_conv_create"),
+        ("conv precision", lambda: lib.tdc_conv_set_precision(None, 3), _lib.ERR_NULL, b"tdc_conv_set_precision"),
+        ("conv forward", lambda: lib.tdc_conv_forward(None, None, None, None), _lib.ERR_NULL, b"tdc_conv_forward"),
+        ("host forward", lambda: lib.tdc_conv_forward_host_async(None, None, None, None), _lib.ERR_NULL, b"tdc_conv_forward_host_async"),
+        ("tkconv create", lambda: lib.tdc_tkconv_create(C.byref(h), 1, 1, 1, 1, 1, 1, 1, 3, 3, 0, 1, None, None, None, None), _lib.ERR_SHAPE, b"tdc_tkconv_create"),
+        ("tkconv forward", lambda: lib.tdc_tkconv_forward(None, None, None, None), _lib.ERR_NULL, b"tdc_tkconv_forward"),
+        ("tc plan", lambda: lib.tdc_tc_plan_make(8, 8, 5, 5, 3, C.byref(plan)), _lib.ERR_UNSUPPORTED, b"5x5"),
+        ("tc unaligned filter", lambda: lib.tdc_conv2d_tc(C.byref(plan), one, odd, one, 1, 4, 4, None, 0, None), _lib.ERR_UNSUPPORTED, b"16-byte"),
+        ("tc prepare unaligned", lambda: lib.tdc_tc_prepare_weights(C.byref(plan), one, 0, odd, None), _lib.ERR_UNSUPPORTED, b"16-byte"),
+        ("tc flags", lambda: lib.tdc_conv2d_tc(C.byref(plan), one, one, one, 1, 4, 4, None, 0x100, None), _lib.ERR_UNSUPPORTED, b"flag"),
+        ("tc ranged other mode", None, None, None),
+    ]
+    for name, call, want, needle in cases:
+        if call is None:
+            continue
+        got = call()
+        msg = lib.tdc_last_error_string()
+        assert got == want and needle in msg, (name, got, msg)
+        assert lib.tdc_tc_last_error_string() == msg, name
+    p3 = _lib.TcPlan()
+    assert lib.tdc_tc_plan_make(8, 8, 3, 3, 3, C.byref(p3)) == 0
+    assert lib.tdc_conv2d_tc_ranged(C.byref(p3), one, one, one, 1, 4, 4, None, 0, None, one, None) == _lib.ERR_UNSUPPORTED
+    assert b"y_absmax" in lib.tdc_last_error_string()
+
+
 @pytest.mark.parametrize("B", [1, 64])
 @pytest.mark.parametrize("H,R1,R2", SWEEP)
 def test_selector_gives_a_launchable_tile(T, B, H, R1, R2):

@@ -72,3 +72,52 @@ def test_sharded_forward_equals_single_process(built, world, batches):
         assert out.shape == whole.shape
         assert torch.allclose(out, whole, atol=1e-6)      # every rank holds the full result, rank order kept
         assert calls == ([b - a] if b > a else [1])       # one forward on its slice (one image if it owns none)
+
+
+def _failing_worker(rank, world, port, q, mode):
+    """Step 1 is healthy.  Then rank 1 leaves between steps (`exit`) or stays but never joins the next gather
+    (`silent`); rank 0 runs step 2 and must get ShardError, with its own slice attached, instead of hanging."""
+    import datetime
+    import time
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.join(ROOT, "ppopp23-tdc_b200"))
+    from tdc_b200.parallel import ShardError, forward_sharded
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    images = torch.arange(8.0).view(8, 1)
+    out = forward_sharded(lambda x: x * 2, images)
+    q.put((rank, "step1", out.flatten().tolist()))
+    def leave():                            # flush the result queue, then go without tearing the broken group down
+        q.close(); q.join_thread()
+        os._exit(0)
+    if rank == 1:
+        if mode == "silent":
+            time.sleep(12)                  # alive, but not in the collective: the group's timeout ends rank 0's wait
+        leave()                             # between steps, nothing in flight
+    t0 = time.time()
+    try:
+        forward_sharded(lambda x: x * 3, images)
+        q.put((rank, "step2", "no error"))
+    except ShardError as e:
+        q.put((rank, "step2", ("ShardError", e.local.flatten().tolist(), time.time() - t0)))
+    leave()
+
+
+@pytest.mark.parametrize("mode", ["exit", "silent"])
+def test_a_rank_that_leaves_between_steps_ends_the_next_gather_with_an_error(built, mode):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, q, mode)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [q.get(timeout=120) for _ in range(3)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    step1 = sorted(g for g in got if g[1] == "step1")
+    assert [g[2] for g in step1] == [[2.0 * i for i in range(8)]] * 2
+    (rank, _, res), = [g for g in got if g[1] == "step2"]
+    assert rank == 0 and res[0] == "ShardError"
+    assert res[1] == [3.0 * i for i in range(4)]          # rank 0's own slice was computed and is handed back
+    assert res[2] < 60                                     # bounded: the connection error or the 4 s group timeout

@@ -52,6 +52,45 @@ def test_module_surfaces(built):
     assert 0 < float(torch.linalg.norm(w - dense) / torch.linalg.norm(dense)) < 0.9
 
 
+def test_reference_m_variant_runs_the_chain_the_gpu_test_compares_with(built):
+    """Where the reference tree is mounted (never on the GPU box): its own TKConv2dM, loaded with our module's state dict,
+    gives bit for bit the F.linear / F.conv2d chain that the GPU test below uses as its reference."""
+    if not ref_import.available():
+        pytest.skip("reference tree not mounted")
+    from tdc_b200.tkconv_variants import TKConv2dM_B200
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(3, 16, 14, 14, generator=g)
+    m = TKConv2dM_B200(16, 24, 3, stride=2, padding=1, hp_dict=HP, name="l")
+    with torch.no_grad():
+        m.bias.normal_(generator=g)
+    F = torch.nn.functional
+    ref = F.linear(x.permute(0, 2, 3, 1), m.first_factor).permute(0, 3, 1, 2)
+    ref = F.conv2d(ref, m.core_kernel, None, 2, 1)
+    ref = F.linear(ref.permute(0, 2, 3, 1), m.last_factor, m.bias).permute(0, 3, 1, 2).detach()
+    TK = ref_import.import_tkconv()
+    rm = TK.TKConv2dM(16, 24, 3, stride=2, padding=1, hp_dict=HP, name="l")
+    rm.load_state_dict(m.state_dict())
+    assert torch.equal(rm(x).detach(), ref)
+
+
+def test_reference_network_builder_takes_our_module_as_its_conv_class(built):
+    """The drop-in claim for the Python surface: the reference's own _tt_resnet(TTBasicBlock, [2,2,2,2], conv=...)
+    (inference/resnet_inet_tt.py:432-448) builds with TKConv2dC_B200 injected as the conv class, and the network it
+    makes has exactly the state-dict keys and shapes it has with the reference's TKConv2dC."""
+    if not ref_import.available():
+        pytest.skip("reference tree not mounted")
+    import tdc_b200 as T
+    R = ref_import.import_resnet()
+    TK = ref_import.import_tkconv()
+    hp = T.HalfRanks((2, 2, 2, 2))
+    ours = R._tt_resnet(R.TTBasicBlock, [2, 2, 2, 2], conv=T.TKConv2dC_B200, hp_dict=hp)
+    theirs = R._tt_resnet(R.TTBasicBlock, [2, 2, 2, 2], conv=TK.TKConv2dC, hp_dict=hp)
+    ko = [(k, tuple(v.shape)) for k, v in ours.state_dict().items()]
+    kt = [(k, tuple(v.shape)) for k, v in theirs.state_dict().items()]
+    assert ko == kt and sum(isinstance(m, T.TKConv2dC_B200) for m in ours.modules()) == 16
+    ours.load_state_dict(theirs.state_dict())           # a checkpoint of the reference network loads unchanged
+
+
 @pytest.mark.gpu
 def test_m_and_r_variants_agree_with_the_reference_chain(built):
     import tdc_b200 as T
@@ -66,11 +105,6 @@ def test_m_and_r_variants_agree_with_the_reference_chain(built):
     ref = F.linear(x.permute(0, 2, 3, 1), m.first_factor).permute(0, 3, 1, 2)
     ref = F.conv2d(ref, m.core_kernel, None, 2, 1)
     ref = F.linear(ref.permute(0, 2, 3, 1), m.last_factor, m.bias).permute(0, 3, 1, 2).detach()
-    if ref_import.available():
-        TK = ref_import.import_tkconv()
-        rm = TK.TKConv2dM(16, 24, 3, stride=2, padding=1, hp_dict=HP, name="l")
-        rm.load_state_dict(m.state_dict())
-        assert torch.equal(rm(x).detach(), ref)
     y = m.cuda()(x.cuda())
     assert rel_err(y.cpu().numpy(), ref.numpy()) <= FP32_TOL
     r = TKConv2dR_B200(16, 24, 3, stride=2, padding=1, hp_dict=HP, name="l")

@@ -55,6 +55,36 @@ def test_two_calls_in_a_row_match_the_regular_entry_point(T):
     assert np.array_equal(y3, y1)
 
 
+def test_the_call_itself_claims_no_device_memory(T):
+    """The property the entry point exists for, measured: with every buffer of the call allocated beforehand, free
+    device memory as the driver reports it (cudaMemGetInfo, which sees every allocation of the process, cached or not)
+    is the same before and after a second and a third call.  (The first call on a device may load the library's code,
+    built-in workspace included; that is the start-up call the header asks for.)"""
+    from tdc_b200 import _lib
+    x, first, core, last, b = draw_block(503, 4, 32, 48, 16, 24, 28, 28, 3, True)
+    xd, fd, cd, ld, bd = x.cuda(), first.cuda(), core.cuda(), last.cuda(), b.cuda()
+    y = torch.empty(4, 48, 28, 28, device="cuda")
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call():
+        rc = T.lib.tdc_tk_block_f32_static(ptr(xd), ptr(fd), ptr(cd), ptr(ld), ptr(bd), ptr(y), 4, 32, 28, 28, 16, 24, 48, 3, 3,
+                                           1, 1, _lib.W_KCRS, _lib.EPI_NONE, None, st)
+        torch.cuda.synchronize()
+        return rc
+    assert call() == 0                                   # start-up call
+    free0 = torch.cuda.mem_get_info()[0]
+    assert call() == 0
+    free1 = torch.cuda.mem_get_info()[0]
+    assert call() == 0
+    free2 = torch.cuda.mem_get_info()[0]
+    assert free0 == free1 == free2
+    # a missing input is refused with a status code, nothing is dereferenced
+    rc = T.lib.tdc_tk_block_f32_static(None, ptr(fd), ptr(cd), ptr(ld), ptr(bd), ptr(y), 4, 32, 28, 28, 16, 24, 48, 3, 3,
+                                       1, 1, _lib.W_KCRS, _lib.EPI_NONE, None, st)
+    assert rc == _lib.ERR_NULL and T.lib.tdc_last_error_string()
+
+
 def test_sizes_beyond_the_built_in_workspace_are_rejected(T):
     from tdc_b200 import _lib
     B, Cc, R1, R2, K, H = 64, 64, 32, 32, 64, 56            # needs 51 MB of intermediates
