@@ -263,14 +263,15 @@ TDC_API int tdc_tk_block_f32_static(const float* x, const float* w1, const float
  *   mode 4  "3xFP16": the same split with fp16 parts (the lo part scaled by 2^11 to stay clear of fp16's
  *           subnormals): the same 22 significant bits per operand at twice the MMA rate and half the
  *           accumulations per output, so both faster and closer to fp64 than mode 3; the input and the filter
- *           are scaled by powers of two into fp16's range (see tdc_conv2d_tc_ranged), so any finite fp32 data is
- *           taken; the prepared filter carries a scratch tail that the call in flight uses, so calls sharing
- *           one prepared filter must not overlap on the GPU
+ *           are scaled by powers of two into fp16's range (see tdc_conv2d_tc_ranged); with TDC_TC_EXACT_RANGE the
+ *           prepared filter's scratch tail is used by the call in flight, so such calls sharing one prepared
+ *           filter must not overlap on the GPU
  *   mode 1  plain TF32: one MMA per product; 5e-3 bar; reported separately
  * Use: tdc_tc_plan_make once per layer shape, tdc_tc_prepare_weights once per weight load
  * into a caller-owned buffer of plan.weights_bytes, then tdc_conv2d_tc per call.  Every
  * device-side wait is bounded; tdc_tc_status reads (and synchronises for) the device status
- * word: 0 = no wait ever ran out.
+ * word: 0 = no wait ever ran out and no mode-4 output was non-finite, 1 = a wait ran out, 2 = a
+ * mode-4 launch produced a value that is not finite (input beyond the scaled fp16 range).
  */
 typedef struct tdc_tc_plan {
     int    C, K, R, S, mode;
@@ -299,14 +300,20 @@ TDC_API int tdc_tc_prepare_weights(const tdc_tc_plan* plan, const float* w, int 
 #define TDC_TC_STRIDE_MASK 0x0F  /* flags & mask = stride - 1 (1x1 filters and general plans)         */
 #define TDC_TC_PAD_MASK    0xF0  /* (flags & mask) >> 4 = padding (general plans); other bits must be 0 */
 #define TDC_TC_PAD_SHIFT   4
+#define TDC_TC_EXACT_RANGE 0x100 /* mode 4: find max|x| with a pass over x instead of sampling it (see tdc_conv2d_tc_ranged) */
 TDC_API int tdc_conv2d_tc(const tdc_tc_plan* plan, const float* x, const void* wt, float* y,
                           int B, int H, int W, const tdc_epilogue* epi, int flags, void* stream);
-/* Mode 4 scales the input by a power of two so that its largest magnitude lands just under 2^15 (fp16 ends at 65504),
- * and undoes the scaling in the epilogue; for that it must know max|x|.  tdc_conv2d_tc finds it with a pass over x
- * ahead of the convolution.  A caller that chains layers (the three steps of TKConv2dC.forward,
- * inference/TKConv.py:90-95) can save that pass: y_absmax, when given, receives the partial maxima of |y|
- * (TDC_TC_ABSMAX_FLOATS floats, every entry written), and the next call takes the same buffer as x_absmax.  Either
- * pointer may be NULL; x_absmax must bound the x of THIS call (a maximum over more data only costs precision).
+/* Mode 4 scales the input by a power of two into fp16's range (which ends at 65504) and undoes the scaling in the
+ * epilogue.  fp16 keeps its 11 significant bits over 30 binades, so the scale need only be roughly right:
+ *   - by default every CTA of the kernel samples some 1300 elements spread over x and puts the largest at 2^8, which
+ *     leaves a factor of 256 for values the sample missed (no extra launch, about a microsecond);
+ *   - with TDC_TC_EXACT_RANGE in `flags` a pass over all of x finds the true maximum first (one more launch);
+ *   - a caller that chains layers (the three steps of TKConv2dC.forward, inference/TKConv.py:90-95) has the bound
+ *     for free: y_absmax, when given, receives the partial maxima of |y| (TDC_TC_ABSMAX_FLOATS floats, every entry
+ *     written), and the next call takes the same buffer as x_absmax (it must bound the x of THAT call; a bound over
+ *     more data only costs precision).
+ * An input that leaves fp16's range all the same (more than 256 times the sampled maximum, or not finite) makes
+ * outputs that are not finite; the kernel sees them and sets the status word that tdc_tc_status reads to 2.
  * Other modes ignore x_absmax and refuse y_absmax. */
 #define TDC_TC_ABSMAX_FLOATS 1024
 TDC_API int tdc_conv2d_tc_ranged(const tdc_tc_plan* plan, const float* x, const void* wt, float* y,

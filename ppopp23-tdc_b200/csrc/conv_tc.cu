@@ -85,21 +85,28 @@ struct Args {
     int nseg, seg_blocks;  // persistent kernel: the channel blocks of a tile are accumulated in nseg runs of seg_blocks
                            // blocks; each run starts fresh accumulators and is added to y in fp32 by the epilogue
     int nbox_cap;          // bulk-tensor loader: boxes a raw slot holds
-    // fp16 operands: the input is scaled by a power of two that brings its largest magnitude just under 2^15 (fp16 ends
-    // at 65504), the filter likewise when it is prepared, and the epilogue undoes both.
-    const float* x_absmax; // [ABSMAX_SLOTS] partial maxima of |x| (every entry valid; the largest one counts)
+    int step_y, step_x;    // bulk-tensor loader: 256 positions = step_y padded rows + step_x columns
+    // fp16 operands: the input is scaled by a power of two into fp16's range (which ends at 65504), the filter likewise
+    // when it is prepared, and the epilogue undoes both.  fp16 keeps its 11 significant bits over 30 binades, so the
+    // scale need not be exact: given a bound of |x| it goes just under 2^14; without one, every CTA takes the largest
+    // of some 1300 elements spread over x (two per thread) and puts that at 2^8, which leaves a factor of 256 for values the sample
+    // missed.  An input beyond even that turns into infinities, which the epilogue sees in its outputs and reports
+    // through the status word (2): never a silent wrong result.
+    const float* x_absmax; // [ABSMAX_SLOTS] partial maxima of |x| (every entry valid; the largest one counts), or nullptr
+    long long x_count;     // elements of x
     const float* w_scale;  // [1] the power of two the prepared filter was multiplied by
     float*       y_absmax; // [ABSMAX_SLOTS] or nullptr: partial maxima of |y| for the next layer (entry = CTA, rest zeroed)
     int* status;           // device status word: 0 ok, else first failure code
 };
 constexpr int ABSMAX_SLOTS = 1024;
 
-// The power of two that brings a tensor whose largest magnitude is m just under 2^15; 1 for an all-zero or non-finite m.
-__host__ __device__ __forceinline__ float range_scale(float m) {
+
+// The power of two that brings a magnitude m just under 2^target; 1 for a zero or non-finite m.
+__host__ __device__ __forceinline__ float range_scale(float m, int target = 14) {
     if (!(m > 0.f) || !(m < 3.0e38f)) return 1.f;
     int e;
     frexpf(m, &e);                                  // m = f * 2^e, 0.5 <= f < 1
-    int k = 15 - e;
+    int k = target - e;
     k = k < -60 ? -60 : (k > 60 ? 60 : k);
     return ldexpf(1.f, k);
 }
@@ -119,6 +126,30 @@ __device__ __forceinline__ float absmax_of(const float* slots, unsigned int* scr
     const float m = __uint_as_float(*scratch);
     __syncthreads();                               // every thread has read the word: the caller may reuse it
     return m;
+}
+
+// The largest magnitude among two elements per thread spread evenly over x (all of x when it is shorter).  Two steps, so
+// that the loads (one memory round trip, cold pages included) run under whatever the caller does between them:
+// range_sample_load issues this thread's loads, range_sample_max reduces them over the warps that need the result.
+constexpr int RANGE_PER_THREAD = 2;
+__device__ __forceinline__ unsigned int range_sample_load(const float* x, long long n) {
+    const int want = RANGE_PER_THREAD * (int)blockDim.x;
+    const long long step = n > want ? n / want : 1;
+    unsigned int m = 0;
+#pragma unroll
+    for (int i = 0; i < RANGE_PER_THREAD; ++i) {
+        const long long k = (long long)(threadIdx.x + i * blockDim.x) * step;
+        if (k < n) m = max(m, __float_as_uint(__ldg(x + k)) & 0x7fffffffu);
+    }
+    return m;
+}
+// `scratch` was zeroed before the block's last barrier; the `threads` threads that call this (whole warps) meet at
+// named barrier 1, the others need not wait for the samples.
+__device__ __forceinline__ float range_sample_max(unsigned int mine, unsigned int* scratch, int threads) {
+    const unsigned int m = __reduce_max_sync(0xffffffffu, mine);
+    if ((threadIdx.x & 31) == 0 && m) atomicMax(scratch, m);
+    asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+    return __uint_as_float(*reinterpret_cast<volatile unsigned int*>(scratch));
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -423,11 +454,11 @@ __device__ __forceinline__ void store_chunk(const Args& a, const uint32_t (&r)[3
 #pragma unroll
         for (int k = 0; k < 32; ++k) v[k] = fmaxf(v[k], 0.f);
     }
-    if (vmax && live) {                              // largest stored magnitude, for the range scaling of the next layer
-        float m = *vmax;
+    if (vmax && live) {                              // largest stored magnitude (as a bit pattern: a NaN must not get lost)
+        unsigned int m = __float_as_uint(*vmax);
 #pragma unroll
-        for (int k = 0; k < 32; ++k) m = fmaxf(m, k < n ? fabsf(v[k]) : 0.f);
-        *vmax = m;
+        for (int k = 0; k < 32; ++k) m = max(m, k < n ? (__float_as_uint(v[k]) & 0x7fffffffu) : 0u);
+        *vmax = __uint_as_float(m);
     }
     if (live) {
         if (n >= 32) {
@@ -985,9 +1016,10 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     a.nkb = p->nkb; a.n_ocb = p->n_ocb; a.hl = p->hl;
     const int taps = taps_r * taps_r;
     const int smem_max = facts.smem_max, sms = facts.sms;
-    // TF32 operands: long reductions get two main accumulators per tile (4*NT columns per tile instead of 2*NT).
-    // fp16 operands: one main accumulator; long reductions are cut into runs instead (below).
-    a.nmain = (!f16 && a.hl == 2 && (long long)p->nkb * taps > 320) ? 2 : 1;
+    // Long reductions get two main accumulators per tile, fed by even and odd channel blocks (4*NT columns per tile
+    // instead of 2*NT): beyond 320 accumulations with TF32 operands, beyond 144 with fp16 operands (whose layers are
+    // held closer to fp64); very long ones are cut into runs on top of that (below).
+    a.nmain = (a.hl == 2 && (long long)p->nkb * taps > (f16 ? 144 : 320)) ? 2 : 1;
     a.tile_cols = (a.nmain == 2 ? 4 : 2) * p->nt;
     // The persistent kernel wins where a CTA tile is short and its prologue and epilogue would otherwise show: split
     // operands with up to 64 output channels per block, and one-tap filters of any block size (with few tiles too:
@@ -1020,7 +1052,8 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     // channel dimension of the tensor map must be a multiple of 16 bytes), 16-byte aligned input.
     const bool bulk_ok = f16 && !p->general && stride == 1 && ((long long)Hin * Win) % 4 == 0 && x_al16 && encode_tiled() != nullptr;
     bool bulk = bulk_ok && (tn.bulk >= 0 ? tn.bulk != 0 : true);
-    if (bulk && mt > 2) mt = 2;                                 // its producer is the fourth issuer warp
+    // a warp computes the pixel runs of the images a patch meets one image per lane: at most 32 images per patch
+    if (bulk && ((long long)2 * M_TILE + 2 * pad * (a.Wp + 1)) / a.Lp + 2 > 32) bulk = false;
     const size_t header = persist ? P_HEADER : 128;
     const int halo_unit = 2 * pad * (a.Wp + 1);
     // Position tiles per CTA: the largest candidate (4, 2, 1; what tensor memory and shared memory hold) that still
@@ -1036,6 +1069,17 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
         if (cap) *cap = c;
         return (size_t)c * BOXC * BOXW * sizeof(float);
     };
+    // The bulk loader holds two position tiles per CTA at most.  Where the ring could hold four (blocks of 32 output
+    // channels leave the shared memory for it) and there are tiles enough for that, the smaller share of halo rows wins:
+    // 56x56x32 at batch 64: ring with four tiles 35.7 us, bulk with two 39.4 us; with blocks of 64 channels both hold
+    // two and the bulk loader wins (56x56x64: 61 against 78 us).
+    if (bulk && tn.bulk < 0 && mt >= 4 && taps == 9) {
+        const int P4 = ((4 * M_TILE + halo_unit) + 7) / 8 * 8;
+        const size_t sb4 = sizeof(float) * ((size_t)a.hl * CB * P4 + (size_t)a.hl * taps * CB * p->nt), rb4 = sizeof(float) * (size_t)cbk * P4;
+        const long long tiles4 = ((a.total_pos + 4ll * M_TILE - 1) / (4ll * M_TILE)) * a.n_ocb;
+        if (2 * sb4 + 2 * rb4 <= room && P4 <= 4 * LOADERS && tiles4 >= sms) bulk = false;
+    }
+    if (bulk && mt > 2) mt = 2;                                 // its producer is the fourth issuer warp
     int best_mt = 0, big_mt = 0;
     double best_cost = 0.0, big_cost = 0.0;
     bool best_l2_bound = false;
@@ -1068,6 +1112,7 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     int cap = 0;
     const size_t raw_bytes = raw_bytes_of(mt, a.P, bulk, &cap);
     a.nbox_cap = cap;
+    a.step_y = LOADERS / a.Wp; a.step_x = LOADERS % a.Wp;
     // One-tap filters (1x1, general plans) do one or two MMAs per channel block and position tile: a stage of one
     // block would be all hand-over.  Their stages take up to four blocks (what leaves room for two stages and,
     // with a raw ring, two raw slots).
@@ -1099,9 +1144,11 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     a.tmem_cols = 32;
     while (a.tmem_cols < nbuf * mt * a.tile_cols) a.tmem_cols *= 2;
     // Runs: at most `chain` MMAs feed one accumulator before the epilogue takes the partial sum over in fp32.  The
-    // error of the tensor core's running sum grows by about 2.5e-8 of the output scale per accumulation.
+    // error of the tensor core's running sum grows by about 2.5e-8 of the output scale per accumulation.  A run
+    // boundary costs an extra pass of the epilogue over y (measured: about a microsecond per MB of y), so the default
+    // only cuts reductions of more than 576 MMAs per output (3x3 filters over more than 1024 channels).
     a.nseg = 1; a.seg_blocks = a.nkb;
-    const int chain = tn.chain >= 0 ? tn.chain : (f16 ? 144 : 0);
+    const int chain = tn.chain >= 0 ? tn.chain : (f16 ? 288 : 0);
     if (persist && chain > 0) {
         const long long accs = ((long long)a.nkb * taps + a.nmain - 1) / a.nmain;
         int nseg = (int)((accs + chain - 1) / chain);
@@ -1168,7 +1215,8 @@ int tdc_conv2d_tc_ranged(const tdc_tc_plan* p, const float* x, const void* wt, f
     if (y_absmax && p->mode != 4) return tc_fail(TDC_ERR_UNSUPPORTED, "y_absmax is written by mode 4 (fp16 operands) only");
     if (B <= 0 || H <= 0 || W <= 0) return tc_fail(TDC_ERR_SHAPE, "B=%d H=%d W=%d", B, H, W);
     const int stride = (flags & TDC_TC_STRIDE_MASK) + 1, gpad = (flags & TDC_TC_PAD_MASK) >> TDC_TC_PAD_SHIFT;
-    if (flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK)) return tc_fail(TDC_ERR_UNSUPPORTED, "unknown flag bits %#x", flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK));
+    if (flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK | TDC_TC_EXACT_RANGE))
+        return tc_fail(TDC_ERR_UNSUPPORTED, "unknown flag bits %#x", flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK | TDC_TC_EXACT_RANGE));
     if (!p->general && stride > 1 && p->R != 1) return tc_fail(TDC_ERR_UNSUPPORTED, "a stride is taken for 1x1 filters and general plans only");
     if (!p->general && gpad != 0) return tc_fail(TDC_ERR_UNSUPPORTED, "a padding is taken for general plans only (the others pad (R-1)/2)");
     if (reinterpret_cast<uintptr_t>(wt) % 16 != 0) return tc_fail(TDC_ERR_UNSUPPORTED, "wt must be 16-byte aligned (the kernels fetch it with bulk copies)");
@@ -1195,14 +1243,14 @@ int tdc_conv2d_tc_ranged(const tdc_tc_plan* p, const float* x, const void* wt, f
     const bool x_al16 = reinterpret_cast<uintptr_t>(x) % 16 == 0;
     Launch L;
     if (tuning_enabled()) {
-        const int rc = plan_launch(p, B, H, W, flags, x_al16, facts, read_tuning(), &L);
+        const int rc = plan_launch(p, B, H, W, flags & ~TDC_TC_EXACT_RANGE, x_al16, facts, read_tuning(), &L);
         if (rc) return rc;
     } else {
-        const LaunchKey key{device, p->C, p->K, p->R, p->S, p->mode, p->nt, p->general, B, H, W, flags, x_al16 ? 1 : 0};
+        const LaunchKey key{device, p->C, p->K, p->R, p->S, p->mode, p->nt, p->general, B, H, W, flags & ~TDC_TC_EXACT_RANGE, x_al16 ? 1 : 0};
         std::lock_guard<std::mutex> lk(g_tc_mu);
         auto it = g_tc_launches.find(key);
         if (it == g_tc_launches.end()) {
-            const int rc = plan_launch(p, B, H, W, flags, x_al16, facts, Tuning{}, &L);
+            const int rc = plan_launch(p, B, H, W, flags & ~TDC_TC_EXACT_RANGE, x_al16, facts, Tuning{}, &L);
             if (rc) return rc;
             it = g_tc_launches.emplace(key, L).first;
         }
@@ -1217,9 +1265,10 @@ int tdc_conv2d_tc_ranged(const tdc_tc_plan* p, const float* x, const void* wt, f
         a.w_scale = tail + ABSMAX_SLOTS;
         a.y_absmax = y_absmax;
         a.x_absmax = x_absmax;
-        if (!x_absmax) {
-            // nobody told us how large the input gets: one pass over it first (x then sits in L2 for the convolution)
-            const long long n = (long long)B * p->C * H * W;
+        a.x_count = (long long)B * p->C * H * W;
+        if (!x_absmax && (flags & TDC_TC_EXACT_RANGE)) {
+            // the caller wants the scale taken from the true maximum: one pass over the input first
+            const long long n = a.x_count;
             const long long want = (n + 8191) / 8192;                      // 32 elements per thread at least
             const unsigned blocks = (unsigned)(want < 1 ? 1 : (want > 4 * facts.sms ? 4 * facts.sms : want));
             absmax_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(x, n, tail);

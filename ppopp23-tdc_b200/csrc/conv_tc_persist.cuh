@@ -40,6 +40,8 @@ namespace tdc_tc {
 #endif
 constexpr int P_GROUPS  = TDC_TC_EPI_GROUPS;          // groups of four epilogue warps
 constexpr int P_THREADS = 384 + 128 * P_GROUPS;     // 8 loader warps, 4 issuer warps (one lane each), the epilogue groups
+constexpr int P_PRODUCER = 11;   // the bulk loader's producer is the fourth issuer warp, free when MT <= 2 (a 21st warp would cost
+                                 // every thread registers: the allocation rounds the CTA up to 768 threads)
 constexpr int P_HEADER  = 1024;  // bytes of barriers, flags and the producer's box table in front of the stages
 constexpr int P_MAXBOX  = 64;    // boxes one raw slot may hold (entries of the box table)
 constexpr int LD_RING = 0, LD_VEC = 1, LD_BULK = 2;
@@ -113,7 +115,7 @@ __device__ unsigned long long g_tc_prof[16];   // [0, 12) kinds of wait or span,
 template <int NT, int MT, int TAPS, int LD, bool F16>
 __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a, const __grid_constant__ CUtensorMap tmap) {
     static_assert(LD != LD_VEC || (TAPS == 1 && !F16), "the 16-byte register loader serves 1x1 filters with TF32 operands");
-    static_assert(LD != LD_BULK || (F16 && MT <= 2), "the bulk loader's producer is issuer warp 3, free when MT <= 2");
+    static_assert(LD != LD_BULK || (F16 && MT <= 2), "the bulk loader converts to fp16 parts; its producer is issuer warp 3, free when MT <= 2");
     constexpr int CBK = KStep<F16>::CH;                               // channels per block
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint64_t* full_bar   = reinterpret_cast<uint64_t*>(smem_raw);    // [ns]  patch stored + filter landed
@@ -124,7 +126,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     uint64_t* rempty_bar = rfull_bar + 8;                             // [depth] ... and have been converted
     uint32_t* tmem_slot  = reinterpret_cast<uint32_t*>(rempty_bar + 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    unsigned int* max_word = reinterpret_cast<unsigned int*>(tmem_slot + 2);   // block-wide maximum: of |x| at the start, of |y| at the end
+    unsigned int* max_word = reinterpret_cast<unsigned int*>(tmem_slot + 2);   // block-wide maximum: of |x| (given bounds) at the start, of |y| at the end
+    unsigned int* range_word = reinterpret_cast<unsigned int*>(tmem_slot + 3); // largest sampled |x|
     int2*     box_tab    = reinterpret_cast<int2*>(smem_raw + 512);   // producer only: (first pixel, image) of each box
     float*    stage0     = reinterpret_cast<float*>(smem_raw + P_HEADER);
 
@@ -141,12 +144,16 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     const uint32_t b_bytes = (uint32_t)b_floats * 4u;
     const int nbuf = a.nbuf;
     const long long ntiles = a.ntiles;          // position tiles x output-channel blocks
+    // fp16 operands without a bound of |x|: this thread's samples of the input, loaded now, reduced after the set-up below
+    unsigned int sampled = 0;
+    if constexpr (F16) { if (!a.x_absmax && (warp < 8 || warp >= 12)) sampled = range_sample_load(a.x, a.x_count); }
 
     if (tid == 0) {
         for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], LOADERS / 32 + 1); mbar_init(&empty_bar[s], MT); }   // one arrival per loader warp + the filter's bytes
         for (int b = 0; b < 8; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4 * (NT / 32)); }   // one per issuer; one per epilogue warp and 32-channel chunk
         for (int d = 0; d < 8; ++d) { mbar_init(&rfull_bar[d], 1); mbar_init(&rempty_bar[d], LOADERS / 32); }    // the producer's arrive + bytes; one per converting warp
         *abort_flag = 0;
+        *range_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 8) {
@@ -160,11 +167,19 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     TDC_PROF_DECL;
     // fp16 operands: the power of two that brings the input just under 2^15, and the factor that undoes it (and the
     // filter's, applied when it was prepared) in the epilogue
+    // (with a bound of |x| everybody reads it here; without one only the converting and the draining warps need the
+    // scale and wait for the samples, at named barrier 1, while the producer and the issuers already start)
     float xs = 1.f, inv = 1.f;
+    constexpr int SCALED_THREADS = LOADERS + 128 * P_GROUPS;
     if constexpr (F16) {
-        xs = range_scale(absmax_of(a.x_absmax, max_word));
+        if (a.x_absmax) {
+            xs = range_scale(absmax_of(a.x_absmax, max_word), 14);
+            if (tid == 0) *max_word = 0;                 // from here on: the largest |y| of this CTA (read after the last barrier)
+        } else if (warp < 8 || warp >= 12) {
+            if (tid == 0) *max_word = 0;
+            xs = range_scale(range_sample_max(sampled, range_word, SCALED_THREADS), 8);
+        }
         inv = 1.f / (xs * a.w_scale[0]);
-        if (tid == 0) *max_word = 0;                 // from here on: the largest |y| of this CTA (read after the last barrier)
     }
 
     if (warp < 8) {
@@ -284,31 +299,42 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 int roff[PPT];
                 TDC_PROF_SPAN_BEGIN;
                 {
-                    int g_img[PPT], g_pix[PPT];            // image and pixel of each owned row (-1: padding)
+                    // Division-free but for the first row: a thread's rows are 256 positions apart, so (image, row,
+                    // column) of the next one follow from the previous by adding (step_y, step_x) with carries.  The
+                    // first position is taken one image up (gp0 may be negative by less than an image), image -1 = before x.
+                    const int Hp = a.Lp / a.Wp;                                  // rows of a padded image (once per tile: two divisions)
+                    const long long g_first = gp0 + tid + a.Lp;
+                    long long bi = image_of(a, g_first);
+                    int rem = (int)(g_first - bi * a.Lp);
+                    int yy = rem / a.Wp, xx = rem - yy * a.Wp;
+                    bi -= 1;
+                    // the runs of the images this patch meets, one image per lane: first pixel (rounded down to 16 bytes),
+                    // boxes, and by a prefix sum the first box of each image in the raw slot
+                    const long long lo = gp0 < 0 ? 0 : gp0, hi = (gp0 + rows < a.total_pos ? gp0 + rows : a.total_pos) - 1;
+                    const long long b_first = image_of(a, lo), b_last = image_of(a, hi);
+                    int my_pix4 = 0, my_nbox = 0;
+                    if (b_first + lane <= b_last) image_run(a.H, a.W, a.Wp, a.Lp, gp0, rows, b_first + lane, my_pix4, my_nbox);
+                    int my_box0 = my_nbox;                                       // inclusive scan, made exclusive below
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+                        const int v = __shfl_up_sync(0xffffffffu, my_box0, d);
+                        if (lane >= d) my_box0 += v;
+                    }
+                    my_box0 -= my_nbox;
 #pragma unroll
                     for (int i = 0; i < PPT; ++i) {
                         const int pp = tid + i * LOADERS;
-                        roff[i] = -1; g_img[i] = -1; g_pix[i] = 0;
-                        const long long g = gp0 + pp;
-                        if (pp < rows && g >= 0 && g < a.total_pos) {
-                            const long long b = image_of(a, g);
-                            const int rem = (int)(g - b * a.Lp);
-                            const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
-                            if (yy < a.H && xx < a.W) { g_img[i] = (int)b; g_pix[i] = yy * a.W + xx; }
+                        const long long j = bi - b_first;                        // lane that holds this row's image
+                        const int src = (j >= 0 && j < 32) ? (int)j : 0;
+                        const int pix4 = __shfl_sync(0xffffffffu, my_pix4, src), box0 = __shfl_sync(0xffffffffu, my_box0, src);
+                        roff[i] = -1;
+                        if (pp < rows && bi >= 0 && bi < a.B && yy < a.H && xx < a.W && j >= 0 && j < 32) {
+                            const int d = yy * a.W + xx - pix4;
+                            roff[i] = (box0 + d / BOXW) * (BOXC * BOXW) + (d & (BOXW - 1));
                         }
-                    }
-                    const long long lo = gp0 < 0 ? 0 : gp0, hi = (gp0 + rows < a.total_pos ? gp0 + rows : a.total_pos) - 1;
-                    int box0 = 0;
-                    for (long long b = image_of(a, lo), b_last = image_of(a, hi); b <= b_last; ++b) {
-                        int pix4, nbox;
-                        image_run(a.H, a.W, a.Wp, a.Lp, gp0, rows, b, pix4, nbox);
-#pragma unroll
-                        for (int i = 0; i < PPT; ++i)
-                            if (g_img[i] == (int)b) {
-                                const int d = g_pix[i] - pix4;
-                                roff[i] = (box0 + d / BOXW) * (BOXC * BOXW) + (d & (BOXW - 1));
-                            }
-                        box0 += nbox;
+                        xx += a.step_x; yy += a.step_y;                          // 256 positions on
+                        if (xx >= a.Wp) { xx -= a.Wp; ++yy; }
+                        while (yy >= Hp) { yy -= Hp; ++bi; }
                     }
                 }
                 TDC_PROF_SPAN_END(6);
@@ -477,7 +503,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     }
     if (warp < 8) TDC_PROF_FLUSH(0);
     if (warp < 8) {}
-    else if (LD == LD_BULK && warp == 11) {
+    else if (LD == LD_BULK && warp == P_PRODUCER) {
+      {
         // ================= producer of the bulk loader: one thread =================
         // Per tile the list of boxes (first pixel, image) is the same for every channel block; a block's boxes go
         // to one raw slot, whose mbarrier counts their bytes (a box is written whole, padding included).
@@ -520,6 +547,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             TDC_PROF_FLUSH(1);
         }
         __syncwarp();
+      }
     }
     else if (warp < 12) {
         // ================= MMA issuers: warp 8+mt owns position tile mt =================
@@ -580,12 +608,12 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
         // The work items of a CTA tile are (position tile, 32-channel chunk) pairs, dealt to the groups in turn: the
         // epilogue is a latency chain (tensor memory -> registers -> residual loads -> stores), and several chains in
         // flight hide more of it than one; all groups start on the first position tile, whose issuer is released first.
-        const int grp = (warp - 12) >> 2;
+        const int grp = (warp - 12) >> 2;          // warps 12 .. 12 + 4 * P_GROUPS - 1
         const int q = warp & 3;
         constexpr int CHUNKS = NT / 32;
         long long j = 0;
-        float ymax = 0.f;                       // largest magnitude this thread stored (kept only when the caller asked for it)
-        float* const track = a.y_absmax ? &ymax : nullptr;
+        float ymax = 0.f;                       // largest magnitude this thread stored, compared as a bit pattern (so a NaN counts as large)
+        float* const track = (F16 || a.y_absmax) ? &ymax : nullptr;
         for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x) {
             long long g0;
             int cnt, ocb;
@@ -634,6 +662,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (*abort_flag && tid == 0 && a.status) atomicCAS(a.status, 0, 1);
+    // an output that is not finite: the input went beyond fp16's range even after scaling (or was not finite itself)
+    if (F16 && tid == 0 && a.status && *max_word >= 0x7f800000u) atomicCAS(a.status, 0, 2);
     if (a.y_absmax) {                           // entry = CTA; CTA 0 clears the entries no CTA owns
         if (tid == 0) a.y_absmax[blockIdx.x] = __uint_as_float(*max_word);
         if (blockIdx.x == 0)

@@ -27,8 +27,10 @@ def _check(code):
 
 
 class TcConv:
-    def __init__(self, weight, mode=3, w_layout=_lib.W_KCRS, general=False):
-        """weight: [K][C][R][S] (or [C][R][S][K] with w_layout=W_CRSK), fp32 CUDA tensor."""
+    def __init__(self, weight, mode=3, w_layout=_lib.W_KCRS, general=False, exact_range=False):
+        """weight: [K][C][R][S] (or [C][R][S][K] with w_layout=W_CRSK), fp32 CUDA tensor.  `exact_range` (mode 4): take
+        the input's scale from its true maximum (a pass over the input per call) instead of from a sample."""
+        self.exact_range = bool(exact_range)
         if w_layout == _lib.W_KCRS:
             K, Cc, R, S = weight.shape
         else:
@@ -92,6 +94,8 @@ class TcConv:
                                          B, H, W, C.byref(e), flags, _stream()))
             return out
         xmax = getattr(x, "_tdc_absmax", None)
+        if xmax is None and self.exact_range:
+            flags |= 0x100                        # TDC_TC_EXACT_RANGE
         ymax = torch.empty(ABSMAX_FLOATS, device=x.device, dtype=torch.float32)
         with _on_device(x.device):
             _check(lib.tdc_conv2d_tc_ranged(C.byref(plan), _dev_f32(x, "x"), wt.data_ptr(), _dev_f32(out, "out"),

@@ -82,7 +82,7 @@ def test_every_refusal_leaves_its_reason_in_the_one_error_string(T):
         ("tc plan", lambda: lib.tdc_tc_plan_make(8, 8, 5, 5, 3, C.byref(plan)), _lib.ERR_UNSUPPORTED, b"5x5"),
         ("tc unaligned filter", lambda: lib.tdc_conv2d_tc(C.byref(plan), one, odd, one, 1, 4, 4, None, 0, None), _lib.ERR_UNSUPPORTED, b"16-byte"),
         ("tc prepare unaligned", lambda: lib.tdc_tc_prepare_weights(C.byref(plan), one, 0, odd, None), _lib.ERR_UNSUPPORTED, b"16-byte"),
-        ("tc flags", lambda: lib.tdc_conv2d_tc(C.byref(plan), one, one, one, 1, 4, 4, None, 0x100, None), _lib.ERR_UNSUPPORTED, b"flag"),
+        ("tc flags", lambda: lib.tdc_conv2d_tc(C.byref(plan), one, one, one, 1, 4, 4, None, 0x800, None), _lib.ERR_UNSUPPORTED, b"flag"),
         ("tc ranged other mode", None, None, None),
     ]
     for name, call, want, needle in cases:

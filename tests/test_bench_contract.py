@@ -39,7 +39,7 @@ def test_product_arm_line_on_gpu():
     for k in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "vs_baseline",
               "dtype", "data", "config", "clocks", "e2e", "gpu_launches", "roofline"):
         assert k in d, k
-    assert d["steps"] == 3 and d["gpu_launches"] == 2 * 8 * 3 and d["scaling"] == "weak" and d["data"] == "synthetic"
+    assert d["steps"] == 3 and d["gpu_launches"] == 8 * 3 and d["scaling"] == "weak" and d["data"] == "synthetic"
     rf = d["roofline"]
     assert rf["bound"] in ("hbm", "tensor") and 0.05 < rf["frac"] < 1.5 and abs(rf["frac"] - rf["achieved"] / rf["peak"]) < 1e-9
     assert rf["traffic"] is None or (isinstance(rf["traffic"], (int, float)) and rf["traffic"] > 0)

@@ -322,6 +322,13 @@ def test_fp16_parts_loaders_runs_and_range(T, B, Cc, K, H, W, R, monkeypatch):
     for sx, sw in ((1e-6, 1.0), (1e20, 1e-9), (3e4, 7e3)):
         ys = T.TcConv(wd * sw, mode=4)(xd * sx)
         assert rel_err(ys.cpu().numpy(), (ref * (sx * sw)).cpu().numpy()) <= max(2 * err, 2e-6), (sx, sw)
+    # the scale taken from the true maximum instead of a sample: the same result to rounding
+    assert rel_err(T.TcConv(wd, mode=4, exact_range=True)(xd).cpu().numpy(), ref.cpu().numpy()) <= max(2 * err, 2e-6)
+    # an outlier 100 times the largest value, which a sample of 4096 elements will not hit: inside the headroom
+    xo = xd.clone()
+    xo.view(-1)[12345 % xo.numel()] = 100.0 * float(xd.abs().max())
+    refo = torch.nn.functional.conv2d(xo.double(), wd.double(), None, 1, (R - 1) // 2)
+    assert rel_err(conv(xo).cpu().numpy(), refo.cpu().numpy()) <= FP32_TOL and tc.status() == 0
     assert float(y._tdc_absmax.max()) == float(y.abs().max())
     y_next = T.TcConv(torch.eye(K).view(K, K, 1, 1).cuda().contiguous(), mode=4)
     plain = y.clone()                                     # no recorded magnitude: the call makes its own pass
