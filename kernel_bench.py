@@ -1,8 +1,10 @@
-"""Times one memory-bound kernel of the library alone and prints its bandwidth.
+"""Times one kernel of the library alone and prints its bandwidth (and, for a convolution, its arithmetic rate).
 
     python kernel_bench.py affine  --batch 32 --channels 224 --of 256 --size 56
     python kernel_bench.py maxpool --batch 256 --channels 64 --size 112      # 3x3 / stride 2 / pad 1
     python kernel_bench.py maxpool2 --batch 128 --channels 64 --size 224     # 2x2 / stride 2
+    python kernel_bench.py conv --mode 4 --batch 64 --channels 64 --size 56 [--filter 3]   # core conv, channels -> channels
+                                                        # --mode 0: fp32 FMA kernel (table tile), 1 / 3 / 4: tensor cores
 
 `affine`: scale, shift and ReLU over the first `--channels` channels of a [batch][--of][size][size] buffer, the
 pre-activation of a DenseNet layer.  Algorithmic bytes = input read once + output written once; the L2 is flushed
@@ -18,9 +20,12 @@ sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "ppo
 
 def main(argv=None):
     import torch
+    import tdc_b200 as T
     from tdc_b200 import ops
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["affine", "maxpool", "maxpool2"])
+    ap.add_argument("kernel", choices=["affine", "maxpool", "maxpool2", "conv"])
+    ap.add_argument("--mode", type=int, default=4, choices=[0, 1, 3, 4])
+    ap.add_argument("--filter", type=int, default=3)
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--channels", type=int, default=224)
     ap.add_argument("--of", type=int, default=None, help="channels of the buffer the input is a prefix of (affine)")
@@ -38,6 +43,20 @@ def main(argv=None):
         out = torch.empty(B, C, H, H, device=dev)
         run = lambda: ops.affine_relu(buf[:, :C], scale, shift, relu=True, out=out)
         nbytes = 2 * out.numel() * 4
+    elif a.kernel == "conv":
+        k = a.filter
+        g = torch.Generator().manual_seed(1)
+        x = torch.randn(B, C, H, H, generator=g).to(dev)
+        w = (torch.randn(C, C, k, k, generator=g) * (2.0 / (C * k * k)) ** 0.5).to(dev)
+        out = torch.empty(B, C, H, H, device=dev)
+        if a.mode:
+            conv = T.TcConv(w, mode=a.mode)
+            run = lambda: conv(x, out=out)
+        else:
+            wc, tile = T.permute_weights(w), T.best_tile(B, C, H, H, C, k, k, (k - 1) // 2, 1)
+            run = lambda: T.core_conv2d(x, wc, 1, (k - 1) // 2, w_layout=T.W_CRSK, tile=tile, out=out)
+        nbytes = (x.numel() + out.numel() + w.numel()) * 4
+        flops = 2.0 * B * C * C * k * k * H * H
     else:
         x = torch.randn(B, C, H, H, device=dev)
         k, s, p = (3, 2, 1) if a.kernel == "maxpool" else (2, 2, 0)
@@ -55,7 +74,8 @@ def main(argv=None):
     t = statistics.median(ts)
     gbs = nbytes / t / 1e9
     frac = "" if a.peak_gbs is None else "  %.2f of %.1f GB/s" % (gbs / a.peak_gbs, a.peak_gbs)
-    print("%s: %.1f us, %.1f MB, %.1f GB/s%s" % (a.kernel, t * 1e6, nbytes / 1e6, gbs, frac))
+    extra = "  %.1f TFLOP/s (mode %d)" % (flops / t / 1e12, a.mode) if a.kernel == "conv" else ""
+    print("%s: %.1f us, %.1f MB, %.1f GB/s%s%s" % (a.kernel, t * 1e6, nbytes / 1e6, gbs, frac, extra))
 
 
 if __name__ == "__main__":
