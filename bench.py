@@ -202,9 +202,11 @@ def torch_reference_forward(torch, m, x):
 
 def bench_tk_block(torch, T, dev, time_layer, peaks):
     """The whole Tucker block (1x1 C->R1, 3x3 core, 1x1 R2->K) for the ResNet-50 bottleneck middles
-    C=K in {64@56, 128@28, 256@14, 512@7}, R1=R2=C/2, at batch 1 and 32: our three-launch chain
-    (tensor cores with split operands where the layer is large enough, fp32 FMA kernels otherwise)
-    beside the same three convolutions through torch/cuDNN.  HBM floor: x in + y out + filters once."""
+    C=K in {64@56, 128@28, 256@14, 512@7}, R1=R2=C/2, at batch 1 and 32, as the module runs it under "auto"
+    (`us`; `strategy` says whether that is the three-launch chain or ONE launch with the factors multiplied into
+    one filter, which keeps no intermediate at all), as three launches (`us_three_launches`), and through
+    torch/cuDNN both as the three convolutions the reference calls and as one dense conv on the same merged
+    filter.  `tflops` counts the block's factored FLOPs.  HBM floor: x in + y out + filters once."""
     import torch.nn.functional as F
 
     class HP:
@@ -229,12 +231,20 @@ def bench_tk_block(torch, T, dev, time_layer, peaks):
                 us = time_layer(lambda: m(x), iters=10)
                 ref = lambda t: F.conv2d(F.conv2d(F.conv2d(t, m.first_kernel), m.core_kernel, None, 1, 1), m.last_kernel)
                 cud = time_layer(lambda: ref(x), iters=10)
+                # the same block as three launches (the factored form as written) and, for cuDNN, as one dense conv too
+                m.precision = "fp16x3"
+                us_chain = time_layer(lambda: m(x), iters=10)
+                m.precision = "auto"
+                wd = m._dense_weight()
+                cud_dense = time_layer(lambda: F.conv2d(x, wd, None, 1, 1), iters=10)
                 y64 = ref(x[:2].double()) if False else F.conv2d(F.conv2d(F.conv2d(x[:2].double(), m.first_kernel.double()),
                                                                            m.core_kernel.double(), None, 1, 1), m.last_kernel.double())
                 err = float((m(x)[:2].double() - y64).abs().max() / y64.abs().max())
             flops = 2.0 * B * H * H * (Cc * R + 9 * R * R + R * Cc)
             by = 4.0 * (2 * B * Cc * H * H + 2 * Cc * R + 9 * R * R)
-            row = dict(C=Cc, H=H, R=R, B=B, us=us, cudnn_us=cud, rel_err_fp64=err, tflops=flops / us / 1e6,
+            from tdc_b200.dispatch import tucker_strategy
+            row = dict(C=Cc, H=H, R=R, B=B, us=us, strategy=tucker_strategy(m, x, "auto"), us_three_launches=us_chain, cudnn_us=cud,
+                       cudnn_dense_us=cud_dense, rel_err_fp64=err, tflops=flops / us / 1e6,
                        hbm_floor_us=by / peaks["hbm_gbs"] / 1e3, gbs=by / us / 1e3)
             if B == 1:
                 # batch-1 latency without host launch gaps on either side: the three launches replayed from a CUDA graph
@@ -764,6 +774,7 @@ def main():
                                    "note": "pinned-memory copies of the step's inputs and outputs alone, both directions at once, all ranks at once"}
     line["e2e"]["frac_of_copy_ceiling"] = copy_s / e2e_s
     del dev_in, dev_out
+    e2e_step()                      # the copies above wrote scratch data over the host outputs: one more real step
     # one parity probe of the end-to-end output against the resident path
     # (the host path runs the batch in chunks, each with a range scale of its own: the same values to rounding, not to the bit)
     y_res = layers[0]["tc4"](layers[0]["x"])

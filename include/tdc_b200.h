@@ -319,6 +319,10 @@ TDC_API int tdc_conv2d_tc(const tdc_tc_plan* plan, const float* x, const void* w
 TDC_API int tdc_conv2d_tc_ranged(const tdc_tc_plan* plan, const float* x, const void* wt, float* y,
                           int B, int H, int W, const tdc_epilogue* epi, int flags,
                           const float* x_absmax, float* y_absmax, void* stream);
+/* Whether tdc_conv2d_tc can launch this plan on images of H x W (TDC_OK), without launching: wide images with many
+ * output channels per block may not leave room for two stages in shared memory (TDC_ERR_SMEM); a plan with a smaller
+ * block (tdc_tc_plan_make_nt) then fits.  The prepared filter depends on the block size, so ask before preparing. */
+TDC_API int tdc_tc_check_launch(const tdc_tc_plan* plan, int B, int H, int W, int flags);
 TDC_API int tdc_tc_status(int* out);
 
 /*
@@ -380,6 +384,12 @@ TDC_API int  tdc_tkconv_create(tdc_tkconv** out, int b, int C, int N1, int N2, i
                        int r, int s, int pad, int stride,
                        const float* host_w1, const float* host_wcore_kcrs,
                        const float* host_w3, const float* host_bias);
+/* 0: the three fp32 launches of tdc_tk_block_f32 (default).  1 / 3 / 4: ONE tensor-core launch (tdc_conv2d_tc in that
+ * mode) on the filter w[k][c][i][j] = sum w3[k][r2] * core[r2][r1][i][j] * w1[r1][c], merged on the host in double and
+ * rounded once — the weight TKConv2dR recovers before its single conv (inference/TKConv.py:310-322).  The same linear
+ * map as conv1 -> conv2 -> conv3 of TkConv::forward (src/BasicBlock.cu:27-32) with neither intermediate ever formed;
+ * more multiply-adds, yet faster on this GPU while the three steps are bound by launches and memory passes. */
+TDC_API int  tdc_tkconv_set_precision(tdc_tkconv* l, int mode);
 TDC_API int  tdc_tkconv_forward(tdc_tkconv* l, const float* dev_in, float** dev_out, void* stream);
 TDC_API int  tdc_tkconv_forward_host(tdc_tkconv* l, const float* host_in, float* host_out);
 TDC_API void tdc_tkconv_destroy(tdc_tkconv* l);

@@ -49,6 +49,37 @@ def _compile(src, obj, verbose):
     return r.stderr if verbose else ""
 
 
+def build_debug_bounds():
+    """libtdc_b200_bounds.so: the same library compiled with -DTDC_DEBUG_BOUNDS, in which every global access of the
+    fp32 kernels checks its offset first and records a violation instead of making the access (tdc_debug_bounds_read).
+    Load it with TDC_B200_LIB=<path>; slower, for tests and for hunting an index error without faulting a GPU."""
+    out = os.path.join(HERE, "tdc_b200", "libtdc_b200_bounds.so")
+    obj_dir = os.path.join(HERE, "build", "bounds")
+    os.makedirs(obj_dir, exist_ok=True)
+    srcs = sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+    hdr = _newest_header()
+    jobs, objs = [], []
+    for f in srcs:
+        src, obj = os.path.join(CSRC, f), os.path.join(obj_dir, f[:-3] + ".o")
+        objs.append(obj)
+        if not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr):
+            jobs.append((src, obj))
+
+    def one(job):
+        r = subprocess.run([_nvcc(), *NVCC_FLAGS, "-DTDC_DEBUG_BOUNDS", "-c", job[0], "-o", job[1]], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed on %s:\n%s" % (job[0], r.stderr))
+    if jobs:
+        with cf.ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as ex:
+            list(ex.map(one, jobs))
+    if jobs or not os.path.exists(out):
+        r = subprocess.run([_nvcc(), "-shared", "-o", out, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"],
+                           capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("link failed:\n%s" % r.stderr)
+    return out
+
+
 def build(force=False, verbose=False):
     os.makedirs(OBJ, exist_ok=True)
     hdr = _newest_header()
@@ -120,5 +151,8 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--debug-bounds", action="store_true", help="also build the range-checked variant of the library")
     a = ap.parse_args()
     print(build(a.force, a.verbose))
+    if a.debug_bounds:
+        print(build_debug_bounds())

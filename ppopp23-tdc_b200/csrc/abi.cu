@@ -29,6 +29,9 @@ using namespace tdc;
 
 namespace {
 
+#ifdef TDC_DEBUG_BOUNDS
+__device__ int g_debug_bounds[4];     // see ConvArgs::bounds
+#endif
 std::mutex g_mu;
 std::map<int, tdc_devinfo> g_dev;                          // per device
 std::map<std::pair<int, const void*>, size_t> g_smem_set;  // (device, kernel) -> opted-in bytes
@@ -130,6 +133,14 @@ int launch_conv_epi(const float* x, const float* w, const tdc_epilogue& epi, flo
     else                        { a.ws_k = 1; a.ws_c = (long long)RS * s.K; a.ws_rs = s.K; }
     a.w_vec = (w_layout == TDC_W_CRSK && s.K % 4 == 0 && (reinterpret_cast<uintptr_t>(w) % 16 == 0)) ? 1 : 0;
     a.y_vec = reinterpret_cast<uintptr_t>(y) % 16 == 0 ? 1 : 0;      // else the epilogue stores element by element
+    a.x_n = (long long)s.B * s.C * s.H * s.W; a.w_n = (long long)s.K * s.C * RS; a.y_n = (long long)s.B * s.K * s.Ho() * s.Wo();
+    a.bounds = nullptr;
+#ifdef TDC_DEBUG_BOUNDS
+    {
+        void* bp = nullptr;
+        if (cudaGetSymbolAddress(&bp, g_debug_bounds) == cudaSuccess) a.bounds = (int*)bp;
+    }
+#endif
     a.relu = epi.relu ? 1 : 0;
     a.tc = t.tc; a.gy = t.gy; a.gx = t.gx; a.imgs = t.imgs; a.ks = t.ks;
     a.in_rows = g.in_rows; a.in_wp = g.in_wp; a.patch = g.patch;
@@ -179,6 +190,16 @@ extern "C" {
 
 const char* tdc_last_error_string(void) { return tdc::last_error(); }
 int tdc_version(void) { return 100; }
+
+#ifdef TDC_DEBUG_BOUNDS
+// Range-checked build only: {violations, kind of the first, its offset (low, high word)} of all fp32-kernel launches so
+// far on the current device; reset != 0 clears the record.  Synchronises.
+__attribute__((visibility("default"))) int tdc_debug_bounds_read(int* out4, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out4, g_debug_bounds, 4 * sizeof(int));
+    if (e == cudaSuccess && reset) { const int z[4] = {0, 0, 0, 0}; e = cudaMemcpyToSymbol(g_debug_bounds, z, sizeof z); }
+    return e == cudaSuccess ? TDC_OK : fail(TDC_ERR_CUDA, "bounds record: %s", cudaGetErrorString(e));
+}
+#endif
 
 int tdc_query_device(int device, tdc_devinfo* out) {
     if (!out) return fail(TDC_ERR_NULL, "out is NULL");

@@ -1204,6 +1204,20 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     return TDC_OK;
 }
 
+int tdc_tc_check_launch(const tdc_tc_plan* p, int B, int H, int W, int flags) {
+    if (!p) return tc_fail(TDC_ERR_NULL, "plan is NULL");
+    if (B <= 0 || H <= 0 || W <= 0) return tc_fail(TDC_ERR_SHAPE, "B=%d H=%d W=%d", B, H, W);
+    int device;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return tc_fail(TDC_ERR_NO_DEVICE, "cudaGetDevice: %s", cudaGetErrorString(e));
+    DevFacts f;
+    if ((e = cudaDeviceGetAttribute(&f.smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, device)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&f.sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess)
+        return tc_fail(TDC_ERR_CUDA, "device query: %s", cudaGetErrorString(e));
+    Launch L;
+    return plan_launch(p, B, H, W, flags & ~TDC_TC_EXACT_RANGE, true, f, Tuning{}, &L);
+}
+
 int tdc_conv2d_tc(const tdc_tc_plan* p, const float* x, const void* wt, float* y, int B, int H, int W,
                   const tdc_epilogue* epi, int flags, void* stream) {
     return tdc_conv2d_tc_ranged(p, x, wt, y, B, H, W, epi, flags, nullptr, nullptr, stream);

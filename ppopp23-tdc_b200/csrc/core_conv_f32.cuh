@@ -55,7 +55,26 @@ struct ConvArgs {
     int patch;           // imgs * in_rows * in_wp, rounded up to a multiple of 4
     int tiles_y, tiles_x, img_groups, n_ocb;
     int stage_floats;    // floats of one stage (input part + weight part)
+    // range-checked build (-DTDC_DEBUG_BOUNDS) only: element counts of x, w and y, and where a violation is recorded
+    long long x_n, w_n, y_n;
+    int* bounds;         // [0] violations seen, [1] kind of the first (1 x, 2 w, 3 y, 4 residual), [2..3] its offset
 };
+
+// Range-checked build: every global access of the kernel first checks its element offset against the tensor it
+// belongs to; an access outside is not made, and the first one is recorded for the host (tdc_debug_bounds_read).
+// This is the library's own stand-in for a memory checker: it finds an index error without faulting the GPU.
+#ifdef TDC_DEBUG_BOUNDS
+__device__ __forceinline__ bool bounds_ok(const ConvArgs& a, long long off, long long n, int kind) {
+    if (off >= 0 && off < n) return true;
+    if (a.bounds && atomicAdd(&a.bounds[0], 1) == 0) {
+        a.bounds[1] = kind; a.bounds[2] = (int)(off & 0xffffffffll); a.bounds[3] = (int)(off >> 32);
+    }
+    return false;
+}
+#define TDC_BOUNDS(a, off, n, kind) bounds_ok(a, off, n, kind)
+#else
+#define TDC_BOUNDS(a, off, n, kind) true
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -184,7 +203,8 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
             float* dst = in_s + cl * a.patch;
             for (int p = tid; p < a.patch; p += nthr) {
                 int o = tab[p];
-                cp_async4(dst + p, src + (o < 0 ? 0 : o), o >= 0);
+                const bool ok = o >= 0 && TDC_BOUNDS(a, (src - a.x) + o, a.x_n, 1);
+                cp_async4(dst + p, src + (ok ? o : 0), ok);
             }
         }
         // weights of the chunk as [channel][r*S+s][OCB]
@@ -195,8 +215,9 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
             for (int i = tid; i < items; i += nthr) {
                 int q = i / V, v = i - q * V;
                 bool ok = (oc0 + 4 * v) < a.K;
+                ok = ok && TDC_BOUNDS(a, (src - a.w) + (long long)q * a.K + 4 * v + 3, a.w_n, 2);
                 int og = v / (TN / 4), h = v - og * (TN / 4);
-                cp_async16(w_s + q * OCB + (h * NOG + og) * 4, src + (long long)q * a.K + (ok ? 4 * v : 0), ok);
+                cp_async16(w_s + q * OCB + (h * NOG + og) * 4, src + (ok ? (long long)q * a.K + 4 * v : 0), ok);
             }
         } else {
             const int rows  = tcc * RS;
@@ -207,6 +228,7 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
                 else             { ol = i / rows; q = i - ol * rows; } // torch filter: (c,r,s) contiguous
                 int cl = q / RS, rs = q - cl * RS;
                 bool ok = (oc0 + ol) < a.K;
+                ok = ok && TDC_BOUNDS(a, (long long)(oc0 + ol) * a.ws_k + (long long)(c0 + cl) * a.ws_c + (long long)rs * a.ws_rs, a.w_n, 2);
                 const float* src = a.w + (ok ? (long long)(oc0 + ol) * a.ws_k + (long long)(c0 + cl) * a.ws_c +
                                                    (long long)rs * a.ws_rs
                                              : 0);
@@ -371,6 +393,12 @@ __global__ void __launch_bounds__(MAXT) conv_f32_kernel(const ConvArgs a) {
             const int oy = oyb + o;
             if (oy >= a.Ho) continue;
             float* yr = yp + (long long)oy * a.Wo + oxb;
+#ifdef TDC_DEBUG_BOUNDS
+            {   // the row this thread is about to write (and, with a residual, read): first and last element
+                const int last = (oxb + TW <= a.Wo ? TW : a.Wo - oxb) - 1;
+                if (last >= 0 && (!TDC_BOUNDS(a, (yr - a.y), a.y_n, 3) || !TDC_BOUNDS(a, (yr - a.y) + last, a.y_n, 3))) continue;
+            }
+#endif
 #pragma unroll
             for (int p = 0; p < TW; ++p) {
                 float v = a.scale ? fmaf(acc[j][o][p], sv, bv) : acc[j][o][p] + bv;

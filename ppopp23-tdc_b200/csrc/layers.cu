@@ -5,6 +5,7 @@
 // same forward in the copy-in / run / copy-out sequence of the per-shape drivers' main()
 // (A100-evaluation/TDC-LAYERS-ORACLE/template_benchmark_cudnn.template:412-498).
 #include <cuda_runtime.h>
+#include <algorithm>
 #include <cstdio>
 #include <vector>
 #include "../../include/tdc_b200.h"
@@ -29,6 +30,10 @@ struct tdc_tkconv {
     float *output = nullptr, *staging_in = nullptr;
     void* workspace = nullptr;
     size_t workspace_bytes = 0;
+    std::vector<float> h_w1, h_core, h_w3;   // the factors as given (all ones when none were), for tdc_tkconv_set_precision
+    int tc_mode = 0;                         // 0: the three fp32 launches; 1 / 3 / 4: ONE tensor-core launch on the merged filter
+    tdc_tc_plan plan{};
+    void* tc_weights = nullptr;
 };
 
 namespace {
@@ -76,9 +81,12 @@ int tdc_conv_set_precision(tdc_conv* l, int mode) {
     int rc = tdc_query_device(-1, &dev);
     if (rc) return rc;
     const int halo = (l->r - 1) / 2;
-    const int nt = tdc_tc_pick_nt(l->n, mode, (long long)l->b * (l->h + halo) * (l->w + halo), dev.sm_count);
-    rc = tdc_tc_plan_make_nt(l->c, l->n, l->r, l->s, mode, 0, nt, &p);
-    if (rc) return rc;
+    int nt = tdc_tc_pick_nt(l->n, mode, (long long)l->b * (l->h + halo) * (l->w + halo), dev.sm_count);
+    for (;; nt /= 2) {      // a wide image may not leave room for two stages beside a large block: take a smaller one
+        rc = tdc_tc_plan_make_nt(l->c, l->n, l->r, l->s, mode, 0, nt, &p);
+        if (rc) return rc;
+        if (nt == 32 || tdc_tc_check_launch(&p, l->b, l->h, l->w, 0) != TDC_ERR_SMEM) break;
+    }
     void* wt = nullptr;
     cudaError_t e = cudaMalloc(&wt, p.weights_bytes);
     if (e != cudaSuccess) return cuda_fail("cudaMalloc", e);
@@ -201,7 +209,7 @@ int tdc_conv_forward_host(tdc_conv* l, const float* host_in, float* host_out) {
 void tdc_tkconv_destroy(tdc_tkconv* l) {
     if (!l) return;
     cudaFree(l->w1); cudaFree(l->wcore); cudaFree(l->w3); cudaFree(l->bias);
-    cudaFree(l->output); cudaFree(l->staging_in); cudaFree(l->workspace);
+    cudaFree(l->output); cudaFree(l->staging_in); cudaFree(l->workspace); cudaFree(l->tc_weights);
     delete l;
 }
 
@@ -217,6 +225,10 @@ int tdc_tkconv_create(tdc_tkconv** out, int b, int C, int N1, int N2, int N3, in
     tdc_tkconv* l = new tdc_tkconv;
     l->b = b; l->C = C; l->N1 = N1; l->N2 = N2; l->N3 = N3; l->h = h; l->w = w; l->r = r; l->s = s;
     l->pad = pad; l->stride = stride;
+    l->h_w1.assign((size_t)N1 * C, 1.0f); l->h_core.assign((size_t)N2 * N1 * r * s, 1.0f); l->h_w3.assign((size_t)N3 * N2, 1.0f);
+    if (host_w1) l->h_w1.assign(host_w1, host_w1 + l->h_w1.size());
+    if (host_wcore_kcrs) l->h_core.assign(host_wcore_kcrs, host_wcore_kcrs + l->h_core.size());
+    if (host_w3) l->h_w3.assign(host_w3, host_w3 + l->h_w3.size());
     l->ho = (h + 2 * pad - r) / stride + 1;
     l->wo = (w + 2 * pad - s) / stride + 1;
     int rc;
@@ -242,8 +254,73 @@ int tdc_tkconv_create(tdc_tkconv** out, int b, int C, int N1, int N2, int N3, in
     return TDC_OK;
 }
 
+int tdc_tkconv_set_precision(tdc_tkconv* l, int mode) {
+    if (!l) return fail(TDC_ERR_NULL, "tdc_tkconv_set_precision: layer is NULL");
+    if (mode == 0) { l->tc_mode = 0; return TDC_OK; }
+    if (l->r != l->s) return fail(TDC_ERR_UNSUPPORTED, "tdc_tkconv_set_precision: the merged form takes square filters, this layer is %dx%d", l->r, l->s);
+    // w[k][c][i][j] = sum_{r2, r1} w3[k][r2] * core[r2][r1][i][j] * w1[r1][c], in double, rounded once: the weight the
+    // reference's TKConv2dR recovers before its single conv (inference/TKConv.py:310-322)
+    const int C = l->C, N1 = l->N1, N2 = l->N2, N3 = l->N3, rs = l->r * l->s;
+    std::vector<double> t((size_t)N2 * C * rs, 0.0);                 // core x w1: [r2][c][ij]
+    for (int r2 = 0; r2 < N2; ++r2)
+        for (int r1 = 0; r1 < N1; ++r1)
+            for (int ij = 0; ij < rs; ++ij) {
+                const double cv = l->h_core[((size_t)r2 * N1 + r1) * rs + ij];
+                double* trow = &t[(size_t)r2 * C * rs + ij];
+                const float* w1row = &l->h_w1[(size_t)r1 * C];
+                for (int c = 0; c < C; ++c) trow[(size_t)c * rs] += cv * w1row[c];
+            }
+    std::vector<float> merged((size_t)N3 * C * rs);
+    std::vector<double> acc((size_t)C * rs);
+    for (int k = 0; k < N3; ++k) {
+        std::fill(acc.begin(), acc.end(), 0.0);
+        for (int r2 = 0; r2 < N2; ++r2) {
+            const double wv = l->h_w3[(size_t)k * N2 + r2];
+            const double* trow = &t[(size_t)r2 * C * rs];
+            for (size_t i = 0; i < acc.size(); ++i) acc[i] += wv * trow[i];
+        }
+        for (size_t i = 0; i < acc.size(); ++i) merged[(size_t)k * C * rs + i] = (float)acc[i];
+    }
+    const bool one_pass = l->stride == 1 && l->pad == (l->r - 1) / 2 && (l->r == 1 || l->r == 3);
+    tdc_tc_plan p;
+    tdc_devinfo dev;
+    int rc = tdc_query_device(-1, &dev);
+    if (rc) return rc;
+    const int halo = one_pass ? (l->r - 1) / 2 : 0;
+    const int flags = (l->stride - 1) | (one_pass ? 0 : (l->pad << TDC_TC_PAD_SHIFT));
+    int nt = tdc_tc_pick_nt(N3, mode, (long long)l->b * (l->ho + halo) * (l->wo + halo), dev.sm_count);
+    for (;; nt /= 2) {      // the block size that suits the layer's position count and still fits beside a wide image's patch
+        rc = tdc_tc_plan_make_nt(C, N3, l->r, l->s, mode, one_pass ? 0 : 1, nt, &p);
+        if (rc) return rc;
+        if (nt == 32 || tdc_tc_check_launch(&p, l->b, l->h, l->w, flags) != TDC_ERR_SMEM) break;
+    }
+    float* dev_w = nullptr;
+    void* wt = nullptr;
+    cudaError_t e;
+    if ((e = cudaMalloc((void**)&dev_w, merged.size() * sizeof(float))) != cudaSuccess || (e = cudaMalloc(&wt, p.weights_bytes)) != cudaSuccess) {
+        cudaFree(dev_w);
+        return cuda_fail("cudaMalloc", e);
+    }
+    e = cudaMemcpy(dev_w, merged.data(), merged.size() * sizeof(float), cudaMemcpyHostToDevice);
+    rc = e == cudaSuccess ? tdc_tc_prepare_weights(&p, dev_w, TDC_W_KCRS, wt, nullptr) : cuda_fail("cudaMemcpy", e);
+    if (!rc && (e = cudaDeviceSynchronize()) != cudaSuccess) rc = cuda_fail("prepare", e);
+    cudaFree(dev_w);
+    if (rc) { cudaFree(wt); return rc; }
+    cudaFree(l->tc_weights);
+    l->tc_weights = wt; l->plan = p; l->tc_mode = mode;
+    return TDC_OK;
+}
+
 int tdc_tkconv_forward(tdc_tkconv* l, const float* dev_in, float** dev_out, void* stream) {
     if (!l || !dev_in || !dev_out) return fail(TDC_ERR_NULL, "tdc_tkconv_forward: layer, dev_in and dev_out must be non-NULL");
+    if (l->tc_mode) {
+        tdc_epilogue e{nullptr, l->bias, nullptr, 0};
+        const int flags = (l->stride - 1) | (l->plan.general ? (l->pad << TDC_TC_PAD_SHIFT) : 0);
+        const int rc = tdc_conv2d_tc(&l->plan, dev_in, l->tc_weights, l->output, l->b, l->h, l->w, &e, flags, stream);
+        if (rc) return rc;
+        *dev_out = l->output;
+        return TDC_OK;
+    }
     int rc = tdc_tk_block_f32(dev_in, l->w1, l->wcore, l->w3, l->bias, l->output, l->b, l->C, l->h, l->w, l->N1,
                               l->N2, l->N3, l->r, l->s, l->pad, l->stride, TDC_W_CRSK, TDC_EPI_NONE, nullptr, l->workspace,
                               l->workspace_bytes, stream);

@@ -29,3 +29,4 @@ __all__ = [
     "fill_deterministic", "tkc_resnet18", "tkc_resnet50", "TKBottleneck", "HalfRanksBottleneck", "core_conv2d", "lib", "out_hw", "permute_weights", "query_device",
     "select_tile", "table_tile", "load_tables", "tile_cost", "tile_info", "tk_block", "tk_block_workspace_bytes",
 ]
+from . import torch_ops  # registers torch.ops.tdc.core_conv2d / tk_block

@@ -75,6 +75,7 @@ _PROTOTYPES = {
     "tdc_tc_prepare_weights": (_i, [C.POINTER(TcPlan), _p, _i, _p, _p]),
     "tdc_conv2d_tc": (_i, [C.POINTER(TcPlan), _p, _p, _p, _i, _i, _i, C.POINTER(Epilogue), _i, _p]),
     "tdc_conv2d_tc_ranged": (_i, [C.POINTER(TcPlan), _p, _p, _p, _i, _i, _i, C.POINTER(Epilogue), _i, _p, _p, _p]),
+    "tdc_tc_check_launch": (_i, [C.POINTER(TcPlan), _i, _i, _i, _i]),
     "tdc_tc_status": (_i, [C.POINTER(_i)]),
     "tdc_select_tile": (_i, [_i] * 9 + [C.POINTER(DevInfo), C.POINTER(Tile)]),
     "tdc_tile_info": (_i, [_i] * 9 + [C.POINTER(Tile), C.POINTER(LaunchInfo)]),
@@ -91,6 +92,7 @@ _PROTOTYPES = {
     "tdc_conv_forward_host_async": (_i, [_p, _p, _p, _p]),
     "tdc_conv_destroy": (None, [_p]),
     "tdc_tkconv_create": (_i, [C.POINTER(_p)] + [_i] * 11 + [_p] * 4),
+    "tdc_tkconv_set_precision": (_i, [_p, _i]),
     "tdc_tkconv_forward": (_i, [_p, _p, C.POINTER(_p), _p]),
     "tdc_tkconv_forward_host": (_i, [_p, _p, _p]),
     "tdc_tkconv_destroy": (None, [_p]),

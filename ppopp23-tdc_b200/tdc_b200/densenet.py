@@ -26,7 +26,7 @@ import torch.nn as nn
 
 from . import ops
 from ._lib import ERR_UNSUPPORTED, TdcError
-from .dispatch import one_conv as _one_conv
+from .dispatch import one_conv as _one_conv, tucker_strategy
 from .resnet import Conv2dB200, _fold_bn, _tk_or_dense
 from .svdconv import SVDConv2dC_B200
 from .tkconv import TKConv2dC_B200
@@ -56,7 +56,7 @@ class Growth32Ranks:
 def _conv(module, x, scale, shift, relu, precision):
     if isinstance(module, SVDConv2dC_B200):
         return module.run(x, scale, shift, None, relu, precision)
-    if isinstance(module, TKConv2dC_B200) and precision != "fp32" and module.fold_pays():
+    if isinstance(module, TKConv2dC_B200) and precision != "fp32" and module.fold_pays() and tucker_strategy(module, x, precision) != "dense":
         # 128 -> 32 -> 32 -> 32: the last 1x1 step multiplied into the core filter — two launches instead of three
         # ("fp32" keeps the reference's three-step chain)
         if module.bias is not None:

@@ -38,3 +38,47 @@ def one_conv(owner, name, x, w_kcrs, w_crsk, scale, shift, residual, relu, strid
             w_crsk = w_crsk()
         return ops.conv2d_epi(x, w_crsk, scale, shift, residual, relu, stride, padding, w_layout=W_CRSK, tile=tile)
     return ops.conv2d_epi(x, w_kcrs.detach(), scale, shift, residual, relu, stride, padding, tile=tile)
+
+
+def _conv_us(B, Cc, K, Ho, Wo, R, stride=1):
+    """Rough time of one convolution on the tensor-core path with fp16 parts, in microseconds: a fixed part per launch
+    plus the slower of arithmetic (at the rates the sweep shapes reach: they rise with the output channels per MMA)
+    and the memory passes over input and output.  Only good for comparing ways to run the same layer."""
+    flops = 2.0 * B * Ho * Wo * Cc * K * R * R
+    if stride > 1 and R > 1:
+        rate = 100e12                                  # the gathering plan is bound by its loaders
+    elif R > 1:
+        rate = 280e12 if K >= 128 else (240e12 if K >= 64 else 110e12)
+    else:
+        rate = 200e12 if K >= 128 else (150e12 if K >= 64 else 80e12)
+    nbytes = 4.0 * B * (Cc * Ho * Wo * stride * stride + K * Ho * Wo)
+    # a CTA walks the channel blocks of a tile one after the other, about 0.1 us per (16 channels x tap) with blocks of
+    # 128 output channels (half that with smaller ones): with few tiles this chain, not the arithmetic, is the time
+    nt = 128 if K > 64 else 64
+    tiles = -(-(B * (Ho + (R > 1)) * (Wo + (R > 1))) // 256) * -(-K // nt)
+    serial = -(-tiles // 148) * (Cc / 16.0) * R * R * (0.1 if nt == 128 else 0.05)
+    return 12.0 + max(flops / rate * 1e6, nbytes / 2.5e12 * 1e6, serial)
+
+
+def tucker_strategy(conv, x, precision):
+    """"dense" or "chain" for a Tucker conv (first 1x1, core, last 1x1).  The dense form (one conv with the factors
+    multiplied into one filter, `TKConv2dC_B200._dense_weight`) does 9CK multiply-adds per pixel where the chain does
+    C*R1 + 9*R1*R2 + R2*K, but it is one launch with no intermediate: measured on the bottleneck middles C = K = 64..512,
+    R = C/2, batch 32: 39 / 38 / 35 / 59 us against 71 / 63 / 57 / 97 us for the chain (batch 1: 16 / 18 / 27 / 57 against
+    36 / 40 / 48 / 91).  Taken under "auto" only (the named precisions run the factored form as written), when the
+    estimate says it is at least a tenth faster."""
+    if precision != "auto":
+        return "chain"
+    from . import tc
+    B, Cc, H, W = x.shape
+    R, S = conv.kernel_size
+    stride, pad = conv.stride[0], conv.padding[0]
+    if R != S or conv.stride[0] != conv.stride[1] or conv.padding[0] != conv.padding[1]:
+        return "chain"
+    Ho, Wo = (H + 2 * pad - R) // stride + 1, (W + 2 * pad - S) // stride + 1
+    K, R1, R2 = conv.out_channels, conv.in_rank, conv.out_rank
+    if not (tc.supported(R, S, stride, pad, W) or tc.general_supported(R, S, stride, pad, Wo)):
+        return "chain"
+    dense = _conv_us(B, Cc, K, Ho, Wo, R, stride)
+    chain = _conv_us(B, Cc, R1, H, W, 1) + _conv_us(B, R1, R2, Ho, Wo, R, stride) + _conv_us(B, R2, K, Ho, Wo, 1)
+    return "dense" if dense <= 0.9 * chain else "chain"

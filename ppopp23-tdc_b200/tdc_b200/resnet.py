@@ -19,7 +19,7 @@ import torch.nn as nn
 
 from . import ops, tiles
 from ._lib import ERR_UNSUPPORTED, W_CRSK, TdcError
-from .dispatch import one_conv as _one_conv
+from .dispatch import one_conv as _one_conv, tucker_strategy
 from .tkconv import TKConv2dC_B200
 
 
@@ -90,6 +90,8 @@ def _tk_or_dense(conv, x, scale, shift, residual, relu, precision="fp32"):
         b = conv.bias.detach() if scale is None else conv.bias.detach() * scale
         shift = b if shift is None else shift + b
     if isinstance(conv, TKConv2dC_B200):
+        if tucker_strategy(conv, x, precision) == "dense":
+            return _one_conv(conv, "dense", x, conv._dense_weight(), None, scale, shift, residual, relu, conv.stride[0], conv.padding[0], precision)
         z1 = _one_conv(conv, "first", x, conv.first_kernel, lambda: conv._factor_channel_last("first_kernel"), None, None, None, False, 1, 0, precision)
         z2 = _one_conv(conv, "core", z1, conv.core_kernel, conv._core_channel_last, None, None, None, False,
                        conv.stride[0], conv.padding[0], precision)

@@ -42,7 +42,7 @@ class TcConv:
         self.wt = self._prepare(self.plan)
         self._by_nt = {self.plan.nt: (self.plan, self.wt)}       # output-channel block size -> (plan, prepared filter)
         self._sms = torch.cuda.get_device_properties(weight.device).multi_processor_count
-        self._nt_of = {}                                         # positions -> block size (the rule is a library call)
+        self._nt_of = {}                                         # (batch, image, flags) -> block size (the rules are library calls)
 
     def _prepare(self, plan):
         wt = torch.empty(plan.weights_bytes, dtype=torch.uint8, device=self._weight.device)
@@ -51,12 +51,22 @@ class TcConv:
                                               wt.data_ptr(), _stream()))
         return wt
 
-    def _for_positions(self, positions):
-        """(plan, prepared filter) with the output-channel block size that suits `positions` output positions: the
-        default for layers with many position tiles, smaller blocks (more CTAs) for few; prepared on first use."""
-        nt = self._nt_of.get(positions)
+    def _for_image(self, B, H, W, Ho, Wo, flags):
+        """(plan, prepared filter) with the output-channel block size that suits this layer: the default for layers with
+        many position tiles, smaller blocks (more CTAs) for few, and smaller again while the block does not leave room
+        for two stages beside the patch of a wide image; prepared on first use."""
+        halo = 0 if self.general else (self.R - 1) // 2
+        key = (B, H, W, flags)
+        nt = self._nt_of.get(key)
         if nt is None:
-            nt = self._nt_of[positions] = lib.tdc_tc_pick_nt(self.K, self.mode, positions, self._sms)
+            nt = lib.tdc_tc_pick_nt(self.K, self.mode, B * (Ho + halo) * (Wo + halo), self._sms)
+            while nt > 32:
+                plan = TcPlan()
+                _check(lib.tdc_tc_plan_make_nt(self.C, self.K, self.R, self.S, self.mode, int(self.general), nt, C.byref(plan)))
+                if lib.tdc_tc_check_launch(C.byref(plan), B, H, W, flags & 0xFF) != _lib.ERR_SMEM:
+                    break
+                nt //= 2
+            self._nt_of[key] = nt
         hit = self._by_nt.get(nt)
         if hit is None:
             plan = TcPlan()
@@ -86,8 +96,7 @@ class TcConv:
         if out is None:
             out = torch.empty((B, self.K, Ho, Wo), device=x.device, dtype=torch.float32)
         e = _epilogue(scale, bias, residual, relu)
-        halo = 0 if self.general else (self.R - 1) // 2
-        plan, wt = self._for_positions(B * (Ho + halo) * (Wo + halo))
+        plan, wt = self._for_image(B, H, W, Ho, Wo, flags)
         if self.mode != 4:
             with _on_device(x.device):
                 _check(lib.tdc_conv2d_tc(C.byref(plan), _dev_f32(x, "x"), wt.data_ptr(), _dev_f32(out, "out"),

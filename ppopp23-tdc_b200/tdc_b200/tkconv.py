@@ -120,6 +120,22 @@ class TKConv2dC_B200(nn.Module):
             hit = self.__dict__["_core_last_cache"] = (key, w, ops.permute_weights(w))
         return hit[1], hit[2]
 
+    def _dense_weight(self):
+        """The block as ONE kh x kw filter C -> K: w[k][c][i][j] = sum_{r2,r1} last[k][r2] * core[r2][r1][i][j] * first[r1][c],
+        summed in fp64 and rounded once; rebuilt when a factor changes.  It is the weight the reference's TKConv2dR
+        recovers before its single conv (inference/TKConv.py:310-322): the same linear map as the three steps, with
+        no intermediate at all.  It costs 9CK multiply-adds per pixel against C*R1 + 9*R1*R2 + R2*K, and on this GPU
+        it is still the faster form whenever the three steps are bound by their launches and memory passes rather
+        than by arithmetic (`dispatch.tucker_strategy` decides)."""
+        ps = (self.first_kernel, self.core_kernel, self.last_kernel)
+        key = tuple((p._version, p.data_ptr()) for p in ps)
+        hit = self.__dict__.get("_dense_cache")
+        if hit is None or hit[0] != key:
+            t = torch.einsum("abij,bc->acij", self.core_kernel.detach().double(), self.first_kernel.detach().double()[:, :, 0, 0])
+            w = torch.einsum("ka,acij->kcij", self.last_kernel.detach().double()[:, :, 0, 0], t).float().contiguous()
+            hit = self.__dict__["_dense_cache"] = (key, w)
+        return hit[1]
+
     def _ws(self, x, shared=False):
         """Workspace for the block's two intermediates: this module's own, or (shared=True) one
         buffer per device that all blocks of a network reuse — they run one after another on one
@@ -142,9 +158,11 @@ class TKConv2dC_B200(nn.Module):
         if self.precision != "fp32" and self.stride[0] == self.stride[1] and self.padding[0] == self.padding[1]:
             # each of the three steps on the kernel that suits it (tensor cores where a plan exists and, under
             # "auto", the step is large enough; the fp32 FMA kernel with its table tile otherwise)
-            from .dispatch import one_conv
+            from .dispatch import one_conv, tucker_strategy
             p = self.precision
             bias = None if self.bias is None else self.bias.detach()
+            if tucker_strategy(self, x, p) == "dense":
+                return one_conv(self, "dense", x, self._dense_weight(), None, None, bias, None, False, self.stride[0], self.padding[0], p)
             z1 = one_conv(self, "first", x, self.first_kernel, lambda: self._factor_channel_last("first_kernel"),
                           None, None, None, False, 1, 0, p)
             z2 = one_conv(self, "core", z1, self.core_kernel, self._core_channel_last, None, None, None, False,

@@ -25,6 +25,7 @@ def built():
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     mod.build()
+    mod.build_debug_bounds()
     import oracle
     oracle.build()
     return True

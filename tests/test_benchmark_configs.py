@@ -77,8 +77,10 @@ def test_tucker_blocks_of_the_bottleneck_middles(T, i, Cc, H, B):
     F = torch.nn.functional
     xd = x.cuda()
     ref = F.conv2d(F.conv2d(F.conv2d(xd.double(), first.cuda().double()), core.cuda().double(), None, 1, 1), last.cuda().double())
+    from tdc_b200.dispatch import tucker_strategy
+    assert tucker_strategy(m, xd, "auto") == "dense" and tucker_strategy(m, xd, "fp16x3") == "chain"
     with torch.no_grad():
-        for precision in ("fp32", "auto", "fp16x3", "tf32x3"):
+        for precision in ("fp32", "auto", "fp16x3", "tf32x3"):          # "auto": one launch on the merged filter; the others: three
             m.precision = precision
             assert rel_err(m(xd).cpu().numpy(), ref.cpu().numpy()) <= FP32_TOL, precision
 

@@ -219,6 +219,15 @@ def test_layer_objects_with_host_buffers(T):
     assert lib.tdc_tkconv_forward_host(tk, fp(xn), fp(out)) == 0
     ref, _, _ = O.tk_block(xn, f2, wn, l2, bn, pad=1, stride=2, f64=True)
     assert rel_err(out, ref) <= FP32_TOL
+    # the same layer as ONE tensor-core launch on the merged filter (here a strided 3x3: the gathering plan), and back
+    for mode in (4, 3):
+        assert lib.tdc_tkconv_set_precision(tk, mode) == 0
+        out2 = np.empty_like(out)
+        assert lib.tdc_tkconv_forward_host(tk, fp(xn), fp(out2)) == 0
+        assert rel_err(out2, ref) <= FP32_TOL and not np.array_equal(out2, out)
+    assert lib.tdc_tkconv_set_precision(tk, 0) == 0
+    out3 = np.empty_like(out)
+    assert lib.tdc_tkconv_forward_host(tk, fp(xn), fp(out3)) == 0 and np.array_equal(out3, out)
     lib.tdc_tkconv_destroy(tk)
 
 
