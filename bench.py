@@ -657,6 +657,9 @@ def main():
         "dominant_launch": {k: dom[k] for k in ("H", "R1", "R2", "tc4_us", "tc4_tflops")},
         "hbm": {"achieved": tot_by / tot_tc4 / 1e3, "peak": peaks["hbm_gbs"], "unit": "GB/s"},
         "vs_fp32_fma_peak": tot_fl / tot_tc4 / 1e6 / fp32_peak,
+        "vs_tf32x3_roof": tot_fl / tot_tc4 / 1e6 / (tf32_peak / 3.0),
+        "note": "the roof of the fp16-parts path is twice that of the TF32-parts path it replaced (fp16 MMAs contract 16 channels where "
+                "TF32 MMAs contract 8): the same achieved rate reads half as high a fraction; vs_tf32x3_roof gives it against the old roof",
         "tf32x3": {"achieved": tot_fl / tot_tc3 / 1e6, "peak": tf32_peak / 3.0, "frac": tot_fl / tot_tc3 / 1e6 / (tf32_peak / 3.0),
                    "note": "the same step with TF32 parts (mode 3) against a third of the dense TF32 rate"},
     }
@@ -805,7 +808,12 @@ def main():
             x1 = L["x"][:1].contiguous()
             t1 = T.best_tile(1, R1, H, H, R2, 3, 3, 1, 1)
             y1 = torch.empty(1, R2, H, H, device=dev)
-            us1 = time_layer(lambda: T.core_conv2d(x1, L["w"], 1, 1, w_layout=T.W_CRSK, tile=t1, out=y1), iters=20)
+            us1_fp32 = time_layer(lambda: T.core_conv2d(x1, L["w"], 1, 1, w_layout=T.W_CRSK, tile=t1, out=y1), iters=20)
+            us1_tc4 = time_layer(lambda: L["tc4"](x1, out=y1), iters=20)
+            # batch 1 as the dispatch rule runs it: tensor cores where the layer has the tiles and the arithmetic for it
+            from tdc_b200 import tc as _tc
+            b1_path = "fp16x3" if _tc.worthwhile(1, R1, H, H, R2, 3) else "fp32"
+            us1 = us1_tc4 if b1_path == "fp16x3" else us1_fp32
             cud64 = time_layer(lambda: F.conv2d(L["x"], wk, None, 1, 1))
             cud1 = time_layer(lambda: F.conv2d(x1, wk, None, 1, 1), iters=20)
             ref = F.conv2d(L["x"][:2].double(), wk.double(), None, 1, 1)
@@ -813,7 +821,8 @@ def main():
             table.append(dict(H=H, R1=R1, R2=R2, us_b64=r64["tc4_us"], us_b64_tf32x3=r64["tc3_us"], us_b64_fp32_fma=r64["simt_us"], us_b64_tf32=r64["tc1_us"],
                               cudnn_us_b64=cud64, rel_err_fp64_b64=r64["tc4_rel_err_fp64"], cudnn_rel_err_fp64_b64=cud_err,
                               frac_b64=conv_flops(BATCH, H, R1, R2) / r64["tc4_us"] / 1e6 / (f16_peak / 3.0),
-                              us_b1=us1, frac_fp32_b1=conv_flops(1, H, R1, R2) / us1 / 1e6 / fp32_peak, cudnn_us_b1=cud1,
+                              us_b1=us1, path_b1=b1_path, us_b1_fp32_fma=us1_fp32, us_b1_fp16x3=us1_tc4,
+                              frac_fp32_b1=conv_flops(1, H, R1, R2) / us1_fp32 / 1e6 / fp32_peak, cudnn_us_b1=cud1,
                               tile_b1=list(t1.as_tuple())))
         line["layers"] = table
         gm = lambda v: float(torch.tensor(v).log().mean().exp())

@@ -279,7 +279,8 @@ typedef struct tdc_tc_plan {
     int    cb;            /* channels per K step: 8 (TF32), 16 (fp16)     */
     int    nkb, n_ocb;    /* channel blocks, output-channel blocks        */
     int    hl;            /* 2 when operands are split (modes 3, 4), else 1 */
-    int    general;       /* 1: made by tdc_tc_plan_make_general          */
+    int    general;       /* 1: made by tdc_tc_plan_make_general, 2: by tdc_tc_plan_make_strided */
+    int    stride;        /* strided-row plans: the stride they were made for, else 0 */
     size_t weights_bytes; /* size of the pre-arranged filter              */
 } tdc_tc_plan;
 
@@ -290,6 +291,13 @@ TDC_API int tdc_tc_plan_make(int C, int K, int R, int S, int mode, tdc_tc_plan* 
  * (channel, filter row, filter column) triples gathered by the loaders, i.e. a classic implicit GEMM
  * that re-reads the input R*S/stride^2 times from cache.  Stride and padding come with the call. */
 TDC_API int tdc_tc_plan_make_general(int C, int K, int R, int S, int mode, tdc_tc_plan* out);
+/* The gathering plan for STRIDED convolutions whose filter is 2 or 4 strides wide (3x3 stride 2: the down-sampling cores;
+ * 7x7 stride 2: the stem, inference/resnet_inet_tt.py:319-320), mode 4.  Input column ox*stride - pad + dx is written
+ * as dx = j*stride + p: the phase p joins (channel, filter row) in the contraction, and the step j becomes a TAP — a
+ * shift by j output positions, which costs no copy at all.  The loaders then gather C*R*stride values per position
+ * instead of C*R*S (42 instead of 147 for the stem).  nt = 0: the default block size.  The stride is part of the plan;
+ * the call must repeat it (and gives the padding) in `flags`. */
+TDC_API int tdc_tc_plan_make_strided(int C, int K, int R, int S, int stride, int mode, int nt, tdc_tc_plan* out);
 /* Output channels per block are 128 / 64 / 32 by K in the plans above, which suits layers with many output positions.
  * tdc_tc_pick_nt gives the block size for a layer with `positions` output positions (B x padded image; smaller blocks
  * mean more CTAs when the positions alone do not fill `sm_count` SMs), tdc_tc_plan_make_nt makes a plan (general or

@@ -66,6 +66,7 @@ struct Args {
     long long HWin;        // input image size (channel pitch of x)
     int gather, gR, gS, gpad, Hin;   // general plan: the channels the MMAs see are (input channel, filter row, filter column) triples
     int taps_r;            // R (= S): 1 or 3
+    int halo, shift;       // patch rows beyond a tile's positions, and how far ahead of the tile the patch starts
     int Wp, Lp;            // row pitch and positions per image of the padded position space
     int P;                 // patch rows staged per CTA (multiple of 8)
     int nkb;               // channel blocks
@@ -311,14 +312,14 @@ __device__ __forceinline__ void issue_block(const Args& a, uint32_t d_main, uint
     if (a.hl == 1) {
 #pragma unroll
         for (int tap = 0; tap < TAPS; ++tap) {
-            const uint32_t a_off = (uint32_t)((tap / (TAPS == 9 ? 3 : 1)) * a.Wp + tap % (TAPS == 9 ? 3 : 1));
+            const uint32_t a_off = TAPS == 9 ? (uint32_t)((tap / 3) * a.Wp + tap % 3) : (uint32_t)tap;   // 3x3: rows and columns; else: columns
             mma_tf32<F16>(d_main, a_hi0 + a_off, b_hi0 + tap * b_tap, idesc_n, (first && tap == 0) ? 0u : 1u);
         }
     } else if (a.nmain == 2 && odd) {
         // odd channel block: second main accumulator; the lo rows of the filter start NT rows (NT x 16 bytes) in
 #pragma unroll
         for (int tap = 0; tap < TAPS; ++tap) {
-            const uint32_t a_off = (uint32_t)((tap / (TAPS == 9 ? 3 : 1)) * a.Wp + tap % (TAPS == 9 ? 3 : 1));
+            const uint32_t a_off = TAPS == 9 ? (uint32_t)((tap / 3) * a.Wp + tap % 3) : (uint32_t)tap;   // 3x3: rows and columns; else: columns
             const uint64_t b_hi = b_hi0 + tap * b_tap;
             mma_tf32<F16>(d_main + 2 * NT, a_hi0 + a_off, b_hi, idesc_n, (first && tap == 0) ? 0u : 1u);   // main1 += hi*hi
             mma_tf32<F16>(d_main + NT, a_hi0 + a_off, b_hi + (uint64_t)NT, idesc_n, 1u);                   // small += hi*lo
@@ -327,7 +328,7 @@ __device__ __forceinline__ void issue_block(const Args& a, uint32_t d_main, uint
     } else {
 #pragma unroll
         for (int tap = 0; tap < TAPS; ++tap) {
-            const uint32_t a_off = (uint32_t)((tap / (TAPS == 9 ? 3 : 1)) * a.Wp + tap % (TAPS == 9 ? 3 : 1));
+            const uint32_t a_off = TAPS == 9 ? (uint32_t)((tap / 3) * a.Wp + tap % 3) : (uint32_t)tap;   // 3x3: rows and columns; else: columns
             const uint64_t b_hi = b_hi0 + tap * b_tap;
             mma_tf32<F16>(d_main, a_hi0 + a_off, b_hi, idesc_2n, (first && tap == 0) ? 0u : 1u);           // main += hi*hi, small += hi*lo
             mma_tf32<F16>(d_main + NT, a_lo0 + a_off, b_hi, idesc_n, 1u);                                  // small += lo*hi
@@ -507,8 +508,7 @@ __global__ void __launch_bounds__(THREADS) conv_tc_kernel(const Args a) {
 
     const int ocb = blockIdx.x % a.n_ocb;
     const long long g0 = (long long)(blockIdx.x / a.n_ocb) * (MT * M_TILE);   // first output position
-    const int pad = (a.taps_r - 1) / 2;
-    const long long gp0 = g0 - (long long)pad * (a.Wp + 1);                // position of patch row 0
+    const long long gp0 = g0 - a.shift;                                    // position of patch row 0
     const long long HW = (long long)a.H * a.W;
 
     if (tid == 0) {
@@ -760,7 +760,8 @@ __global__ void __launch_bounds__(256) absmax_kernel(const float* __restrict__ x
 }
 
 __global__ void __launch_bounds__(256) prepare_weights_kernel(const float* __restrict__ w, int kcrs, float* __restrict__ wt, int C, int K, int taps,
-                                       int nt, int nkb, int n_ocb, int hl, int f16, const float* __restrict__ w_absmax, float* __restrict__ w_scale) {
+                                       int nt, int nkb, int n_ocb, int hl, int f16, const float* __restrict__ w_absmax, float* __restrict__ w_scale,
+                                       int row_S, int row_stride) {
     float ws = 1.f;                                           // fp16: the filter is scaled to the top of fp16's range
     if (f16) {
         __shared__ unsigned int word;
@@ -781,7 +782,11 @@ __global__ void __launch_bounds__(256) prepare_weights_kernel(const float* __res
         const int ocb = (int)t;
         const int oc = ocb * nt + nn, c = (kb * 2 + word) * epw + e;
         float val = 0.f;
-        if (oc < K && c < C) val = kcrs ? w[((long long)oc * C + c) * taps + tap] : w[((long long)c * taps + tap) * K + oc];
+        if (row_stride) {
+            // strided-row plan: channel c = (input channel, filter row) x column phase, tap = the filter's columns in steps of the stride
+            const int cid = c / row_stride, dx = tap * row_stride + c % row_stride, Cr = C / row_stride;
+            if (oc < K && c < C && dx < row_S) val = kcrs ? w[((long long)oc * Cr + cid) * row_S + dx] : w[((long long)cid * row_S + dx) * K + oc];
+        } else if (oc < K && c < C) val = kcrs ? w[((long long)oc * C + c) * taps + tap] : w[((long long)c * taps + tap) * K + oc];
         if (f16) {
             val *= ws;
             const __half hi = __float2half_rn(val);
@@ -870,7 +875,7 @@ EncodeTiledFn encode_tiled() {
 }
 
 // Boxes the fullest raw slot of a launch needs: the patch of every position-tile start, with the rows of a full tile.
-int max_boxes(int H, int W, int Wp, int Lp, long long total_pos, int mt, int halo_rows, int pad) {
+int max_boxes(int H, int W, int Wp, int Lp, long long total_pos, int mt, int halo_rows, int shift) {
     using namespace tdc_tc;
     const long long ptiles = (total_pos + M_TILE - 1) / M_TILE;
     // the pattern of image boundaries against tile starts repeats after lcm(Lp, 128) positions = Lp / gcd(Lp, 128) starts
@@ -882,7 +887,7 @@ int max_boxes(int H, int W, int Wp, int Lp, long long total_pos, int mt, int hal
     for (long long k = 0; k < scan; ++k) {
         const long long g0 = k * M_TILE, left = ptiles - k;
         const int rows = (int)(left < mt ? left : mt) * M_TILE + halo_rows;
-        const long long gp0 = g0 - (long long)pad * (Wp + 1);
+        const long long gp0 = g0 - shift;
         const long long lo = gp0 < 0 ? 0 : gp0, hi = (gp0 + rows < total_pos ? gp0 + rows : total_pos) - 1;
         int nb = 0;
         for (long long b = lo / Lp; b <= hi / Lp; ++b) {
@@ -901,20 +906,23 @@ extern "C" {
 
 const char* tdc_tc_last_error_string(void) { return tdc::last_error(); }
 
-static int plan_fill(int C, int K, int R, int S, int mode, int general, tdc_tc_plan* out, int nt = 0) {
+static int plan_fill(int C, int K, int R, int S, int mode, int general, tdc_tc_plan* out, int nt = 0, int stride = 0) {
     if (!out) return tc_fail(TDC_ERR_NULL, "out is NULL");
     if (C <= 0 || K <= 0) return tc_fail(TDC_ERR_SHAPE, "C=%d K=%d", C, K);
     if (mode != 1 && mode != 3 && mode != 4) return tc_fail(TDC_ERR_UNSUPPORTED, "mode %d (1 = TF32, 3 = 3xTF32, 4 = 3xFP16)", mode);
     out->C = C; out->K = K; out->R = R; out->S = S; out->mode = mode;
     out->nt = nt ? nt : pick_nt(K);
     out->cb = mode == 4 ? 16 : 8;
-    // a general plan contracts over (channel, filter row, filter column) triples, one tap
-    out->nkb = cdiv(general ? C * R * S : C, out->cb);
+    // a general plan contracts over (channel, filter row, filter column) triples, one tap; a strided-row plan over
+    // (channel, filter row, column phase) triples, with the filter's columns in steps of the stride as taps
+    out->stride = general == 2 ? stride : 0;
+    const int taps_of = general == 2 ? cdiv(S, stride) : (general ? 1 : R * S);
+    out->nkb = cdiv(general == 2 ? C * R * stride : (general ? C * R * S : C), out->cb);
     out->n_ocb = cdiv(K, out->nt);
     out->hl = mode == 1 ? 1 : 2;
     out->general = general;
     // per (output block, channel block, tap): 32 bytes (one K step) for each of the hl * nt operand rows
-    out->weights_bytes = sizeof(float) * (size_t)out->hl * (general ? 1 : R * S) * tdc_tc::CB * out->nt * out->nkb * out->n_ocb;
+    out->weights_bytes = sizeof(float) * (size_t)out->hl * taps_of * tdc_tc::CB * out->nt * out->nkb * out->n_ocb;
     // fp16 operands: a tail of scratch behind the filter holds the partial maxima of |x| of the call in flight and the
     // power of two the filter was scaled by (see tc_tail)
     if (mode == 4) out->weights_bytes += TC_TAIL_BYTES;
@@ -959,6 +967,17 @@ int tdc_tc_plan_make_nt(int C, int K, int R, int S, int mode, int general, int n
     return plan_fill(C, K, R, S, mode, general ? 1 : 0, out, nt);
 }
 
+int tdc_tc_plan_make_strided(int C, int K, int R, int S, int stride, int mode, int nt, tdc_tc_plan* out) {
+    if (nt != 0 && nt != 32 && nt != 64 && nt != 128) return tc_fail(TDC_ERR_UNSUPPORTED, "nt %d (0, 32, 64 or 128)", nt);
+    if (R <= 0 || S <= 0 || R > 15 || S > 15) return tc_fail(TDC_ERR_SHAPE, "filter %dx%d", R, S);
+    if (stride < 2 || stride > 15) return tc_fail(TDC_ERR_UNSUPPORTED, "the strided-row plan is for strides 2..15, not %d", stride);
+    const int taps = (S + stride - 1) / stride;
+    if (taps != 2 && taps != 4) return tc_fail(TDC_ERR_UNSUPPORTED, "the strided-row plan is built for 2 or 4 column taps (S/stride rounded up), not %d", taps);
+    if (mode != 4) return tc_fail(TDC_ERR_UNSUPPORTED, "the strided-row plan is built for mode 4 (fp16 parts)");
+    if ((long long)C * R * stride > (1 << 20)) return tc_fail(TDC_ERR_SHAPE, "C*R*stride = %lld is too long a contraction", (long long)C * R * stride);
+    return plan_fill(C, K, R, S, mode, 2, out, nt, stride);
+}
+
 int tdc_tc_plan_make_general(int C, int K, int R, int S, int mode, tdc_tc_plan* out) {
     if (R <= 0 || S <= 0 || R > 15 || S > 15) return tc_fail(TDC_ERR_SHAPE, "filter %dx%d", R, S);
     if ((long long)C * R * S > (1 << 20)) return tc_fail(TDC_ERR_SHAPE, "C*R*S = %lld is too long a contraction", (long long)C * R * S);
@@ -979,10 +998,13 @@ int tdc_tc_prepare_weights(const tdc_tc_plan* p, const float* w, int w_layout, v
     }
     // a general plan: the filter is a 1x1 filter over C*R*S channels; in both layouts channel, row and column are
     // adjacent index digits, so the flattened filter is addressed exactly as a 1x1 one
-    const int Cw = p->general ? p->C * p->R * p->S : p->C, taps = p->general ? 1 : p->R * p->S;
+    const bool rows = p->general == 2;
+    const int Cw = rows ? p->C * p->R * p->stride : (p->general ? p->C * p->R * p->S : p->C);
+    const int taps = rows ? cdiv(p->S, p->stride) : (p->general ? 1 : p->R * p->S);
     tdc_tc::prepare_weights_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(w, w_layout == TDC_W_KCRS, (float*)wt, Cw, p->K,
                                                                            taps, p->nt, p->nkb, p->n_ocb, p->hl, f16 ? 1 : 0, tail,
-                                                                           tail ? tail + tdc_tc::ABSMAX_SLOTS : nullptr);
+                                                                           tail ? tail + tdc_tc::ABSMAX_SLOTS : nullptr,
+                                                                           rows ? p->S : 0, rows ? p->stride : 0);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "prepare launch: %s", cudaGetErrorString(e));
 }
@@ -1006,15 +1028,24 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     } else {
         H = (H - 1) / stride + 1; W = (W - 1) / stride + 1;
     }
-    const int taps_r = p->general ? 1 : p->R;     // filter size as the MMAs see it
-    a.B = B; a.C = p->general ? p->C * p->R * p->S : p->C; a.H = H; a.W = W; a.K = p->K; a.taps_r = taps_r;
+    const bool rows = p->general == 2;            // strided-row plan
+    const int taps_r = p->general ? 1 : p->R;     // filter size as the MMAs see it (one-pass plans)
+    a.B = B; a.C = rows ? p->C * p->R * p->stride : (p->general ? p->C * p->R * p->S : p->C); a.H = H; a.W = W; a.K = p->K; a.taps_r = taps_r;
     const int pad = (taps_r - 1) / 2;
-    a.Wp = W + pad;                       // one shared zero column per row when the filter has a halo
-    a.Lp = (H + pad) * a.Wp;              // and one zero row after the image
+    const int taps = rows ? cdiv(p->S, p->stride) : taps_r * taps_r;
+    if (rows) {
+        a.gS = p->stride;                 // the loaders' third index runs over the column phases, not the filter's columns
+        a.Wp = W + taps - 1;              // a row of positions, then the taps' reach beyond it (gathered like any position)
+        a.Lp = H * a.Wp;
+        a.halo = taps - 1; a.shift = 0;
+    } else {
+        a.Wp = W + pad;                       // one shared zero column per row when the filter has a halo
+        a.Lp = (H + pad) * a.Wp;              // and one zero row after the image
+        a.halo = 2 * pad * (a.Wp + 1); a.shift = pad * (a.Wp + 1);
+    }
     a.total_pos = (long long)B * a.Lp;
     if (W > 256) return tc_fail(TDC_ERR_UNSUPPORTED, "image width %d is too large for the tensor-core path (max 256)", W);
     a.nkb = p->nkb; a.n_ocb = p->n_ocb; a.hl = p->hl;
-    const int taps = taps_r * taps_r;
     const int smem_max = facts.smem_max, sms = facts.sms;
     // Long reductions get two main accumulators per tile, fed by even and odd channel blocks (4*NT columns per tile
     // instead of 2*NT): beyond 320 accumulations with TF32 operands, beyond 144 with fp16 operands (whose layers are
@@ -1053,9 +1084,9 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     const bool bulk_ok = f16 && !p->general && stride == 1 && ((long long)Hin * Win) % 4 == 0 && x_al16 && encode_tiled() != nullptr;
     bool bulk = bulk_ok && (tn.bulk >= 0 ? tn.bulk != 0 : true);
     // a warp computes the pixel runs of the images a patch meets one image per lane: at most 32 images per patch
-    if (bulk && ((long long)2 * M_TILE + 2 * pad * (a.Wp + 1)) / a.Lp + 2 > 32) bulk = false;
+    if (bulk && ((long long)2 * M_TILE + a.halo) / a.Lp + 2 > 32) bulk = false;
     const size_t header = persist ? P_HEADER : 128;
-    const int halo_unit = 2 * pad * (a.Wp + 1);
+    const int halo_unit = a.halo;
     // Position tiles per CTA: the largest candidate (4, 2, 1; what tensor memory and shared memory hold) that still
     // gives every SM a tile.  One exception: when few position tiles share a large filter, streaming the filter
     // from L2 once per tile is what bounds the launch; then a larger candidate is taken if the estimate below
@@ -1065,7 +1096,7 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     auto raw_bytes_of = [&](int m, int P, bool use_bulk, int* cap) -> size_t {
         if (!persist || vec) return 0;
         if (!use_bulk) return sizeof(float) * (size_t)cbk * P;
-        const int c = max_boxes(H, W, a.Wp, a.Lp, a.total_pos, m, halo_unit, pad);
+        const int c = max_boxes(H, W, a.Wp, a.Lp, a.total_pos, m, halo_unit, a.shift);
         if (cap) *cap = c;
         return (size_t)c * BOXC * BOXW * sizeof(float);
     };
@@ -1181,6 +1212,8 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
 #define TDC_TC_ONE(NT_, MT_) (taps == 9 ? (const void*)&conv_tc_kernel<NT_, MT_, 9, false> : \
                               (vec ? (const void*)&conv_tc_kernel<NT_, MT_, 1, true> : (const void*)&conv_tc_kernel<NT_, MT_, 1, false>))
 #define TDC_TC_PER(NT_, MT_) (f16 ? (taps == 9 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 9, LD_RING, true> \
+                                     : taps == 4 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 4, LD_RING, true> \
+                                     : taps == 2 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 2, LD_RING, true> \
                                                : (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_RING, true>) \
                                   : (taps == 9 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 9, LD_RING, false> \
                                                : (vec ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_VEC, false> \
@@ -1233,6 +1266,7 @@ int tdc_conv2d_tc_ranged(const tdc_tc_plan* p, const float* x, const void* wt, f
         return tc_fail(TDC_ERR_UNSUPPORTED, "unknown flag bits %#x", flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK | TDC_TC_EXACT_RANGE));
     if (!p->general && stride > 1 && p->R != 1) return tc_fail(TDC_ERR_UNSUPPORTED, "a stride is taken for 1x1 filters and general plans only");
     if (!p->general && gpad != 0) return tc_fail(TDC_ERR_UNSUPPORTED, "a padding is taken for general plans only (the others pad (R-1)/2)");
+    if (p->general == 2 && stride != p->stride) return tc_fail(TDC_ERR_UNSUPPORTED, "this strided-row plan was made for stride %d, the call asks for %d", p->stride, stride);
     if (reinterpret_cast<uintptr_t>(wt) % 16 != 0) return tc_fail(TDC_ERR_UNSUPPORTED, "wt must be 16-byte aligned (the kernels fetch it with bulk copies)");
     using namespace tdc_tc;
     int device;

@@ -133,13 +133,12 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
 
     // patch rows per loader thread: MT x 128 positions, plus two image rows of halo for a 3x3 filter (the host keeps
     // the patch within PPT x 256 rows; images up to 256 wide)
-    constexpr int PPT = TAPS == 1 ? (MT >= 2 ? MT / 2 : 1) : (MT == 1 ? 3 : 4);
+    constexpr int PPT = TAPS == 1 ? (MT >= 2 ? MT / 2 : 1) : (TAPS == 9 ? (MT == 1 ? 3 : 4) : (MT * M_TILE + 8 + LOADERS - 1) / LOADERS);
     // a stage holds a.kps channel blocks (one for 3x3 filters; several for one-tap filters, whose stages would
     // otherwise be all hand-over and no work): [kps input blocks][kps filter blocks]
     const int a_floats = a.hl * CB * a.P, b_floats = a.hl * TAPS * CB * NT, stage_floats = a.kps * (a_floats + b_floats);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int pad = (a.taps_r - 1) / 2;
-    const int halo_rows = 2 * pad * (a.Wp + 1);                  // patch rows beyond the positions of a tile
+    const int halo_rows = a.halo;                                // patch rows beyond the positions of a tile
     const long long HW = (long long)a.H * a.W;
     const uint32_t b_bytes = (uint32_t)b_floats * 4u;
     const int nbuf = a.nbuf;
@@ -293,7 +292,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 int cnt, ocb;
                 tile_of<MT>(a, t, g0, cnt, ocb);
                 const int rows = cnt * M_TILE + halo_rows;
-                const long long gp0 = g0 - (long long)pad * (a.Wp + 1);
+                const long long gp0 = g0 - a.shift;
                 const float* wt_tile = a.wt + (long long)ocb * a.nkb * b_floats;
                 // offset of channel 0 of each owned patch row within a raw slot, -1 = a row of zeros
                 int roff[PPT];
@@ -375,20 +374,21 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             long long src_off[PPT];              // of the tile being copied: offset of channel 0 of each owned row, -1 = zeros
             long long l_tile = blockIdx.x;       // copy side: tile, channel block and raw slot of the next block to issue
             int l_kb = 0, l_slot = 0, l_rows = 0, c_rows = 0;   // rows of the tile being copied / converted
-            // general plan (TAPS == 1 only): a "channel" is an (input channel, filter row, filter column) triple
-            // and a patch row is an output position, whose window starts at input (iy0, ix0), possibly outside
+            // gathering plans (TAPS != 9): a "channel" is an (input channel, filter row, filter column) triple — or, in the
+            // strided-row plan, an (input channel, filter row, column phase) triple, the rest of the filter's columns
+            // being taps — and a patch row is an output position, whose window starts at input (iy0, ix0), possibly outside
             const float* rbase[PPT];             // x at (image, channel 0, iy0, ix0) of each owned row (only formed, never read, when outside)
             int rmask[PPT];                      // bit dy: input row iy0 + dy exists; bit 16 + dx: input column ix0 + dx exists; 0 = no such position
             int g_ci = 0, g_dy = 0, g_dx = 0;    // the triple of the next channel to copy
-            const int g_cin = (TAPS == 1 && a.gather) ? a.C / (a.gR * a.gS) : 0;
+            const int g_cin = (TAPS != 9 && a.gather) ? a.C / (a.gR * a.gS) : 0;
             auto issue = [&](long long li) {
                 if (li < total) {
-                    if (TAPS == 1 && a.gather) {
+                    if (TAPS != 9 && a.gather) {
                         if (l_kb == 0) {
                             long long g0;
                             int cnt, ocb;
                             tile_of<MT>(a, l_tile, g0, cnt, ocb);
-                            l_rows = cnt * M_TILE;
+                            l_rows = cnt * M_TILE + halo_rows;
 #pragma unroll
                             for (int i = 0; i < PPT; ++i) {
                                 const int pp = tid + i * LOADERS;
@@ -430,7 +430,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                             int cnt, ocb;
                             tile_of<MT>(a, l_tile, g0, cnt, ocb);
                             l_rows = cnt * M_TILE + halo_rows;
-                            const long long gp0 = g0 - (long long)pad * (a.Wp + 1);
+                            const long long gp0 = g0 - a.shift;
 #pragma unroll
                             for (int i = 0; i < PPT; ++i) {
                                 const int pp = tid + i * LOADERS;
@@ -517,7 +517,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 int cnt, ocb;
                 tile_of<MT>(a, t, g0, cnt, ocb);
                 const int rows = cnt * M_TILE + halo_rows;
-                const long long gp0 = g0 - (long long)pad * (a.Wp + 1);
+                const long long gp0 = g0 - a.shift;
                 const long long lo = gp0 < 0 ? 0 : gp0, hi = (gp0 + rows < a.total_pos ? gp0 + rows : a.total_pos) - 1;
                 int nb = 0;
                 for (long long b = image_of(a, lo), b_last = image_of(a, hi); b <= b_last; ++b) {

@@ -26,12 +26,20 @@ def one_conv(owner, name, x, w_kcrs, w_crsk, scale, shift, residual, relu, strid
             (precision != "auto" or tc.worthwhile(B, Cc, (H - 1) // stride + 1, (W - 1) // stride + 1, K, R)):
         return tc.cached(owner, name, w_kcrs, MODES.get(precision, AUTO_MODE))(x, scale, shift, residual, relu, stride=stride)
     Ho, Wo = (H + 2 * padding - R) // stride + 1, (W + 2 * padding - S) // stride + 1
-    if precision != "fp32" and not one_pass and tc.general_supported(R, S, stride, padding, Wo) and \
-            (precision != "auto" or (2.0 * B * Ho * Wo * Cc * K * R * S >= 0.5e9 and B * Ho * Wo >= 256 * 128)):
-        # strided 3x3 cores, the 7x7 stem: the gathering plan (under "auto" only with at least 256 position tiles:
-        # it pays per channel block and tile, and with few tiles the fp32 kernel's slices and clusters win)
-        return tc.cached(owner, name, w_kcrs, MODES.get(precision, AUTO_MODE), general=True)(
-            x, scale, shift, residual, relu, stride=stride, padding=padding)
+    if precision != "fp32" and not one_pass and tc.general_supported(R, S, stride, padding, Wo):
+        flops, positions = 2.0 * B * Ho * Wo * Cc * K * R * S, B * Ho * Wo
+        if tc.strided_rows(S, stride):
+            # stride 2 with a 3- or 7-wide filter: the plan that gathers (channel, filter row, column phase) and takes the
+            # column steps as MMA taps.  Measured against the fp32 kernel at batch 256 / 32: stem 556 / 87 us against
+            # 1794 / 250; 32->64 at 56: 119 / 57 against 258 / 49; 128->256 at 14: 194 / 98 against 258 / 59
+            enough = flops >= 2e9 and positions >= 64 * 128
+        else:
+            # every (channel, filter row, filter column) gathered: it pays per channel block and tile, and with few
+            # tiles the fp32 kernel's slices and clusters win
+            enough = flops >= 0.5e9 and positions >= 256 * 128
+        if precision != "auto" or enough:
+            return tc.cached(owner, name, w_kcrs, MODES.get(precision, AUTO_MODE), general=True)(
+                x, scale, shift, residual, relu, stride=stride, padding=padding)
     tile = tiles.table_tile(B, Cc, H, W, K, R, S, padding, stride)
     if w_crsk is not None:
         if callable(w_crsk):          # made (and cached by the owner) only when this path is taken
@@ -46,7 +54,7 @@ def _conv_us(B, Cc, K, Ho, Wo, R, stride=1):
     and the memory passes over input and output.  Only good for comparing ways to run the same layer."""
     flops = 2.0 * B * Ho * Wo * Cc * K * R * R
     if stride > 1 and R > 1:
-        rate = 100e12                                  # the gathering plan is bound by its loaders
+        rate = 150e12                                  # the gathering plans are bound by their loaders
     elif R > 1:
         rate = 280e12 if K >= 128 else (240e12 if K >= 64 else 110e12)
     else:

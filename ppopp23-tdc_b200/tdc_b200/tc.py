@@ -40,7 +40,7 @@ class TcConv:
         self.C, self.K, self.R, self.S, self.mode, self.general = Cc, K, R, S, mode, bool(general)
         self._weight, self._w_layout = weight, w_layout
         self.wt = self._prepare(self.plan)
-        self._by_nt = {self.plan.nt: (self.plan, self.wt)}       # output-channel block size -> (plan, prepared filter)
+        self._by_nt = {(self.plan.nt, 0): (self.plan, self.wt)}  # (output-channel block size, strided-row stride) -> (plan, prepared filter)
         self._sms = torch.cuda.get_device_properties(weight.device).multi_processor_count
         self._nt_of = {}                                         # (batch, image, flags) -> block size (the rules are library calls)
 
@@ -51,27 +51,34 @@ class TcConv:
                                               wt.data_ptr(), _stream()))
         return wt
 
-    def _for_image(self, B, H, W, Ho, Wo, flags):
+    def _make_plan(self, nt, rows_stride):
+        plan = TcPlan()
+        if rows_stride:
+            _check(lib.tdc_tc_plan_make_strided(self.C, self.K, self.R, self.S, rows_stride, self.mode, nt, C.byref(plan)))
+        else:
+            _check(lib.tdc_tc_plan_make_nt(self.C, self.K, self.R, self.S, self.mode, int(self.general), nt, C.byref(plan)))
+        return plan
+
+    def _for_image(self, B, H, W, Ho, Wo, flags, rows_stride=0):
         """(plan, prepared filter) with the output-channel block size that suits this layer: the default for layers with
         many position tiles, smaller blocks (more CTAs) for few, and smaller again while the block does not leave room
-        for two stages beside the patch of a wide image; prepared on first use."""
+        for two stages beside the patch of a wide image; prepared on first use.  `rows_stride`: the strided-row plan
+        for that stride instead of the triple-gathering one."""
         halo = 0 if self.general else (self.R - 1) // 2
-        key = (B, H, W, flags)
+        key = (B, H, W, flags, rows_stride)
         nt = self._nt_of.get(key)
         if nt is None:
             nt = lib.tdc_tc_pick_nt(self.K, self.mode, B * (Ho + halo) * (Wo + halo), self._sms)
             while nt > 32:
-                plan = TcPlan()
-                _check(lib.tdc_tc_plan_make_nt(self.C, self.K, self.R, self.S, self.mode, int(self.general), nt, C.byref(plan)))
+                plan = self._make_plan(nt, rows_stride)
                 if lib.tdc_tc_check_launch(C.byref(plan), B, H, W, flags & 0xFF) != _lib.ERR_SMEM:
                     break
                 nt //= 2
             self._nt_of[key] = nt
-        hit = self._by_nt.get(nt)
+        hit = self._by_nt.get((nt, rows_stride))
         if hit is None:
-            plan = TcPlan()
-            _check(lib.tdc_tc_plan_make_nt(self.C, self.K, self.R, self.S, self.mode, int(self.general), nt, C.byref(plan)))
-            hit = self._by_nt[nt] = (plan, self._prepare(plan))
+            plan = self._make_plan(nt, rows_stride)
+            hit = self._by_nt[(nt, rows_stride)] = (plan, self._prepare(plan))
         return hit
 
     def __call__(self, x, scale=None, bias=None, residual=None, relu=False, out=None, stride=1, padding=None):
@@ -96,7 +103,10 @@ class TcConv:
         if out is None:
             out = torch.empty((B, self.K, Ho, Wo), device=x.device, dtype=torch.float32)
         e = _epilogue(scale, bias, residual, relu)
-        plan, wt = self._for_image(B, H, W, Ho, Wo, flags)
+        # strided filters 2 or 4 strides wide (the 3x3 stride-2 cores, the 7x7 stride-2 stem): the strided-row plan, whose
+        # loaders gather C*R*stride values per position instead of C*R*S
+        rows_stride = stride if (self.general and self.mode == 4 and strided_rows(self.S, stride)) else 0
+        plan, wt = self._for_image(B, H, W, Ho, Wo, flags, rows_stride)
         if self.mode != 4:
             with _on_device(x.device):
                 _check(lib.tdc_conv2d_tc(C.byref(plan), _dev_f32(x, "x"), wt.data_ptr(), _dev_f32(out, "out"),
@@ -122,6 +132,12 @@ def supported(R, S, stride, padding, W):
 def general_supported(R, S, stride, padding, Wo):
     """True when a general plan (any filter, stride, padding) can run this convolution."""
     return 1 <= R <= 15 and 1 <= S <= 15 and 1 <= stride <= 16 and 0 <= padding <= 15 and Wo <= 256
+
+
+def strided_rows(S, stride):
+    """True when a strided convolution takes the plan that gathers (channel, filter row, column phase) and runs the
+    column steps as 2 or 4 MMA taps (fp16 parts only): 3-wide to 8-wide filters at stride 2, for instance."""
+    return stride >= 2 and -(-S // stride) in (2, 4)
 
 
 def worthwhile(B, C, H, W, K, R):

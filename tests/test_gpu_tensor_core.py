@@ -33,6 +33,14 @@ def test_plan_is_made_on_the_host(T):
     assert T.lib.tdc_tc_plan_make(64, 64, 3, 3, 4, C.byref(p)) == 0                   # fp16 parts: 16 channels per K step, a scratch tail
     assert (p.nt, p.cb, p.nkb, p.n_ocb, p.hl) == (64, 16, 4, 1, 2) and p.weights_bytes == 4 * 2 * 9 * 8 * 64 * 4 + 4 * (1024 + 64)
     assert T.lib.tdc_tc_plan_make(64, 64, 3, 3, 2, C.byref(p)) == _lib.ERR_UNSUPPORTED
+    # strided rows: the stem gathers 3 channels x 7 filter rows x 2 column phases = 42 values in 3 blocks of 16 and takes
+    # the 4 column steps as taps; a 3x3 stride-2 core gathers 6 per channel and takes 2 taps
+    assert T.lib.tdc_tc_plan_make_strided(3, 64, 7, 7, 2, 4, 0, C.byref(p)) == 0
+    assert (p.general, p.stride, p.nt, p.cb, p.nkb) == (2, 2, 64, 16, 3) and p.weights_bytes == 4 * 2 * 4 * 8 * 64 * 3 + 4 * (1024 + 64)
+    assert T.lib.tdc_tc_plan_make_strided(64, 128, 3, 3, 2, 4, 0, C.byref(p)) == 0
+    assert (p.general, p.stride, p.nt, p.nkb) == (2, 2, 128, 24) and p.weights_bytes == 4 * 2 * 2 * 8 * 128 * 24 + 4 * (1024 + 64)
+    assert T.lib.tdc_tc_plan_make_strided(8, 8, 5, 5, 2, 4, 0, C.byref(p)) == _lib.ERR_UNSUPPORTED      # 3 column steps
+    assert T.lib.tdc_tc_plan_make_strided(8, 8, 3, 3, 2, 3, 0, C.byref(p)) == _lib.ERR_UNSUPPORTED      # fp16 parts only
     assert T.lib.tdc_tc_plan_make(0, 64, 3, 3, 3, C.byref(p)) == _lib.ERR_SHAPE
     assert b"mode" in T.lib.tdc_tc_last_error_string() or b"C=" in T.lib.tdc_tc_last_error_string()
 
@@ -237,6 +245,36 @@ def test_general_plan(T, B, Cc, K, H, W, R, stride, pad):
     assert torch.equal(y2, T.TcConv(w.cuda(), mode=3, general=True)(x.cuda(), stride=stride, padding=pad))
     if R == 1:
         assert torch.equal(y2, T.TcConv(w.cuda(), mode=3)(x.cuda(), stride=stride))
+    assert tc.status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,Cc,K,H,W,R,S,stride,pad", [(2, 3, 64, 38, 38, 7, 7, 2, 3), (3, 16, 24, 15, 13, 3, 3, 2, 1), (70, 32, 48, 14, 14, 3, 3, 2, 1),
+                                                        (2, 5, 9, 11, 17, 4, 4, 2, 0), (1, 7, 130, 9, 9, 8, 8, 2, 3), (2, 6, 8, 21, 20, 3, 7, 4, 2),
+                                                        (3, 33, 40, 10, 12, 2, 4, 3, 1), (300, 8, 16, 5, 5, 3, 3, 2, 1), (2, 64, 64, 56, 56, 3, 3, 2, 1)])
+def test_strided_row_plan(T, B, Cc, K, H, W, R, S, stride, pad):
+    """The plan for strided layers with 2 or 4 column steps (stem 7x7 / 2, cores 3x3 / 2): the contraction runs over
+    (channel, filter row, column phase) and the column steps are MMA taps one output position apart.  Against the fp64
+    arbiter with and without the epilogue, both filter layouts bit-identical, odd images, filters wider than tall,
+    strides 2 to 4, batches that put many images in one tile and spread them over many CTAs."""
+    from tdc_b200 import tc
+    assert tc.strided_rows(S, stride)
+    g = torch.Generator().manual_seed(2900 + B + Cc + H + S)
+    x = torch.randn(B, Cc, H, W, generator=g)
+    w = torch.randn(K, Cc, R, S, generator=g) * (2.0 / (Cc * R * S)) ** 0.5
+    sel = sorted({0, B // 2, B - 1})
+    ref = torch.nn.functional.conv2d(x[sel].double(), w.double(), None, stride, pad).numpy()
+    conv = T.TcConv(w.cuda(), mode=4, general=True)
+    y = conv(x.cuda(), stride=stride, padding=pad)
+    assert tuple(y.shape[1:]) == ref.shape[1:] and rel_err(y[sel].cpu().numpy(), ref) <= FP32_TOL, rel_err(y[sel].cpu().numpy(), ref)
+    assert any(k[1] == stride for k in conv._by_nt), "the strided-row plan did not run"
+    scale, shift = (torch.rand(K, generator=g) + 0.5), torch.randn(K, generator=g)
+    res = torch.randn(y.shape, generator=g)
+    y2 = conv(x.cuda(), scale.cuda(), shift.cuda(), res.cuda(), True, stride=stride, padding=pad)
+    want = np.maximum(ref * scale.numpy()[None, :, None, None] + shift.numpy()[None, :, None, None] + res[sel].numpy(), 0)
+    assert rel_err(y2[sel].cpu().numpy(), want) <= FP32_TOL
+    crsk = torch.from_numpy(np.ascontiguousarray(w.numpy().transpose(1, 2, 3, 0))).cuda()
+    assert torch.equal(y, T.TcConv(crsk, mode=4, w_layout=T.W_CRSK, general=True)(x.cuda(), stride=stride, padding=pad))
     assert tc.status() == 0
 
 
