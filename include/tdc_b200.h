@@ -309,6 +309,13 @@ TDC_API int tdc_tc_prepare_weights(const tdc_tc_plan* plan, const float* w, int 
 #define TDC_TC_PAD_MASK    0xF0  /* (flags & mask) >> 4 = padding (general plans); other bits must be 0 */
 #define TDC_TC_PAD_SHIFT   4
 #define TDC_TC_EXACT_RANGE 0x100 /* mode 4: find max|x| with a pass over x instead of sampling it (see tdc_conv2d_tc_ranged) */
+/* Modes 3 and 4: the tensor core truncates its fp32 running sum toward zero at every accumulation, so a sum of n
+ * accumulations comes out n * 2^-26 too small on average.  With this flag the epilogue puts that expected loss back
+ * (one factor 1 + n * 2^-26 on the main accumulator): the error left has no sign and no longer adds up through the
+ * layers of a network (the assemblies and the Tucker module set it).  Without it the sums are stored as the tensor
+ * core returns them: sums of small integers, where nothing is truncated, are exact, which is what the reference
+ * drivers check (template_benchmark_cudnn.template:404-411,489-498). */
+#define TDC_TC_UNBIASED    0x200
 TDC_API int tdc_conv2d_tc(const tdc_tc_plan* plan, const float* x, const void* wt, float* y,
                           int B, int H, int W, const tdc_epilogue* epi, int flags, void* stream);
 /* Mode 4 scales the input by a power of two into fp16's range (which ends at 65504) and undoes the scaling in the

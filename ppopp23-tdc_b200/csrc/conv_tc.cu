@@ -67,6 +67,7 @@ struct Args {
     int gather, gR, gS, gpad, Hin;   // general plan: the channels the MMAs see are (input channel, filter row, filter column) triples
     int taps_r;            // R (= S): 1 or 3
     int halo, shift;       // patch rows beyond a tile's positions, and how far ahead of the tile the patch starts
+    float rz_unit;         // expected truncation loss of a sum per channel block (see load_chunk); 0: none put back
     int Wp, Lp;            // row pitch and positions per image of the padded position space
     int P;                 // patch rows staged per CTA (multiple of 8)
     int nkb;               // channel blocks
@@ -348,20 +349,28 @@ __device__ __forceinline__ void load_chunk(const Args& a, uint32_t taddr, uint32
         uint32_t r2[32];
         tmem_ld32(taddr + NT, r2);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        // The tensor core truncates its fp32 running sum toward zero at every accumulation, which shrinks a sum of n
+        // accumulations by n * 2^-26 on average (measured: -1.55e-8 .. -1.72e-8 per accumulation for 18..288 of
+        // them, whatever the layer or the sign pattern of its input).  `rz_unit` = 2^-26 x accumulations per channel
+        // block and main accumulator (0 = leave the sums as they are): the expected loss is put back here, so that the
+        // error left has no sign and does not add up from layer to layer of a network.
+        const float comp = fmaf(a.rz_unit, (float)blocks, 1.f);
         if constexpr (F16) {
             // `inv` undoes the range scaling of input and filter; the small accumulator also carries the 2^11 of the lo halves
             const float inv_small = inv * (1.f / 2048.f);
+            inv *= comp;
 #pragma unroll
             for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(fmaf(__uint_as_float(r2[k]), inv_small, __uint_as_float(r[k]) * inv));
         } else {
+            inv = comp;
 #pragma unroll
-            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(__uint_as_float(r[k]) + __uint_as_float(r2[k]));
+            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(fmaf(__uint_as_float(r[k]), inv, __uint_as_float(r2[k])));
         }
         if (a.nmain == 2 && blocks > 1) {          // second main accumulator (odd channel blocks)
             tmem_ld32(taddr + 2 * NT, r2);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(fmaf(__uint_as_float(r2[k]), F16 ? inv : 1.f, __uint_as_float(r[k])));
+            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(fmaf(__uint_as_float(r2[k]), inv, __uint_as_float(r[k])));
         }
     } else {
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -1052,6 +1061,7 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     // held closer to fp64); very long ones are cut into runs on top of that (below).
     a.nmain = (a.hl == 2 && (long long)p->nkb * taps > (f16 ? 144 : 320)) ? 2 : 1;
     a.tile_cols = (a.nmain == 2 ? 4 : 2) * p->nt;
+    a.rz_unit = (a.hl == 2 && (flags & TDC_TC_UNBIASED)) ? 0x1p-26f * (float)taps / (float)a.nmain : 0.f;
     // The persistent kernel wins where a CTA tile is short and its prologue and epilogue would otherwise show: split
     // operands with up to 64 output channels per block, and one-tap filters of any block size (with few tiles too:
     // its cp.async ring has all loader threads and several channel blocks in flight, 20 % faster than the one-tile
@@ -1262,8 +1272,8 @@ int tdc_conv2d_tc_ranged(const tdc_tc_plan* p, const float* x, const void* wt, f
     if (y_absmax && p->mode != 4) return tc_fail(TDC_ERR_UNSUPPORTED, "y_absmax is written by mode 4 (fp16 operands) only");
     if (B <= 0 || H <= 0 || W <= 0) return tc_fail(TDC_ERR_SHAPE, "B=%d H=%d W=%d", B, H, W);
     const int stride = (flags & TDC_TC_STRIDE_MASK) + 1, gpad = (flags & TDC_TC_PAD_MASK) >> TDC_TC_PAD_SHIFT;
-    if (flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK | TDC_TC_EXACT_RANGE))
-        return tc_fail(TDC_ERR_UNSUPPORTED, "unknown flag bits %#x", flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK | TDC_TC_EXACT_RANGE));
+    if (flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK | TDC_TC_EXACT_RANGE | TDC_TC_UNBIASED))
+        return tc_fail(TDC_ERR_UNSUPPORTED, "unknown flag bits %#x", flags & ~(TDC_TC_STRIDE_MASK | TDC_TC_PAD_MASK | TDC_TC_EXACT_RANGE | TDC_TC_UNBIASED));
     if (!p->general && stride > 1 && p->R != 1) return tc_fail(TDC_ERR_UNSUPPORTED, "a stride is taken for 1x1 filters and general plans only");
     if (!p->general && gpad != 0) return tc_fail(TDC_ERR_UNSUPPORTED, "a padding is taken for general plans only (the others pad (R-1)/2)");
     if (p->general == 2 && stride != p->stride) return tc_fail(TDC_ERR_UNSUPPORTED, "this strided-row plan was made for stride %d, the call asks for %d", p->stride, stride);

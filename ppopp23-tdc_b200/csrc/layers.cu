@@ -141,7 +141,8 @@ static int conv_forward_images(tdc_conv* l, const float* dev_in, int b0, int nb,
     float* y = l->output + (size_t)b0 * l->n * l->ho * l->wo;
     if (l->tc_mode) {
         tdc_epilogue e{nullptr, l->bias, nullptr, 0};
-        return tdc_conv2d_tc(&l->plan, x, l->tc_weights, y, nb, l->h, l->w, &e, 0, stream);
+        // layer objects are chained into networks: sums without the tensor core's truncation bias
+        return tdc_conv2d_tc(&l->plan, x, l->tc_weights, y, nb, l->h, l->w, &e, l->tc_mode == 1 ? 0 : TDC_TC_UNBIASED, stream);
     }
     return tdc_conv2d_f32(x, l->kernel, l->bias, y, nb, l->c, l->h, l->w, l->n, l->r, l->s, l->pad, l->stride, TDC_W_CRSK,
                           TDC_EPI_NONE, (l->has_tile && nb == l->b) ? &l->tile : nullptr, stream);
@@ -315,7 +316,7 @@ int tdc_tkconv_forward(tdc_tkconv* l, const float* dev_in, float** dev_out, void
     if (!l || !dev_in || !dev_out) return fail(TDC_ERR_NULL, "tdc_tkconv_forward: layer, dev_in and dev_out must be non-NULL");
     if (l->tc_mode) {
         tdc_epilogue e{nullptr, l->bias, nullptr, 0};
-        const int flags = (l->stride - 1) | (l->plan.general ? (l->pad << TDC_TC_PAD_SHIFT) : 0);
+        const int flags = (l->stride - 1) | (l->plan.general ? (l->pad << TDC_TC_PAD_SHIFT) : 0) | (l->tc_mode == 1 ? 0 : TDC_TC_UNBIASED);
         const int rc = tdc_conv2d_tc(&l->plan, dev_in, l->tc_weights, l->output, l->b, l->h, l->w, &e, flags, stream);
         if (rc) return rc;
         *dev_out = l->output;

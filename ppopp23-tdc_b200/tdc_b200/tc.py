@@ -27,10 +27,12 @@ def _check(code):
 
 
 class TcConv:
-    def __init__(self, weight, mode=3, w_layout=_lib.W_KCRS, general=False, exact_range=False):
+    def __init__(self, weight, mode=3, w_layout=_lib.W_KCRS, general=False, exact_range=False, unbiased=False):
         """weight: [K][C][R][S] (or [C][R][S][K] with w_layout=W_CRSK), fp32 CUDA tensor.  `exact_range` (mode 4): take
-        the input's scale from its true maximum (a pass over the input per call) instead of from a sample."""
-        self.exact_range = bool(exact_range)
+        the input's scale from its true maximum (a pass over the input per call) instead of from a sample.  `unbiased`
+        (modes 3, 4): put back the expected loss of the tensor core's truncating accumulation (TDC_TC_UNBIASED); sums of
+        small integers are then no longer exact."""
+        self.exact_range, self.unbiased = bool(exact_range), bool(unbiased)
         if w_layout == _lib.W_KCRS:
             K, Cc, R, S = weight.shape
         else:
@@ -107,6 +109,8 @@ class TcConv:
         # loaders gather C*R*stride values per position instead of C*R*S
         rows_stride = stride if (self.general and self.mode == 4 and strided_rows(self.S, stride)) else 0
         plan, wt = self._for_image(B, H, W, Ho, Wo, flags, rows_stride)
+        if self.unbiased and self.mode != 1:
+            flags |= 0x200                        # TDC_TC_UNBIASED
         if self.mode != 4:
             with _on_device(x.device):
                 _check(lib.tdc_conv2d_tc(C.byref(plan), _dev_f32(x, "x"), wt.data_ptr(), _dev_f32(out, "out"),
@@ -161,12 +165,13 @@ def cached(owner, name, weight, mode, w_layout=_lib.W_KCRS, general=False):
     """TcConv for `weight`, kept on the module that owns the weight (`owner`) under `name`, and
     rebuilt when the tensor is written to or replaced (version / storage check).  Keeping it on the
     owner — not in a table keyed by address — means a freed network's entries can never be taken
-    for those of a new network whose weights happen to land on the same addresses."""
+    for those of a new network whose weights happen to land on the same addresses.  These are the convolutions of the
+    modules and networks, which chain many layers: they run with `unbiased` set."""
     store = owner.__dict__.setdefault("_tc_convs", {})
     key = (weight._version, weight.data_ptr(), tuple(weight.shape))
     hit = store.get((name, mode, w_layout, general))
     if hit is None or hit[0] != key:
-        hit = store[(name, mode, w_layout, general)] = (key, TcConv(weight.detach(), mode, w_layout, general))
+        hit = store[(name, mode, w_layout, general)] = (key, TcConv(weight.detach(), mode, w_layout, general, unbiased=True))
     return hit[1]
 
 

@@ -327,6 +327,35 @@ def test_random_shapes_against_fp64(T):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("Cc,H,R,general", [(64, 56, 3, False), (256, 14, 3, False), (1024, 7, 3, False), (1024, 7, 1, False), (256, 14, 3, True)])
+def test_unbiased_sums(T, Cc, H, R, general):
+    """The tensor core truncates its running sum toward zero: raw sums come out too small by about 1.6e-8 per
+    accumulation (the slope of error against exact value).  TDC_TC_UNBIASED puts the expected loss back: the slope
+    drops under a third of the raw one (and under 7e-7), the largest and the rms error fall too; without the flag sums of
+    small integers stay exact (the reference drivers' check), with it they are within the fp32 bar."""
+    g = torch.Generator().manual_seed(40 + Cc)
+    x = torch.randn(4, Cc, H, H, generator=g).relu().cuda()
+    w = (torch.randn(Cc, Cc, R, R, generator=g) * (2.0 / (Cc * R * R)) ** 0.5).cuda()
+    kw = dict(stride=2, padding=1) if general else {}
+    ref = torch.nn.functional.conv2d(x.double(), w.double(), None, 2 if general else 1, 1 if general else (R - 1) // 2).flatten()
+    for mode in (4, 3):
+        stats = []
+        for unbiased in (False, True):
+            e = T.TcConv(w, mode=mode, general=general, unbiased=unbiased)(x, **kw).double().flatten() - ref
+            stats.append((float((e * ref).sum() / (ref * ref).sum()), float(e.abs().max() / ref.abs().max()), float(e.pow(2).mean().sqrt())))
+        (a0, m0, r0), (a1, m1, r1) = stats
+        accs = -(-Cc // (16 if mode == 4 else 8)) * (R * R if not general else 2 if mode == 4 else 9)
+        assert a0 < -0.3e-8 * accs, (mode, stats)                      # raw sums shrink (two main accumulators halve it)
+        assert abs(a1) <= max(0.3 * abs(a0), 1e-7) and abs(a1) <= 7e-7 and m1 < m0 and r1 < r0, (mode, stats)
+        assert m1 <= FP32_TOL / 2
+    xi = torch.randint(0, 10, (2, Cc, H, H), generator=g).float().cuda()
+    ones = torch.ones(32, Cc, R, R).cuda()
+    want = torch.nn.functional.conv2d(xi.double(), ones.double(), None, 2 if general else 1, 1 if general else (R - 1) // 2)
+    assert torch.equal(T.TcConv(ones, mode=4, general=general)(xi, **kw).double(), want)
+    assert rel_err(T.TcConv(ones, mode=4, general=general, unbiased=True)(xi, **kw).cpu().numpy(), want.cpu().numpy()) <= FP32_TOL
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("B,Cc,K,H,W,R", [(9, 64, 64, 56, 56, 3), (70, 24, 40, 14, 14, 3), (2, 256, 256, 14, 14, 3), (16, 32, 32, 28, 28, 1),
                                            (3, 520, 256, 12, 12, 1), (5, 33, 130, 8, 10, 3)])
 def test_fp16_parts_loaders_runs_and_range(T, B, Cc, K, H, W, R, monkeypatch):
