@@ -278,6 +278,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr));
 }
 
+// ... and 16 of them (the persistent kernel's epilogue works in half chunks: it has fewer registers per thread).
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+
 // One lane of a converged warp, chosen by the hardware.  The MMA issue loops run warp-uniform
 // (every lane waits on the barriers and computes the same descriptors) and only the MMA and
 // commit instructions sit under this predicate: operands the compiler can prove warp-uniform
@@ -342,12 +353,12 @@ __device__ __forceinline__ void issue_block(const Args& a, uint32_t d_main, uint
 // blocks of the run these accumulators hold (the second main exists from two blocks on).
 // With fp16 operands the lo halves were scaled by 2^11 on both sides (so that they stay
 // clear of fp16's subnormal range); the small accumulator carries that factor.
-template <int NT, bool F16 = false>
-__device__ __forceinline__ void load_chunk(const Args& a, uint32_t taddr, uint32_t (&r)[32], int blocks, float inv = 1.f) {
-    tmem_ld32(taddr, r);
+template <int NT, bool F16 = false, int W = 32>
+__device__ __forceinline__ void load_chunk(const Args& a, uint32_t taddr, uint32_t (&r)[W], int blocks, float inv = 1.f) {
+    tmem_ld(taddr, r);
     if (a.hl == 2) {
-        uint32_t r2[32];
-        tmem_ld32(taddr + NT, r2);
+        uint32_t r2[W];
+        tmem_ld(taddr + NT, r2);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         // The tensor core truncates its fp32 running sum toward zero at every accumulation, which shrinks a sum of n
         // accumulations by n * 2^-26 on average (measured: -1.55e-8 .. -1.72e-8 per accumulation for 18..288 of
@@ -360,17 +371,17 @@ __device__ __forceinline__ void load_chunk(const Args& a, uint32_t taddr, uint32
             const float inv_small = inv * (1.f / 2048.f);
             inv *= comp;
 #pragma unroll
-            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(fmaf(__uint_as_float(r2[k]), inv_small, __uint_as_float(r[k]) * inv));
+            for (int k = 0; k < W; ++k) r[k] = __float_as_uint(fmaf(__uint_as_float(r2[k]), inv_small, __uint_as_float(r[k]) * inv));
         } else {
             inv = comp;
 #pragma unroll
-            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(fmaf(__uint_as_float(r[k]), inv, __uint_as_float(r2[k])));
+            for (int k = 0; k < W; ++k) r[k] = __float_as_uint(fmaf(__uint_as_float(r[k]), inv, __uint_as_float(r2[k])));
         }
         if (a.nmain == 2 && blocks > 1) {          // second main accumulator (odd channel blocks)
-            tmem_ld32(taddr + 2 * NT, r2);
+            tmem_ld(taddr + 2 * NT, r2);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int k = 0; k < 32; ++k) r[k] = __float_as_uint(fmaf(__uint_as_float(r2[k]), inv, __uint_as_float(r[k])));
+            for (int k = 0; k < W; ++k) r[k] = __float_as_uint(fmaf(__uint_as_float(r2[k]), inv, __uint_as_float(r[k])));
         }
     } else {
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -386,48 +397,49 @@ __device__ __forceinline__ void load_chunk(const Args& a, uint32_t taddr, uint32
 // `accum`: these accumulators are a later run of the tile's channel blocks: y already holds the sum of the
 // earlier runs (written by this same thread) and is added first.  `final`: this is the tile's last run, the
 // fused options apply; otherwise the bare partial sum is stored.
-__device__ __forceinline__ void store_chunk(const Args& a, const uint32_t (&r)[32], long long out_off, int oc0, long long HW,
+template <int W = 32>
+__device__ __forceinline__ void store_chunk(const Args& a, const uint32_t (&r)[W], long long out_off, int oc0, long long HW,
                                             bool accum = false, bool final = true, float* vmax = nullptr) {
     const int lane = threadIdx.x & 31;
     const bool live = out_off >= 0;
     const long long o0 = (live ? out_off : 0) + (long long)oc0 * HW;
     float* yp = a.y + o0;
     const int n = a.K - oc0;                      // channels of this chunk that exist
-    if (n >= 32 && !accum && (!final || (!a.scale && !a.bias && !a.residual && !a.relu))) {
+    if (n >= W && !accum && (!final || (!a.scale && !a.bias && !a.residual && !a.relu))) {
         if (live) {
 #pragma unroll
-            for (int k = 0; k < 32; ++k) { *yp = __uint_as_float(r[k]); yp += HW; }
+            for (int k = 0; k < W; ++k) { *yp = __uint_as_float(r[k]); yp += HW; }
             if (vmax) {                               // magnitudes compare like their bit patterns
                 unsigned int m = __float_as_uint(*vmax);
 #pragma unroll
-                for (int k = 0; k < 32; ++k) m = max(m, r[k] & 0x7fffffffu);
+                for (int k = 0; k < W; ++k) m = max(m, r[k] & 0x7fffffffu);
                 *vmax = __uint_as_float(m);
             }
         }
         return;
     }
-    float v[32];
+    float v[W];
 #pragma unroll
-    for (int k = 0; k < 32; ++k) v[k] = __uint_as_float(r[k]);
+    for (int k = 0; k < W; ++k) v[k] = __uint_as_float(r[k]);
     if (accum && live) {
         const float* q = yp;                       // one stepping pointer, not 32 addresses
 #pragma unroll
-        for (int k = 0; k < 32; ++k) { if (k < n) v[k] += *q; q += HW; }
+        for (int k = 0; k < W; ++k) { if (k < n) v[k] += *q; q += HW; }
     }
     if (!final) {
         if (live) {
 #pragma unroll
-            for (int k = 0; k < 32; ++k)
+            for (int k = 0; k < W; ++k)
                 if (k < n) yp[k * HW] = v[k];
         }
         return;
     }
-    if (n >= 32 && a.epi_vec) {
+    if (n >= W && a.epi_vec) {
         // a whole chunk, 16-byte aligned scale / bias: eight warp-uniform 16-byte loads each instead of 32 shuffles
         if (a.scale) {
             const float4* sp = reinterpret_cast<const float4*>(a.scale + oc0);
 #pragma unroll
-            for (int k4 = 0; k4 < 8; ++k4) {
+            for (int k4 = 0; k4 < W / 4; ++k4) {
                 const float4 t = __ldg(sp + k4);
                 v[4 * k4] *= t.x; v[4 * k4 + 1] *= t.y; v[4 * k4 + 2] *= t.z; v[4 * k4 + 3] *= t.w;
             }
@@ -435,48 +447,48 @@ __device__ __forceinline__ void store_chunk(const Args& a, const uint32_t (&r)[3
         if (a.bias) {
             const float4* bp = reinterpret_cast<const float4*>(a.bias + oc0);
 #pragma unroll
-            for (int k4 = 0; k4 < 8; ++k4) {
+            for (int k4 = 0; k4 < W / 4; ++k4) {
                 const float4 t = __ldg(bp + k4);
                 v[4 * k4] += t.x; v[4 * k4 + 1] += t.y; v[4 * k4 + 2] += t.z; v[4 * k4 + 3] += t.w;
             }
         }
     } else {
-        const float sc = (a.scale && lane < n) ? __ldg(a.scale + oc0 + lane) : 1.f;
-        const float bi = (a.bias && lane < n) ? __ldg(a.bias + oc0 + lane) : 0.f;
+        const float sc = (a.scale && lane < n && lane < W) ? __ldg(a.scale + oc0 + lane) : 1.f;
+        const float bi = (a.bias && lane < n && lane < W) ? __ldg(a.bias + oc0 + lane) : 0.f;
         if (a.scale) {
 #pragma unroll
-            for (int k = 0; k < 32; ++k) v[k] *= __shfl_sync(0xffffffffu, sc, k);
+            for (int k = 0; k < W; ++k) v[k] *= __shfl_sync(0xffffffffu, sc, k);
         }
         if (a.bias) {
 #pragma unroll
-            for (int k = 0; k < 32; ++k) v[k] += __shfl_sync(0xffffffffu, bi, k);
+            for (int k = 0; k < W; ++k) v[k] += __shfl_sync(0xffffffffu, bi, k);
         }
     }
     if (a.residual && live) {
         const float* rp = a.residual + o0;
-        float rv[32];
+        float rv[W];
 #pragma unroll
-        for (int k = 0; k < 32; ++k) rv[k] = k < n ? rp[k * HW] : 0.f;
+        for (int k = 0; k < W; ++k) rv[k] = k < n ? rp[k * HW] : 0.f;
 #pragma unroll
-        for (int k = 0; k < 32; ++k) v[k] += rv[k];
+        for (int k = 0; k < W; ++k) v[k] += rv[k];
     }
     if (a.relu) {
 #pragma unroll
-        for (int k = 0; k < 32; ++k) v[k] = fmaxf(v[k], 0.f);
+        for (int k = 0; k < W; ++k) v[k] = fmaxf(v[k], 0.f);
     }
     if (vmax && live) {                              // largest stored magnitude (as a bit pattern: a NaN must not get lost)
         unsigned int m = __float_as_uint(*vmax);
 #pragma unroll
-        for (int k = 0; k < 32; ++k) m = max(m, k < n ? (__float_as_uint(v[k]) & 0x7fffffffu) : 0u);
+        for (int k = 0; k < W; ++k) m = max(m, k < n ? (__float_as_uint(v[k]) & 0x7fffffffu) : 0u);
         *vmax = __uint_as_float(m);
     }
     if (live) {
-        if (n >= 32) {
+        if (n >= W) {
 #pragma unroll
-            for (int k = 0; k < 32; ++k) { *yp = v[k]; yp += HW; }
+            for (int k = 0; k < W; ++k) { *yp = v[k]; yp += HW; }
         } else {
 #pragma unroll
-            for (int k = 0; k < 32; ++k)
+            for (int k = 0; k < W; ++k)
                 if (k < n) yp[k * HW] = v[k];
         }
     }
@@ -1118,7 +1130,7 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
         const int P4 = ((4 * M_TILE + halo_unit) + 7) / 8 * 8;
         const size_t sb4 = sizeof(float) * ((size_t)a.hl * CB * P4 + (size_t)a.hl * taps * CB * p->nt), rb4 = sizeof(float) * (size_t)cbk * P4;
         const long long tiles4 = ((a.total_pos + 4ll * M_TILE - 1) / (4ll * M_TILE)) * a.n_ocb;
-        if (2 * sb4 + 2 * rb4 <= room && P4 <= 4 * LOADERS && tiles4 >= sms) bulk = false;
+        if (2 * sb4 + 2 * rb4 <= room && P4 <= p_rows_cap(4) && tiles4 >= sms) bulk = false;
     }
     if (bulk && mt > 2) mt = 2;                                 // its producer is the fourth issuer warp
     int best_mt = 0, big_mt = 0;
@@ -1131,7 +1143,7 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
             const size_t sb = sizeof(float) * ((size_t)a.hl * CB * P + (size_t)a.hl * taps * CB * p->nt);
             int cap = 0;
             const size_t rb = raw_bytes_of(m, P, bulk, &cap);
-            if (2 * sb + 2 * rb > room || P > (persist && m > 1 ? 4 : 3) * LOADERS || (bulk && (cap > P_MAXBOX || cap == 0))) continue;   // rows per loader thread the kernels are built for
+            if (2 * sb + 2 * rb > room || P > (persist ? p_rows_cap(m) : 3 * LOADERS) || (bulk && (cap > P_MAXBOX || cap == 0))) continue;   // rows per loader thread the kernels are built for
             const double ntl = (double)((a.total_pos + (long long)m * M_TILE - 1) / ((long long)m * M_TILE)) * a.n_ocb;
             const double rounds = (double)(((long long)ntl + sms - 1) / sms);
             const double tile_clk = a.nkb * (m * taps * op_bytes + (double)sb + 2.0 * rb) / 128.0 + 2000.0 * m * (p->nt / 32);
@@ -1153,7 +1165,7 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     int cap = 0;
     const size_t raw_bytes = raw_bytes_of(mt, a.P, bulk, &cap);
     a.nbox_cap = cap;
-    a.step_y = LOADERS / a.Wp; a.step_x = LOADERS % a.Wp;
+    a.step_y = P_LOADERS / a.Wp; a.step_x = P_LOADERS % a.Wp;
     // One-tap filters (1x1, general plans) do one or two MMAs per channel block and position tile: a stage of one
     // block would be all hand-over.  Their stages take up to four blocks (what leaves room for two stages and,
     // with a raw ring, two raw slots).

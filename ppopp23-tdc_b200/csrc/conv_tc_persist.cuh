@@ -38,10 +38,23 @@ namespace tdc_tc {
 #ifndef TDC_TC_EPI_GROUPS
 #define TDC_TC_EPI_GROUPS 2
 #endif
+#ifndef TDC_TC_LOADER_WARPS
+#define TDC_TC_LOADER_WARPS 8
+#endif
 constexpr int P_GROUPS  = TDC_TC_EPI_GROUPS;          // groups of four epilogue warps
-constexpr int P_THREADS = 384 + 128 * P_GROUPS;     // 8 loader warps, 4 issuer warps (one lane each), the epilogue groups
-constexpr int P_PRODUCER = 11;   // the bulk loader's producer is the fourth issuer warp, free when MT <= 2 (a 21st warp would cost
-                                 // every thread registers: the allocation rounds the CTA up to 768 threads)
+constexpr int P_LOADERS = 32 * TDC_TC_LOADER_WARPS;   // threads that stage the input: the kernel is paced by their instruction latency
+constexpr int P_IW0     = TDC_TC_LOADER_WARPS;        // first of the four issuer warps (a multiple of 4: the epilogue warps that
+constexpr int P_EW0     = P_IW0 + 4;                  // follow them read the lane quarter warp % 4 of tensor memory)
+constexpr int P_THREADS = P_LOADERS + 128 + 128 * P_GROUPS;   // loader warps, 4 issuer warps (one lane each), the epilogue groups
+constexpr int P_PRODUCER = P_IW0 + 3;   // the bulk loader's producer is the fourth issuer warp, free when MT <= 2
+static_assert(TDC_TC_LOADER_WARPS % 4 == 0, "whole warpgroups of loaders");
+// With 12 loader warps (768 threads, 80 registers each, the epilogue in half chunks so that nothing spills) the
+// loader-bound layers gain 3-8 % (56x56x64 at batch 256: 200 -> 188 us, the 7x7 stem 567 -> 525 us) and the layers with
+// many output channels per position lose as much (64 -> 256 1x1: 304 -> 353 us, 14x14x128: 25.6 -> 27.6 us): level
+// over the sweep, so 8 it stays.  Trading registers between the roles (setmaxnreg) made ptxas spill 1.7 KB per thread.
+constexpr int P_EPI_W = P_THREADS > 640 ? 16 : 32;   // channels an epilogue thread holds at a time
+// patch rows a CTA may stage (3x3 filters: MT x 128 positions plus two image rows of halo, images up to 256 wide)
+__host__ __device__ constexpr int p_rows_cap(int mt) { return mt == 1 ? 768 : 1024; }
 constexpr int P_HEADER  = 1024;  // bytes of barriers, flags and the producer's box table in front of the stages
 constexpr int P_MAXBOX  = 64;    // boxes one raw slot may hold (entries of the box table)
 constexpr int LD_RING = 0, LD_VEC = 1, LD_BULK = 2;
@@ -133,7 +146,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
 
     // patch rows per loader thread: MT x 128 positions, plus two image rows of halo for a 3x3 filter (the host keeps
     // the patch within PPT x 256 rows; images up to 256 wide)
-    constexpr int PPT = TAPS == 1 ? (MT >= 2 ? MT / 2 : 1) : (TAPS == 9 ? (MT == 1 ? 3 : 4) : (MT * M_TILE + 8 + LOADERS - 1) / LOADERS);
+    constexpr int PPT = TAPS == 1 ? (MT * M_TILE + P_LOADERS - 1) / P_LOADERS
+                                   : (TAPS == 9 ? (p_rows_cap(MT) + P_LOADERS - 1) / P_LOADERS : (MT * M_TILE + 8 + P_LOADERS - 1) / P_LOADERS);
     // a stage holds a.kps channel blocks (one for 3x3 filters; several for one-tap filters, whose stages would
     // otherwise be all hand-over and no work): [kps input blocks][kps filter blocks]
     const int a_floats = a.hl * CB * a.P, b_floats = a.hl * TAPS * CB * NT, stage_floats = a.kps * (a_floats + b_floats);
@@ -145,17 +159,17 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     const long long ntiles = a.ntiles;          // position tiles x output-channel blocks
     // fp16 operands without a bound of |x|: this thread's samples of the input, loaded now, reduced after the set-up below
     unsigned int sampled = 0;
-    if constexpr (F16) { if (!a.x_absmax && (warp < 8 || warp >= 12)) sampled = range_sample_load(a.x, a.x_count); }
+    if constexpr (F16) { if (!a.x_absmax && (warp < P_IW0 || warp >= P_EW0)) sampled = range_sample_load(a.x, a.x_count); }
 
     if (tid == 0) {
-        for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], LOADERS / 32 + 1); mbar_init(&empty_bar[s], MT); }   // one arrival per loader warp + the filter's bytes
-        for (int b = 0; b < 8; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4 * (NT / 32)); }   // one per issuer; one per epilogue warp and 32-channel chunk
-        for (int d = 0; d < 8; ++d) { mbar_init(&rfull_bar[d], 1); mbar_init(&rempty_bar[d], LOADERS / 32); }    // the producer's arrive + bytes; one per converting warp
+        for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], P_LOADERS / 32 + 1); mbar_init(&empty_bar[s], MT); }   // one arrival per loader warp + the filter's bytes
+        for (int b = 0; b < 8; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4 * (NT / P_EPI_W)); }   // one per issuer; one per epilogue warp and chunk of channels
+        for (int d = 0; d < 8; ++d) { mbar_init(&rfull_bar[d], 1); mbar_init(&rempty_bar[d], P_LOADERS / 32); }    // the producer's arrive + bytes; one per converting warp
         *abort_flag = 0;
         *range_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {
+    if (warp == P_IW0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)a.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -169,19 +183,19 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     // (with a bound of |x| everybody reads it here; without one only the converting and the draining warps need the
     // scale and wait for the samples, at named barrier 1, while the producer and the issuers already start)
     float xs = 1.f, inv = 1.f;
-    constexpr int SCALED_THREADS = LOADERS + 128 * P_GROUPS;
+    constexpr int SCALED_THREADS = P_LOADERS + 128 * P_GROUPS;
     if constexpr (F16) {
         if (a.x_absmax) {
             xs = range_scale(absmax_of(a.x_absmax, max_word), 14);
             if (tid == 0) *max_word = 0;                 // from here on: the largest |y| of this CTA (read after the last barrier)
-        } else if (warp < 8 || warp >= 12) {
+        } else if (warp < P_IW0 || warp >= P_EW0) {
             if (tid == 0) *max_word = 0;
             xs = range_scale(range_sample_max(sampled, range_word, SCALED_THREADS), 8);
         }
         inv = 1.f / (xs * a.w_scale[0]);
     }
 
-    if (warp < 8) {
+    if (warp < P_IW0) {
         // ================= loaders =================
         // no division in these loops: the loaders are bound by instruction latency (two warps per scheduler), so the
         // ring positions are counters that wrap, not quotients of a running index
@@ -231,11 +245,11 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 const int rows = cnt * M_TILE;                           // a one-tap filter has no halo
                 const float* wt_tile = a.wt + (long long)ocb * a.nkb * b_floats;
                 bool ok = true;
-                constexpr int NI = (MT * M_TILE / 2 + LOADERS - 1) / LOADERS;
+                constexpr int NI = (MT * M_TILE / 2 + P_LOADERS - 1) / P_LOADERS;
                 long long off[NI];
 #pragma unroll
                 for (int i = 0; i < NI; ++i) {
-                    const int quad = (tid + i * LOADERS) >> 1;
+                    const int quad = (tid + i * P_LOADERS) >> 1;
                     off[i] = -1;
                     if (quad * 4 < rows) {
                         const long long g = g0 + quad * 4;
@@ -246,7 +260,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 auto load = [&](int kb, float4 (&v)[NI][4]) {
 #pragma unroll
                     for (int i = 0; i < NI; ++i) {
-                        const int c0 = kb * CB + ((tid + i * LOADERS) & 1) * 4;
+                        const int c0 = kb * CB + ((tid + i * P_LOADERS) & 1) * 4;
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
                             v[i][j] = (off[i] >= 0 && c0 + j < a.C) ? __ldg(reinterpret_cast<const float4*>(a.x + off[i] + (long long)(c0 + j) * HW))
@@ -258,7 +272,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     if (!A) return false;
 #pragma unroll
                     for (int i = 0; i < NI; ++i) {
-                        const int item = tid + i * LOADERS, q = item & 1, pp = (item >> 1) * 4;
+                        const int item = tid + i * P_LOADERS, q = item & 1, pp = (item >> 1) * 4;
                         if (pp < rows) {
                             put(A, q, pp + 0, v[i][0].x, v[i][1].x, v[i][2].x, v[i][3].x);
                             put(A, q, pp + 1, v[i][0].y, v[i][1].y, v[i][2].y, v[i][3].y);
@@ -322,7 +336,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     my_box0 -= my_nbox;
 #pragma unroll
                     for (int i = 0; i < PPT; ++i) {
-                        const int pp = tid + i * LOADERS;
+                        const int pp = tid + i * P_LOADERS;
                         const long long j = bi - b_first;                        // lane that holds this row's image
                         const int src = (j >= 0 && j < 32) ? (int)j : 0;
                         const int pix4 = __shfl_sync(0xffffffffu, my_pix4, src), box0 = __shfl_sync(0xffffffffu, my_box0, src);
@@ -345,7 +359,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     TDC_PROF_SPAN_BEGIN;
 #pragma unroll
                     for (int i = 0; i < PPT; ++i) {
-                        const int pp = tid + i * LOADERS;
+                        const int pp = tid + i * P_LOADERS;
                         if (pp < rows) {
                             float c[CBK];
 #pragma unroll
@@ -391,7 +405,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                             l_rows = cnt * M_TILE + halo_rows;
 #pragma unroll
                             for (int i = 0; i < PPT; ++i) {
-                                const int pp = tid + i * LOADERS;
+                                const int pp = tid + i * P_LOADERS;
                                 rmask[i] = 0; rbase[i] = a.x;
                                 const long long g = g0 + pp;
                                 if (pp < l_rows && g < a.total_pos) {
@@ -415,11 +429,11 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                             const int sel = g_ci < g_cin ? ((1 << g_dy) | (0x10000 << g_dx)) : -1;   // -1 never matches a mask
 #pragma unroll
                             for (int i = 0; i < PPT; ++i) {
-                                if (tid + i * LOADERS < l_rows) {
+                                if (tid + i * P_LOADERS < l_rows) {
                                     const bool real = (rmask[i] & sel) == sel;
                                     const float* src = real ? rbase[i] + delta : a.x;
                                     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;"
-                                                 ::"r"(dst0 + (uint32_t)((j * a.P + i * LOADERS) * 4)), "l"(src), "r"(real ? 4u : 0u) : "memory");
+                                                 ::"r"(dst0 + (uint32_t)((j * a.P + i * P_LOADERS) * 4)), "l"(src), "r"(real ? 4u : 0u) : "memory");
                                 }
                             }
                             if (++g_dx == a.gS) { g_dx = 0; if (++g_dy == a.gR) { g_dy = 0; ++g_ci; } }
@@ -433,7 +447,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                             const long long gp0 = g0 - a.shift;
 #pragma unroll
                             for (int i = 0; i < PPT; ++i) {
-                                const int pp = tid + i * LOADERS;
+                                const int pp = tid + i * P_LOADERS;
                                 src_off[i] = -1;
                                 if (pp < l_rows) {
                                     const long long g = gp0 + pp;
@@ -450,7 +464,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                         const int c0 = l_kb * CBK;
 #pragma unroll
                         for (int i = 0; i < PPT; ++i) {
-                            const int pp = tid + i * LOADERS;
+                            const int pp = tid + i * P_LOADERS;
                             if (pp < l_rows) {
                                 const float* src = a.x + (src_off[i] >= 0 ? src_off[i] + (long long)c0 * a.HWin : 0);
 #pragma unroll
@@ -486,7 +500,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 if (++c_slot == depth) c_slot = 0;
 #pragma unroll
                 for (int i = 0; i < PPT; ++i) {
-                    const int pp = tid + i * LOADERS;
+                    const int pp = tid + i * P_LOADERS;
                     if (pp < c_rows) {
                         float c[CBK];
 #pragma unroll
@@ -501,8 +515,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             asm volatile("cp.async.wait_all;" ::: "memory");
         }
     }
-    if (warp < 8) TDC_PROF_FLUSH(0);
-    if (warp < 8) {}
+    if (warp < P_IW0) TDC_PROF_FLUSH(0);
+    if (warp < P_IW0) {}
     else if (LD == LD_BULK && warp == P_PRODUCER) {
       {
         // ================= producer of the bulk loader: one thread =================
@@ -549,9 +563,9 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
         __syncwarp();
       }
     }
-    else if (warp < 12) {
-        // ================= MMA issuers: warp 8+mt owns position tile mt =================
-        const int mt = __shfl_sync(0xffffffffu, warp - 8, 0);
+    else if (warp < P_EW0) {
+        // ================= MMA issuers: warp P_IW0 + mt owns position tile mt =================
+        const int mt = __shfl_sync(0xffffffffu, warp - P_IW0, 0);
         if (mt < MT) {
             long long j = 0;                    // accumulator hand-overs so far: one per tile and run
             int st_idx = 0, st_use = 0;         // stage to consume next, parity of its use count
@@ -608,9 +622,9 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
         // The work items of a CTA tile are (position tile, 32-channel chunk) pairs, dealt to the groups in turn: the
         // epilogue is a latency chain (tensor memory -> registers -> residual loads -> stores), and several chains in
         // flight hide more of it than one; all groups start on the first position tile, whose issuer is released first.
-        const int grp = (warp - 12) >> 2;          // warps 12 .. 12 + 4 * P_GROUPS - 1
+        const int grp = (warp - P_EW0) >> 2;       // warps P_EW0 .. P_EW0 + 4 * P_GROUPS - 1
         const int q = warp & 3;
-        constexpr int CHUNKS = NT / 32;
+        constexpr int CHUNKS = NT / P_EPI_W;
         long long j = 0;
         float ymax = 0.f;                       // largest magnitude this thread stored, compared as a bit pattern (so a NaN counts as large)
         float* const track = (F16 || a.y_absmax) ? &ymax : nullptr;
@@ -637,15 +651,15 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                         const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
                         if (yy < a.H && xx < a.W) out_off = b * a.K * HW + (long long)yy * a.W + xx;
                     }
-                    uint32_t r[32];
-                    load_chunk<NT, F16>(a, tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * a.tile_cols + chunk * 32), r, blocks, inv);
+                    uint32_t r[P_EPI_W];
+                    load_chunk<NT, F16, P_EPI_W>(a, tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(slot * a.tile_cols + chunk * P_EPI_W), r, blocks, inv);
                     // this chunk of the slot is in registers: one arrival per warp and chunk hands the slot back when
                     // all of its chunks have been read, before the stores
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tempty_bar[slot])) : "memory");
                     { TDC_PROF_SPAN_BEGIN;
-                      store_chunk(a, r, out_off, ocb * NT + chunk * 32, HW, seg > 0, seg == a.nseg - 1, seg == a.nseg - 1 ? track : nullptr);
+                      store_chunk<P_EPI_W>(a, r, out_off, ocb * NT + chunk * P_EPI_W, HW, seg > 0, seg == a.nseg - 1, seg == a.nseg - 1 ? track : nullptr);
                       TDC_PROF_SPAN_END(7); }
                 }
             }
@@ -669,7 +683,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
         if (blockIdx.x == 0)
             for (int i = gridDim.x + tid; i < ABSMAX_SLOTS; i += P_THREADS) a.y_absmax[i] = 0.f;
     }
-    if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)a.tmem_cols) : "memory");
+    if (warp == P_IW0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)a.tmem_cols) : "memory");
 }
 
 }  // namespace tdc_tc
