@@ -5,6 +5,8 @@
     python kernel_bench.py maxpool2 --batch 128 --channels 64 --size 224     # 2x2 / stride 2
     python kernel_bench.py conv --mode 4 --batch 64 --channels 64 --size 56 [--filter 3]   # core conv, channels -> channels
                                                         # --mode 0: fp32 FMA kernel (table tile), 1 / 3 / 4: tensor cores
+    python kernel_bench.py conv --mode 4 --batch 32 --channels 3 --out-channels 64 --size 224 --filter 7 --stride 2 --pad 3
+                                                        # a strided layer (here the ResNet stem) on the gathering plans
 
 `affine`: scale, shift and ReLU over the first `--channels` channels of a [batch][--of][size][size] buffer, the
 pre-activation of a DenseNet layer.  Algorithmic bytes = input read once + output written once; the L2 is flushed
@@ -26,6 +28,9 @@ def main(argv=None):
     ap.add_argument("kernel", choices=["affine", "maxpool", "maxpool2", "conv"])
     ap.add_argument("--mode", type=int, default=4, choices=[0, 1, 3, 4])
     ap.add_argument("--filter", type=int, default=3)
+    ap.add_argument("--out-channels", type=int, default=None, help="output channels of the conv (default: --channels)")
+    ap.add_argument("--stride", type=int, default=1)
+    ap.add_argument("--pad", type=int, default=None, help="padding of the conv (default: (filter - 1) / 2)")
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--channels", type=int, default=224)
     ap.add_argument("--of", type=int, default=None, help="channels of the buffer the input is a prefix of (affine)")
@@ -44,19 +49,23 @@ def main(argv=None):
         run = lambda: ops.affine_relu(buf[:, :C], scale, shift, relu=True, out=out)
         nbytes = 2 * out.numel() * 4
     elif a.kernel == "conv":
-        k = a.filter
+        k, K, st = a.filter, a.out_channels or C, a.stride
+        pad = (k - 1) // 2 if a.pad is None else a.pad
+        Ho = (H + 2 * pad - k) // st + 1
         g = torch.Generator().manual_seed(1)
         x = torch.randn(B, C, H, H, generator=g).to(dev)
-        w = (torch.randn(C, C, k, k, generator=g) * (2.0 / (C * k * k)) ** 0.5).to(dev)
-        out = torch.empty(B, C, H, H, device=dev)
+        w = (torch.randn(K, C, k, k, generator=g) * (2.0 / (C * k * k)) ** 0.5).to(dev)
+        out = torch.empty(B, K, Ho, Ho, device=dev)
+        general = not (k in (1, 3) and pad == (k - 1) // 2 and (st == 1 or k == 1))
         if a.mode:
-            conv = T.TcConv(w, mode=a.mode)
-            run = lambda: conv(x, out=out)
+            conv = T.TcConv(w, mode=a.mode, general=general)
+            kw = dict(stride=st, padding=pad) if general else dict(stride=st)
+            run = lambda: conv(x, out=out, **kw)
         else:
-            wc, tile = T.permute_weights(w), T.best_tile(B, C, H, H, C, k, k, (k - 1) // 2, 1)
-            run = lambda: T.core_conv2d(x, wc, 1, (k - 1) // 2, w_layout=T.W_CRSK, tile=tile, out=out)
+            wc, tile = T.permute_weights(w), T.best_tile(B, C, H, H, K, k, k, pad, st)
+            run = lambda: T.core_conv2d(x, wc, st, pad, w_layout=T.W_CRSK, tile=tile, out=out)
         nbytes = (x.numel() + out.numel() + w.numel()) * 4
-        flops = 2.0 * B * C * C * k * k * H * H
+        flops = 2.0 * B * C * K * k * k * Ho * Ho
     else:
         x = torch.randn(B, C, H, H, device=dev)
         k, s, p = (3, 2, 1) if a.kernel == "maxpool" else (2, 2, 0)
