@@ -281,6 +281,7 @@ typedef struct tdc_tc_plan {
     int    hl;            /* 2 when operands are split (modes 3, 4), else 1 */
     int    general;       /* 1: made by tdc_tc_plan_make_general, 2: by tdc_tc_plan_make_strided */
     int    stride;        /* strided-row plans: the stride they were made for, else 0 */
+    int    phase;         /* strided-row plans: 1 when the column phases count from an even input column (odd padding at stride 2) */
     size_t weights_bytes; /* size of the pre-arranged filter              */
 } tdc_tc_plan;
 
@@ -295,9 +296,12 @@ TDC_API int tdc_tc_plan_make_general(int C, int K, int R, int S, int mode, tdc_t
  * 7x7 stride 2: the stem, inference/resnet_inet_tt.py:319-320), mode 4.  Input column ox*stride - pad + dx is written
  * as dx = j*stride + p: the phase p joins (channel, filter row) in the contraction, and the step j becomes a TAP — a
  * shift by j output positions, which costs no copy at all.  The loaders then gather C*R*stride values per position
- * instead of C*R*S (42 instead of 147 for the stem).  nt = 0: the default block size.  The stride is part of the plan;
- * the call must repeat it (and gives the padding) in `flags`. */
-TDC_API int tdc_tc_plan_make_strided(int C, int K, int R, int S, int stride, int mode, int nt, tdc_tc_plan* out);
+ * instead of C*R*S (42 instead of 147 for the stem).  At stride 2 the two phases of a (channel, filter row) are
+ * neighbours in memory; the plan counts them from an even input column (with an odd padding the filter's first column
+ * becomes a tap one position to the left), so that one 8-byte copy fetches both when the image is an even number of
+ * pixels wide and x is 16-byte aligned (4-byte copies otherwise).  nt = 0: the default block size.  Stride and the
+ * parity of the padding are part of the plan; the call repeats stride and padding in `flags`. */
+TDC_API int tdc_tc_plan_make_strided(int C, int K, int R, int S, int stride, int pad, int mode, int nt, tdc_tc_plan* out);
 /* Output channels per block are 128 / 64 / 32 by K in the plans above, which suits layers with many output positions.
  * tdc_tc_pick_nt gives the block size for a layer with `positions` output positions (B x padded image; smaller blocks
  * mean more CTAs when the positions alone do not fill `sm_count` SMs), tdc_tc_plan_make_nt makes a plan (general or

@@ -65,6 +65,7 @@ struct Args {
     int stride, Win;       // input step per output position and input row length
     long long HWin;        // input image size (channel pitch of x)
     int gather, gR, gS, gpad, Hin;   // general plan: the channels the MMAs see are (input channel, filter row, filter column) triples
+    int gpadx, gpair;      // column padding as the loaders see it (strided rows: less the plan's phase); stride 2: both phases by one 8-byte copy
     int taps_r;            // R (= S): 1 or 3
     int halo, shift;       // patch rows beyond a tile's positions, and how far ahead of the tile the patch starts
     float rz_unit;         // expected truncation loss of a sum per channel block (see load_chunk); 0: none put back
@@ -782,7 +783,7 @@ __global__ void __launch_bounds__(256) absmax_kernel(const float* __restrict__ x
 
 __global__ void __launch_bounds__(256) prepare_weights_kernel(const float* __restrict__ w, int kcrs, float* __restrict__ wt, int C, int K, int taps,
                                        int nt, int nkb, int n_ocb, int hl, int f16, const float* __restrict__ w_absmax, float* __restrict__ w_scale,
-                                       int row_S, int row_stride) {
+                                       int row_S, int row_stride, int row_phase) {
     float ws = 1.f;                                           // fp16: the filter is scaled to the top of fp16's range
     if (f16) {
         __shared__ unsigned int word;
@@ -805,8 +806,8 @@ __global__ void __launch_bounds__(256) prepare_weights_kernel(const float* __res
         float val = 0.f;
         if (row_stride) {
             // strided-row plan: channel c = (input channel, filter row) x column phase, tap = the filter's columns in steps of the stride
-            const int cid = c / row_stride, dx = tap * row_stride + c % row_stride, Cr = C / row_stride;
-            if (oc < K && c < C && dx < row_S) val = kcrs ? w[((long long)oc * Cr + cid) * row_S + dx] : w[((long long)cid * row_S + dx) * K + oc];
+            const int cid = c / row_stride, dx = (tap - (row_phase ? 1 : 0)) * row_stride + c % row_stride + row_phase, Cr = C / row_stride;
+            if (oc < K && c < C && dx >= 0 && dx < row_S) val = kcrs ? w[((long long)oc * Cr + cid) * row_S + dx] : w[((long long)cid * row_S + dx) * K + oc];
         } else if (oc < K && c < C) val = kcrs ? w[((long long)oc * C + c) * taps + tap] : w[((long long)c * taps + tap) * K + oc];
         if (f16) {
             val *= ws;
@@ -927,7 +928,7 @@ extern "C" {
 
 const char* tdc_tc_last_error_string(void) { return tdc::last_error(); }
 
-static int plan_fill(int C, int K, int R, int S, int mode, int general, tdc_tc_plan* out, int nt = 0, int stride = 0) {
+static int plan_fill(int C, int K, int R, int S, int mode, int general, tdc_tc_plan* out, int nt = 0, int stride = 0, int phase = 0) {
     if (!out) return tc_fail(TDC_ERR_NULL, "out is NULL");
     if (C <= 0 || K <= 0) return tc_fail(TDC_ERR_SHAPE, "C=%d K=%d", C, K);
     if (mode != 1 && mode != 3 && mode != 4) return tc_fail(TDC_ERR_UNSUPPORTED, "mode %d (1 = TF32, 3 = 3xTF32, 4 = 3xFP16)", mode);
@@ -937,7 +938,8 @@ static int plan_fill(int C, int K, int R, int S, int mode, int general, tdc_tc_p
     // a general plan contracts over (channel, filter row, filter column) triples, one tap; a strided-row plan over
     // (channel, filter row, column phase) triples, with the filter's columns in steps of the stride as taps
     out->stride = general == 2 ? stride : 0;
-    const int taps_of = general == 2 ? cdiv(S, stride) : (general ? 1 : R * S);
+    out->phase = general == 2 ? phase : 0;
+    const int taps_of = general == 2 ? cdiv(S + phase, stride) : (general ? 1 : R * S);
     out->nkb = cdiv(general == 2 ? C * R * stride : (general ? C * R * S : C), out->cb);
     out->n_ocb = cdiv(K, out->nt);
     out->hl = mode == 1 ? 1 : 2;
@@ -988,15 +990,27 @@ int tdc_tc_plan_make_nt(int C, int K, int R, int S, int mode, int general, int n
     return plan_fill(C, K, R, S, mode, general ? 1 : 0, out, nt);
 }
 
-int tdc_tc_plan_make_strided(int C, int K, int R, int S, int stride, int mode, int nt, tdc_tc_plan* out) {
+// Column phase of a strided-row plan.  With stride 2 the loaders fetch both phases of a (channel, filter row) with one
+// 8-byte copy, which must start on an even input column: the phases then count from column ox*2 - pad + phase with
+// phase = pad mod 2, and the filter's first column becomes a tap of its own one position to the left (the plan keeps
+// 2 or 4 taps for 3- and 7-wide filters; where the shift would add a tap the phase stays 0).
+static int rows_phase(int S, int stride, int pad) {
+    if (stride != 2 || !(pad & 1)) return 0;
+    const int taps = cdiv(S + 1, 2);
+    return (taps == 2 || taps == 4) ? 1 : 0;
+}
+
+int tdc_tc_plan_make_strided(int C, int K, int R, int S, int stride, int pad, int mode, int nt, tdc_tc_plan* out) {
     if (nt != 0 && nt != 32 && nt != 64 && nt != 128) return tc_fail(TDC_ERR_UNSUPPORTED, "nt %d (0, 32, 64 or 128)", nt);
     if (R <= 0 || S <= 0 || R > 15 || S > 15) return tc_fail(TDC_ERR_SHAPE, "filter %dx%d", R, S);
     if (stride < 2 || stride > 15) return tc_fail(TDC_ERR_UNSUPPORTED, "the strided-row plan is for strides 2..15, not %d", stride);
-    const int taps = (S + stride - 1) / stride;
+    if (pad < 0 || pad > 15) return tc_fail(TDC_ERR_UNSUPPORTED, "padding %d (0..15)", pad);
+    const int phase = rows_phase(S, stride, pad);
+    const int taps = cdiv(S + phase, stride);
     if (taps != 2 && taps != 4) return tc_fail(TDC_ERR_UNSUPPORTED, "the strided-row plan is built for 2 or 4 column taps (S/stride rounded up), not %d", taps);
     if (mode != 4) return tc_fail(TDC_ERR_UNSUPPORTED, "the strided-row plan is built for mode 4 (fp16 parts)");
     if ((long long)C * R * stride > (1 << 20)) return tc_fail(TDC_ERR_SHAPE, "C*R*stride = %lld is too long a contraction", (long long)C * R * stride);
-    return plan_fill(C, K, R, S, mode, 2, out, nt, stride);
+    return plan_fill(C, K, R, S, mode, 2, out, nt, stride, phase);
 }
 
 int tdc_tc_plan_make_general(int C, int K, int R, int S, int mode, tdc_tc_plan* out) {
@@ -1021,11 +1035,11 @@ int tdc_tc_prepare_weights(const tdc_tc_plan* p, const float* w, int w_layout, v
     // adjacent index digits, so the flattened filter is addressed exactly as a 1x1 one
     const bool rows = p->general == 2;
     const int Cw = rows ? p->C * p->R * p->stride : (p->general ? p->C * p->R * p->S : p->C);
-    const int taps = rows ? cdiv(p->S, p->stride) : (p->general ? 1 : p->R * p->S);
+    const int taps = rows ? cdiv(p->S + p->phase, p->stride) : (p->general ? 1 : p->R * p->S);
     tdc_tc::prepare_weights_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(w, w_layout == TDC_W_KCRS, (float*)wt, Cw, p->K,
                                                                            taps, p->nt, p->nkb, p->n_ocb, p->hl, f16 ? 1 : 0, tail,
                                                                            tail ? tail + tdc_tc::ABSMAX_SLOTS : nullptr,
-                                                                           rows ? p->S : 0, rows ? p->stride : 0);
+                                                                           rows ? p->S : 0, rows ? p->stride : 0, rows ? p->phase : 0);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "prepare launch: %s", cudaGetErrorString(e));
 }
@@ -1042,7 +1056,7 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     a.stride = stride; a.Win = W; a.HWin = (long long)H * W; a.Hin = H;
     const int Hin = H, Win = W;
     if (p->general) {
-        a.gather = 1; a.gR = p->R; a.gS = p->S; a.gpad = gpad;
+        a.gather = 1; a.gR = p->R; a.gS = p->S; a.gpad = gpad; a.gpadx = gpad;
         if (H + 2 * gpad < p->R || W + 2 * gpad < p->S) return tc_fail(TDC_ERR_SHAPE, "the %dx%d filter does not fit the padded %dx%d image", p->R, p->S, H, W);
         H = (H + 2 * gpad - p->R) / stride + 1; W = (W + 2 * gpad - p->S) / stride + 1;
         if ((long long)p->C * a.HWin >= (1ll << 31)) return tc_fail(TDC_ERR_SHAPE, "channels x image = %lld elements is too large for a general plan", (long long)p->C * a.HWin);
@@ -1053,12 +1067,17 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     const int taps_r = p->general ? 1 : p->R;     // filter size as the MMAs see it (one-pass plans)
     a.B = B; a.C = rows ? p->C * p->R * p->stride : (p->general ? p->C * p->R * p->S : p->C); a.H = H; a.W = W; a.K = p->K; a.taps_r = taps_r;
     const int pad = (taps_r - 1) / 2;
-    const int taps = rows ? cdiv(p->S, p->stride) : taps_r * taps_r;
+    const int taps = rows ? cdiv(p->S + p->phase, p->stride) : taps_r * taps_r;
     if (rows) {
+        if (rows_phase(p->S, stride, gpad) != p->phase)
+            return tc_fail(TDC_ERR_UNSUPPORTED, "this strided-row plan was made for a padding of the other parity than %d", gpad);
+        a.gpadx = gpad - p->phase;
+        // both phases of a (channel, filter row) are neighbours in memory: one 8-byte copy when they start on an even element
+        a.gpair = (stride == 2 && Win % 2 == 0 && x_al16 && !(a.gpadx & 1)) ? 1 : 0;
         a.gS = p->stride;                 // the loaders' third index runs over the column phases, not the filter's columns
         a.Wp = W + taps - 1;              // a row of positions, then the taps' reach beyond it (gathered like any position)
         a.Lp = H * a.Wp;
-        a.halo = taps - 1; a.shift = 0;
+        a.halo = taps - 1; a.shift = p->phase ? 1 : 0;     // with a phase the first tap looks one position to the left
     } else {
         a.Wp = W + pad;                       // one shared zero column per row when the filter has a halo
         a.Lp = (H + pad) * a.Wp;              // and one zero row after the image

@@ -407,12 +407,12 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                             for (int i = 0; i < PPT; ++i) {
                                 const int pp = tid + i * P_LOADERS;
                                 rmask[i] = 0; rbase[i] = a.x;
-                                const long long g = g0 + pp;
-                                if (pp < l_rows && g < a.total_pos) {
+                                const long long g = g0 - a.shift + pp;               // a plan with a phase starts one position early
+                                if (pp < l_rows && g >= 0 && g < a.total_pos) {
                                     const long long b = image_of(a, g);
                                     const int rem = (int)(g - b * a.Lp);
                                     const int oy = rem / a.Wp, ox = rem - oy * a.Wp;
-                                    const int iy0 = oy * a.stride - a.gpad, ix0 = ox * a.stride - a.gpad;
+                                    const int iy0 = oy * a.stride - a.gpad, ix0 = ox * a.stride - a.gpadx;
                                     int m = 0;
                                     for (int d = 0; d < a.gR; ++d) m |= ((unsigned)(iy0 + d) < (unsigned)a.Hin) << d;
                                     for (int d = 0; d < a.gS; ++d) m |= ((unsigned)(ix0 + d) < (unsigned)a.Win) << (16 + d);
@@ -422,6 +422,26 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                             }
                             g_ci = g_dy = g_dx = 0;
                         }
+                        if (a.gpair) {
+                            // stride 2: the two column phases of a (channel, filter row) are neighbours in memory, on an even
+                            // element: one 8-byte copy per pair; the raw slot holds [pair][patch row][2]
+                            const uint32_t dst0 = smem_u32(raw0 + l_slot * raw_floats) + (uint32_t)tid * 8u;
+#pragma unroll
+                            for (int jp = 0; jp < CBK / 2; ++jp) {
+                                const int delta = g_ci * (int)a.HWin + g_dy * a.Win;
+                                const int sel = g_ci < g_cin ? ((1 << g_dy) | 0x10000) : -1;
+#pragma unroll
+                                for (int i = 0; i < PPT; ++i) {
+                                    if (tid + i * P_LOADERS < l_rows) {
+                                        const bool real = (rmask[i] & sel) == sel;
+                                        const float* src = real ? rbase[i] + delta : a.x;
+                                        asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;"
+                                                     ::"r"(dst0 + (uint32_t)((jp * a.P + i * P_LOADERS) * 8)), "l"(src), "r"(real ? 8u : 0u) : "memory");
+                                    }
+                                }
+                                if (++g_dy == a.gR) { g_dy = 0; ++g_ci; }
+                            }
+                        } else {
                         const uint32_t dst0 = smem_u32(raw0 + l_slot * raw_floats) + (uint32_t)tid * 4u;
 #pragma unroll
                         for (int j = 0; j < CBK; ++j) {
@@ -437,6 +457,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                                 }
                             }
                             if (++g_dx == a.gS) { g_dx = 0; if (++g_dy == a.gR) { g_dy = 0; ++g_ci; } }
+                        }
                         }
                     } else {
                         if (l_kb == 0) {
@@ -503,8 +524,16 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     const int pp = tid + i * P_LOADERS;
                     if (pp < c_rows) {
                         float c[CBK];
+                        if (TAPS != 9 && a.gpair) {
 #pragma unroll
-                        for (int j = 0; j < CBK; ++j) c[j] = R[j * a.P + pp];
+                            for (int jp = 0; jp < CBK / 2; ++jp) {
+                                const float2 v = reinterpret_cast<const float2*>(R)[jp * a.P + pp];
+                                c[2 * jp] = v.x; c[2 * jp + 1] = v.y;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < CBK; ++j) c[j] = R[j * a.P + pp];
+                        }
                         store_row<F16>(A, a.P, a.hl, pp, c, xs);
                     }
                 }

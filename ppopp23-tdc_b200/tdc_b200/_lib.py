@@ -38,7 +38,7 @@ class Epilogue(C.Structure):
 
 class TcPlan(C.Structure):
     """tdc_tc_plan: layer-shape facts of the tensor-core variant."""
-    _fields_ = [(n, C.c_int) for n in ("C", "K", "R", "S", "mode", "nt", "cb", "nkb", "n_ocb", "hl", "general", "stride")] + \
+    _fields_ = [(n, C.c_int) for n in ("C", "K", "R", "S", "mode", "nt", "cb", "nkb", "n_ocb", "hl", "general", "stride", "phase")] + \
                [("weights_bytes", C.c_size_t)]
 
 
@@ -70,7 +70,7 @@ _PROTOTYPES = {
     "tdc_affine_relu_f32": (_i, [_p, _p, _p, _p, _i, _i, _i, C.c_longlong, C.c_longlong, _i, _p]),
     "tdc_tc_plan_make": (_i, [_i] * 5 + [C.POINTER(TcPlan)]),
     "tdc_tc_plan_make_general": (_i, [_i] * 5 + [C.POINTER(TcPlan)]),
-    "tdc_tc_plan_make_strided": (_i, [_i] * 7 + [C.POINTER(TcPlan)]),
+    "tdc_tc_plan_make_strided": (_i, [_i] * 8 + [C.POINTER(TcPlan)]),
     "tdc_tc_pick_nt": (_i, [_i, _i, C.c_longlong, _i]),
     "tdc_tc_plan_make_nt": (_i, [_i] * 7 + [C.POINTER(TcPlan)]),
     "tdc_tc_prepare_weights": (_i, [C.POINTER(TcPlan), _p, _i, _p, _p]),

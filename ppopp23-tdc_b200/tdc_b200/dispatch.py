@@ -30,9 +30,10 @@ def one_conv(owner, name, x, w_kcrs, w_crsk, scale, shift, residual, relu, strid
         flops, positions = 2.0 * B * Ho * Wo * Cc * K * R * S, B * Ho * Wo
         if tc.strided_rows(S, stride):
             # stride 2 with a 3- or 7-wide filter: the plan that gathers (channel, filter row, column phase) and takes the
-            # column steps as MMA taps.  Measured against the fp32 kernel at batch 256 / 32: stem 556 / 87 us against
-            # 1794 / 250; 32->64 at 56: 119 / 57 against 258 / 49; 128->256 at 14: 194 / 98 against 258 / 59
-            enough = flops >= 2e9 and positions >= 64 * 128
+            # column steps as MMA taps.  Measured against the fp32 kernel at batch 256 / 32: stem 485 / 76 us against
+            # 1794 / 250 (batch 1: 16 against 20); 32->64 at 56: 93 / 39 against 257 / 49; 128->256 at 14: 126 / 64
+            # against 258 / 59
+            enough = flops >= 0.2e9 and positions >= 64 * 128
         else:
             # every (channel, filter row, filter column) gathered: it pays per channel block and tile, and with few
             # tiles the fp32 kernel's slices and clusters win

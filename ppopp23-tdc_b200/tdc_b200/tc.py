@@ -42,7 +42,7 @@ class TcConv:
         self.C, self.K, self.R, self.S, self.mode, self.general = Cc, K, R, S, mode, bool(general)
         self._weight, self._w_layout = weight, w_layout
         self.wt = self._prepare(self.plan)
-        self._by_nt = {(self.plan.nt, 0): (self.plan, self.wt)}  # (output-channel block size, strided-row stride) -> (plan, prepared filter)
+        self._by_nt = {(self.plan.nt, None): (self.plan, self.wt)}  # (output-channel block size, strided-row (stride, padding parity)) -> (plan, prepared filter)
         self._sms = torch.cuda.get_device_properties(weight.device).multi_processor_count
         self._nt_of = {}                                         # (batch, image, flags) -> block size (the rules are library calls)
 
@@ -53,34 +53,34 @@ class TcConv:
                                               wt.data_ptr(), _stream()))
         return wt
 
-    def _make_plan(self, nt, rows_stride):
+    def _make_plan(self, nt, rows):
         plan = TcPlan()
-        if rows_stride:
-            _check(lib.tdc_tc_plan_make_strided(self.C, self.K, self.R, self.S, rows_stride, self.mode, nt, C.byref(plan)))
+        if rows:
+            _check(lib.tdc_tc_plan_make_strided(self.C, self.K, self.R, self.S, rows[0], rows[1], self.mode, nt, C.byref(plan)))
         else:
             _check(lib.tdc_tc_plan_make_nt(self.C, self.K, self.R, self.S, self.mode, int(self.general), nt, C.byref(plan)))
         return plan
 
-    def _for_image(self, B, H, W, Ho, Wo, flags, rows_stride=0):
+    def _for_image(self, B, H, W, Ho, Wo, flags, rows=None):
         """(plan, prepared filter) with the output-channel block size that suits this layer: the default for layers with
         many position tiles, smaller blocks (more CTAs) for few, and smaller again while the block does not leave room
-        for two stages beside the patch of a wide image; prepared on first use.  `rows_stride`: the strided-row plan
-        for that stride instead of the triple-gathering one."""
+        for two stages beside the patch of a wide image; prepared on first use.  `rows` = (stride, parity of the padding):
+        the strided-row plan for them instead of the triple-gathering one."""
         halo = 0 if self.general else (self.R - 1) // 2
-        key = (B, H, W, flags, rows_stride)
+        key = (B, H, W, flags, rows)
         nt = self._nt_of.get(key)
         if nt is None:
             nt = lib.tdc_tc_pick_nt(self.K, self.mode, B * (Ho + halo) * (Wo + halo), self._sms)
             while nt > 32:
-                plan = self._make_plan(nt, rows_stride)
+                plan = self._make_plan(nt, rows)
                 if lib.tdc_tc_check_launch(C.byref(plan), B, H, W, flags & 0xFF) != _lib.ERR_SMEM:
                     break
                 nt //= 2
             self._nt_of[key] = nt
-        hit = self._by_nt.get((nt, rows_stride))
+        hit = self._by_nt.get((nt, rows))
         if hit is None:
-            plan = self._make_plan(nt, rows_stride)
-            hit = self._by_nt[(nt, rows_stride)] = (plan, self._prepare(plan))
+            plan = self._make_plan(nt, rows)
+            hit = self._by_nt[(nt, rows)] = (plan, self._prepare(plan))
         return hit
 
     def __call__(self, x, scale=None, bias=None, residual=None, relu=False, out=None, stride=1, padding=None):
@@ -107,8 +107,8 @@ class TcConv:
         e = _epilogue(scale, bias, residual, relu)
         # strided filters 2 or 4 strides wide (the 3x3 stride-2 cores, the 7x7 stride-2 stem): the strided-row plan, whose
         # loaders gather C*R*stride values per position instead of C*R*S
-        rows_stride = stride if (self.general and self.mode == 4 and strided_rows(self.S, stride)) else 0
-        plan, wt = self._for_image(B, H, W, Ho, Wo, flags, rows_stride)
+        rows = (stride, padding & 1) if (self.general and self.mode == 4 and strided_rows(self.S, stride)) else None
+        plan, wt = self._for_image(B, H, W, Ho, Wo, flags, rows)
         if self.unbiased and self.mode != 1:
             flags |= 0x200                        # TDC_TC_UNBIASED
         if self.mode != 4:

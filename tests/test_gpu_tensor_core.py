@@ -35,12 +35,16 @@ def test_plan_is_made_on_the_host(T):
     assert T.lib.tdc_tc_plan_make(64, 64, 3, 3, 2, C.byref(p)) == _lib.ERR_UNSUPPORTED
     # strided rows: the stem gathers 3 channels x 7 filter rows x 2 column phases = 42 values in 3 blocks of 16 and takes
     # the 4 column steps as taps; a 3x3 stride-2 core gathers 6 per channel and takes 2 taps
-    assert T.lib.tdc_tc_plan_make_strided(3, 64, 7, 7, 2, 4, 0, C.byref(p)) == 0
-    assert (p.general, p.stride, p.nt, p.cb, p.nkb) == (2, 2, 64, 16, 3) and p.weights_bytes == 4 * 2 * 4 * 8 * 64 * 3 + 4 * (1024 + 64)
-    assert T.lib.tdc_tc_plan_make_strided(64, 128, 3, 3, 2, 4, 0, C.byref(p)) == 0
-    assert (p.general, p.stride, p.nt, p.nkb) == (2, 2, 128, 24) and p.weights_bytes == 4 * 2 * 2 * 8 * 128 * 24 + 4 * (1024 + 64)
-    assert T.lib.tdc_tc_plan_make_strided(8, 8, 5, 5, 2, 4, 0, C.byref(p)) == _lib.ERR_UNSUPPORTED      # 3 column steps
-    assert T.lib.tdc_tc_plan_make_strided(8, 8, 3, 3, 2, 3, 0, C.byref(p)) == _lib.ERR_UNSUPPORTED      # fp16 parts only
+    assert T.lib.tdc_tc_plan_make_strided(3, 64, 7, 7, 2, 3, 4, 0, C.byref(p)) == 0
+    assert (p.general, p.stride, p.phase, p.nt, p.cb, p.nkb) == (2, 2, 1, 64, 16, 3) and p.weights_bytes == 4 * 2 * 4 * 8 * 64 * 3 + 4 * (1024 + 64)
+    assert T.lib.tdc_tc_plan_make_strided(64, 128, 3, 3, 2, 1, 4, 0, C.byref(p)) == 0
+    assert (p.general, p.stride, p.phase, p.nt, p.nkb) == (2, 2, 1, 128, 24) and p.weights_bytes == 4 * 2 * 2 * 8 * 128 * 24 + 4 * (1024 + 64)
+    # an even padding needs no phase; a 4-wide filter keeps its 2 taps only without one; other strides have none
+    assert T.lib.tdc_tc_plan_make_strided(64, 128, 3, 3, 2, 0, 4, 0, C.byref(p)) == 0 and p.phase == 0
+    assert T.lib.tdc_tc_plan_make_strided(8, 8, 4, 4, 2, 1, 4, 0, C.byref(p)) == 0 and p.phase == 0
+    assert T.lib.tdc_tc_plan_make_strided(8, 8, 3, 7, 4, 1, 4, 0, C.byref(p)) == 0 and p.phase == 0
+    assert T.lib.tdc_tc_plan_make_strided(8, 8, 5, 5, 2, 2, 4, 0, C.byref(p)) == _lib.ERR_UNSUPPORTED      # 3 column steps
+    assert T.lib.tdc_tc_plan_make_strided(8, 8, 3, 3, 2, 1, 3, 0, C.byref(p)) == _lib.ERR_UNSUPPORTED      # fp16 parts only
     assert T.lib.tdc_tc_plan_make(0, 64, 3, 3, 3, C.byref(p)) == _lib.ERR_SHAPE
     assert b"mode" in T.lib.tdc_tc_last_error_string() or b"C=" in T.lib.tdc_tc_last_error_string()
 
@@ -251,7 +255,9 @@ def test_general_plan(T, B, Cc, K, H, W, R, stride, pad):
 @pytest.mark.gpu
 @pytest.mark.parametrize("B,Cc,K,H,W,R,S,stride,pad", [(2, 3, 64, 38, 38, 7, 7, 2, 3), (3, 16, 24, 15, 13, 3, 3, 2, 1), (70, 32, 48, 14, 14, 3, 3, 2, 1),
                                                         (2, 5, 9, 11, 17, 4, 4, 2, 0), (1, 7, 130, 9, 9, 8, 8, 2, 3), (2, 6, 8, 21, 20, 3, 7, 4, 2),
-                                                        (3, 33, 40, 10, 12, 2, 4, 3, 1), (300, 8, 16, 5, 5, 3, 3, 2, 1), (2, 64, 64, 56, 56, 3, 3, 2, 1)])
+                                                        (3, 33, 40, 10, 12, 2, 4, 3, 1), (300, 8, 16, 5, 5, 3, 3, 2, 1), (2, 64, 64, 56, 56, 3, 3, 2, 1),
+                                                        (3, 9, 20, 12, 14, 3, 3, 2, 0), (2, 6, 10, 16, 18, 7, 7, 2, 2), (5, 12, 16, 9, 11, 3, 3, 2, 1),
+                                                        (2, 4, 8, 10, 10, 7, 3, 2, 1)])
 def test_strided_row_plan(T, B, Cc, K, H, W, R, S, stride, pad):
     """The plan for strided layers with 2 or 4 column steps (stem 7x7 / 2, cores 3x3 / 2): the contraction runs over
     (channel, filter row, column phase) and the column steps are MMA taps one output position apart.  Against the fp64
@@ -267,7 +273,7 @@ def test_strided_row_plan(T, B, Cc, K, H, W, R, S, stride, pad):
     conv = T.TcConv(w.cuda(), mode=4, general=True)
     y = conv(x.cuda(), stride=stride, padding=pad)
     assert tuple(y.shape[1:]) == ref.shape[1:] and rel_err(y[sel].cpu().numpy(), ref) <= FP32_TOL, rel_err(y[sel].cpu().numpy(), ref)
-    assert any(k[1] == stride for k in conv._by_nt), "the strided-row plan did not run"
+    assert any(k[1] == (stride, pad & 1) for k in conv._by_nt), "the strided-row plan did not run"
     scale, shift = (torch.rand(K, generator=g) + 0.5), torch.randn(K, generator=g)
     res = torch.randn(y.shape, generator=g)
     y2 = conv(x.cuda(), scale.cuda(), shift.cuda(), res.cuda(), True, stride=stride, padding=pad)
@@ -275,6 +281,12 @@ def test_strided_row_plan(T, B, Cc, K, H, W, R, S, stride, pad):
     assert rel_err(y2[sel].cpu().numpy(), want) <= FP32_TOL
     crsk = torch.from_numpy(np.ascontiguousarray(w.numpy().transpose(1, 2, 3, 0))).cuda()
     assert torch.equal(y, T.TcConv(crsk, mode=4, w_layout=T.W_CRSK, general=True)(x.cuda(), stride=stride, padding=pad))
+    # an input that starts 4 bytes off a 16-byte boundary takes the 4-byte copies instead of the 8-byte pairs: the same values
+    # through the same arithmetic, so every bit agrees
+    off = torch.empty(x.numel() + 1, device="cuda")
+    xv = off[1:].view(x.shape)
+    xv.copy_(x)
+    assert xv.data_ptr() % 16 != 0 and torch.equal(y, conv(xv, stride=stride, padding=pad))
     assert tc.status() == 0
 
 
