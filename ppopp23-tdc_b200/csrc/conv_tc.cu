@@ -855,7 +855,7 @@ float* tc_tail(const tdc_tc_plan* p, const void* wt) {
 //   buffers, TDC_TC_VEC 0/1 16-byte register loader of one-tap filters, TDC_TC_DEPTH raw slots, TDC_TC_KPS channel
 //   blocks per stage (one-tap filters), TDC_TC_TAIL 0 = no smaller tiles in the last round, TDC_TC_CHAIN
 //   accumulations per run (0 = one run), TDC_TC_BULK 0/1 bulk-tensor loader.
-struct Tuning { int persist = -1, mt = -1, ns = -1, nbuf = -1, vec = -1, depth = -1, kps = -1, tail = -1, chain = -1, bulk = -1; };
+struct Tuning { int persist = -1, mt = -1, ns = -1, nbuf = -1, vec = -1, depth = -1, kps = -1, tail = -1, chain = -1, bulk = -1, pdl = -1; };
 bool tuning_enabled() {
     static const bool on = [] { const char* v = getenv("TDC_TC_TUNING"); return v && atoi(v) != 0; }();
     return on;
@@ -866,7 +866,7 @@ Tuning read_tuning() {
     auto get = [](const char* name) { const char* v = getenv(name); return v ? atoi(v) : -1; };
     t.persist = get("TDC_TC_PERSIST"); t.mt = get("TDC_TC_MT"); t.ns = get("TDC_TC_NS"); t.nbuf = get("TDC_TC_NBUF");
     t.vec = get("TDC_TC_VEC"); t.depth = get("TDC_TC_DEPTH"); t.kps = get("TDC_TC_KPS"); t.tail = get("TDC_TC_TAIL");
-    t.chain = get("TDC_TC_CHAIN"); t.bulk = get("TDC_TC_BULK");
+    t.chain = get("TDC_TC_CHAIN"); t.bulk = get("TDC_TC_BULK"); t.pdl = get("TDC_TC_PDL");
     return t;
 }
 
@@ -877,7 +877,7 @@ struct Launch {
     unsigned ctas = 0;
     int threads = 0;
     size_t smem = 0;
-    bool persist = false, bulk = false;
+    bool persist = false, bulk = false, pdl = false;
 };
 using LaunchKey = std::tuple<int, int, int, int, int, int, int, int, int, int, int, int, int>;
 std::map<LaunchKey, Launch> g_tc_launches;
@@ -1275,6 +1275,7 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
 #undef TDC_TC_ONE
     out->a = a; out->fn = fn; out->ctas = (unsigned)ctas; out->threads = persist ? P_THREADS : THREADS; out->smem = smem;
     out->persist = persist; out->bulk = bulk;
+    out->pdl = persist && tn.pdl != 0;        // the persistent kernel waits for the grids before it on its own (griddepcontrol.wait)
     return TDC_OK;
 }
 
@@ -1387,7 +1388,18 @@ int tdc_conv2d_tc_ranged(const tdc_tc_plan* p, const float* x, const void* wt, f
         }
     }
     void* args[] = {&a, &tmap};
-    e = cudaLaunchKernel(L.fn, dim3(L.ctas), dim3(L.threads), args, L.smem, (cudaStream_t)stream);
+    // Programmatic dependent launch: the persistent kernel may be scheduled while the kernel before it in the stream is
+    // still running (its CTAs land on SMs as they become free, set up their barriers and tensor memory) and waits with
+    // griddepcontrol.wait, which returns when every grid before it has completed and its writes are visible, before it
+    // touches x, y or anything else a kernel before it may have written.  Only kernels launched with this attribute
+    // start early, and every one of them waits; a kernel before or after without it is ordered as always.
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(L.ctas); cfg.blockDim = dim3(L.threads); cfg.dynamicSmemBytes = L.smem; cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = L.pdl ? 1 : 0;
+    e = cudaLaunchKernelExC(&cfg, L.fn, args);
     return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "launch: %s", cudaGetErrorString(e));
 }
 

@@ -158,10 +158,18 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     const int nbuf = a.nbuf;
     const long long ntiles = a.ntiles;          // position tiles x output-channel blocks
     // fp16 operands without a bound of |x|: this thread's samples of the input, loaded now, reduced after the set-up below
+    // The kernel may have been scheduled before the kernels ahead of it in the stream have finished (programmatic
+    // dependent launch): nothing they may have written (x, the bound of |x|, y, the residual) is touched before
+    // griddepcontrol.wait, which every thread passes once.  The warps that sample the input wait here, so that their
+    // loads are in flight during the set-up below (done by warps that touch no global memory until they have waited too).
     unsigned int sampled = 0;
-    if constexpr (F16) { if (!a.x_absmax && (warp < P_IW0 || warp >= P_EW0)) sampled = range_sample_load(a.x, a.x_count); }
+    const bool samples = F16 && !a.x_absmax && (warp < P_IW0 || warp >= P_EW0);
+    if (samples) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        sampled = range_sample_load(a.x, a.x_count);
+    }
 
-    if (tid == 0) {
+    if (tid == (P_IW0 + 1) * 32) {
         for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], P_LOADERS / 32 + 1); mbar_init(&empty_bar[s], MT); }   // one arrival per loader warp + the filter's bytes
         for (int b = 0; b < 8; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4 * (NT / P_EPI_W)); }   // one per issuer; one per epilogue warp and chunk of channels
         for (int d = 0; d < 8; ++d) { mbar_init(&rfull_bar[d], 1); mbar_init(&rempty_bar[d], P_LOADERS / 32); }    // the producer's arrive + bytes; one per converting warp
@@ -177,6 +185,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
+    if (!samples) asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the kernel after this one may be scheduled as SMs become free
     TDC_PROF_DECL;
     // fp16 operands: the power of two that brings the input just under 2^15, and the factor that undoes it (and the
     // filter's, applied when it was prepared) in the epilogue

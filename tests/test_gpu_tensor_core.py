@@ -291,6 +291,47 @@ def test_strided_row_plan(T, B, Cc, K, H, W, R, S, stride, pad):
 
 
 @pytest.mark.gpu
+def test_dependent_launches_wait_for_their_input(T, monkeypatch):
+    """The persistent kernel is launched so that it may be scheduled while the kernel before it still runs (programmatic
+    dependent launch) and waits inside for that kernel's results.  A chain in which every launch reads what the one before
+    wrote — on one stream, with no host synchronisation, also as a CUDA graph, also through a buffer that is written,
+    read and overwritten in turn — must give the bits of the same chain run with a synchronisation after every launch
+    and of the chain without early scheduling."""
+    from tdc_b200 import tc
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(16, 64, 28, 28, generator=g).cuda()
+    convs = [T.TcConv((torch.randn(64, 64, 3, 3, generator=g) * (2.0 / (64 * 9)) ** 0.5).cuda(), mode=4) for _ in range(3)]
+    bufs = [torch.empty_like(x), torch.empty_like(x)]
+
+    def chain(sync):
+        t = x
+        for i in range(9):
+            t = convs[i % 3](t, relu=True, out=bufs[i & 1])          # ping-pong: launch i+1 overwrites what launch i read
+            if sync:
+                torch.cuda.synchronize()
+        return t.clone()
+    want = chain(True)
+    assert torch.isfinite(want).all() and float(want.abs().max()) > 0
+    for _ in range(3):
+        assert torch.equal(chain(False), want)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        chain(False)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = chain(False)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    monkeypatch.setenv("TDC_TC_PDL", "0")
+    assert torch.equal(chain(False), want)
+    assert tc.status() == 0
+
+
+@pytest.mark.gpu
 def test_random_shapes_against_fp64(T):
     """Sixty seeded random layers (ragged channel counts, tiny and odd images, batch sizes around the tile and SM
     counts, one-pass and gathering plans, random epilogue options) against the same convolution in fp64 on the GPU:
@@ -387,7 +428,7 @@ def test_fp16_parts_loaders_runs_and_range(T, B, Cc, K, H, W, R, monkeypatch):
     err = rel_err(y.cpu().numpy(), ref.cpu().numpy())
     assert err <= FP32_TOL
     for knobs in ({"TDC_TC_BULK": "0"}, {"TDC_TC_BULK": "1"}, {"TDC_TC_BULK": "1", "TDC_TC_DEPTH": "2"}, {"TDC_TC_BULK": "0", "TDC_TC_MT": "1"},
-                  {"TDC_TC_BULK": "1", "TDC_TC_MT": "1", "TDC_TC_NBUF": "1"}, {"TDC_TC_NS": "2"}, {"TDC_TC_TAIL": "0"}):
+                  {"TDC_TC_BULK": "1", "TDC_TC_MT": "1", "TDC_TC_NBUF": "1"}, {"TDC_TC_NS": "2"}, {"TDC_TC_TAIL": "0"}, {"TDC_TC_PDL": "0"}):
         for k, v in knobs.items():
             monkeypatch.setenv(k, v)
         assert torch.equal(conv(xd), y), knobs
