@@ -848,6 +848,11 @@ def main():
                               frac_fp32_b1=conv_flops(1, H, R1, R2) / us1_fp32 / 1e6 / fp32_peak, cudnn_us_b1=cud1,
                               tile_b1=list(t1.as_tuple())))
         line["layers"] = table
+        # what the timing itself costs: a kernel that does nothing, between the same pair of events after the same flush
+        one = torch.zeros(1, device=dev)
+        line["timing_floor_us"] = {"value": time_layer(lambda: one.add_(1), iters=20),
+                                   "note": "a one-element torch kernel in the per-layer harness (events around one launch, L2 flushed before): "
+                                           "the part of every us_b1 figure, ours and cuDNN's, that no kernel can remove"}
         gm = lambda v: float(torch.tensor(v).log().mean().exp())
         line["speedup_vs_cudnn_geomean"] = {"b64": gm([r["cudnn_us_b64"] / r["us_b64"] for r in table]),
                                             "b64_tf32x3": gm([r["cudnn_us_b64"] / r["us_b64_tf32x3"] for r in table]),
