@@ -11,7 +11,7 @@
 //     issues the MMAs of position tile mt and may start the next CTA tile as soon as ITS
 //     accumulators have been read, while the other issuers still work on this one (and tensor
 //     memory holds two CTA tiles outright when 2 x MT x columns-per-tile fits in 512 columns);
-//   * two groups of four epilogue warps (12-15, 16-19) take the (position tile, 32-channel chunk)
+//   * four groups of four epilogue warps (12-27) take the (position tile, 16-channel chunk)
 //     items of a CTA tile in turn; an accumulator is handed back as soon as all its chunks are in
 //     registers, before the stores.
 //
@@ -36,7 +36,7 @@
 namespace tdc_tc {
 
 #ifndef TDC_TC_EPI_GROUPS
-#define TDC_TC_EPI_GROUPS 2
+#define TDC_TC_EPI_GROUPS 4
 #endif
 #ifndef TDC_TC_LOADER_WARPS
 #define TDC_TC_LOADER_WARPS 8
@@ -48,10 +48,14 @@ constexpr int P_EW0     = P_IW0 + 4;                  // follow them read the la
 constexpr int P_THREADS = P_LOADERS + 128 + 128 * P_GROUPS;   // loader warps, 4 issuer warps (one lane each), the epilogue groups
 constexpr int P_PRODUCER = P_IW0 + 3;   // the bulk loader's producer is the fourth issuer warp, free when MT <= 2
 static_assert(TDC_TC_LOADER_WARPS % 4 == 0, "whole warpgroups of loaders");
-// With 12 loader warps (768 threads, 80 registers each, the epilogue in half chunks so that nothing spills) the
-// loader-bound layers gain 3-8 % (56x56x64 at batch 256: 200 -> 188 us, the 7x7 stem 567 -> 525 us) and the layers with
-// many output channels per position lose as much (64 -> 256 1x1: 304 -> 353 us, 14x14x128: 25.6 -> 27.6 us): level
-// over the sweep, so 8 it stays.  Trading registers between the roles (setmaxnreg) made ptxas spill 1.7 KB per thread.
+// Epilogue groups.  The epilogue is a latency chain per work item (tensor memory -> registers -> scale, shift, residual,
+// ReLU -> 32-byte-per-lane stores), and in a network every launch carries those options: with four groups of four warps
+// (896 threads, 72 registers each, items of 16 channels so that nothing spills) TK-ResNet-18 at batch 256 takes 4.10 ms
+// against 4.36 with two groups (items of 32 channels, 640 threads at 96 registers), TK-ResNet-50 at batch 64 5.12 against
+// 5.57 ms, a TK-VGG-16 chunk of 128 10.2 against 10.7 ms; the bare sweep layers are level (368 against 366 us over the
+// eight).  Loader warps: with 12 instead of 8 (and two epilogue groups) the loader-bound layers gained 3-8 % and the
+// layers with many output channels lost as much; trading registers between the roles (setmaxnreg) made ptxas spill
+// 1.7 KB per thread.
 constexpr int P_EPI_W = P_THREADS > 640 ? 16 : 32;   // channels an epilogue thread holds at a time
 // patch rows a CTA may stage (3x3 filters: MT x 128 positions plus two image rows of halo, images up to 256 wide)
 __host__ __device__ constexpr int p_rows_cap(int mt) { return mt == 1 ? 768 : 1024; }
