@@ -662,7 +662,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
         }
     } else {
         // ================= epilogue: P_GROUPS groups of four warps (one lane quarter of tensor memory per warp).
-        // The work items of a CTA tile are (position tile, 32-channel chunk) pairs, dealt to the groups in turn: the
+        // The work items of a CTA tile are (position tile, chunk of P_EPI_W channels) pairs, dealt to the groups in turn: the
         // epilogue is a latency chain (tensor memory -> registers -> residual loads -> stores), and several chains in
         // flight hide more of it than one; all groups start on the first position tile, whose issuer is released first.
         const int grp = (warp - P_EW0) >> 2;       // warps P_EW0 .. P_EW0 + 4 * P_GROUPS - 1
