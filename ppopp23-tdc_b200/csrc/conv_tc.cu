@@ -855,7 +855,7 @@ float* tc_tail(const tdc_tc_plan* p, const void* wt) {
 //   buffers, TDC_TC_VEC 0/1 16-byte register loader of one-tap filters, TDC_TC_DEPTH raw slots, TDC_TC_KPS channel
 //   blocks per stage (one-tap filters), TDC_TC_TAIL 0 = no smaller tiles in the last round, TDC_TC_CHAIN
 //   accumulations per run (0 = one run), TDC_TC_BULK 0/1 bulk-tensor loader.
-struct Tuning { int persist = -1, mt = -1, ns = -1, nbuf = -1, vec = -1, depth = -1, kps = -1, tail = -1, chain = -1, bulk = -1, pdl = -1; };
+struct Tuning { int persist = -1, mt = -1, ns = -1, nbuf = -1, vec = -1, depth = -1, kps = -1, tail = -1, chain = -1, bulk = -1, pdl = -1, lw = -1; };
 bool tuning_enabled() {
     static const bool on = [] { const char* v = getenv("TDC_TC_TUNING"); return v && atoi(v) != 0; }();
     return on;
@@ -866,7 +866,7 @@ Tuning read_tuning() {
     auto get = [](const char* name) { const char* v = getenv(name); return v ? atoi(v) : -1; };
     t.persist = get("TDC_TC_PERSIST"); t.mt = get("TDC_TC_MT"); t.ns = get("TDC_TC_NS"); t.nbuf = get("TDC_TC_NBUF");
     t.vec = get("TDC_TC_VEC"); t.depth = get("TDC_TC_DEPTH"); t.kps = get("TDC_TC_KPS"); t.tail = get("TDC_TC_TAIL");
-    t.chain = get("TDC_TC_CHAIN"); t.bulk = get("TDC_TC_BULK"); t.pdl = get("TDC_TC_PDL");
+    t.chain = get("TDC_TC_CHAIN"); t.bulk = get("TDC_TC_BULK"); t.pdl = get("TDC_TC_PDL"); t.lw = get("TDC_TC_LW");
     return t;
 }
 
@@ -874,6 +874,7 @@ Tuning read_tuning() {
 struct Launch {
     tdc_tc::Args a;
     const void* fn = nullptr;
+    const void* fn12 = nullptr;       // the same kernel with 12 loader warps and three epilogue groups (fp16 parts), or null
     unsigned ctas = 0;
     int threads = 0;
     size_t smem = 0;
@@ -1184,7 +1185,6 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     int cap = 0;
     const size_t raw_bytes = raw_bytes_of(mt, a.P, bulk, &cap);
     a.nbox_cap = cap;
-    a.step_y = P_LOADERS / a.Wp; a.step_x = P_LOADERS % a.Wp;
     // One-tap filters (1x1, general plans) do one or two MMAs per channel block and position tile: a stage of one
     // block would be all hand-over.  Their stages take up to four blocks (what leaves room for two stages and,
     // with a raw ring, two raw slots).
@@ -1249,30 +1249,40 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
     a.ntiles = tiles * a.n_ocb;
     if (a.ntiles >= (1ll << 31)) return tc_fail(TDC_ERR_TILE, "grid too large");
     const long long ctas = persist ? (a.ntiles < sms ? a.ntiles : sms) : a.ntiles;
-    const void* fn = nullptr;
+    // The persistent kernel with fp16 parts exists with 8 loader warps and four epilogue groups and with 12 and three;
+    // which one a call takes depends on its epilogue and is decided per call (fn / fn_loaders below).  The TF32 kernels
+    // exist with 8 only.
+    const void *fn = nullptr, *fn12 = nullptr;
 #define TDC_TC_ONE(NT_, MT_) (taps == 9 ? (const void*)&conv_tc_kernel<NT_, MT_, 9, false> : \
                               (vec ? (const void*)&conv_tc_kernel<NT_, MT_, 1, true> : (const void*)&conv_tc_kernel<NT_, MT_, 1, false>))
-#define TDC_TC_PER(NT_, MT_) (f16 ? (taps == 9 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 9, LD_RING, true> \
-                                     : taps == 4 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 4, LD_RING, true> \
-                                     : taps == 2 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 2, LD_RING, true> \
-                                               : (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_RING, true>) \
-                                  : (taps == 9 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 9, LD_RING, false> \
-                                               : (vec ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_VEC, false> \
-                                                      : (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_RING, false>)))
-#define TDC_TC_BLK(NT_, MT_) (taps == 9 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 9, LD_BULK, true> \
-                                        : (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_BULK, true>)
-#define TDC_TC_PICK(NT_, MT_) (persist ? TDC_TC_PER(NT_, MT_) : TDC_TC_ONE(NT_, MT_))
-    if (bulk) {
-        if (p->nt == 128) fn = mt == 2 ? TDC_TC_BLK(128, 2) : TDC_TC_BLK(128, 1);
-        else if (p->nt == 64) fn = mt == 2 ? TDC_TC_BLK(64, 2) : TDC_TC_BLK(64, 1);
-        else fn = mt == 2 ? TDC_TC_BLK(32, 2) : TDC_TC_BLK(32, 1);
-    } else if (p->nt == 128) fn = mt == 2 ? TDC_TC_PICK(128, 2) : TDC_TC_PICK(128, 1);
-    else if (p->nt == 64) fn = mt == 4 ? TDC_TC_PICK(64, 4) : (mt == 2 ? TDC_TC_PICK(64, 2) : TDC_TC_PICK(64, 1));
-    else fn = mt == 4 ? TDC_TC_PICK(32, 4) : (mt == 2 ? TDC_TC_PICK(32, 2) : TDC_TC_PICK(32, 1));
+#define TDC_TC_PER(NT_, MT_, LW_) (f16 ? (taps == 9 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 9, LD_RING, true, LW_> \
+                                          : taps == 4 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 4, LD_RING, true, LW_> \
+                                          : taps == 2 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 2, LD_RING, true, LW_> \
+                                                    : (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_RING, true, LW_>) \
+                                       : (taps == 9 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 9, LD_RING, false> \
+                                                    : (vec ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_VEC, false> \
+                                                           : (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_RING, false>)))
+#define TDC_TC_BLK(NT_, MT_, LW_) (taps == 9 ? (const void*)&conv_tc_persist_kernel<NT_, MT_, 9, LD_BULK, true, LW_> \
+                                             : (const void*)&conv_tc_persist_kernel<NT_, MT_, 1, LD_BULK, true, LW_>)
+#define TDC_TC_PICK(NT_, MT_, LW_) (persist ? TDC_TC_PER(NT_, MT_, LW_) : TDC_TC_ONE(NT_, MT_))
+#define TDC_TC_ALL(LW_, FN_)                                                                                                     \
+    if (bulk) {                                                                                                                  \
+        if (p->nt == 128) FN_ = mt == 2 ? TDC_TC_BLK(128, 2, LW_) : TDC_TC_BLK(128, 1, LW_);                                     \
+        else if (p->nt == 64) FN_ = mt == 2 ? TDC_TC_BLK(64, 2, LW_) : TDC_TC_BLK(64, 1, LW_);                                   \
+        else FN_ = mt == 2 ? TDC_TC_BLK(32, 2, LW_) : TDC_TC_BLK(32, 1, LW_);                                                    \
+    } else if (p->nt == 128) FN_ = mt == 2 ? TDC_TC_PICK(128, 2, LW_) : TDC_TC_PICK(128, 1, LW_);                                \
+    else if (p->nt == 64) FN_ = mt == 4 ? TDC_TC_PICK(64, 4, LW_) : (mt == 2 ? TDC_TC_PICK(64, 2, LW_) : TDC_TC_PICK(64, 1, LW_)); \
+    else FN_ = mt == 4 ? TDC_TC_PICK(32, 4, LW_) : (mt == 2 ? TDC_TC_PICK(32, 2, LW_) : TDC_TC_PICK(32, 1, LW_));
+    TDC_TC_ALL(8, fn)
+    if (persist && f16) { TDC_TC_ALL(12, fn12) }
+#undef TDC_TC_ALL
 #undef TDC_TC_PICK
 #undef TDC_TC_BLK
 #undef TDC_TC_PER
 #undef TDC_TC_ONE
+    if (tn.lw == 8) fn12 = nullptr;
+    if (tn.lw == 12 && fn12) fn = fn12;
+    out->fn12 = fn12;
     out->a = a; out->fn = fn; out->ctas = (unsigned)ctas; out->threads = persist ? P_THREADS : THREADS; out->smem = smem;
     out->persist = persist; out->bulk = bulk;
     out->pdl = persist && tn.pdl != 0;        // the persistent kernel waits for the grids before it on its own (griddepcontrol.wait)
@@ -1349,6 +1359,13 @@ int tdc_conv2d_tc_ranged(const tdc_tc_plan* p, const float* x, const void* wt, f
     Args& a = L.a;
     a.x = x; a.wt = (const float*)wt; a.y = y;
     if (epi) { a.scale = epi->scale; a.bias = epi->bias; a.residual = epi->residual; a.relu = epi->relu ? 1 : 0; }
+    // The CTA's 28 warps: a launch whose epilogue only stores is paced by its loaders (12 loader warps, three epilogue
+    // groups); one that scales, shifts, adds a residual or clamps wants the fourth epilogue group instead (8 loader warps).
+    const void* fn_call = L.fn;
+    int loader_threads = 256;
+    if (L.fn12 && !(a.scale || a.bias || a.residual || a.relu)) { fn_call = L.fn12; loader_threads = 384; }
+    if (L.fn12 && L.fn == L.fn12) loader_threads = 384;                 // forced by the tuning switch
+    a.step_y = loader_threads / a.Wp; a.step_x = loader_threads % a.Wp;   // bulk loader: a thread's next row is this far on
     a.epi_vec = reinterpret_cast<uintptr_t>(a.scale) % 16 == 0 && reinterpret_cast<uintptr_t>(a.bias) % 16 == 0;
     if (p->mode == 4) {
         float* tail = tc_tail(p, wt);
@@ -1380,9 +1397,9 @@ int tdc_conv2d_tc_ranged(const tdc_tc_plan* p, const float* x, const void* wt, f
     }
     {
         std::lock_guard<std::mutex> lk(g_tc_mu);
-        size_t& have = g_tc_smem_set[{device, L.fn}];
+        size_t& have = g_tc_smem_set[{device, fn_call}];
         if (L.smem > have) {
-            e = cudaFuncSetAttribute(L.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.smem);
+            e = cudaFuncSetAttribute(fn_call, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.smem);
             if (e != cudaSuccess) return tc_fail(TDC_ERR_CUDA, "cudaFuncSetAttribute(%zu): %s", L.smem, cudaGetErrorString(e));
             have = L.smem;
         }
@@ -1399,7 +1416,7 @@ int tdc_conv2d_tc_ranged(const tdc_tc_plan* p, const float* x, const void* wt, f
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = L.pdl ? 1 : 0;
-    e = cudaLaunchKernelExC(&cfg, L.fn, args);
+    e = cudaLaunchKernelExC(&cfg, fn_call, args);
     return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "launch: %s", cudaGetErrorString(e));
 }
 

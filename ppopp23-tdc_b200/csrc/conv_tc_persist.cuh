@@ -35,28 +35,22 @@
 
 namespace tdc_tc {
 
-#ifndef TDC_TC_EPI_GROUPS
-#define TDC_TC_EPI_GROUPS 4
-#endif
-#ifndef TDC_TC_LOADER_WARPS
-#define TDC_TC_LOADER_WARPS 8
-#endif
-constexpr int P_GROUPS  = TDC_TC_EPI_GROUPS;          // groups of four epilogue warps
-constexpr int P_LOADERS = 32 * TDC_TC_LOADER_WARPS;   // threads that stage the input: the kernel is paced by their instruction latency
-constexpr int P_IW0     = TDC_TC_LOADER_WARPS;        // first of the four issuer warps (a multiple of 4: the epilogue warps that
-constexpr int P_EW0     = P_IW0 + 4;                  // follow them read the lane quarter warp % 4 of tensor memory)
-constexpr int P_THREADS = P_LOADERS + 128 + 128 * P_GROUPS;   // loader warps, 4 issuer warps (one lane each), the epilogue groups
-constexpr int P_PRODUCER = P_IW0 + 3;   // the bulk loader's producer is the fourth issuer warp, free when MT <= 2
-static_assert(TDC_TC_LOADER_WARPS % 4 == 0, "whole warpgroups of loaders");
-// Epilogue groups.  The epilogue is a latency chain per work item (tensor memory -> registers -> scale, shift, residual,
-// ReLU -> 32-byte-per-lane stores), and in a network every launch carries those options: with four groups of four warps
-// (896 threads, 72 registers each, items of 16 channels so that nothing spills) TK-ResNet-18 at batch 256 takes 4.10 ms
-// against 4.36 with two groups (items of 32 channels, 640 threads at 96 registers), TK-ResNet-50 at batch 64 5.12 against
-// 5.57 ms, a TK-VGG-16 chunk of 128 10.2 against 10.7 ms; the bare sweep layers are level (368 against 366 us over the
-// eight).  Loader warps: with 12 instead of 8 (and two epilogue groups) the loader-bound layers gained 3-8 % and the
-// layers with many output channels lost as much; trading registers between the roles (setmaxnreg) made ptxas spill
-// 1.7 KB per thread.
-constexpr int P_EPI_W = P_THREADS > 640 ? 16 : 32;   // channels an epilogue thread holds at a time
+// A CTA is 28 warps: LW loader warps (8 or 12, a template parameter), 4 issuer warps (one lane each), and what is left
+// as groups of four epilogue warps (4 or 3 groups).  LW is a multiple of 4, so the epilogue warps that follow the
+// issuers read the lane quarter warp % 4 of tensor memory.  Which split a call takes follows from its epilogue, a
+// latency chain per work item (tensor memory -> registers -> scale, shift, residual, ReLU -> stores): a launch that
+// carries those options wants the four groups, a launch that only stores (the first two steps of a Tucker chain, a
+// bare layer) is paced by its loaders and takes the twelve loader warps.  Measured on one GPU in one run, batch 256 /
+// 64 / 128: TK-ResNet-18 4.10 ms, TK-ResNet-50 5.17 ms, a TK-VGG-16 chunk 10.4 ms with the split chosen per call;
+// 4.11 / 5.13 / 10.9 with 8 loader warps for every launch; 4.18 / 5.45 / 11.0 with 12 for every launch; 4.35 / 5.57 /
+// 10.7 with the earlier two groups of 32-channel items (640 threads at 96 registers).  The bare sweep layers are level
+// in all of these (365 .. 368 us over the eight); the gathering plans gain a tenth from the twelve (stem 484 -> 436 us).
+// The loader count is a compile-time constant because it sizes the per-thread row arrays (one or two rows with 384
+// loaders where 256 need two to four); as a launch parameter of one kernel the twelve gained nothing.
+// Work items are 16 channels wide so that 72 registers per thread hold them without spills.
+constexpr int P_WARPS   = 28;
+constexpr int P_THREADS = 32 * P_WARPS;
+constexpr int P_EPI_W   = 16;           // channels an epilogue thread holds at a time
 // patch rows a CTA may stage (3x3 filters: MT x 128 positions plus two image rows of halo, images up to 256 wide)
 __host__ __device__ constexpr int p_rows_cap(int mt) { return mt == 1 ? 768 : 1024; }
 constexpr int P_HEADER  = 1024;  // bytes of barriers, flags and the producer's box table in front of the stages
@@ -129,11 +123,14 @@ __device__ unsigned long long g_tc_prof[16];   // [0, 12) kinds of wait or span,
 #define TDC_PROF_FLUSH(role)
 #endif
 
-template <int NT, int MT, int TAPS, int LD, bool F16>
+template <int NT, int MT, int TAPS, int LD, bool F16, int LW = 8>
 __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a, const __grid_constant__ CUtensorMap tmap) {
     static_assert(LD != LD_VEC || (TAPS == 1 && !F16), "the 16-byte register loader serves 1x1 filters with TF32 operands");
     static_assert(LD != LD_BULK || (F16 && MT <= 2), "the bulk loader converts to fp16 parts; its producer is issuer warp 3, free when MT <= 2");
     constexpr int CBK = KStep<F16>::CH;                               // channels per block
+    // the roles of this instantiation (see the top of the file)
+    static_assert(LW == 8 || LW == 12, "8 loader warps and four epilogue groups, or 12 and three");
+    constexpr int P_LOADERS = LW * 32, P_IW0 = LW, P_EW0 = LW + 4, P_GROUPS = (P_WARPS - P_EW0) / 4, P_PRODUCER = P_IW0 + 3;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint64_t* full_bar   = reinterpret_cast<uint64_t*>(smem_raw);    // [ns]  patch stored + filter landed
     uint64_t* empty_bar  = full_bar + 4;                              // [ns]  MMAs that read the stage are done
