@@ -428,7 +428,8 @@ def test_fp16_parts_loaders_runs_and_range(T, B, Cc, K, H, W, R, monkeypatch):
     err = rel_err(y.cpu().numpy(), ref.cpu().numpy())
     assert err <= FP32_TOL
     for knobs in ({"TDC_TC_BULK": "0"}, {"TDC_TC_BULK": "1"}, {"TDC_TC_BULK": "1", "TDC_TC_DEPTH": "2"}, {"TDC_TC_BULK": "0", "TDC_TC_MT": "1"},
-                  {"TDC_TC_BULK": "1", "TDC_TC_MT": "1", "TDC_TC_NBUF": "1"}, {"TDC_TC_NS": "2"}, {"TDC_TC_TAIL": "0"}, {"TDC_TC_PDL": "0"}):
+                  {"TDC_TC_BULK": "1", "TDC_TC_MT": "1", "TDC_TC_NBUF": "1"}, {"TDC_TC_NS": "2"}, {"TDC_TC_TAIL": "0"}, {"TDC_TC_PDL": "0"}, {"TDC_TC_LW": "8"}, {"TDC_TC_LW": "12"},
+                  {"TDC_TC_LW": "12", "TDC_TC_BULK": "0"}):
         for k, v in knobs.items():
             monkeypatch.setenv(k, v)
         assert torch.equal(conv(xd), y), knobs
