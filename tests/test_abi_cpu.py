@@ -98,6 +98,30 @@ def test_every_refusal_leaves_its_reason_in_the_one_error_string(T):
     assert b"y_absmax" in lib.tdc_last_error_string()
 
 
+def test_tensor_core_plans_are_host_arithmetic(T):
+    """The plan makers run on the host alone: block sizes, channel blocks and prepared-filter sizes of the one-pass,
+    gathering and strided-row plans; the strided-row plan's column phase (1 with an odd padding at stride 2 when the shift
+    keeps 2 or 4 taps); what each refusal says."""
+    from tdc_b200 import _lib
+    from tdc_b200 import tc
+    lib = T.lib
+    p = _lib.TcPlan()
+    assert lib.tdc_tc_plan_make(64, 64, 3, 3, 4, C.byref(p)) == 0
+    assert (p.nt, p.cb, p.nkb, p.n_ocb, p.hl, p.general) == (64, 16, 4, 1, 2, 0)
+    assert lib.tdc_tc_plan_make_general(3, 64, 7, 7, 3, C.byref(p)) == 0 and (p.general, p.nkb) == (1, 19)
+    for (Cc, K, R, S, stride, pad, phase, nkb, taps) in ((3, 64, 7, 7, 2, 3, 1, 3, 4), (64, 128, 3, 3, 2, 1, 1, 24, 2), (64, 128, 3, 3, 2, 0, 0, 24, 2),
+                                                        (8, 8, 4, 4, 2, 1, 0, 4, 2), (8, 8, 3, 7, 4, 1, 0, 6, 2), (16, 32, 8, 8, 2, 3, 0, 16, 4)):
+        assert tc.strided_rows(S, stride)
+        assert lib.tdc_tc_plan_make_strided(Cc, K, R, S, stride, pad, 4, 0, C.byref(p)) == 0, lib.tdc_last_error_string()
+        assert (p.general, p.stride, p.phase, p.nkb) == (2, stride, phase, nkb), (Cc, K, R, S, stride, pad)
+        assert p.weights_bytes == 4 * 2 * taps * 8 * p.nt * p.nkb * p.n_ocb + 4 * (1024 + 64)
+    assert not tc.strided_rows(5, 2) and not tc.strided_rows(3, 1)
+    for args, needle in (((8, 8, 5, 5, 2, 2, 4, 0), b"2 or 4 column taps"), ((8, 8, 3, 3, 2, 1, 3, 0), b"mode 4"),
+                         ((8, 8, 3, 3, 1, 1, 4, 0), b"strides 2..15"), ((8, 8, 3, 3, 2, 1, 4, 48), b"nt 48")):
+        assert lib.tdc_tc_plan_make_strided(*args, C.byref(p)) == _lib.ERR_UNSUPPORTED
+        assert needle in lib.tdc_last_error_string(), (args, lib.tdc_last_error_string())
+
+
 @pytest.mark.parametrize("B", [1, 64])
 @pytest.mark.parametrize("H,R1,R2", SWEEP)
 def test_selector_gives_a_launchable_tile(T, B, H, R1, R2):
