@@ -320,6 +320,10 @@ TDC_API int tdc_tc_prepare_weights(const tdc_tc_plan* plan, const float* w, int 
  * core returns them: sums of small integers, where nothing is truncated, are exact, which is what the reference
  * drivers check (template_benchmark_cudnn.template:404-411,489-498). */
 #define TDC_TC_UNBIASED    0x200
+/* Stream order is kept as with any launch.  (The persistent kernel is launched with programmatic stream serialization:
+ * its CTAs may be scheduled while the kernel before it in the stream still runs, and wait inside, before they touch any
+ * global memory but the filter plan's constants, until that kernel has completed and its writes are visible.  A caller
+ * sees nothing of it but shorter gaps between launches; it also holds under stream capture into a CUDA graph.) */
 TDC_API int tdc_conv2d_tc(const tdc_tc_plan* plan, const float* x, const void* wt, float* y,
                           int B, int H, int W, const tdc_epilogue* epi, int flags, void* stream);
 /* Mode 4 scales the input by a power of two into fp16's range (which ends at 65504) and undoes the scaling in the
