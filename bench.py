@@ -276,7 +276,7 @@ def bench_resnet(torch, T, dev, dist, world, rank, stream):
     model = T.fill_deterministic(T.tkc_resnet18(precision="auto").eval(), seed=0).to(dev)
     out = {}
     with torch.no_grad():
-        for B, iters in ((256, 5), (1, 30)):
+        for B, iters in ((256, 5), (32, 20), (1, 30)):
             x = torch.randn(B, 3, 224, 224, generator=torch.Generator().manual_seed(4001 + rank)).to(dev)
 
             def fwd():
