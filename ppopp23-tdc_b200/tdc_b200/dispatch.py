@@ -24,7 +24,7 @@ def one_conv(owner, name, x, w_kcrs, w_crsk, scale, shift, residual, relu, strid
     one_pass = tc.supported(R, S, stride, padding, W)
     Ho, Wo = (H + 2 * padding - R) // stride + 1, (W + 2 * padding - S) // stride + 1
     if precision != "fp32" and (one_pass or tc.general_supported(R, S, stride, padding, Wo)) and \
-            (precision != "auto" or _on_tensor_cores(B, Cc, K, H, W, R, S, stride, padding)):
+            (precision != "auto" or _auto_path(owner, name, B, Cc, K, H, W, R, S, stride, padding)):
         mode = MODES.get(precision, AUTO_MODE)
         if one_pass and not _thin_and_wide(Cc, W, R, stride):
             return tc.cached(owner, name, w_kcrs, mode)(x, scale, shift, residual, relu, stride=stride)
@@ -35,6 +35,16 @@ def one_conv(owner, name, x, w_kcrs, w_crsk, scale, shift, residual, relu, strid
             w_crsk = w_crsk()
         return ops.conv2d_epi(x, w_crsk, scale, shift, residual, relu, stride, padding, w_layout=W_CRSK, tile=tile)
     return ops.conv2d_epi(x, w_kcrs.detach(), scale, shift, residual, relu, stride, padding, tile=tile)
+
+
+def _auto_path(owner, name, *shape):
+    """`_on_tensor_cores` for this layer and shape, remembered on the module that owns the weight: the answer depends on
+    shapes only, and a batch-1 forward would otherwise spend more host time on it than the launch costs."""
+    memo = owner.__dict__.setdefault("_auto_paths", {})
+    hit = memo.get((name, shape))
+    if hit is None:
+        hit = memo[(name, shape)] = _on_tensor_cores(*shape)
+    return hit
 
 
 def _thin_and_wide(Cc, W, R, stride):
@@ -106,6 +116,14 @@ def tucker_strategy(conv, x, precision):
     14x14, stride 2, batch 32: 341 us merged, 107 us as the chain)."""
     if precision != "auto":
         return "chain"
+    memo = conv.__dict__.setdefault("_strategies", {})     # the choice depends on shapes only
+    hit = memo.get(tuple(x.shape))
+    if hit is None:
+        hit = memo[tuple(x.shape)] = _tucker_strategy(conv, x)
+    return hit
+
+
+def _tucker_strategy(conv, x):
     from . import tc
     B, Cc, H, W = x.shape
     R, S = conv.kernel_size

@@ -23,7 +23,14 @@ def _dev_f32(t, name):
     return t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current CUDA stream of the current device as the integer the C ABI takes (the raw query where this torch has
+    it: a tenth of the host time of building a Stream object, and a batch-1 forward asks some twenty times)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
