@@ -146,19 +146,20 @@ def strided_rows(S, stride):
 
 def worthwhile(B, C, H, W, K, R):
     """The tensor-core kernel works on tiles of 128 positions x up to 128 channels; with too few position tiles or too
-    little arithmetic the fp32 kernel with its channel slices and clusters is the faster one.  Measured crossovers: a
-    3x3 layer wants about 4 position tiles and 0.1 GFLOP (sweep shapes at batch 1..8, Tucker blocks at batch 32).  A
-    1x1 layer with few tiles is one CTA walking all input channels, about 12 us + 0.085 us per channel whatever the
-    tile count, while the fp32 kernel's time follows the arithmetic: 92 layers of 3..49 tiles (64..2048 channels,
-    7..56 pixels, batch 2..32) timed on both paths give the three cases below, within 1 % of always taking the faster
-    one (the rule they replace, 0.2 GFLOP and 16 tiles: 10 %)."""
+    little arithmetic the fp32 kernel with its channel slices and clusters is the faster one.  The thresholds are a fit
+    to 420 layers (3x3 and 1x1, 32..2048 channels, 7..112 pixels, batch 1..32) timed on both paths in one run.  A 3x3
+    layer wants 3 position tiles and 0.1 GFLOP: 0.2 % from always taking the faster path.  A 1x1 layer with few tiles
+    is one CTA walking all input channels, about 12 us + 0.085 us per channel whatever the tile count, while the fp32
+    kernel's time follows the arithmetic; the three cases below are 1.2 % from the faster path (the thresholds they
+    replace, which asked for 12..24 tiles: 4.3 %), and on CUDA-graphed forwards at batch 1..16 they are never slower
+    and up to 23 % faster (TK-ResNet-50 at batch 4: 2.50 -> 1.91 ms; TK-DenseNet-121 at batch 8: 4.70 -> 3.65 ms)."""
     pad = (R - 1) // 2
     flops, positions = 2.0 * B * H * W * C * K * R * R, B * (H + pad) * (W + pad)
     if R == 1:
         tiles = positions / 128.0
-        return (tiles >= 24 and flops >= 0.04e9) or (tiles >= 3 and K >= 2 * C and flops >= 0.1e9) or \
-               (tiles >= 12 and flops >= 0.4e9 and (2 * K >= C or flops >= 2e9))
-    return flops >= 0.1e9 and positions >= 4 * 128
+        return (tiles >= 4 and flops >= 0.02e9) or (C <= 512 and flops >= 0.2e9) or \
+               (tiles >= 3 and K >= 2 * C and flops >= 0.1e9)
+    return flops >= 0.1e9 and positions >= 3 * 128
 
 
 def cached(owner, name, weight, mode, w_layout=_lib.W_KCRS, general=False):
