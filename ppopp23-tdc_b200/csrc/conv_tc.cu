@@ -131,27 +131,40 @@ __device__ __forceinline__ float absmax_of(const float* slots, unsigned int* scr
     return m;
 }
 
-// The largest magnitude among two elements per thread spread evenly over x (all of x when it is shorter).  Two steps, so
-// that the loads (one memory round trip, cold pages included) run under whatever the caller does between them:
-// range_sample_load issues this thread's loads, range_sample_max reduces them over the warps that need the result.
-constexpr int RANGE_PER_THREAD = 2;
-__device__ __forceinline__ unsigned int range_sample_load(const float* x, long long n) {
-    const int want = RANGE_PER_THREAD * (int)blockDim.x;
-    const long long step = n > want ? n / want : 1;
-    unsigned int m = 0;
+// The range of the input of a launch with fp16 operands, found by `threads` threads of the block (whole warps; `idx` =
+// the thread's index among them): the largest of the given ABSMAX_SLOTS partial maxima of |x|, or, without such a bound,
+// the largest magnitude among RANGE_PER_THREAD elements per thread spread evenly over x (all of x when it is shorter).
+// Two steps, so that the loads (one memory round trip, cold pages included) run under whatever the caller does between
+// them: range_load issues this thread's loads and hands back the raw words — nothing uses the loaded registers until
+// range_max reduces them.
+constexpr int RANGE_PER_THREAD = 4;
+__device__ __forceinline__ void range_load(const float* slots, const float* x, long long n, int idx, int threads, unsigned int (&raw)[RANGE_PER_THREAD]) {
+    if (slots) {
 #pragma unroll
-    for (int i = 0; i < RANGE_PER_THREAD; ++i) {
-        const long long k = (long long)(threadIdx.x + i * blockDim.x) * step;
-        if (k < n) m = max(m, __float_as_uint(__ldg(x + k)) & 0x7fffffffu);
+        for (int i = 0; i < RANGE_PER_THREAD; ++i) raw[i] = idx + i * threads < ABSMAX_SLOTS ? __float_as_uint(slots[idx + i * threads]) : 0u;
+    } else {
+        const int want = RANGE_PER_THREAD * threads;
+        const long long step = n > want ? n / want : 1;
+#pragma unroll
+        for (int i = 0; i < RANGE_PER_THREAD; ++i) {
+            const long long k = (long long)(idx + i * threads) * step;
+            raw[i] = k < n ? __float_as_uint(__ldg(x + k)) : 0u;
+        }
     }
-    return m;
 }
-// `scratch` was zeroed before the block's last barrier; the `threads` threads that call this (whole warps) meet at
-// named barrier 1, the others need not wait for the samples.
-__device__ __forceinline__ float range_sample_max(unsigned int mine, unsigned int* scratch, int threads) {
+// `scratch` was zeroed before the block's last barrier.  The threads that loaded reduce into it and meet the threads
+// that only need the result (range_wait) at named barrier 1, `meeting` threads in all; the rest of the block does not wait.
+__device__ __forceinline__ float range_max(const unsigned int (&raw)[RANGE_PER_THREAD], unsigned int* scratch, int meeting) {
+    unsigned int mine = 0;
+#pragma unroll
+    for (int i = 0; i < RANGE_PER_THREAD; ++i) mine = max(mine, raw[i] & 0x7fffffffu);
     const unsigned int m = __reduce_max_sync(0xffffffffu, mine);
     if ((threadIdx.x & 31) == 0 && m) atomicMax(scratch, m);
-    asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"r"(meeting) : "memory");
+    return __uint_as_float(*reinterpret_cast<volatile unsigned int*>(scratch));
+}
+__device__ __forceinline__ float range_wait(unsigned int* scratch, int meeting) {
+    asm volatile("bar.sync 1, %0;" ::"r"(meeting) : "memory");
     return __uint_as_float(*reinterpret_cast<volatile unsigned int*>(scratch));
 }
 

@@ -158,16 +158,19 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     const uint32_t b_bytes = (uint32_t)b_floats * 4u;
     const int nbuf = a.nbuf;
     const long long ntiles = a.ntiles;          // position tiles x output-channel blocks
-    // fp16 operands without a bound of |x|: this thread's samples of the input, loaded now, reduced after the set-up below
+    // fp16 operands: the range of the input (its given partial maxima of |x|, or samples of x when there is no bound) is
+    // loaded by the draining warps, which have nothing else to do yet and no registers in use, and reduced only where the
+    // first value is needed (below): the round trip runs under the set-up and the index work of the first tile.
     // The kernel may have been scheduled before the kernels ahead of it in the stream have finished (programmatic
     // dependent launch): nothing they may have written (x, the bound of |x|, y, the residual) is touched before
-    // griddepcontrol.wait, which every thread passes once.  The warps that sample the input wait here, so that their
+    // griddepcontrol.wait, which every thread passes once.  The warps that load the range wait here, so that their
     // loads are in flight during the set-up below (done by warps that touch no global memory until they have waited too).
-    unsigned int sampled = 0;
-    const bool samples = F16 && !a.x_absmax && (warp < P_IW0 || warp >= P_EW0);
+    constexpr int SCALED_THREADS = P_LOADERS + 128 * P_GROUPS;       // the converting and the draining warps
+    unsigned int range_raw[RANGE_PER_THREAD] = {};
+    const bool samples = F16 && warp >= P_EW0;
     if (samples) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        sampled = range_sample_load(a.x, a.x_count);
+        range_load(a.x_absmax, a.x, a.x_count, tid - P_EW0 * 32, 128 * P_GROUPS, range_raw);
     }
 
     if (tid == (P_IW0 + 1) * 32) {
@@ -176,6 +179,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
         for (int d = 0; d < 8; ++d) { mbar_init(&rfull_bar[d], 1); mbar_init(&rempty_bar[d], P_LOADERS / 32); }    // the producer's arrive + bytes; one per converting warp
         *abort_flag = 0;
         *range_word = 0;
+        *max_word = 0;                                   // the largest |y| of this CTA (read after the last barrier)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == P_IW0) {
@@ -189,22 +193,12 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     if (!samples) asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the kernel after this one may be scheduled as SMs become free
     TDC_PROF_DECL;
-    // fp16 operands: the power of two that brings the input just under 2^15, and the factor that undoes it (and the
-    // filter's, applied when it was prepared) in the epilogue
-    // (with a bound of |x| everybody reads it here; without one only the converting and the draining warps need the
-    // scale and wait for the samples, at named barrier 1, while the producer and the issuers already start)
+    // fp16 operands: the power of two that brings the input just under 2^15 (2^9 when the range is only sampled), and
+    // the factor that undoes it (and the filter's, applied when it was prepared) in the epilogue.  Only the converting
+    // and the draining warps need them, and they meet once at named barrier 1: the draining warps at once, the loaders
+    // after the index work of their first tile, or after their loop when the CTA has no tile — the producer, the issuers
+    // and that index work do not wait for the range.
     float xs = 1.f, inv = 1.f;
-    constexpr int SCALED_THREADS = P_LOADERS + 128 * P_GROUPS;
-    if constexpr (F16) {
-        if (a.x_absmax) {
-            xs = range_scale(absmax_of(a.x_absmax, max_word), 14);
-            if (tid == 0) *max_word = 0;                 // from here on: the largest |y| of this CTA (read after the last barrier)
-        } else if (warp < P_IW0 || warp >= P_EW0) {
-            if (tid == 0) *max_word = 0;
-            xs = range_scale(range_sample_max(sampled, range_word, SCALED_THREADS), 8);
-        }
-        inv = 1.f / (xs * a.w_scale[0]);
-    }
 
     if (warp < P_IW0) {
         // ================= loaders =================
@@ -214,14 +208,26 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
         float* stage_A = nullptr;                // the stage being filled
         // where channel block kb of the current tile goes; its first block of a stage waits for the stage and starts
         // the copy of the stage's filter blocks
-        auto open_stage = [&](const float* wt_tile, int kb) -> float* {
+        // The filter blocks of the very first stage are asked for before the index work of the first tile (first_filter),
+        // so that they land under it; open_stage then skips that copy.
+        auto first_filter = [&](const float* wt_tile) {
+            if (tid == 0) {
+                const uint32_t bytes = (uint32_t)(a.nkb < a.kps ? a.nkb : a.kps) * b_bytes;
+                mbar_expect_tx(&full_bar[0], bytes);
+                bulk_g2s(stage0 + a.kps * a_floats, wt_tile, bytes, &full_bar[0]);
+            }
+        };
+        // the loaders' side of the meeting at named barrier 1
+        auto scale_here = [&]() { if constexpr (F16) xs = range_scale(range_wait(range_word, SCALED_THREADS), a.x_absmax ? 14 : 8); };
+        // `first`: the first block of this CTA, whose filter copy first_filter has issued
+        auto open_stage = [&](const float* wt_tile, int kb, bool first) -> float* {
             const int k = st_k;
             if (k == 0) {
                 const int s = st_idx;
                 stage_A = stage0 + (long long)s * stage_floats;
                 // use number u of this stage waits for the MMAs of use u-1; the first use passes at once
                 if (!TDC_PROF_WAIT(0, mbar_wait(&empty_bar[s], (uint32_t)(st_use ^ 1)))) { *abort_flag = 1; return nullptr; }
-                if (tid == 0) {
+                if (tid == 0 && !first) {
                     const uint32_t bytes = (uint32_t)(a.nkb - kb < a.kps ? a.nkb - kb : a.kps) * b_bytes;
                     mbar_expect_tx(&full_bar[s], bytes);
                     bulk_g2s(stage_A + a.kps * a_floats, wt_tile + (long long)kb * b_floats, bytes, &full_bar[s]);
@@ -255,6 +261,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 tile_of<MT>(a, t, g0, cnt, ocb);
                 const int rows = cnt * M_TILE;                           // a one-tap filter has no halo
                 const float* wt_tile = a.wt + (long long)ocb * a.nkb * b_floats;
+                if (t == blockIdx.x) first_filter(wt_tile);
                 bool ok = true;
                 constexpr int NI = (MT * M_TILE / 2 + P_LOADERS - 1) / P_LOADERS;
                 long long off[NI];
@@ -279,7 +286,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     }
                 };
                 auto stage = [&](int kb, float4 (&v)[NI][4]) -> bool {
-                    float* A = open_stage(wt_tile, kb);
+                    float* A = open_stage(wt_tile, kb, t == blockIdx.x && kb == 0);
                     if (!A) return false;
 #pragma unroll
                     for (int i = 0; i < NI; ++i) {
@@ -312,13 +319,15 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             const float* raw0 = stage0 + (long long)a.ns * stage_floats;
             const int slot_floats = a.nbox_cap * (BOXC * BOXW), depth = a.depth;
             int r_slot = 0, r_use = 0;
-            for (long long t = blockIdx.x; t < ntiles && !*abort_flag; t += gridDim.x) {
+            long long t = blockIdx.x;
+            for (; t < ntiles && !*abort_flag; t += gridDim.x) {
                 long long g0;
                 int cnt, ocb;
                 tile_of<MT>(a, t, g0, cnt, ocb);
                 const int rows = cnt * M_TILE + halo_rows;
                 const long long gp0 = g0 - a.shift;
                 const float* wt_tile = a.wt + (long long)ocb * a.nkb * b_floats;
+                if (t == blockIdx.x) first_filter(wt_tile);
                 // offset of channel 0 of each owned patch row within a raw slot, -1 = a row of zeros
                 int roff[PPT];
                 TDC_PROF_SPAN_BEGIN;
@@ -362,9 +371,10 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     }
                 }
                 TDC_PROF_SPAN_END(6);
+                if (t == blockIdx.x) scale_here();                               // the range's round trip ran under the index work
                 bool ok = true;
                 for (int kb = 0; kb < a.nkb; ++kb) {
-                    float* A = open_stage(wt_tile, kb);
+                    float* A = open_stage(wt_tile, kb, t == blockIdx.x && kb == 0);
                     if (!A || !TDC_PROF_WAIT(1, mbar_wait(&rfull_bar[r_slot], (uint32_t)r_use))) { *abort_flag = 1; ok = false; break; }
                     const float* R = raw0 + (long long)r_slot * slot_floats;
                     TDC_PROF_SPAN_BEGIN;
@@ -384,8 +394,9 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     if (++r_slot == depth) { r_slot = 0; r_use ^= 1; }
                     { TDC_PROF_SPAN_BEGIN; close_stage(kb); TDC_PROF_SPAN_END(9); }
                 }
-                if (!ok) break;
+                if (!ok) { t = -1; break; }
             }
+            if (t == blockIdx.x) scale_here();             // no tile was started: the draining warps still wait at the barrier
         } else {
             // The input goes global -> (cp.async, 4 bytes, zero-filled where the patch is padding) -> a ring of
             // raw fp32 slots in shared memory -> registers -> hi/lo split -> operand layout.  A thread copies and
@@ -512,7 +523,14 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 }
                 asm volatile("cp.async.commit_group;" ::: "memory");      // an empty group past the end keeps the count uniform
             };
+            if (total > 0) {
+                long long g0_first;
+                int cnt_first, ocb_first;
+                tile_of<MT>(a, blockIdx.x, g0_first, cnt_first, ocb_first);
+                first_filter(a.wt + (long long)ocb_first * a.nkb * b_floats);
+            }
             for (int d = 0; d < depth; ++d) issue(d);
+            scale_here();                                  // the range's round trip ran under the index work and the first copies
             long long c_tile = blockIdx.x;
             int c_kb = 0, c_slot = 0;
             const float* wt_tile = a.wt;
@@ -525,7 +543,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             };
             if (total > 0) enter_tile();
             for (long long ci = 0; ci < total && !*abort_flag; ++ci) {
-                float* A = open_stage(wt_tile, c_kb);
+                float* A = open_stage(wt_tile, c_kb, ci == 0);
                 if (!A) break;
                 { TDC_PROF_SPAN_BEGIN; cp_async_wait_pending(depth - 1); TDC_PROF_SPAN_END(1); }   // block ci has landed (this thread's part)
                 const float* R = raw0 + c_slot * raw_floats;
@@ -663,6 +681,10 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
         // epilogue is a latency chain (tensor memory -> registers -> residual loads -> stores), and several chains in
         // flight hide more of it than one; all groups start on the first position tile, whose issuer is released first.
         const int grp = (warp - P_EW0) >> 2;       // warps P_EW0 .. P_EW0 + 4 * P_GROUPS - 1
+        if constexpr (F16) {
+            xs = range_scale(range_max(range_raw, range_word, SCALED_THREADS), a.x_absmax ? 14 : 8);
+            inv = 1.f / (xs * a.w_scale[0]);
+        }
         const int q = warp & 3;
         constexpr int CHUNKS = NT / P_EPI_W;
         long long j = 0;
