@@ -8,6 +8,15 @@
     python kernel_bench.py conv --mode 4 --batch 32 --channels 3 --out-channels 64 --size 224 --filter 7 --stride 2 --pad 3
                                                         # a strided layer (here the ResNet stem) on the gathering plans
 
+    python kernel_bench.py phases [--batch 64] [--level 1]  # where a launch of the tensor-core kernel spends its time, per sweep layer
+
+`phases` builds the measurement variant of the library (build.py: build_profile, -DTDC_TC_PROFILE=level), loads it in
+place of the normal one and, for each of the eight sweep layers (mode 4, no epilogue options), prints the averages over
+the CTAs that had a tile: the time from the start of a CTA to the end of its set-up, to its first full stage, to the end
+of its first MMA issuer and to its last barrier (clocks / the SM clock read through nvidia-smi while it runs), and the
+issuer's shares: waiting for accumulators, waiting for a full stage, issuing (which blocks while the tensor core's
+queue is full) and the rest.  Level 1 leaves the kernel's timing as it is; level 2 adds every role's waits.
+
 `affine`: scale, shift and ReLU over the first `--channels` channels of a [batch][--of][size][size] buffer, the
 pre-activation of a DenseNet layer.  Algorithmic bytes = input read once + output written once; the L2 is flushed
 before every timed launch (a 256 MB memset), times are CUDA events on the launching stream, median of `--iters`.
@@ -20,7 +29,70 @@ import sys
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "ppopp23-tdc_b200"))
 
 
+def phases(argv):
+    """See the module docstring."""
+    import ctypes
+    import subprocess
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["phases"])
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--level", type=int, default=1, choices=[1, 2])
+    a = ap.parse_args(argv)
+    import importlib.util
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location("tdc_build", os.path.join(here, "ppopp23-tdc_b200", "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    os.environ["TDC_B200_LIB"] = mod.build_profile(a.level)
+    import torch
+    import tdc_b200 as T
+    lib = T.lib
+    lib.tdc_tc_profile_read.argtypes = [ctypes.POINTER(ctypes.c_ulonglong), ctypes.c_int]
+    dev = torch.device("cuda")
+    buf = (ctypes.c_ulonglong * 24)()
+    names = ["ld:free stage", "ld:raw slot", "pr:free raw slot", "is:accumulators", "is:full stage", "ep:accumulators", "ld:index work",
+             "ep:stores", "ld:convert", "ld:hand-over"]
+    role_of = [0, 0, 1, 2, 2, 3, 0, 3, 0, 0]
+    for H, C in ((56, 32), (56, 64), (28, 64), (28, 128), (14, 128), (14, 256), (7, 256), (7, 512)):
+        g = torch.Generator().manual_seed(1)
+        x = torch.randn(a.batch, C, H, H, generator=g).to(dev)
+        w = (torch.randn(C, C, 3, 3, generator=g) * (2.0 / (C * 9)) ** 0.5).to(dev)
+        conv, y = T.TcConv(w, mode=4), torch.empty(a.batch, C, H, H, device=dev)
+        for _ in range(3):
+            conv(x, out=y)
+        torch.cuda.synchronize()
+        lib.tdc_tc_profile_read(buf, 1)
+        reps = 20
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            conv(x, out=y)
+        e1.record()
+        mhz = float(subprocess.run(["nvidia-smi", "--query-gpu=clocks.sm", "--format=csv,noheader,nounits", "-i", str(torch.cuda.current_device())],
+                                   capture_output=True, text=True).stdout.split()[0])
+        torch.cuda.synchronize()
+        lib.tdc_tc_profile_read(buf, 1)
+        for _ in range(reps):                    # one launch at a time: a CTA that starts under the launch before it would count its wait for it
+            conv(x, out=y)
+            torch.cuda.synchronize()
+        lib.tdc_tc_profile_read(buf, 1)
+        v = list(buf)
+        ctas = max(1, v[20])
+        us = lambda clocks: clocks / ctas / mhz
+        tot = max(1, v[14])
+        print("3x3 %3d -> %3d at %2dx%2d, batch %d: %.1f us per launch back to back (SM clock %d MHz); per CTA (%d with a tile): set-up done %.1f us, "
+              "first full stage %.1f, first issuer done %.1f, last barrier %.1f | issuer: waits for accumulators %.1f %%, for a full stage %.1f %%, "
+              "issues %.1f %% (%.0f clocks per stage use), rest %.1f %%" % (
+                  C, C, H, H, a.batch, e0.elapsed_time(e1) * 1e3 / reps, mhz, ctas // reps, us(v[16]), us(v[17]), us(v[18]), us(v[19]),
+                  100.0 * v[3] / tot, 100.0 * v[4] / tot, 100.0 * v[10] / tot, v[10] / max(1, v[11]), 100.0 * (tot - v[3] - v[4] - v[10]) / tot), flush=True)
+        if a.level >= 2:
+            print("    shares within a role: " + ", ".join("%s %.0f %%" % (names[i], 100.0 * v[i] / v[12 + role_of[i]]) for i in range(10) if v[12 + role_of[i]] and v[i]), flush=True)
+    return 0
+
+
 def main(argv=None):
+    if (argv if argv is not None else sys.argv[1:])[:1] == ["phases"]:
+        return phases(argv if argv is not None else sys.argv[1:])
     import torch
     import tdc_b200 as T
     from tdc_b200 import ops

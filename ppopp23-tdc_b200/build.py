@@ -80,6 +80,28 @@ def build_debug_bounds():
     return out
 
 
+def build_profile(level=1):
+    """libtdc_b200_profile.so: the library with the tensor-core kernels compiled as a measurement build
+    (-DTDC_TC_PROFILE=level, see csrc/conv_tc_persist.cuh; exports tdc_tc_profile_read).  Level 1 marks the phases of a
+    CTA and times the issuers without slowing the kernel; level 2 times every role.  `python kernel_bench.py phases`
+    builds and loads it; the other objects are those of the normal build."""
+    build()
+    out = os.path.join(HERE, "tdc_b200", "libtdc_b200_profile.so")
+    obj_dir = os.path.join(HERE, "build", "profile%d" % level)
+    os.makedirs(obj_dir, exist_ok=True)
+    src, obj = os.path.join(CSRC, "conv_tc.cu"), os.path.join(obj_dir, "conv_tc.o")
+    if not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), _newest_header()):
+        r = subprocess.run([_nvcc(), *NVCC_FLAGS, "-DTDC_TC_PROFILE=%d" % level, "-c", src, "-o", obj], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed on %s:\n%s" % (src, r.stderr))
+    objs = [obj] + [os.path.join(OBJ, f[:-3] + ".o") for f in sorted(os.listdir(CSRC)) if f.endswith(".cu") and f != "conv_tc.cu"]
+    r = subprocess.run([_nvcc(), "-shared", "-o", out, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("link failed:\n%s" % r.stderr)
+    return out
+
+
 def build(force=False, verbose=False):
     os.makedirs(OBJ, exist_ok=True)
     hdr = _newest_header()
@@ -103,6 +125,7 @@ def build(force=False, verbose=False):
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
     build_baseline_tool(force)
     build_layer_driver(force)
+    build_rates_tool(force)
     return LIB
 
 
@@ -122,6 +145,21 @@ def build_layer_driver(force=False, defines=()):
     if r.returncode != 0:
         raise RuntimeError("layer_driver failed to build:\n%s\n%s" % (r.stdout, r.stderr))
     return DRIVER_EXE
+
+
+RATES_SRC = os.path.join(HERE, "drivers", "tc_rates.cu")
+RATES_EXE = os.path.join(HERE, "tdc_b200", "tc_rates")
+
+
+def build_rates_tool(force=False):
+    """drivers/tc_rates.cu: a standalone microbenchmark of the two per-SM rates that bound the tensor-core kernel (MMA
+    issue from shared memory, bulk copies out of L2); links nothing of the library."""
+    if not force and os.path.exists(RATES_EXE) and os.path.getmtime(RATES_EXE) >= os.path.getmtime(RATES_SRC):
+        return RATES_EXE
+    r = subprocess.run([_nvcc(), "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", RATES_SRC, "-o", RATES_EXE], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("tc_rates failed to build:\n%s\n%s" % (r.stdout, r.stderr))
+    return RATES_EXE
 
 
 BASELINE_SRC = os.path.join(HERE, "baselines", "cudnn_layer.cpp")

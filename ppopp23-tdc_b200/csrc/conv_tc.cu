@@ -1434,11 +1434,11 @@ int tdc_conv2d_tc_ranged(const tdc_tc_plan* p, const float* x, const void* wt, f
 }
 
 #ifdef TDC_TC_PROFILE
-// Measurement build only: the sixteen clock sums of the persistent kernel's roles (see conv_tc_persist.cuh); reset != 0 clears them.
+// Measurement builds only: the 24 sums of the persistent kernel (see conv_tc_persist.cuh); reset != 0 clears them.
 __attribute__((visibility("default"))) int tdc_tc_profile_read(unsigned long long* out, int reset) {
-    cudaError_t e = cudaMemcpyFromSymbol(out, tdc_tc::g_tc_prof, sizeof(unsigned long long) * 16);
+    cudaError_t e = cudaMemcpyFromSymbol(out, tdc_tc::g_tc_prof, sizeof(unsigned long long) * 24);
     if (e == cudaSuccess && reset) {
-        unsigned long long z[16] = {};
+        unsigned long long z[24] = {};
         e = cudaMemcpyToSymbol(tdc_tc::g_tc_prof, z, sizeof z);
     }
     return e == cudaSuccess ? TDC_OK : tc_fail(TDC_ERR_CUDA, "profile read: %s", cudaGetErrorString(e));

@@ -105,22 +105,42 @@ __device__ __forceinline__ void bulk_tensor_3d(void* dst, const CUtensorMap* map
                  ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
 }
 
-// Measurement build (-DTDC_TC_PROFILE): every role sums the clocks it spends in each kind of wait and in total; one
-// lane per warp adds them to g_tc_prof, which tdc_tc_profile_read hands to the host.  Not compiled otherwise.
+// Measurement builds (not compiled otherwise); tdc_tc_profile_read hands g_tc_prof to the host.
+//   -DTDC_TC_PROFILE=1  phases of a CTA and the issuers' waits only, which leaves the kernel's timing as it is: per CTA
+//                       that has a tile, the clocks from its start to the end of the set-up [16], to its first full stage
+//                       [17], to the end of its first issuer [18] and to its last barrier [19], and the CTAs counted [20];
+//                       per stage use of an issuer the clocks spent issuing it [10] and the uses counted [11];
+//   -DTDC_TC_PROFILE=2  also every role's waits and spans [0, 12) and role totals [12, 16): the clock reads in the
+//                       loaders' loops slow the kernel by a third or more, so only the shares within a role mean something.
 #ifdef TDC_TC_PROFILE
-__device__ unsigned long long g_tc_prof[16];   // [0, 12) kinds of wait or span, [12, 16) role totals
-#define TDC_PROF_DECL long long prof_t[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_start = clock64()
-#define TDC_PROF_WAIT(kind, call) ([&]() { const long long t0_ = clock64(); const bool ok_ = (call); prof_t[kind] += clock64() - t0_; return ok_; }())
-#define TDC_PROF_SPAN_BEGIN const long long span0_ = clock64()
-#define TDC_PROF_SPAN_END(kind) prof_t[kind] += clock64() - span0_
-#define TDC_PROF_FLUSH(role) do { if (lane == 0) { for (int k_ = 0; k_ < 12; ++k_) if (prof_t[k_]) atomicAdd(&g_tc_prof[k_], (unsigned long long)prof_t[k_]); \
+__device__ unsigned long long g_tc_prof[24];
+#define TDC_PROF_LIGHT(kind) ((kind) == 3 || (kind) == 4)            /* the issuers' two waits */
+#define TDC_PROF_DECL long long prof_t[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_start = clock64(); bool prof_first = true
+#define TDC_PROF_WAIT(kind, call) ([&]() { if (TDC_TC_PROFILE < 2 && !TDC_PROF_LIGHT(kind)) return (bool)(call); \
+                                           const long long t0_ = clock64(); const bool ok_ = (call); prof_t[kind] += clock64() - t0_; return ok_; }())
+#define TDC_PROF_SPAN_BEGIN const long long span0_ = TDC_TC_PROFILE < 2 ? 0 : clock64()
+#define TDC_PROF_SPAN_END(kind) do { if (TDC_TC_PROFILE >= 2) prof_t[kind] += clock64() - span0_; } while (0)
+#define TDC_PROF_FLUSH(role) do { if (lane == 0 && (TDC_TC_PROFILE >= 2 || (role) == 2)) { \
+                                  for (int k_ = 0; k_ < 12; ++k_) if (prof_t[k_]) atomicAdd(&g_tc_prof[k_], (unsigned long long)prof_t[k_]); \
                                   atomicAdd(&g_tc_prof[12 + (role)], (unsigned long long)(clock64() - prof_start)); } } while (0)
+#define TDC_PROF_ISSUE_BEGIN const long long issue0_ = clock64()
+#define TDC_PROF_ISSUE_END do { prof_t[10] += clock64() - issue0_; prof_t[11] += 1; } while (0)
+/* a phase mark by one thread of a CTA that has a tile (`once`: only the first time this thread comes by) */
+#define TDC_PROF_MARK(slot, cond, once) do { if ((cond) && blockIdx.x < ntiles && (!(once) || prof_first)) { if (once) prof_first = false; \
+                                             atomicAdd(&g_tc_prof[slot], (unsigned long long)(clock64() - prof_cta0)); } } while (0)
+#define TDC_PROF_COUNT(slot, cond) do { if ((cond) && blockIdx.x < ntiles) atomicAdd(&g_tc_prof[slot], 1ull); } while (0)
+#define TDC_PROF_CTA_START const long long prof_cta0 = clock64()
 #else
 #define TDC_PROF_DECL
 #define TDC_PROF_WAIT(kind, call) (call)
 #define TDC_PROF_SPAN_BEGIN
 #define TDC_PROF_SPAN_END(kind)
 #define TDC_PROF_FLUSH(role)
+#define TDC_PROF_ISSUE_BEGIN
+#define TDC_PROF_ISSUE_END
+#define TDC_PROF_MARK(slot, cond, once)
+#define TDC_PROF_COUNT(slot, cond)
+#define TDC_PROF_CTA_START
 #endif
 
 template <int NT, int MT, int TAPS, int LD, bool F16, int LW = 8>
@@ -131,6 +151,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     // the roles of this instantiation (see the top of the file)
     static_assert(LW == 8 || LW == 12, "8 loader warps and four epilogue groups, or 12 and three");
     constexpr int P_LOADERS = LW * 32, P_IW0 = LW, P_EW0 = LW + 4, P_GROUPS = (P_WARPS - P_EW0) / 4, P_PRODUCER = P_IW0 + 3;
+    TDC_PROF_CTA_START;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint64_t* full_bar   = reinterpret_cast<uint64_t*>(smem_raw);    // [ns]  patch stored + filter landed
     uint64_t* empty_bar  = full_bar + 4;                              // [ns]  MMAs that read the stage are done
@@ -158,20 +179,9 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     const uint32_t b_bytes = (uint32_t)b_floats * 4u;
     const int nbuf = a.nbuf;
     const long long ntiles = a.ntiles;          // position tiles x output-channel blocks
-    // fp16 operands: the range of the input (its given partial maxima of |x|, or samples of x when there is no bound) is
-    // loaded by the draining warps, which have nothing else to do yet and no registers in use, and reduced only where the
-    // first value is needed (below): the round trip runs under the set-up and the index work of the first tile.
-    // The kernel may have been scheduled before the kernels ahead of it in the stream have finished (programmatic
-    // dependent launch): nothing they may have written (x, the bound of |x|, y, the residual) is touched before
-    // griddepcontrol.wait, which every thread passes once.  The warps that load the range wait here, so that their
-    // loads are in flight during the set-up below (done by warps that touch no global memory until they have waited too).
     constexpr int SCALED_THREADS = P_LOADERS + 128 * P_GROUPS;       // the converting and the draining warps
-    unsigned int range_raw[RANGE_PER_THREAD] = {};
-    const bool samples = F16 && warp >= P_EW0;
-    if (samples) {
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        range_load(a.x_absmax, a.x, a.x_count, tid - P_EW0 * 32, 128 * P_GROUPS, range_raw);
-    }
+    // the producer's first copy would otherwise wait for the fetch of the tensor map
+    if (LD == LD_BULK && tid == P_PRODUCER * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap)) : "memory");
 
     if (tid == (P_IW0 + 1) * 32) {
         for (int s = 0; s < a.ns; ++s) { mbar_init(&full_bar[s], P_LOADERS / 32 + 1); mbar_init(&empty_bar[s], MT); }   // one arrival per loader warp + the filter's bytes
@@ -190,9 +200,13 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
-    if (!samples) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // The kernel may have been scheduled before the kernels ahead of it in the stream have finished (programmatic
+    // dependent launch): nothing they may have written (x, the bound of |x|, y, the residual) is touched before
+    // griddepcontrol.wait, which every thread passes once, here.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");      // the kernel after this one may be scheduled as SMs become free
     TDC_PROF_DECL;
+    TDC_PROF_MARK(16, tid == 0, false);
     // fp16 operands: the power of two that brings the input just under 2^15 (2^9 when the range is only sampled), and
     // the factor that undoes it (and the filter's, applied when it was prepared) in the epilogue.  Only the converting
     // and the draining warps need them, and they meet once at named barrier 1: the draining warps at once, the loaders
@@ -656,6 +670,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                         const int s = st_idx;
                         if (!TDC_PROF_WAIT(4, mbar_wait(&full_bar[s], (uint32_t)st_use))) { *abort_flag = 1; ok = false; break; }
                         if (++st_idx == a.ns) { st_idx = 0; st_use ^= 1; }
+                        TDC_PROF_MARK(17, mt == 0 && lane == 0, true);
+                        TDC_PROF_ISSUE_BEGIN;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const float* A = stage0 + (long long)s * stage_floats;
                         const int kend = kb0 + a.kps < kb_hi ? kb0 + a.kps : kb_hi;
@@ -669,10 +685,12 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                             if (kend == kb_hi) mma_commit(&tfull_bar[slot]);  // and this run's accumulators are complete
                         }
                         __syncwarp();
+                        TDC_PROF_ISSUE_END;
                     }
                 }
                 if (!ok) break;
             }
+            TDC_PROF_MARK(18, mt == 0 && lane == 0, false);
             TDC_PROF_FLUSH(2);
         }
     } else {
@@ -681,7 +699,12 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
         // epilogue is a latency chain (tensor memory -> registers -> residual loads -> stores), and several chains in
         // flight hide more of it than one; all groups start on the first position tile, whose issuer is released first.
         const int grp = (warp - P_EW0) >> 2;       // warps P_EW0 .. P_EW0 + 4 * P_GROUPS - 1
+        // fp16 operands: the range of the input (its given partial maxima of |x|, or samples of x when there is no bound)
+        // is loaded by these warps, which have nothing else to do yet and no registers in use; the round trip runs under
+        // the index work of the loaders' first tile, which meet them at the barrier when that is done.
         if constexpr (F16) {
+            unsigned int range_raw[RANGE_PER_THREAD];
+            range_load(a.x_absmax, a.x, a.x_count, tid - P_EW0 * 32, 128 * P_GROUPS, range_raw);
             xs = range_scale(range_max(range_raw, range_word, SCALED_THREADS), a.x_absmax ? 14 : 8);
             inv = 1.f / (xs * a.w_scale[0]);
         }
@@ -737,6 +760,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
     __syncwarp();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    TDC_PROF_MARK(19, tid == 0, false);
+    TDC_PROF_COUNT(20, tid == 0);
     if (*abort_flag && tid == 0 && a.status) atomicCAS(a.status, 0, 1);
     // an output that is not finite: the input went beyond fp16's range even after scaling (or was not finite itself)
     if (F16 && tid == 0 && a.status && *max_word >= 0x7f800000u) atomicCAS(a.status, 0, 2);
