@@ -81,7 +81,8 @@ __device__ __forceinline__ void issue_block(const Geometry& g, uint32_t d, uint3
     }
 }
 
-__global__ void __launch_bounds__(512) mma_kernel(int pattern, int blocks, int copiers, const float* src, const Geometry g, long long* clocks, int* status) {
+template <int pattern>
+__global__ void __launch_bounds__(512) mma_kernel(int blocks, int copiers, const float* src, const Geometry g, long long* clocks, int* status) {
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* done_bar = reinterpret_cast<uint64_t*>(smem);
     uint64_t* block_bar = done_bar + 1;                          // the per-block commits of LOOP128 land here; nobody waits on it
@@ -104,7 +105,7 @@ __global__ void __launch_bounds__(512) mma_kernel(int pattern, int blocks, int c
     const uint32_t tmem = *tmem_slot;
     if (warp == 0) {
         const long long t0 = clock64();
-        if (pattern == LOOP128) {
+        if constexpr (pattern == LOOP128) {
             for (int kb = 0; kb < blocks; ++kb) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (elect_one()) {
@@ -117,14 +118,14 @@ __global__ void __launch_bounds__(512) mma_kernel(int pattern, int blocks, int c
             const uint64_t a_hi = make_desc(smem_u32(A), P_MAX * 16, 128), a_lo = make_desc(smem_u32(A + A_BYTES), P_MAX * 16, 128);
             const uint64_t b128 = make_desc(smem_u32(B0), 256 * 16, 128), b64 = make_desc(smem_u32(B0), 128 * 16, 128);
             for (int kb = 0; kb < blocks; ++kb) {
-                if (pattern == N128) {
+                if constexpr (pattern == N128) {
 #pragma unroll
                     for (int i = 0; i < 27; ++i) mma(tmem, a_hi + (uint64_t)((i / 9) * 16 + i % 3), b128 + (uint64_t)((i % 9) * (B_TAP / 16)), idesc_of(128), 1u);
                 } else {
 #pragma unroll
                     for (int tap = 0; tap < 9; ++tap) {
                         const uint64_t off = (uint64_t)((tap / 3) * 16 + tap % 3);
-                        if (pattern == CONV128) {
+                        if constexpr (pattern == CONV128) {
                             mma(tmem, a_hi + off, b128 + (uint64_t)(tap * (B_TAP / 16)), idesc_of(256), 1u);
                             mma(tmem + 128, a_lo + off, b128 + (uint64_t)(tap * (B_TAP / 16)), idesc_of(128), 1u);
                         } else {
@@ -191,7 +192,9 @@ int main() {
     int sms = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
     if (sms <= 0 || sms > 1024) { printf("no device\n"); return 1; }
-    cudaFuncSetAttribute(mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    using MmaKernel = void (*)(int, int, const float*, const Geometry, long long*, int*);
+    const MmaKernel mma_kernels[4] = {mma_kernel<N128>, mma_kernel<CONV128>, mma_kernel<CONV64>, mma_kernel<LOOP128>};
+    for (MmaKernel k : mma_kernels) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     cudaFuncSetAttribute(copy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + 147456);
     const size_t src_bytes = 9437184;           // 512 x 512 x 9 filter values in two fp16 parts
     float* src; long long* clocks; int* status;
@@ -209,7 +212,7 @@ int main() {
     for (int copiers : {0, 12})
         for (int p = 0; p < 4; ++p)
             for (int gi = 0; gi < (p == LOOP128 ? 3 : 1); ++gi) {
-                for (int rep = 0; rep < 2; ++rep) mma_kernel<<<sms, 128 + 32 * copiers, SMEM>>>(p, blocks, copiers, src, geo[gi], clocks, status);
+                for (int rep = 0; rep < 2; ++rep) mma_kernels[p]<<<sms, 128 + 32 * copiers, SMEM>>>(blocks, copiers, src, geo[gi], clocks, status);
                 if (!fine()) return 1;
                 printf("mma  %-8s patch rows %3d, image row %2d, %2d cp.async warps beside it: %.1f clocks per 128x128x16 unit (slowest of %d SMs)\n",
                        names[p], geo[gi].P, geo[gi].Wp, copiers, worst(sms) / (blocks * units[p]), sms);
