@@ -328,8 +328,8 @@ TDC_API int tdc_conv2d_tc(const tdc_tc_plan* plan, const float* x, const void* w
                           int B, int H, int W, const tdc_epilogue* epi, int flags, void* stream);
 /* Mode 4 scales the input by a power of two into fp16's range (which ends at 65504) and undoes the scaling in the
  * epilogue.  fp16 keeps its 11 significant bits over 30 binades, so the scale need only be roughly right:
- *   - by default every CTA of the kernel samples some 1300 elements spread over x and puts the largest at 2^8, which
- *     leaves a factor of 256 for values the sample missed (no extra launch, about a microsecond);
+ *   - by default every CTA of the kernel samples 1500 - 2000 elements spread over x and puts the largest at 2^8, which
+ *     leaves a factor of 256 for values the sample missed (no extra launch; the loads run under the CTA's start-up);
  *   - with TDC_TC_EXACT_RANGE in `flags` a pass over all of x finds the true maximum first (one more launch);
  *   - a caller that chains layers (the three steps of TKConv2dC.forward, inference/TKConv.py:90-95) has the bound
  *     for free: y_absmax, when given, receives the partial maxima of |y| (TDC_TC_ABSMAX_FLOATS floats, every entry

@@ -92,7 +92,7 @@ struct Args {
     // fp16 operands: the input is scaled by a power of two into fp16's range (which ends at 65504), the filter likewise
     // when it is prepared, and the epilogue undoes both.  fp16 keeps its 11 significant bits over 30 binades, so the
     // scale need not be exact: given a bound of |x| it goes just under 2^14; without one, every CTA takes the largest
-    // of some 1300 elements spread over x (two per thread) and puts that at 2^8, which leaves a factor of 256 for values the sample
+    // of 1500 - 2000 elements spread over x (four per thread of its draining warps) and puts that at 2^8, which leaves a factor of 256 for values the sample
     // missed.  An input beyond even that turns into infinities, which the epilogue sees in its outputs and reports
     // through the status word (2): never a silent wrong result.
     const float* x_absmax; // [ABSMAX_SLOTS] partial maxima of |x| (every entry valid; the largest one counts), or nullptr
