@@ -81,9 +81,9 @@ def phases(argv):
         us = lambda clocks: clocks / ctas / mhz
         tot = max(1, v[14])
         print("3x3 %3d -> %3d at %2dx%2d, batch %d: %.1f us per launch back to back (SM clock %d MHz); per CTA (%d with a tile): set-up done %.1f us, "
-              "first full stage %.1f, first issuer done %.1f, last barrier %.1f | issuer: waits for accumulators %.1f %%, for a full stage %.1f %%, "
+              "first full stage %.1f (producer's first copy issued %.1f, loaders' first index work done %.1f, first raw block landed %.1f), first issuer done %.1f, last barrier %.1f | issuer: waits for accumulators %.1f %%, for a full stage %.1f %%, "
               "issues %.1f %% (%.0f clocks per stage use), rest %.1f %%" % (
-                  C, C, H, H, a.batch, e0.elapsed_time(e1) * 1e3 / reps, mhz, ctas // reps, us(v[16]), us(v[17]), us(v[18]), us(v[19]),
+                  C, C, H, H, a.batch, e0.elapsed_time(e1) * 1e3 / reps, mhz, ctas // reps, us(v[16]), us(v[17]), us(v[21]), us(v[22]), us(v[23]), us(v[18]), us(v[19]),
                   100.0 * v[3] / tot, 100.0 * v[4] / tot, 100.0 * v[10] / tot, v[10] / max(1, v[11]), 100.0 * (tot - v[3] - v[4] - v[10]) / tot), flush=True)
         if a.level >= 2:
             print("    shares within a role: " + ", ".join("%s %.0f %%" % (names[i], 100.0 * v[i] / v[12 + role_of[i]]) for i in range(10) if v[12 + role_of[i]] and v[i]), flush=True)

@@ -54,6 +54,23 @@ template <bool F16> struct KStep { static constexpr int CH = F16 ? 16 : 8; };
 constexpr int LOADERS  = 256;   // threads of warps 0-7, which stage the input patch
 constexpr int THREADS  = 384;   // + warps 8-11: MMA issuers (lane 0 of each), everyone drains tensor memory
 
+// Division of a non-negative number below 2^31 by a fixed divisor as one widening multiply and a shift: the index
+// arithmetic of the loaders, the producer and the epilogue divides by the row pitch, the positions per image and the
+// number of output-channel blocks once or more per tile and work item, and an integer division is 20 (32-bit) to
+// 100 (64-bit) dependent instructions of a single warp.  mul = floor(2^(31+s) / d) + 1 with 2^(s-1) < d <= 2^s:
+// n * mul >> (31 + s) == n / d for every 0 <= n < 2^31 (the excess mul * d - 2^(31+s) is at most d <= 2^s, so the
+// product overshoots n / d by less than 1 / d).
+struct FastDiv { uint32_t mul, shift; };
+inline FastDiv fastdiv_make(uint32_t d) {
+    uint32_t s = 0;
+    while ((1ull << s) < d) ++s;
+    FastDiv f;
+    f.mul = (uint32_t)(((1ull << (31 + s)) / d) + 1ull);
+    f.shift = 31 + s;
+    return f;
+}
+__host__ __device__ __forceinline__ uint32_t fastdiv(uint32_t n, FastDiv f) { return (uint32_t)(((unsigned long long)n * f.mul) >> f.shift); }
+
 struct Args {
     const float* x;        // [B][C][H][W]
     const float* wt;       // pre-arranged filter, see prepare kernel
@@ -70,6 +87,9 @@ struct Args {
     int halo, shift;       // patch rows beyond a tile's positions, and how far ahead of the tile the patch starts
     float rz_unit;         // expected truncation loss of a sum per channel block (see load_chunk); 0: none put back
     int Wp, Lp;            // row pitch and positions per image of the padded position space
+    int Hp;                // Lp / Wp: rows of a padded image
+    FastDiv fd_Wp, fd_Lp, fd_nocb;   // the divisors of the index arithmetic (valid while positions and tiles stay below 2^31: `small`)
+    int small;             // total_pos and ntiles fit 31 bits: the kernels divide by multiplication
     int P;                 // patch rows staged per CTA (multiple of 8)
     int nkb;               // channel blocks
     int n_ocb;             // output-channel blocks
@@ -1098,8 +1118,11 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
         a.halo = 2 * pad * (a.Wp + 1); a.shift = pad * (a.Wp + 1);
     }
     a.total_pos = (long long)B * a.Lp;
+    a.Hp = a.Lp / a.Wp;
+    a.fd_Wp = fastdiv_make((uint32_t)a.Wp); a.fd_Lp = fastdiv_make((uint32_t)a.Lp);
     if (W > 256) return tc_fail(TDC_ERR_UNSUPPORTED, "image width %d is too large for the tensor-core path (max 256)", W);
     a.nkb = p->nkb; a.n_ocb = p->n_ocb; a.hl = p->hl;
+    a.fd_nocb = fastdiv_make((uint32_t)a.n_ocb);
     const int smem_max = facts.smem_max, sms = facts.sms;
     // Long reductions get two main accumulators per tile, fed by even and odd channel blocks (4*NT columns per tile
     // instead of 2*NT): beyond 320 accumulations with TF32 operands, beyond 144 with fp16 operands (whose layers are
@@ -1260,6 +1283,7 @@ static int plan_launch(const tdc_tc_plan* p, int B, int H, int W, int flags, boo
         }
     }
     a.ntiles = tiles * a.n_ocb;
+    a.small = a.total_pos + (long long)a.Lp + 4096 <= 0x7fffffffLL && a.ntiles <= 0x7fffffffLL;
     if (a.ntiles >= (1ll << 31)) return tc_fail(TDC_ERR_TILE, "grid too large");
     const long long ctas = persist ? (a.ntiles < sms ? a.ntiles : sms) : a.ntiles;
     // The persistent kernel with fp16 parts exists with 8 loader warps and four epilogue groups and with 12 and three;

@@ -65,18 +65,21 @@ template <int MT>
 __device__ __forceinline__ void tile_of(const Args& a, long long t, long long& g0, int& cnt, int& ocb) {
     long long tg = t;
     ocb = 0;
-    if (a.n_ocb > 1) { tg = t / a.n_ocb; ocb = (int)(t - tg * a.n_ocb); }
+    if (a.n_ocb > 1) { tg = a.small ? (long long)fastdiv((uint32_t)t, a.fd_nocb) : t / a.n_ocb; ocb = (int)(t - tg * a.n_ocb); }
     if (tg < a.full_groups) { g0 = tg * (MT * M_TILE); cnt = MT; return; }
     const long long first = a.tail_first_pt + (tg - a.full_groups) * a.tail_cnt, left = a.pt_total - first;
     g0 = first * M_TILE;
     cnt = left < a.tail_cnt ? (int)left : a.tail_cnt;
 }
 
-// Image of padded position g (0 <= g < total_pos).  Position counts fit 32 bits for every layer of practical size, and a
-// 32-bit division is a fifth of the instructions of a 64-bit one: the per-tile index arithmetic of the loaders and
-// the epilogue is made of these.
+// Image of padded position g (0 <= g < total_pos + Lp), and row of position `rem` within a padded image.  Position counts
+// fit 31 bits for every layer of practical size (`small`), and then a division is a multiply and a shift (FastDiv): the
+// per-tile index arithmetic of the loaders and the producer and the per-item arithmetic of the epilogue are made of these.
 __device__ __forceinline__ long long image_of(const Args& a, long long g) {
-    return a.total_pos <= 0x7fffffffLL ? (long long)((unsigned)g / (unsigned)a.Lp) : g / a.Lp;
+    return a.small ? (long long)fastdiv((uint32_t)g, a.fd_Lp) : g / a.Lp;
+}
+__device__ __forceinline__ int row_of(const Args& a, int rem) {
+    return a.small ? (int)fastdiv((uint32_t)rem, a.fd_Wp) : rem / a.Wp;
 }
 
 // The pixels of image b that the patch [gp0, gp0 + rows) of padded positions needs: the run starts at pixel
@@ -100,6 +103,25 @@ __host__ __device__ __forceinline__ void image_run(int H, int W, int Wp, int Lp,
     nbox = (pe - pix4 + BOXW - 1) / BOXW;
 }
 
+// The same on the device, dividing by multiplication.
+__device__ __forceinline__ void image_run(const Args& a, long long gp0, int rows, long long b, int& pix4, int& nbox) {
+    const int H = a.H, W = a.W, Wp = a.Wp, Lp = a.Lp;
+    const long long img0 = b * Lp;
+    const int ls = gp0 > img0 ? (int)(gp0 - img0) : 0;
+    const int le = gp0 + rows < img0 + Lp ? (int)(gp0 + rows - img0) : Lp;
+    nbox = 0; pix4 = 0;
+    if (le <= ls) return;
+    int y0 = row_of(a, ls), x0 = ls - y0 * Wp;
+    if (x0 >= W) { ++y0; x0 = 0; }
+    int y1 = row_of(a, le - 1), x1 = (le - 1) - y1 * Wp;
+    if (y1 >= H) { y1 = H - 1; x1 = W - 1; } else if (x1 >= W) x1 = W - 1;
+    if (y0 >= H) return;
+    const int ps = y0 * W + x0, pe = y1 * W + x1 + 1;
+    if (pe <= ps) return;
+    pix4 = ps & ~3;
+    nbox = (pe - pix4 + BOXW - 1) / BOXW;
+}
+
 __device__ __forceinline__ void bulk_tensor_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                  ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
@@ -109,6 +131,8 @@ __device__ __forceinline__ void bulk_tensor_3d(void* dst, const CUtensorMap* map
 //   -DTDC_TC_PROFILE=1  phases of a CTA and the issuers' waits only, which leaves the kernel's timing as it is: per CTA
 //                       that has a tile, the clocks from its start to the end of the set-up [16], to its first full stage
 //                       [17], to the end of its first issuer [18] and to its last barrier [19], and the CTAs counted [20];
+//                       within the start-up: to the producer's first copy issued [21] (bulk loader), to the end of the
+//                       loaders' first index work [22] and to their first raw block landed [23];
 //                       per stage use of an issuer the clocks spent issuing it [10] and the uses counted [11];
 //   -DTDC_TC_PROFILE=2  also every role's waits and spans [0, 12) and role totals [12, 16): the clock reads in the
 //                       loaders' loops slow the kernel by a third or more, so only the shares within a role mean something.
@@ -349,18 +373,18 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     // Division-free but for the first row: a thread's rows are 256 positions apart, so (image, row,
                     // column) of the next one follow from the previous by adding (step_y, step_x) with carries.  The
                     // first position is taken one image up (gp0 may be negative by less than an image), image -1 = before x.
-                    const int Hp = a.Lp / a.Wp;                                  // rows of a padded image (once per tile: two divisions)
+                    const int Hp = a.Hp;                                         // rows of a padded image
                     const long long g_first = gp0 + tid + a.Lp;
                     long long bi = image_of(a, g_first);
                     int rem = (int)(g_first - bi * a.Lp);
-                    int yy = rem / a.Wp, xx = rem - yy * a.Wp;
+                    int yy = row_of(a, rem), xx = rem - yy * a.Wp;
                     bi -= 1;
                     // the runs of the images this patch meets, one image per lane: first pixel (rounded down to 16 bytes),
                     // boxes, and by a prefix sum the first box of each image in the raw slot
                     const long long lo = gp0 < 0 ? 0 : gp0, hi = (gp0 + rows < a.total_pos ? gp0 + rows : a.total_pos) - 1;
                     const long long b_first = image_of(a, lo), b_last = image_of(a, hi);
                     int my_pix4 = 0, my_nbox = 0;
-                    if (b_first + lane <= b_last) image_run(a.H, a.W, a.Wp, a.Lp, gp0, rows, b_first + lane, my_pix4, my_nbox);
+                    if (b_first + lane <= b_last) image_run(a, gp0, rows, b_first + lane, my_pix4, my_nbox);
                     int my_box0 = my_nbox;                                       // inclusive scan, made exclusive below
 #pragma unroll
                     for (int d = 1; d < 32; d <<= 1) {
@@ -385,12 +409,14 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     }
                 }
                 TDC_PROF_SPAN_END(6);
+                TDC_PROF_MARK(22, tid == 32, true);
                 if (t == blockIdx.x) scale_here();                               // the range's round trip ran under the index work
                 bool ok = true;
                 for (int kb = 0; kb < a.nkb; ++kb) {
                     float* A = open_stage(wt_tile, kb, t == blockIdx.x && kb == 0);
                     if (!A || !TDC_PROF_WAIT(1, mbar_wait(&rfull_bar[r_slot], (uint32_t)r_use))) { *abort_flag = 1; ok = false; break; }
                     const float* R = raw0 + (long long)r_slot * slot_floats;
+                    TDC_PROF_MARK(23, tid == 64, true);
                     TDC_PROF_SPAN_BEGIN;
 #pragma unroll
                     for (int i = 0; i < PPT; ++i) {
@@ -419,7 +445,8 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
             // flight to cover the memory latency and leaves no cold start at the beginning of a tile.
             float* raw0 = stage0 + (long long)a.ns * stage_floats;
             const int raw_floats = CBK * a.P, depth = a.depth;
-            const long long my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+            const long long my_tiles = blockIdx.x >= ntiles ? 0 : a.small ? (long long)((uint32_t)(ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x)
+                                                                            : (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
             const long long total = my_tiles * a.nkb;
             long long src_off[PPT];              // of the tile being copied: offset of channel 0 of each owned row, -1 = zeros
             long long l_tile = blockIdx.x;       // copy side: tile, channel block and raw slot of the next block to issue
@@ -447,7 +474,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                                 if (pp < l_rows && g >= 0 && g < a.total_pos) {
                                     const long long b = image_of(a, g);
                                     const int rem = (int)(g - b * a.Lp);
-                                    const int oy = rem / a.Wp, ox = rem - oy * a.Wp;
+                                    const int oy = row_of(a, rem), ox = rem - oy * a.Wp;
                                     const int iy0 = oy * a.stride - a.gpad, ix0 = ox * a.stride - a.gpadx;
                                     int m = 0;
                                     for (int d = 0; d < a.gR; ++d) m |= ((unsigned)(iy0 + d) < (unsigned)a.Hin) << d;
@@ -511,7 +538,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                                     if (g >= 0 && g < a.total_pos) {
                                         const long long b = image_of(a, g);
                                         const int rem = (int)(g - b * a.Lp);
-                                        const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
+                                        const int yy = row_of(a, rem), xx = rem - yy * a.Wp;
                                         if (yy < a.H && xx < a.W) src_off[i] = b * a.C * a.HWin + (long long)(yy * a.stride) * a.Win + xx * a.stride;
                                     }
                                 }
@@ -544,6 +571,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 first_filter(a.wt + (long long)ocb_first * a.nkb * b_floats);
             }
             for (int d = 0; d < depth; ++d) issue(d);
+            TDC_PROF_MARK(22, tid == 32, true);
             scale_here();                                  // the range's round trip ran under the index work and the first copies
             long long c_tile = blockIdx.x;
             int c_kb = 0, c_slot = 0;
@@ -560,6 +588,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 float* A = open_stage(wt_tile, c_kb, ci == 0);
                 if (!A) break;
                 { TDC_PROF_SPAN_BEGIN; cp_async_wait_pending(depth - 1); TDC_PROF_SPAN_END(1); }   // block ci has landed (this thread's part)
+                TDC_PROF_MARK(23, tid == 64, true);
                 const float* R = raw0 + c_slot * raw_floats;
                 if (++c_slot == depth) c_slot = 0;
 #pragma unroll
@@ -608,7 +637,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 int nb = 0;
                 for (long long b = image_of(a, lo), b_last = image_of(a, hi); b <= b_last; ++b) {
                     int pix4, nbox;
-                    image_run(a.H, a.W, a.Wp, a.Lp, gp0, rows, b, pix4, nbox);
+                    image_run(a, gp0, rows, b, pix4, nbox);
                     for (int k = 0; k < nbox; ++k, ++nb)
                         if (nb < a.nbox_cap) box_tab[nb] = make_int2(pix4 + k * BOXW, (int)b);
                 }
@@ -621,6 +650,7 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     for (int i = 0; i < nb; ++i) {
                         const int2 bx = box_tab[i];
                         bulk_tensor_3d(dst + i * (BOXC * BOXW), &tmap, bx.x, kb * BOXC, bx.y, &rfull_bar[p_slot]);
+                        TDC_PROF_MARK(21, true, true);
                     }
                     if (++p_slot == depth) { p_slot = 0; p_use ^= 1; }
                 }
@@ -660,10 +690,10 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                 }
                 bool ok = true;
                 for (int seg = 0; seg < a.nseg && ok; ++seg, ++j) {
-                    const int slot = (int)(j % nbuf) * MT + mt;
+                    const int slot = (nbuf == 2 ? (int)(j & 1) : 0) * MT + mt;       // nbuf is 1 or 2
                     const int kb_lo = seg * a.seg_blocks, kb_hi = kb_lo + a.seg_blocks < a.nkb ? kb_lo + a.seg_blocks : a.nkb;
                     // the epilogue must have emptied this accumulator slot (its previous use); the first use passes at once
-                    if (!TDC_PROF_WAIT(3, mbar_wait(&tempty_bar[slot], (uint32_t)(((j / nbuf) & 1) ^ 1)))) { *abort_flag = 1; ok = false; break; }
+                    if (!TDC_PROF_WAIT(3, mbar_wait(&tempty_bar[slot], (uint32_t)((((nbuf == 2 ? j >> 1 : j)) & 1) ^ 1)))) { *abort_flag = 1; ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t d_main = tmem + (uint32_t)(slot * a.tile_cols);
                     for (int kb0 = kb_lo; kb0 < kb_hi; kb0 += a.kps) {
@@ -725,15 +755,15 @@ __global__ void __launch_bounds__(P_THREADS) conv_tc_persist_kernel(const Args a
                     const int mt = item / CHUNKS, chunk = item - mt * CHUNKS;
                     // the position tiles of a CTA tile are handed over one by one: while this one is drained, the
                     // issuers of the others still run, and its own issuer may start on the next run or CTA tile
-                    const int slot = (int)(j % nbuf) * MT + mt;
-                    if (!TDC_PROF_WAIT(5, mbar_wait(&tfull_bar[slot], (uint32_t)((j / nbuf) & 1)))) { *abort_flag = 1; ok = false; break; }
+                    const int slot = (nbuf == 2 ? (int)(j & 1) : 0) * MT + mt;
+                    if (!TDC_PROF_WAIT(5, mbar_wait(&tfull_bar[slot], (uint32_t)((nbuf == 2 ? j >> 1 : j) & 1)))) { *abort_flag = 1; ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const long long g = g0 + mt * M_TILE + q * 32 + lane;
                     long long out_off = -1;
                     if (g < a.total_pos) {
                         const long long b = image_of(a, g);
                         const int rem = (int)(g - b * a.Lp);
-                        const int yy = rem / a.Wp, xx = rem - yy * a.Wp;
+                        const int yy = row_of(a, rem), xx = rem - yy * a.Wp;
                         if (yy < a.H && xx < a.W) out_off = b * a.K * HW + (long long)yy * a.W + xx;
                     }
                     uint32_t r[P_EPI_W];
