@@ -147,7 +147,8 @@ def strided_rows(S, stride):
 def worthwhile(B, C, H, W, K, R):
     """The tensor-core kernel works on tiles of 128 positions x up to 128 channels; with too few position tiles or too
     little arithmetic the fp32 kernel with its channel slices and clusters is the faster one.  The thresholds are a fit
-    to 420 layers (3x3 and 1x1, 32..2048 channels, 7..112 pixels, batch 1..32) timed on both paths in one run.  A 3x3
+    to 420 layers (3x3 and 1x1, 32..2048 channels, 7..56 pixels, batch 1..64) timed on both paths in one run
+    (tests/golden/tc_vs_fp32_times_b200.json, which a CPU test holds the rule to).  A 3x3
     layer wants 3 position tiles and 0.1 GFLOP: 0.2 % from always taking the faster path.  A 1x1 layer with few tiles
     is one CTA walking all input channels, about 12 us + 0.085 us per channel whatever the tile count, while the fp32
     kernel's time follows the arithmetic; the three cases below are 1.2 % from the faster path (the thresholds they

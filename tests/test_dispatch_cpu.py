@@ -44,6 +44,27 @@ def test_tensor_cores_only_where_they_fill_the_gpu(tc):
     assert not tc.worthwhile(64, 3, 56, 56, 8, 1)
 
 
+def test_thresholds_against_the_recorded_timings(tc):
+    """tests/golden/tc_vs_fp32_times_b200.json: 420 layers timed on both kernels on a B200 (make_tc_vs_fp32_times.py
+    beside it).  Summed over the file, the time of the kernel the rule picks stays within 2 % of the time of the faster
+    kernel per layer, for the 3x3 and for the 1x1 layers, and no single pick costs more than 1.7x."""
+    import json
+    import os
+    from helpers import ROOT
+    rows = json.load(open(os.path.join(ROOT, "tests", "golden", "tc_vs_fp32_times_b200.json")))
+    assert len(rows) == 420
+    for R, bar in ((3, 1.01), (1, 1.02)):
+        picked = best = 0.0
+        for (r, C, K, H, B, t_tc, t_fp) in rows:
+            if r != R:
+                continue
+            mine = t_tc if tc.worthwhile(B, C, H, H, K, r) else t_fp
+            assert mine <= 1.7 * min(t_tc, t_fp), (r, C, K, H, B, t_tc, t_fp)
+            picked += mine
+            best += min(t_tc, t_fp)
+        assert picked <= bar * best, (R, picked / best)
+
+
 def test_block_size_by_position_count(built):
     """tdc_tc_pick_nt: the default block (128 / 64 / 32 output channels by K) for layers with many position tiles,
     smaller blocks where the positions alone leave SMs idle — a host-side rule, no GPU."""
